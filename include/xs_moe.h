@@ -1,0 +1,158 @@
+/*
+ * xs_moe.h -- C ABI of the B200 (sm_100a) MoE forward path.
+ *
+ * Plain pointers and sizes only; no C++ or framework types cross this boundary, no exception leaves it.
+ * Every entry point returns 0 on success or a negative XsMoeStatus; xs_moe_status_string() names it and
+ * xs_moe_last_error() gives the detail message of the calling thread's last failure.
+ *
+ * The reference engine reaches its kernels through per-op `<op>_launch(void*..., DType)` functions that
+ * are declared in CUDA-free headers and defined in .cu files (reference: xstar_cpp/include/ops/mlp.h:95-102,
+ * xstar_cpp/include/ops/gemm.h:165-176, xstar_cpp/include/ops/softmax.h:75-80,
+ * xstar_cpp/include/ops/embedding.h:58-63, xstar_cpp/include/ops/add.h:38) and through the allocator
+ * wrappers of xstar_cpp/include/cuda/cuda_allocator.h:32-69.  The functions below are what a `moe` op in
+ * that engine binds in the same way; each one cites the reference interface whose role it takes.
+ *
+ * Device pointers are marked _dev.  All index arrays are int32, row-major, contiguous.
+ * Streams are passed as void* (a cudaStream_t; NULL = the default stream).  Calls enqueue work and return;
+ * they do not synchronise unless stated.
+ */
+#ifndef XS_MOE_H
+#define XS_MOE_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum XsMoeStatus {
+    XS_MOE_OK = 0,
+    XS_MOE_ERR_INVALID_ARG = -1,   /* null pointer, bad dimension, unsupported combination */
+    XS_MOE_ERR_UNSUPPORTED = -2,   /* format / shape not implemented by this build */
+    XS_MOE_ERR_WORKSPACE = -3,     /* workspace too small or misaligned */
+    XS_MOE_ERR_CUDA = -4,          /* a CUDA runtime/driver call failed; see xs_moe_last_error() */
+    XS_MOE_ERR_DEVICE = -5,        /* not an sm_100 device, or the kernel image is missing */
+    XS_MOE_ERR_KERNEL_TIMEOUT = -6 /* a bounded device-side wait gave up (reported by xs_moe_check_flags) */
+} XsMoeStatus;
+
+/* storage format of expert weights */
+typedef enum XsMoeFormat {
+    XS_MOE_BF16 = 0,          /* bf16, (rows, K) row-major */
+    XS_MOE_FP8_BLOCK128 = 1,  /* e4m3 codes + f32 scale per 128x128 block, scales (rows/128, K/128) */
+    XS_MOE_FP4_MX32 = 2       /* e2m1 packed 2/byte (low nibble = even k) + e8m0 scale per 32 along K */
+} XsMoeFormat;
+
+typedef struct XsMoeConfig {
+    int32_t num_tokens;     /* T: rows of x handled by this call */
+    int32_t hidden;         /* H */
+    int32_t num_experts;    /* E: routed experts the ROUTER scores (global count) */
+    int32_t top_k;          /* k */
+    int32_t intermediate;   /* I */
+    int32_t num_shared;     /* 0 or 1 shared expert */
+    int32_t routed_format;  /* XsMoeFormat of gate_up_w / down_w */
+    int32_t shared_format;  /* XsMoeFormat of the shared expert */
+    int32_t local_expert_begin; /* expert parallelism: this device owns experts [begin, begin+count) */
+    int32_t local_expert_count; /* == num_experts when not sharded */
+    int32_t gemm_impl;      /* 0 = tcgen05 tensor-core kernels (the product path);
+                               1 = plain CUDA-core cross-check kernels (bf16 only; used by tests to
+                                   validate the tensor-core path on the device, never a fallback) */
+    int32_t reserved[5];    /* must be zero */
+} XsMoeConfig;
+
+typedef struct XsMoeWeights {
+    const void *router_w_dev;             /* (E, H) bf16 */
+    const float *router_bias_dev;         /* (E) f32, selection only; may be NULL */
+    const void *gate_up_w_dev;            /* (E_local, 2I, H) rows [gate; up] as xstar_cpp/include/ops/mlp.h:34 */
+    const void *gate_up_scale_dev;        /* FP8: f32 (E_local, 2I/128, H/128); FP4: u8 (E_local, 2I, H/32) */
+    const void *down_w_dev;               /* (E_local, H, I) */
+    const void *down_scale_dev;           /* FP8: f32 (E_local, H/128, I/128); FP4: u8 (E_local, H, I/32) */
+    const void *shared_gate_up_w_dev;     /* (2I, H) or NULL */
+    const void *shared_gate_up_scale_dev;
+    const void *shared_down_w_dev;        /* (H, I) or NULL */
+    const void *shared_down_scale_dev;
+} XsMoeWeights;
+
+/* ---- library / device ----------------------------------------------------------------------------- */
+
+/* Takes the role of CHECK_CUDA's message (reference: xstar_cpp/include/cuda/cuda_check.h:23-31). */
+const char *xs_moe_status_string(int status);
+const char *xs_moe_last_error(void);
+
+/* 0 if the current device can run this library (compute capability 10.x), else XS_MOE_ERR_DEVICE. */
+int xs_moe_device_check(void);
+
+/* Allocator wrappers with the reference's meaning (xstar_cpp/include/cuda/cuda_allocator.h:32-69):
+ * raw device allocation, synchronous copies, free-memory probe. */
+int xs_moe_device_alloc(void **ptr_dev, size_t bytes);
+int xs_moe_device_free(void *ptr_dev);
+int xs_moe_memcpy_h2d(void *dst_dev, const void *src_host, size_t bytes);
+int xs_moe_memcpy_d2h(void *dst_host, const void *src_dev, size_t bytes);
+int xs_moe_memcpy_d2d(void *dst_dev, const void *src_dev, size_t bytes);
+int xs_moe_device_free_bytes(size_t *bytes);
+int xs_moe_stream_synchronize(void *stream);
+
+/* ---- workspace ------------------------------------------------------------------------------------ */
+
+/* Bytes of scratch xs_moe_forward needs for `cfg` (an upper bound over all routings).  The caller owns
+ * the buffer (256-byte aligned) and may reuse it across calls that do not overlap on the device.
+ * Replaces the per-temporary Tensor allocations of the reference's ops (xstar_cpp/src/ops/mlp.cpp:66). */
+int xs_moe_workspace_bytes(const XsMoeConfig *cfg, size_t *bytes);
+
+/* Clears the status word at the head of a workspace.  Call once after allocating it (and after a
+ * failed xs_moe_check_flags, which also clears it). */
+int xs_moe_workspace_init(void *workspace_dev, size_t workspace_bytes, void *stream);
+
+/* ---- the whole layer -------------------------------------------------------------------------------- */
+
+/* out(T,H) bf16 = MoE(x(T,H) bf16).  The slot `mlp(x, gate_up_w, down_w)` fills in the reference's block
+ * (xstar_cpp/src/ops/transformer_block.cpp:353; op contract xstar_cpp/include/ops/mlp.h:51). */
+int xs_moe_forward(const XsMoeConfig *cfg, const XsMoeWeights *w, const void *x_dev, void *out_dev,
+                   void *workspace_dev, size_t workspace_bytes, void *stream);
+
+/* Same with x and out in HOST memory: copies x in, runs, copies out back and synchronises -- the
+ * "returns => finished" behaviour of every reference op (xstar_cpp/src/ops/mlp.cu:188-189). */
+int xs_moe_forward_host(const XsMoeConfig *cfg, const XsMoeWeights *w, const void *x_host, void *out_host,
+                        void *x_staging_dev, void *out_staging_dev, void *workspace_dev, size_t workspace_bytes,
+                        void *stream);
+
+/* ---- stages (used by the layer, by expert parallelism and by the parity tests) -------------------- */
+
+/* Router logits + selection.  logits(T,E) f32 are accumulated per output in ascending k (the order of
+ * gemm_cpu, xstar_cpp/include/ops/gemm.h:57-83; linear's x*W^T, xstar_cpp/src/ops/linear.cpp:20-31);
+ * key = logit + bias; the k largest keys, ties to the lower id; slots in ascending expert id;
+ * weights = max-shifted softmax over the selected unbiased logits (xstar_cpp/src/ops/softmax.cpp:56-93).
+ * logits_dev may be NULL when the caller does not want them (scratch is then taken from the workspace). */
+int xs_moe_route(const XsMoeConfig *cfg, const void *x_dev, const void *router_w_dev, const float *router_bias_dev,
+                 float *logits_dev, int32_t *topk_ids_dev, float *topk_w_dev, void *workspace_dev,
+                 size_t workspace_bytes, void *stream);
+
+/* Deterministic permutation: rows sorted by (expert asc, token asc).  counts(E), offsets(E+1),
+ * perm(T*k): row -> t*k+slot, inv(T*k): t*k+slot -> row.  The index-array convention (raw integers next
+ * to the tensors) is that of the reference's gather op (xstar_cpp/include/ops/embedding.h:12-13,34). */
+int xs_moe_permute(const XsMoeConfig *cfg, const int32_t *topk_ids_dev, int32_t *counts_dev, int32_t *offsets_dev,
+                   int32_t *perm_dev, int32_t *inv_dev, void *workspace_dev, size_t workspace_bytes, void *stream);
+
+/* Per-expert SwiGLU MLPs over already-routed rows: rows_dev(M,H) bf16 are grouped by LOCAL expert
+ * (expert e owns rows [offsets[e], offsets[e+1]), e in [0, local_expert_count)); y_dev(M,H) f32 receives
+ * down(silu(gate x) * up x) per row.  Takes the role of gemm_silu_and_mul_launch + the down linear
+ * (xstar_cpp/include/ops/mlp.h:95-102, xstar_cpp/src/ops/mlp.cpp:64-70), once per expert segment.
+ * max_rows is the capacity of rows_dev / y_dev (the true M is offsets[E_local], read on the device). */
+int xs_moe_grouped_mlp_workspace_bytes(const XsMoeConfig *cfg, int32_t max_rows, size_t *bytes);
+int xs_moe_grouped_mlp(const XsMoeConfig *cfg, const XsMoeWeights *w, const void *rows_dev,
+                       const int32_t *offsets_dev, int32_t max_rows, float *y_dev, void *workspace_dev,
+                       size_t workspace_bytes, void *stream);
+
+/* out[t] = sum_j w[t,j] * y[inv[t,j]] (+ shared[t]), slot order, shared last, f32, one RNE downcast
+ * (add's contract, xstar_cpp/src/ops/add.cpp:27-49).  shared_dev (T,H) f32 may be NULL. */
+int xs_moe_combine(const XsMoeConfig *cfg, const float *y_dev, const int32_t *inv_dev, const float *topk_w_dev,
+                   const float *shared_dev, void *out_dev, void *stream);
+
+/* Reads and clears the device-side status word the kernels of the last calls on this workspace wrote
+ * (bounded waits that gave up, index checks that failed).  Synchronises the stream. */
+int xs_moe_check_flags(void *workspace_dev, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

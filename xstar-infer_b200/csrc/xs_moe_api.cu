@@ -1,0 +1,638 @@
+// C ABI of the MoE forward path (declared in include/xs_moe.h): argument checks, workspace planning,
+// tensor-map construction and kernel launches.  No exception leaves this file; every failure becomes a
+// negative status plus a thread-local message.
+#include "xs_moe.h"
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+#include <string>
+
+#include "xs_grouped_gemm.cuh"
+#include "xs_permute.cuh"
+#include "xs_route.cuh"
+
+namespace {
+
+thread_local std::string g_last_error;
+
+int fail(int status, const char *fmt, ...)
+{
+    char buf[512];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof(buf), fmt, ap);
+    va_end(ap);
+    g_last_error = buf;
+    return status;
+}
+
+#define XS_CUDA(call)                                                                                       \
+    do {                                                                                                    \
+        cudaError_t err__ = (call);                                                                         \
+        if (err__ != cudaSuccess)                                                                           \
+            return fail(XS_MOE_ERR_CUDA, "CUDA error: %s (%s) at %s:%d", cudaGetErrorString(err__), #call, \
+                        __FILE__, __LINE__);                                                                \
+    } while (0)
+
+inline size_t align_up(size_t v, size_t a)
+{
+    return (v + a - 1) / a * a;
+}
+
+// ---- driver entry point for tensor maps (no link-time dependency on libcuda) ---------------------------
+using EncodeTiledFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                   const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode_fn()
+{
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    });
+    return fn;
+}
+
+// 2-D row-major matrix (rows, cols) of `elem_bytes`-wide elements; box = (box_cols, box_rows); 128-byte swizzle.
+int make_tmap_2d(CUtensorMap *m, CUtensorMapDataType dt, int elem_bytes, const void *base, uint64_t rows, uint64_t cols,
+                 uint32_t box_rows, uint32_t box_cols)
+{
+    EncodeTiledFn fn = get_encode_fn();
+    if (!fn)
+        return fail(XS_MOE_ERR_CUDA, "CUDA error: cuTensorMapEncodeTiled entry point not available");
+    if (reinterpret_cast<uintptr_t>(base) % 16 != 0 || (cols * elem_bytes) % 16 != 0)
+        return fail(XS_MOE_ERR_INVALID_ARG, "tensor map operand must be 16-byte aligned with a 16-byte multiple row pitch");
+    if (box_cols * elem_bytes != 128)
+        return fail(XS_MOE_ERR_INVALID_ARG, "internal: swizzled box must be 128 bytes wide");
+    cuuint64_t dims[2] = {cols, rows};
+    cuuint64_t strides[1] = {cols * static_cast<uint64_t>(elem_bytes)};
+    cuuint32_t box[2] = {box_cols, box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(m, dt, 2, const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS)
+        return fail(XS_MOE_ERR_CUDA, "CUDA error: cuTensorMapEncodeTiled failed with code %d (rows=%llu cols=%llu)", (int)r,
+                    (unsigned long long)rows, (unsigned long long)cols);
+    return 0;
+}
+
+struct DeviceInfo {
+    int ok = 0;
+    int sms = 0;
+    int max_smem = 0;
+};
+
+int device_info(DeviceInfo *out)
+{
+    int dev = 0;
+    XS_CUDA(cudaGetDevice(&dev));
+    static DeviceInfo cache[64];
+    if (dev < 64 && cache[dev].ok) {
+        *out = cache[dev];
+        return 0;
+    }
+    int major = 0, sms = 0, smem = 0;
+    XS_CUDA(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev));
+    XS_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    XS_CUDA(cudaDeviceGetAttribute(&smem, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev));
+    if (major != 10)
+        return fail(XS_MOE_ERR_DEVICE, "this library holds sm_100a kernels only; device %d has compute capability %d.x", dev, major);
+    DeviceInfo d;
+    d.ok = 1;
+    d.sms = sms;
+    d.max_smem = smem;
+    if (dev < 64)
+        cache[dev] = d;
+    *out = d;
+    return 0;
+}
+
+// ---- configuration checks ------------------------------------------------------------------------------
+int check_cfg(const XsMoeConfig *c)
+{
+    if (!c)
+        return fail(XS_MOE_ERR_INVALID_ARG, "config is null");
+    if (c->num_tokens < 0 || c->hidden <= 0 || c->num_experts <= 0 || c->intermediate <= 0)
+        return fail(XS_MOE_ERR_INVALID_ARG, "shape mismatch: non-positive dimension");
+    if (c->top_k <= 0 || c->top_k > c->num_experts || c->top_k > 32)
+        return fail(XS_MOE_ERR_INVALID_ARG, "top_k out of range");
+    if (c->num_experts > 1024)
+        return fail(XS_MOE_ERR_UNSUPPORTED, "expert count mismatch: at most 1024 routed experts");
+    if (c->num_shared < 0 || c->num_shared > 1)
+        return fail(XS_MOE_ERR_INVALID_ARG, "num_shared must be 0 or 1");
+    if (c->hidden % 128 != 0 || c->intermediate % 128 != 0)
+        return fail(XS_MOE_ERR_UNSUPPORTED, "shape mismatch: hidden and intermediate must be multiples of 128");
+    if (c->local_expert_begin < 0 || c->local_expert_count <= 0 ||
+        c->local_expert_begin + c->local_expert_count > c->num_experts)
+        return fail(XS_MOE_ERR_INVALID_ARG, "expert count mismatch: local expert range outside [0, num_experts)");
+    if (c->routed_format != XS_MOE_BF16 || (c->num_shared && c->shared_format != XS_MOE_BF16))
+        return fail(XS_MOE_ERR_UNSUPPORTED, "unsupported dtype: only bf16 expert weights in this build");
+    if (c->gemm_impl != 0 && c->gemm_impl != 1)
+        return fail(XS_MOE_ERR_INVALID_ARG, "gemm_impl must be 0 or 1");
+    for (int i = 0; i < 5; i++)
+        if (c->reserved[i] != 0)
+            return fail(XS_MOE_ERR_INVALID_ARG, "reserved fields must be zero");
+    return 0;
+}
+
+int pick_n_tile(long rows, int groups)
+{
+    const long avg = groups > 0 ? (rows + groups - 1) / groups : rows;
+    if (avg <= 8)
+        return 16;
+    if (avg <= 20)
+        return 32;
+    if (avg <= 48)
+        return 64;
+    return 128;
+}
+
+// ---- workspace plans -----------------------------------------------------------------------------------
+struct GroupedPlan { // scratch of one grouped MLP over `max_rows` rows and `groups` experts
+    int n_tile = 0, max_tiles = 0;
+    size_t off_tile_expert = 0, off_tile_row0 = 0, off_num_tiles = 0, off_act = 0, bytes = 0;
+};
+
+GroupedPlan plan_grouped(int max_rows, int groups, int I)
+{
+    GroupedPlan p;
+    p.n_tile = pick_n_tile(max_rows, groups);
+    p.max_tiles = max_rows / p.n_tile + groups + 1;
+    size_t o = 0;
+    p.off_tile_expert = o; o = align_up(o + sizeof(int32_t) * p.max_tiles, 256);
+    p.off_tile_row0 = o;   o = align_up(o + sizeof(int32_t) * p.max_tiles, 256);
+    p.off_num_tiles = o;   o = align_up(o + sizeof(int32_t), 256);
+    p.off_act = o;         o = align_up(o + static_cast<size_t>(max_rows) * I * 2, 256);
+    p.bytes = o;
+    return p;
+}
+
+constexpr size_t kStatusBytes = 256;
+
+struct ForwardPlan {
+    int chunks = 0;
+    size_t off_logits = 0, off_ids = 0, off_w = 0, off_counts = 0, off_offsets = 0, off_perm = 0, off_inv = 0;
+    size_t off_chunk_counts = 0, off_chunk_base = 0, off_sh_offsets = 0, off_rows = 0, off_y = 0, off_ysh = 0;
+    size_t off_grouped = 0, off_grouped_sh = 0;
+    GroupedPlan routed, shared;
+    size_t bytes = 0;
+};
+
+ForwardPlan plan_forward(const XsMoeConfig *c)
+{
+    ForwardPlan p;
+    const size_t T = c->num_tokens, H = c->hidden, E = c->num_experts, K = c->top_k, I = c->intermediate, S = c->num_shared;
+    p.chunks = static_cast<int>((T + xs::kChunkTokens - 1) / xs::kChunkTokens);
+    if (p.chunks == 0)
+        p.chunks = 1;
+    size_t o = kStatusBytes;
+    auto take = [&](size_t bytes) {
+        size_t at = o;
+        o = align_up(o + bytes, 256);
+        return at;
+    };
+    p.off_logits = take(T * E * 4);
+    p.off_ids = take(T * K * 4);
+    p.off_w = take(T * K * 4);
+    p.off_counts = take(E * 4);
+    p.off_offsets = take((E + 1) * 4);
+    p.off_perm = take(T * K * 4);
+    p.off_inv = take(T * K * 4);
+    p.off_chunk_counts = take(static_cast<size_t>(p.chunks) * E * 4);
+    p.off_chunk_base = take(static_cast<size_t>(p.chunks) * E * 4);
+    p.off_sh_offsets = take(2 * 4);
+    p.off_rows = take((T * K + S * T) * H * 2);
+    p.off_y = take(T * K * H * 4);
+    p.off_ysh = take(S * T * H * 4);
+    p.routed = plan_grouped(static_cast<int>(T * K), static_cast<int>(E), static_cast<int>(I));
+    p.off_grouped = take(p.routed.bytes);
+    if (S) {
+        p.shared = plan_grouped(static_cast<int>(T), 1, static_cast<int>(I));
+        p.off_grouped_sh = take(p.shared.bytes);
+    }
+    p.bytes = o;
+    return p;
+}
+
+int check_workspace(const void *ws, size_t have, size_t need)
+{
+    if (!ws)
+        return fail(XS_MOE_ERR_WORKSPACE, "workspace is null");
+    if (reinterpret_cast<uintptr_t>(ws) % 256 != 0)
+        return fail(XS_MOE_ERR_WORKSPACE, "workspace must be 256-byte aligned");
+    if (have < need)
+        return fail(XS_MOE_ERR_WORKSPACE, "workspace too small: %zu bytes given, %zu needed", have, need);
+    return 0;
+}
+
+// ---- launches --------------------------------------------------------------------------------------------
+int launch_route(const XsMoeConfig *c, const void *x, const void *rw, const float *bias, float *logits, int32_t *ids, float *w,
+                 cudaStream_t st)
+{
+    const int T = c->num_tokens, H = c->hidden, E = c->num_experts, K = c->top_k;
+    if (T == 0)
+        return 0;
+    dim3 grid((E + xs::kRtExperts - 1) / xs::kRtExperts, (T + xs::kRtTokens - 1) / xs::kRtTokens);
+    xs::router_logits_kernel<<<grid, xs::kRtThreads, 0, st>>>(static_cast<const __nv_bfloat16 *>(x),
+                                                              static_cast<const __nv_bfloat16 *>(rw), logits, T, H, E);
+    XS_CUDA(cudaGetLastError());
+    const int blocks = (T + 3) / 4;
+    if (E <= 32)
+        xs::topk_kernel<1><<<blocks, 128, 0, st>>>(logits, bias, ids, w, T, E, K);
+    else if (E <= 256)
+        xs::topk_kernel<8><<<blocks, 128, 0, st>>>(logits, bias, ids, w, T, E, K);
+    else
+        xs::topk_kernel<32><<<blocks, 128, 0, st>>>(logits, bias, ids, w, T, E, K);
+    XS_CUDA(cudaGetLastError());
+    return 0;
+}
+
+int launch_permute(const XsMoeConfig *c, const int32_t *ids, int32_t *counts, int32_t *offsets, int32_t *perm, int32_t *inv,
+                   int32_t *chunk_counts, int32_t *chunk_base, int chunks, int32_t *status, cudaStream_t st)
+{
+    const int T = c->num_tokens, E = c->num_experts, K = c->top_k;
+    const size_t smem = static_cast<size_t>(E) * xs::kChunkWords * 4;
+    xs::permute_count_kernel<<<chunks, xs::kChunkTokens, smem, st>>>(ids, chunk_counts, T, E, K, status);
+    XS_CUDA(cudaGetLastError());
+    const int threads = (E + 31) / 32 * 32;
+    xs::permute_scan_kernel<<<1, threads, 0, st>>>(chunk_counts, counts, offsets, chunk_base, chunks, E);
+    XS_CUDA(cudaGetLastError());
+    xs::permute_fill_kernel<<<chunks, xs::kChunkTokens, smem, st>>>(ids, chunk_base, perm, inv, T, E, K, status);
+    XS_CUDA(cudaGetLastError());
+    return 0;
+}
+
+template <int N_TILE, bool GATE_UP>
+int launch_gemm_t(const CUtensorMap &tw, const CUtensorMap &tx, const int32_t *offsets, xs::TileTable tt, int w_rows, int n_out,
+                  int K, void *out, int32_t *status, int max_work, cudaStream_t st)
+{
+    DeviceInfo di;
+    if (int rc = device_info(&di))
+        return rc;
+    const int stage_bytes = xs::gemm_stage_bytes(N_TILE, GATE_UP);
+    int stages = (di.max_smem - 1024 - 256) / stage_bytes;
+    if (stages > 8)
+        stages = 8;
+    if (stages < 2)
+        return fail(XS_MOE_ERR_DEVICE, "not enough shared memory for the GEMM pipeline");
+    const int smem = stages * stage_bytes + 1024 + 256;
+    auto kern = xs::grouped_gemm_bf16_kernel<N_TILE, GATE_UP>;
+    static bool configured[64] = {};
+    int dev = 0;
+    XS_CUDA(cudaGetDevice(&dev));
+    if (dev >= 64 || !configured[dev]) {
+        XS_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        if (dev < 64)
+            configured[dev] = true;
+    }
+    int grid = di.sms < max_work ? di.sms : max_work;
+    if (grid < 1)
+        grid = 1;
+    kern<<<grid, xs::kGemmThreads, smem, st>>>(tw, tx, offsets, tt, w_rows, n_out, K, out, status, stages);
+    XS_CUDA(cudaGetLastError());
+    return 0;
+}
+
+template <bool GATE_UP>
+int launch_gemm(int n_tile, const CUtensorMap &tw, const CUtensorMap &tx, const int32_t *offsets, xs::TileTable tt, int w_rows,
+                int n_out, int K, void *out, int32_t *status, int max_work, cudaStream_t st)
+{
+    switch (n_tile) {
+    case 16: return launch_gemm_t<16, GATE_UP>(tw, tx, offsets, tt, w_rows, n_out, K, out, status, max_work, st);
+    case 32: return launch_gemm_t<32, GATE_UP>(tw, tx, offsets, tt, w_rows, n_out, K, out, status, max_work, st);
+    case 64: return launch_gemm_t<64, GATE_UP>(tw, tx, offsets, tt, w_rows, n_out, K, out, status, max_work, st);
+    case 128: return launch_gemm_t<128, GATE_UP>(tw, tx, offsets, tt, w_rows, n_out, K, out, status, max_work, st);
+    }
+    return fail(XS_MOE_ERR_INVALID_ARG, "internal: bad token tile %d", n_tile);
+}
+
+// One grouped SwiGLU MLP: rows (max_rows, H) bf16 grouped by `groups` experts through offsets (groups+1);
+// y (max_rows, H) f32.  `scratch` follows GroupedPlan.
+int run_grouped_mlp(int H, int I, int groups, int gemm_impl, const void *gate_up_w, const void *down_w, const void *rows,
+                    const int32_t *offsets, int max_rows, float *y, uint8_t *scratch, const GroupedPlan &gp, int32_t *status,
+                    cudaStream_t st)
+{
+    if (max_rows == 0)
+        return 0;
+    void *act = scratch + gp.off_act;
+    if (gemm_impl == 1) {
+        dim3 grid(max_rows, 8);
+        xs::grouped_gemm_bf16_simt_kernel<true><<<grid, 256, 0, st>>>(static_cast<const __nv_bfloat16 *>(gate_up_w),
+                                                                      static_cast<const __nv_bfloat16 *>(rows), offsets, groups,
+                                                                      2 * I, I, H, act);
+        XS_CUDA(cudaGetLastError());
+        xs::grouped_gemm_bf16_simt_kernel<false><<<grid, 256, 0, st>>>(static_cast<const __nv_bfloat16 *>(down_w),
+                                                                       static_cast<const __nv_bfloat16 *>(act), offsets, groups, H,
+                                                                       H, I, y);
+        XS_CUDA(cudaGetLastError());
+        return 0;
+    }
+    xs::TileTable tt;
+    int32_t *tile_expert = reinterpret_cast<int32_t *>(scratch + gp.off_tile_expert);
+    int32_t *tile_row0 = reinterpret_cast<int32_t *>(scratch + gp.off_tile_row0);
+    int32_t *num_tiles = reinterpret_cast<int32_t *>(scratch + gp.off_num_tiles);
+    tt.tile_expert = tile_expert;
+    tt.tile_row0 = tile_row0;
+    tt.num_tiles = num_tiles;
+    const int threads = (groups + 31) / 32 * 32;
+    xs::tile_table_kernel<<<1, threads, 0, st>>>(offsets, groups, gp.n_tile, gp.max_tiles, tile_expert, tile_row0, num_tiles,
+                                                 status);
+    XS_CUDA(cudaGetLastError());
+
+    CUtensorMap t_wgu, t_wd, t_x, t_act;
+    if (int rc = make_tmap_2d(&t_wgu, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, gate_up_w, static_cast<uint64_t>(groups) * 2 * I, H,
+                              xs::kTileM, xs::kBlockK))
+        return rc;
+    if (int rc = make_tmap_2d(&t_wd, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, down_w, static_cast<uint64_t>(groups) * H, I, xs::kTileM,
+                              xs::kBlockK))
+        return rc;
+    if (int rc = make_tmap_2d(&t_x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, rows, max_rows, H, gp.n_tile, xs::kBlockK))
+        return rc;
+    if (int rc = make_tmap_2d(&t_act, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, act, max_rows, I, gp.n_tile, xs::kBlockK))
+        return rc;
+    if (int rc = launch_gemm<true>(gp.n_tile, t_wgu, t_x, offsets, tt, 2 * I, I, H, act, status, gp.max_tiles * (I / xs::kTileM), st))
+        return rc;
+    if (int rc = launch_gemm<false>(gp.n_tile, t_wd, t_act, offsets, tt, H, H, I, y, status, gp.max_tiles * (H / xs::kTileM), st))
+        return rc;
+    return 0;
+}
+
+__global__ void set_two_ints_kernel(int32_t *p, int a, int b)
+{
+    p[0] = a;
+    p[1] = b;
+}
+
+} // namespace
+
+// =========================================================================================================
+extern "C" {
+
+const char *xs_moe_status_string(int status)
+{
+    switch (status) {
+    case XS_MOE_OK: return "ok";
+    case XS_MOE_ERR_INVALID_ARG: return "invalid argument";
+    case XS_MOE_ERR_UNSUPPORTED: return "unsupported";
+    case XS_MOE_ERR_WORKSPACE: return "workspace too small or misaligned";
+    case XS_MOE_ERR_CUDA: return "CUDA error";
+    case XS_MOE_ERR_DEVICE: return "unsupported device";
+    case XS_MOE_ERR_KERNEL_TIMEOUT: return "device-side wait timed out";
+    }
+    return "unknown status";
+}
+
+const char *xs_moe_last_error(void)
+{
+    return g_last_error.c_str();
+}
+
+int xs_moe_device_check(void)
+{
+    DeviceInfo di;
+    return device_info(&di);
+}
+
+int xs_moe_device_alloc(void **ptr, size_t bytes)
+{
+    if (!ptr)
+        return fail(XS_MOE_ERR_INVALID_ARG, "null out-pointer");
+    *ptr = nullptr;
+    XS_CUDA(cudaMalloc(ptr, bytes ? bytes : 1));
+    return 0;
+}
+int xs_moe_device_free(void *ptr)
+{
+    XS_CUDA(cudaFree(ptr));
+    return 0;
+}
+int xs_moe_memcpy_h2d(void *dst, const void *src, size_t bytes)
+{
+    XS_CUDA(cudaMemcpy(dst, src, bytes, cudaMemcpyHostToDevice));
+    return 0;
+}
+int xs_moe_memcpy_d2h(void *dst, const void *src, size_t bytes)
+{
+    XS_CUDA(cudaMemcpy(dst, src, bytes, cudaMemcpyDeviceToHost));
+    return 0;
+}
+int xs_moe_memcpy_d2d(void *dst, const void *src, size_t bytes)
+{
+    XS_CUDA(cudaMemcpy(dst, src, bytes, cudaMemcpyDeviceToDevice));
+    return 0;
+}
+int xs_moe_device_free_bytes(size_t *bytes)
+{
+    size_t f = 0, t = 0;
+    XS_CUDA(cudaMemGetInfo(&f, &t));
+    if (bytes)
+        *bytes = f;
+    return 0;
+}
+int xs_moe_stream_synchronize(void *stream)
+{
+    XS_CUDA(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
+    return 0;
+}
+
+int xs_moe_workspace_bytes(const XsMoeConfig *cfg, size_t *bytes)
+{
+    if (int rc = check_cfg(cfg))
+        return rc;
+    if (!bytes)
+        return fail(XS_MOE_ERR_INVALID_ARG, "null out-pointer");
+    *bytes = plan_forward(cfg).bytes;
+    return 0;
+}
+
+int xs_moe_route(const XsMoeConfig *cfg, const void *x, const void *rw, const float *bias, float *logits, int32_t *ids, float *w,
+                 void *ws, size_t ws_bytes, void *stream)
+{
+    if (int rc = check_cfg(cfg))
+        return rc;
+    if (!x || !rw || !ids || !w)
+        return fail(XS_MOE_ERR_INVALID_ARG, "null tensor pointer");
+    if (!logits) {
+        ForwardPlan p = plan_forward(cfg);
+        if (int rc = check_workspace(ws, ws_bytes, p.off_logits + static_cast<size_t>(cfg->num_tokens) * cfg->num_experts * 4))
+            return rc;
+        logits = reinterpret_cast<float *>(static_cast<uint8_t *>(ws) + p.off_logits);
+    }
+    return launch_route(cfg, x, rw, bias, logits, ids, w, static_cast<cudaStream_t>(stream));
+}
+
+int xs_moe_permute(const XsMoeConfig *cfg, const int32_t *ids, int32_t *counts, int32_t *offsets, int32_t *perm, int32_t *inv,
+                   void *ws, size_t ws_bytes, void *stream)
+{
+    if (int rc = check_cfg(cfg))
+        return rc;
+    if (!ids || !counts || !offsets || !perm || !inv)
+        return fail(XS_MOE_ERR_INVALID_ARG, "null tensor pointer");
+    ForwardPlan p = plan_forward(cfg);
+    if (int rc = check_workspace(ws, ws_bytes, p.off_chunk_base + static_cast<size_t>(p.chunks) * cfg->num_experts * 4))
+        return rc;
+    uint8_t *b = static_cast<uint8_t *>(ws);
+    return launch_permute(cfg, ids, counts, offsets, perm, inv, reinterpret_cast<int32_t *>(b + p.off_chunk_counts),
+                          reinterpret_cast<int32_t *>(b + p.off_chunk_base), p.chunks, reinterpret_cast<int32_t *>(b),
+                          static_cast<cudaStream_t>(stream));
+}
+
+int xs_moe_grouped_mlp_workspace_bytes(const XsMoeConfig *cfg, int32_t max_rows, size_t *bytes)
+{
+    if (int rc = check_cfg(cfg))
+        return rc;
+    if (!bytes || max_rows < 0)
+        return fail(XS_MOE_ERR_INVALID_ARG, "bad arguments");
+    *bytes = kStatusBytes + plan_grouped(max_rows, cfg->local_expert_count, cfg->intermediate).bytes;
+    return 0;
+}
+
+int xs_moe_grouped_mlp(const XsMoeConfig *cfg, const XsMoeWeights *w, const void *rows, const int32_t *offsets, int32_t max_rows,
+                       float *y, void *ws, size_t ws_bytes, void *stream)
+{
+    if (int rc = check_cfg(cfg))
+        return rc;
+    if (!w || !rows || !offsets || !y || !w->gate_up_w_dev || !w->down_w_dev)
+        return fail(XS_MOE_ERR_INVALID_ARG, "null tensor pointer");
+    if (max_rows < 0)
+        return fail(XS_MOE_ERR_INVALID_ARG, "shape mismatch: negative row capacity");
+    if (cfg->gemm_impl == 0)
+        if (int rc = xs_moe_device_check())
+            return rc;
+    GroupedPlan gp = plan_grouped(max_rows, cfg->local_expert_count, cfg->intermediate);
+    if (int rc = check_workspace(ws, ws_bytes, kStatusBytes + gp.bytes))
+        return rc;
+    uint8_t *b = static_cast<uint8_t *>(ws);
+    return run_grouped_mlp(cfg->hidden, cfg->intermediate, cfg->local_expert_count, cfg->gemm_impl, w->gate_up_w_dev, w->down_w_dev,
+                           rows, offsets, max_rows, y, b + kStatusBytes, gp, reinterpret_cast<int32_t *>(b),
+                           static_cast<cudaStream_t>(stream));
+}
+
+int xs_moe_combine(const XsMoeConfig *cfg, const float *y, const int32_t *inv, const float *topk_w, const float *shared, void *out,
+                   void *stream)
+{
+    if (int rc = check_cfg(cfg))
+        return rc;
+    if (!y || !inv || !topk_w || !out)
+        return fail(XS_MOE_ERR_INVALID_ARG, "null tensor pointer");
+    const int T = cfg->num_tokens, H = cfg->hidden, K = cfg->top_k;
+    if (T == 0)
+        return 0;
+    int gy = (H + 1023) / 1024;
+    xs::combine_kernel<<<dim3(T, gy), 128, 0, static_cast<cudaStream_t>(stream)>>>(y, inv, topk_w, shared,
+                                                                                  static_cast<__nv_bfloat16 *>(out), T, H, K);
+    XS_CUDA(cudaGetLastError());
+    return 0;
+}
+
+int xs_moe_forward(const XsMoeConfig *cfg, const XsMoeWeights *w, const void *x, void *out, void *ws, size_t ws_bytes, void *stream)
+{
+    if (int rc = check_cfg(cfg))
+        return rc;
+    if (!w || !x || !out || !w->router_w_dev || !w->gate_up_w_dev || !w->down_w_dev)
+        return fail(XS_MOE_ERR_INVALID_ARG, "null tensor pointer");
+    if (cfg->num_shared && (!w->shared_gate_up_w_dev || !w->shared_down_w_dev))
+        return fail(XS_MOE_ERR_INVALID_ARG, "shared expert weights missing");
+    if (cfg->local_expert_begin != 0 || cfg->local_expert_count != cfg->num_experts)
+        return fail(XS_MOE_ERR_INVALID_ARG, "expert count mismatch: xs_moe_forward needs all experts on this device; "
+                                            "sharded layers are composed from the stage calls");
+    if (cfg->gemm_impl == 0)
+        if (int rc = xs_moe_device_check())
+            return rc;
+    const ForwardPlan p = plan_forward(cfg);
+    if (int rc = check_workspace(ws, ws_bytes, p.bytes))
+        return rc;
+    const int T = cfg->num_tokens, H = cfg->hidden, E = cfg->num_experts, K = cfg->top_k, I = cfg->intermediate, S = cfg->num_shared;
+    if (T == 0)
+        return 0;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    uint8_t *b = static_cast<uint8_t *>(ws);
+    int32_t *status = reinterpret_cast<int32_t *>(b);
+    float *logits = reinterpret_cast<float *>(b + p.off_logits);
+    int32_t *ids = reinterpret_cast<int32_t *>(b + p.off_ids);
+    float *tw = reinterpret_cast<float *>(b + p.off_w);
+    int32_t *counts = reinterpret_cast<int32_t *>(b + p.off_counts);
+    int32_t *offsets = reinterpret_cast<int32_t *>(b + p.off_offsets);
+    int32_t *perm = reinterpret_cast<int32_t *>(b + p.off_perm);
+    int32_t *inv = reinterpret_cast<int32_t *>(b + p.off_inv);
+    uint8_t *rows = b + p.off_rows;
+    float *y = reinterpret_cast<float *>(b + p.off_y);
+    float *ysh = S ? reinterpret_cast<float *>(b + p.off_ysh) : nullptr;
+
+    if (int rc = launch_route(cfg, x, w->router_w_dev, w->router_bias_dev, logits, ids, tw, st))
+        return rc;
+    if (int rc = launch_permute(cfg, ids, counts, offsets, perm, inv, reinterpret_cast<int32_t *>(b + p.off_chunk_counts),
+                                reinterpret_cast<int32_t *>(b + p.off_chunk_base), p.chunks, status, st))
+        return rc;
+    const int n_routed = T * K, n_total = T * K + S * T;
+    xs::gather_rows_kernel<<<n_total, 256, 0, st>>>(static_cast<const uint8_t *>(x), perm, rows, n_routed, n_total, K, H * 2);
+    XS_CUDA(cudaGetLastError());
+    if (int rc = run_grouped_mlp(H, I, E, cfg->gemm_impl, w->gate_up_w_dev, w->down_w_dev, rows, offsets, n_routed, y,
+                                 b + p.off_grouped, p.routed, status, st))
+        return rc;
+    if (S) {
+        int32_t *sh_off = reinterpret_cast<int32_t *>(b + p.off_sh_offsets);
+        set_two_ints_kernel<<<1, 1, 0, st>>>(sh_off, 0, T);
+        XS_CUDA(cudaGetLastError());
+        if (int rc = run_grouped_mlp(H, I, 1, cfg->gemm_impl, w->shared_gate_up_w_dev, w->shared_down_w_dev,
+                                     rows + static_cast<size_t>(n_routed) * H * 2, sh_off, T, ysh, b + p.off_grouped_sh, p.shared,
+                                     status, st))
+            return rc;
+    }
+    return xs_moe_combine(cfg, y, inv, tw, ysh, out, stream);
+}
+
+int xs_moe_check_flags(void *ws, void *stream)
+{
+    if (!ws)
+        return fail(XS_MOE_ERR_WORKSPACE, "workspace is null");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    int32_t flags = 0;
+    XS_CUDA(cudaMemcpyAsync(&flags, ws, sizeof(flags), cudaMemcpyDeviceToHost, st));
+    XS_CUDA(cudaStreamSynchronize(st));
+    if (flags != 0) {
+        XS_CUDA(cudaMemsetAsync(ws, 0, sizeof(flags), st));
+        XS_CUDA(cudaStreamSynchronize(st));
+        if (flags & xs::kStatusWaitTimeout)
+            return fail(XS_MOE_ERR_KERNEL_TIMEOUT, "a kernel gave up a bounded wait (status word 0x%x)", flags);
+        return fail(XS_MOE_ERR_INVALID_ARG, "a kernel met an out-of-range index (status word 0x%x)", flags);
+    }
+    return 0;
+}
+
+int xs_moe_workspace_init(void *ws, size_t ws_bytes, void *stream)
+{
+    if (int rc = check_workspace(ws, ws_bytes, kStatusBytes))
+        return rc;
+    XS_CUDA(cudaMemsetAsync(ws, 0, kStatusBytes, static_cast<cudaStream_t>(stream)));
+    return 0;
+}
+
+int xs_moe_forward_host(const XsMoeConfig *cfg, const XsMoeWeights *w, const void *x_host, void *out_host, void *x_stage, void *out_stage,
+                        void *ws, size_t ws_bytes, void *stream)
+{
+    if (int rc = check_cfg(cfg))
+        return rc;
+    if (!x_host || !out_host || !x_stage || !out_stage)
+        return fail(XS_MOE_ERR_INVALID_ARG, "null tensor pointer");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const size_t bytes = static_cast<size_t>(cfg->num_tokens) * cfg->hidden * 2;
+    XS_CUDA(cudaMemcpyAsync(x_stage, x_host, bytes, cudaMemcpyHostToDevice, st));
+    if (int rc = xs_moe_forward(cfg, w, x_stage, out_stage, ws, ws_bytes, stream))
+        return rc;
+    XS_CUDA(cudaMemcpyAsync(out_host, out_stage, bytes, cudaMemcpyDeviceToHost, st));
+    XS_CUDA(cudaStreamSynchronize(st));
+    return xs_moe_check_flags(ws, stream);
+}
+
+} // extern "C"

@@ -1,0 +1,237 @@
+// Deterministic token permutation (rows sorted by expert, then token), tile tables for the grouped GEMMs,
+// the row gather, and the weighted combine.  No order-dependent atomics: membership bitmaps are built with
+// atomicOr (whose result does not depend on arrival order) and ranks are popcounts over them.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace xs {
+
+constexpr int kChunkTokens = 256; // tokens per block in the counting / ranking kernels
+constexpr int kChunkWords = kChunkTokens / 32;
+
+// bits[e][w]: bit (t & 31) of word (t >> 5) is set iff local token t of this chunk selected expert e.
+__device__ __forceinline__ void build_bits(uint32_t *bits, const int32_t *__restrict__ topk_ids, int T, int E, int K, int chunk,
+                                           int32_t *status)
+{
+    for (int i = threadIdx.x; i < E * kChunkWords; i += blockDim.x)
+        bits[i] = 0u;
+    __syncthreads();
+    const int tl = threadIdx.x;
+    const int t = chunk * kChunkTokens + tl;
+    if (t < T) {
+        for (int j = 0; j < K; j++) {
+            const int e = topk_ids[static_cast<size_t>(t) * K + j];
+            if (e < 0 || e >= E) {
+                atomicOr(status, 2);
+                continue;
+            }
+            atomicOr(&bits[e * kChunkWords + (tl >> 5)], 1u << (tl & 31));
+        }
+    }
+    __syncthreads();
+}
+
+// grid = chunks, block = kChunkTokens, dynamic smem = E * kChunkWords * 4
+__global__ void __launch_bounds__(kChunkTokens)
+permute_count_kernel(const int32_t *__restrict__ topk_ids, int32_t *__restrict__ chunk_counts, int T, int E, int K,
+                     int32_t *status)
+{
+    extern __shared__ uint32_t bits[];
+    build_bits(bits, topk_ids, T, E, K, blockIdx.x, status);
+    for (int e = threadIdx.x; e < E; e += blockDim.x) {
+        int c = 0;
+#pragma unroll
+        for (int w = 0; w < kChunkWords; w++)
+            c += __popc(bits[e * kChunkWords + w]);
+        chunk_counts[static_cast<size_t>(blockIdx.x) * E + e] = c;
+    }
+}
+
+// block-wide exclusive scan of one int per thread (blockDim.x <= 1024); returns the exclusive prefix and
+// leaves the grand total in *total_smem
+__device__ __forceinline__ int block_exclusive_scan(int v, int *warp_sums, int *total_smem)
+{
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    int inc = v;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const int n = __shfl_up_sync(0xffffffffu, inc, o);
+        if (lane >= o)
+            inc += n;
+    }
+    if (lane == 31)
+        warp_sums[warp] = inc;
+    __syncthreads();
+    if (warp == 0) {
+        int s = (lane < (blockDim.x + 31) / 32) ? warp_sums[lane] : 0;
+        int sinc = s;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int n = __shfl_up_sync(0xffffffffu, sinc, o);
+            if (lane >= o)
+                sinc += n;
+        }
+        warp_sums[lane] = sinc - s; // exclusive
+        if (lane == 31)
+            *total_smem = sinc;
+    }
+    __syncthreads();
+    const int res = warp_sums[warp] + inc - v;
+    __syncthreads();
+    return res;
+}
+
+// one block, blockDim.x >= E (rounded up to a warp multiple).  counts, offsets (exclusive scan), and the
+// first row of every (chunk, expert) group.
+__global__ void __launch_bounds__(1024)
+permute_scan_kernel(const int32_t *__restrict__ chunk_counts, int32_t *__restrict__ counts, int32_t *__restrict__ offsets,
+                    int32_t *__restrict__ chunk_base, int num_chunks, int E)
+{
+    __shared__ int warp_sums[32];
+    __shared__ int total;
+    const int e = threadIdx.x;
+    int c = 0;
+    if (e < E)
+        for (int ch = 0; ch < num_chunks; ch++)
+            c += chunk_counts[static_cast<size_t>(ch) * E + e];
+    const int off = block_exclusive_scan(c, warp_sums, &total);
+    if (e < E) {
+        counts[e] = c;
+        offsets[e] = off;
+        int b = off;
+        for (int ch = 0; ch < num_chunks; ch++) {
+            chunk_base[static_cast<size_t>(ch) * E + e] = b;
+            b += chunk_counts[static_cast<size_t>(ch) * E + e];
+        }
+    }
+    if (threadIdx.x == 0)
+        offsets[E] = total;
+}
+
+// one block, blockDim.x >= E.  Token tiles of n_tile rows per expert segment, in expert order.
+__global__ void __launch_bounds__(1024)
+tile_table_kernel(const int32_t *__restrict__ offsets, int E, int n_tile, int max_tiles, int32_t *__restrict__ tile_expert,
+                  int32_t *__restrict__ tile_row0, int32_t *__restrict__ num_tiles, int32_t *status)
+{
+    __shared__ int warp_sums[32];
+    __shared__ int total;
+    const int e = threadIdx.x;
+    int rows = 0, start = 0;
+    if (e < E) {
+        start = offsets[e];
+        rows = offsets[e + 1] - start;
+        if (rows < 0) {
+            rows = 0;
+            atomicOr(status, 2);
+        }
+    }
+    const int nt = (rows + n_tile - 1) / n_tile;
+    const int first = block_exclusive_scan(nt, warp_sums, &total);
+    for (int i = 0; i < nt; i++) {
+        if (first + i >= max_tiles) {
+            atomicOr(status, 2);
+            break;
+        }
+        tile_expert[first + i] = e;
+        tile_row0[first + i] = start + i * n_tile;
+    }
+    if (threadIdx.x == 0)
+        *num_tiles = total < max_tiles ? total : max_tiles;
+}
+
+// grid = chunks, block = kChunkTokens.  row = first row of (chunk, expert) + number of earlier tokens of the
+// chunk that chose the same expert.
+__global__ void __launch_bounds__(kChunkTokens)
+permute_fill_kernel(const int32_t *__restrict__ topk_ids, const int32_t *__restrict__ chunk_base, int32_t *__restrict__ perm,
+                    int32_t *__restrict__ inv, int T, int E, int K, int32_t *status)
+{
+    extern __shared__ uint32_t bits[];
+    build_bits(bits, topk_ids, T, E, K, blockIdx.x, status);
+    const int tl = threadIdx.x;
+    const int t = blockIdx.x * kChunkTokens + tl;
+    if (t >= T)
+        return;
+    for (int j = 0; j < K; j++) {
+        const int e = topk_ids[static_cast<size_t>(t) * K + j];
+        if (e < 0 || e >= E)
+            continue;
+        const uint32_t *b = bits + e * kChunkWords;
+        int rank = __popc(b[tl >> 5] & ((1u << (tl & 31)) - 1u));
+        for (int w = 0; w < (tl >> 5); w++)
+            rank += __popc(b[w]);
+        const int row = chunk_base[static_cast<size_t>(blockIdx.x) * E + e] + rank;
+        perm[row] = t * K + j;
+        inv[static_cast<size_t>(t) * K + j] = row;
+    }
+}
+
+// rows_out[row] = x[perm[row] / K] for row < n_routed;  rows_out[n_routed + t] = x[t] for the shared expert.
+// 16-byte copies; row_bytes % 16 == 0.
+__global__ void __launch_bounds__(256)
+gather_rows_kernel(const uint8_t *__restrict__ x, const int32_t *__restrict__ perm, uint8_t *__restrict__ rows_out, int n_routed,
+                   int n_total, int K, int row_bytes)
+{
+    const int row = blockIdx.x;
+    if (row >= n_total)
+        return;
+    const int t = row < n_routed ? perm[row] / K : row - n_routed;
+    const uint4 *src = reinterpret_cast<const uint4 *>(x + static_cast<size_t>(t) * row_bytes);
+    uint4 *dst = reinterpret_cast<uint4 *>(rows_out + static_cast<size_t>(row) * row_bytes);
+    for (int i = threadIdx.x; i < row_bytes / 16; i += blockDim.x)
+        dst[i] = src[i];
+}
+
+// out[t,h] = bf16( sum_j w[t,j] * y[inv[t,j], h]  (+ shared[t,h]) ), slot order, shared last; separate
+// multiply and add (no contraction) so the sum is the same sequence of IEEE operations as the CPU's.
+// Eight outputs per thread: two 16-byte loads per row, one 16-byte store.
+__global__ void __launch_bounds__(128)
+combine_kernel(const float *__restrict__ y, const int32_t *__restrict__ inv, const float *__restrict__ topk_w,
+               const float *__restrict__ shared, __nv_bfloat16 *__restrict__ out, int T, int H, int K)
+{
+    const int t = blockIdx.x;
+    if (t >= T)
+        return;
+    __shared__ int s_row[32];
+    __shared__ float s_w[32];
+    if (threadIdx.x < K) {
+        s_row[threadIdx.x] = inv[static_cast<size_t>(t) * K + threadIdx.x];
+        s_w[threadIdx.x] = topk_w[static_cast<size_t>(t) * K + threadIdx.x];
+    }
+    __syncthreads();
+    for (int h0 = (blockIdx.y * blockDim.x + threadIdx.x) * 8; h0 < H; h0 += gridDim.y * blockDim.x * 8) {
+        float acc[8];
+#pragma unroll
+        for (int i = 0; i < 8; i++)
+            acc[i] = 0.0f;
+        for (int j = 0; j < K; j++) {
+            const float4 *p = reinterpret_cast<const float4 *>(y + static_cast<size_t>(s_row[j]) * H + h0);
+            const float4 a = p[0], b = p[1];
+            const float w = s_w[j];
+            acc[0] = __fadd_rn(acc[0], __fmul_rn(w, a.x));
+            acc[1] = __fadd_rn(acc[1], __fmul_rn(w, a.y));
+            acc[2] = __fadd_rn(acc[2], __fmul_rn(w, a.z));
+            acc[3] = __fadd_rn(acc[3], __fmul_rn(w, a.w));
+            acc[4] = __fadd_rn(acc[4], __fmul_rn(w, b.x));
+            acc[5] = __fadd_rn(acc[5], __fmul_rn(w, b.y));
+            acc[6] = __fadd_rn(acc[6], __fmul_rn(w, b.z));
+            acc[7] = __fadd_rn(acc[7], __fmul_rn(w, b.w));
+        }
+        if (shared) {
+            const float4 *p = reinterpret_cast<const float4 *>(shared + static_cast<size_t>(t) * H + h0);
+            const float4 a = p[0], b = p[1];
+            acc[0] = __fadd_rn(acc[0], a.x); acc[1] = __fadd_rn(acc[1], a.y);
+            acc[2] = __fadd_rn(acc[2], a.z); acc[3] = __fadd_rn(acc[3], a.w);
+            acc[4] = __fadd_rn(acc[4], b.x); acc[5] = __fadd_rn(acc[5], b.y);
+            acc[6] = __fadd_rn(acc[6], b.z); acc[7] = __fadd_rn(acc[7], b.w);
+        }
+        __nv_bfloat162 o[4];
+#pragma unroll
+        for (int i = 0; i < 4; i++)
+            o[i] = __floats2bfloat162_rn(acc[2 * i], acc[2 * i + 1]);
+        *reinterpret_cast<uint4 *>(out + static_cast<size_t>(t) * H + h0) = *reinterpret_cast<uint4 *>(o);
+    }
+}
+
+} // namespace xs

@@ -1,0 +1,188 @@
+// Router: logits = x . router_w^T with each output accumulated in ascending k in f32 (so that the logits
+// equal, bit for bit, a sequential CPU loop and near-ties cannot flip an expert choice), then per-token
+// selection of the k largest keys with warp-shuffle reductions.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace xs {
+
+constexpr int kRtTokens = 16;  // tokens per block
+constexpr int kRtExperts = 64; // experts per block
+constexpr int kRtK = 64;       // k elements staged per step
+constexpr int kRtThreads = 128;
+constexpr int kRtPad = 4;      // bf16 elements of row padding: row stride 136 B keeps 8-byte reads conflict-free
+
+// Products of two bf16 values are exact in f32, so fma(x, w, acc) rounds once exactly like the CPU's
+// separate multiply and add; only the ORDER of the additions matters and it is ascending k here:
+// every accumulator is touched once per k, k = 0, 1, 2, ...
+__global__ void __launch_bounds__(kRtThreads)
+router_logits_kernel(const __nv_bfloat16 *__restrict__ x, const __nv_bfloat16 *__restrict__ rw, float *__restrict__ logits,
+                     int T, int H, int E)
+{
+    __shared__ __align__(16) __nv_bfloat16 xs[kRtTokens][kRtK + kRtPad];
+    __shared__ __align__(16) __nv_bfloat16 ws[kRtExperts][kRtK + kRtPad];
+
+    const int tid = threadIdx.x;
+    const int tx = tid & 15; // expert lane: experts j*16 + tx, j = 0..3
+    const int ty = tid >> 4; // token pair: tokens 2*ty, 2*ty+1
+    const int t0 = blockIdx.y * kRtTokens;
+    const int e0 = blockIdx.x * kRtExperts;
+
+    float acc[2][4];
+#pragma unroll
+    for (int i = 0; i < 2; i++)
+#pragma unroll
+        for (int j = 0; j < 4; j++)
+            acc[i][j] = 0.0f;
+
+    for (int k0 = 0; k0 < H; k0 += kRtK) {
+        // stage x (16 rows x 64) and w (64 rows x 64): 8-byte pieces
+        for (int p = tid; p < (kRtTokens + kRtExperts) * (kRtK / 4); p += kRtThreads) {
+            const int r = p / (kRtK / 4);
+            const int c = (p - r * (kRtK / 4)) * 4;
+            uint2 v = make_uint2(0u, 0u);
+            if (r < kRtTokens) {
+                const int t = t0 + r;
+                if (t < T)
+                    v = *reinterpret_cast<const uint2 *>(x + static_cast<size_t>(t) * H + k0 + c);
+                *reinterpret_cast<uint2 *>(&xs[r][c]) = v;
+            } else {
+                const int e = e0 + r - kRtTokens;
+                if (e < E)
+                    v = *reinterpret_cast<const uint2 *>(rw + static_cast<size_t>(e) * H + k0 + c);
+                *reinterpret_cast<uint2 *>(&ws[r - kRtTokens][c]) = v;
+            }
+        }
+        __syncthreads();
+#pragma unroll 4
+        for (int k = 0; k < kRtK; k += 4) {
+            float xv[2][4], wv[4][4];
+#pragma unroll
+            for (int i = 0; i < 2; i++) {
+                const uint2 v = *reinterpret_cast<const uint2 *>(&xs[2 * ty + i][k]);
+                xv[i][0] = __uint_as_float(v.x << 16);
+                xv[i][1] = __uint_as_float(v.x & 0xffff0000u);
+                xv[i][2] = __uint_as_float(v.y << 16);
+                xv[i][3] = __uint_as_float(v.y & 0xffff0000u);
+            }
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                const uint2 v = *reinterpret_cast<const uint2 *>(&ws[j * 16 + tx][k]);
+                wv[j][0] = __uint_as_float(v.x << 16);
+                wv[j][1] = __uint_as_float(v.x & 0xffff0000u);
+                wv[j][2] = __uint_as_float(v.y << 16);
+                wv[j][3] = __uint_as_float(v.y & 0xffff0000u);
+            }
+#pragma unroll
+            for (int kk = 0; kk < 4; kk++)
+#pragma unroll
+                for (int i = 0; i < 2; i++)
+#pragma unroll
+                    for (int j = 0; j < 4; j++)
+                        acc[i][j] = __fmaf_rn(xv[i][kk], wv[j][kk], acc[i][j]);
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 2; i++) {
+        const int t = t0 + 2 * ty + i;
+        if (t >= T)
+            continue;
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const int e = e0 + j * 16 + tx;
+            if (e < E)
+                logits[static_cast<size_t>(t) * E + e] = acc[i][j];
+        }
+    }
+}
+
+// One warp per token.  Lane l holds experts l, l+32, l+64, ...  (NPL per lane).
+// Selection: K rounds of "largest key, ties to the lower expert id" by butterfly shuffles.
+// Output slots are in ascending expert id.  Weights: softmax over the selected unbiased logits,
+// max-shifted, summed in slot order.
+template <int NPL>
+__global__ void __launch_bounds__(128)
+topk_kernel(const float *__restrict__ logits, const float *__restrict__ bias, int32_t *__restrict__ topk_ids,
+            float *__restrict__ topk_w, int T, int E, int K)
+{
+    const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (warp >= T)
+        return;
+    const float *l = logits + static_cast<size_t>(warp) * E;
+    float key[NPL], lg[NPL];
+    uint32_t selected = 0; // bit i: expert lane + 32*i chosen
+#pragma unroll
+    for (int i = 0; i < NPL; i++) {
+        const int e = lane + 32 * i;
+        if (e < E) {
+            lg[i] = l[e];
+            key[i] = bias ? __fadd_rn(lg[i], bias[e]) : lg[i];
+        } else {
+            lg[i] = 0.0f;
+            key[i] = 0.0f;
+            selected |= 1u << i; // never eligible
+        }
+    }
+    const uint32_t never = selected;
+    for (int r = 0; r < K; r++) {
+        // local best among the not yet selected
+        float bk = 0.0f;
+        int be = 0x7fffffff;
+#pragma unroll
+        for (int i = 0; i < NPL; i++) {
+            const int e = lane + 32 * i;
+            const bool free_ = !((selected >> i) & 1u);
+            if (free_ && (be == 0x7fffffff || key[i] > bk)) { // ascending e within the lane: strict > keeps the lower id
+                bk = key[i];
+                be = e;
+            }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ok = __shfl_xor_sync(0xffffffffu, bk, o);
+            const int oe = __shfl_xor_sync(0xffffffffu, be, o);
+            const bool take = (oe != 0x7fffffff) && (be == 0x7fffffff || ok > bk || (ok == bk && oe < be));
+            if (take) {
+                bk = ok;
+                be = oe;
+            }
+        }
+        if (be != 0x7fffffff && (be & 31) == lane)
+            selected |= 1u << (be >> 5);
+    }
+    const uint32_t chosen = selected & ~never;
+    // ascending expert id = ascending i, then ascending lane
+    int base = 0;
+    float m = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < NPL; i++) {
+        const bool c = (chosen >> i) & 1u;
+        const uint32_t mask = __ballot_sync(0xffffffffu, c);
+        if (c) {
+            const int slot = base + __popc(mask & ((1u << lane) - 1u));
+            topk_ids[static_cast<size_t>(warp) * K + slot] = lane + 32 * i;
+            topk_w[static_cast<size_t>(warp) * K + slot] = lg[i]; // raw logit for now
+            m = fmaxf(m, lg[i]);
+        }
+        base += __popc(mask);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1)
+        m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    __syncwarp();
+    // slot-ordered softmax; K <= 32: lane j owns slot j
+    float ex = 0.0f;
+    if (lane < K)
+        ex = expf(topk_w[static_cast<size_t>(warp) * K + lane] - m);
+    float sum = 0.0f;
+    for (int j = 0; j < K; j++)
+        sum = __fadd_rn(sum, __shfl_sync(0xffffffffu, ex, j));
+    if (lane < K)
+        topk_w[static_cast<size_t>(warp) * K + lane] = __fdiv_rn(ex, sum);
+}
+
+} // namespace xs

@@ -1,0 +1,129 @@
+"""ctypes binding of the C ABI in include/xs_moe.h.
+
+This is plumbing for the tests and the benchmark: it passes raw device pointers (from torch tensors or
+from the library's own allocator) straight to the `extern "C"` entry points.  There is no fallback: if the
+shared library is missing the import fails, and if a call fails a RuntimeError carries the library's message.
+"""
+import ctypes as C
+import os
+
+_PKG = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+LIB_PATH = os.path.join(_PKG, "libxs_moe.so")
+
+BF16, FP8_BLOCK128, FP4_MX32 = 0, 1, 2
+
+
+class XsMoeConfig(C.Structure):
+    _fields_ = [
+        ("num_tokens", C.c_int32),
+        ("hidden", C.c_int32),
+        ("num_experts", C.c_int32),
+        ("top_k", C.c_int32),
+        ("intermediate", C.c_int32),
+        ("num_shared", C.c_int32),
+        ("routed_format", C.c_int32),
+        ("shared_format", C.c_int32),
+        ("local_expert_begin", C.c_int32),
+        ("local_expert_count", C.c_int32),
+        ("gemm_impl", C.c_int32),
+        ("reserved", C.c_int32 * 5),
+    ]
+
+
+class XsMoeWeights(C.Structure):
+    _fields_ = [(n, C.c_void_p) for n in (
+        "router_w_dev", "router_bias_dev", "gate_up_w_dev", "gate_up_scale_dev", "down_w_dev", "down_scale_dev",
+        "shared_gate_up_w_dev", "shared_gate_up_scale_dev", "shared_down_w_dev", "shared_down_scale_dev")]
+
+
+EXPORTS = [
+    "xs_moe_status_string", "xs_moe_last_error", "xs_moe_device_check", "xs_moe_device_alloc", "xs_moe_device_free",
+    "xs_moe_memcpy_h2d", "xs_moe_memcpy_d2h", "xs_moe_memcpy_d2d", "xs_moe_device_free_bytes",
+    "xs_moe_stream_synchronize", "xs_moe_workspace_bytes", "xs_moe_workspace_init", "xs_moe_forward",
+    "xs_moe_forward_host", "xs_moe_route", "xs_moe_permute", "xs_moe_grouped_mlp_workspace_bytes",
+    "xs_moe_grouped_mlp", "xs_moe_combine", "xs_moe_check_flags",
+]
+
+_lib = None
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise ImportError(f"{LIB_PATH} is missing: build it with `python __graft_entry__.py` (nvcc, sm_100a)")
+        L = C.CDLL(LIB_PATH)
+        L.xs_moe_status_string.restype = C.c_char_p
+        L.xs_moe_status_string.argtypes = [C.c_int]
+        L.xs_moe_last_error.restype = C.c_char_p
+        vp, sz, i32 = C.c_void_p, C.c_size_t, C.c_int32
+        cfgp, wp = C.POINTER(XsMoeConfig), C.POINTER(XsMoeWeights)
+        sig = {
+            "xs_moe_device_check": [],
+            "xs_moe_device_alloc": [C.POINTER(vp), sz],
+            "xs_moe_device_free": [vp],
+            "xs_moe_memcpy_h2d": [vp, vp, sz],
+            "xs_moe_memcpy_d2h": [vp, vp, sz],
+            "xs_moe_memcpy_d2d": [vp, vp, sz],
+            "xs_moe_device_free_bytes": [C.POINTER(sz)],
+            "xs_moe_stream_synchronize": [vp],
+            "xs_moe_workspace_bytes": [cfgp, C.POINTER(sz)],
+            "xs_moe_workspace_init": [vp, sz, vp],
+            "xs_moe_forward": [cfgp, wp, vp, vp, vp, sz, vp],
+            "xs_moe_forward_host": [cfgp, wp, vp, vp, vp, vp, vp, sz, vp],
+            "xs_moe_route": [cfgp, vp, vp, vp, vp, vp, vp, vp, sz, vp],
+            "xs_moe_permute": [cfgp, vp, vp, vp, vp, vp, vp, sz, vp],
+            "xs_moe_grouped_mlp_workspace_bytes": [cfgp, i32, C.POINTER(sz)],
+            "xs_moe_grouped_mlp": [cfgp, wp, vp, vp, i32, vp, vp, sz, vp],
+            "xs_moe_combine": [cfgp, vp, vp, vp, vp, vp, vp],
+            "xs_moe_check_flags": [vp, vp],
+        }
+        for name, args in sig.items():
+            fn = getattr(L, name)
+            fn.restype = C.c_int
+            fn.argtypes = args
+        _lib = L
+    return _lib
+
+
+def check(rc):
+    if rc != 0:
+        L = lib()
+        raise RuntimeError(f"{L.xs_moe_status_string(rc).decode()}: {L.xs_moe_last_error().decode()}")
+
+
+def make_config(T, H, E, K, I, S, routed_format=BF16, shared_format=BF16, local_begin=0, local_count=None, gemm_impl=0):
+    c = XsMoeConfig()
+    c.num_tokens, c.hidden, c.num_experts, c.top_k, c.intermediate, c.num_shared = T, H, E, K, I, S
+    c.routed_format, c.shared_format = routed_format, shared_format
+    c.local_expert_begin = local_begin
+    c.local_expert_count = E if local_count is None else local_count
+    c.gemm_impl = gemm_impl
+    return c
+
+
+def ptr(t):
+    """Device (or host) address of a torch tensor / None."""
+    return None if t is None else C.c_void_p(t.data_ptr())
+
+
+def make_weights(d):
+    """d: dict of torch tensors keyed like the oracle's arguments (see synth.make_inputs)."""
+    w = XsMoeWeights()
+    w.router_w_dev = ptr(d["router_w"])
+    w.router_bias_dev = ptr(d.get("router_bias"))
+    w.gate_up_w_dev = ptr(d["gate_up_w"])
+    w.gate_up_scale_dev = ptr(d.get("gate_up_scale"))
+    w.down_w_dev = ptr(d["down_w"])
+    w.down_scale_dev = ptr(d.get("down_scale"))
+    w.shared_gate_up_w_dev = ptr(d.get("shared_gate_up_w"))
+    w.shared_gate_up_scale_dev = ptr(d.get("shared_gate_up_scale"))
+    w.shared_down_w_dev = ptr(d.get("shared_down_w"))
+    w.shared_down_scale_dev = ptr(d.get("shared_down_scale"))
+    return w
+
+
+def workspace_bytes(cfg):
+    n = C.c_size_t(0)
+    check(lib().xs_moe_workspace_bytes(C.byref(cfg), C.byref(n)))
+    return n.value
