@@ -1,0 +1,345 @@
+#!/usr/bin/env python
+"""MoE-layer throughput on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl ours|reference]
+
+One step = one forward of the MoE layer (router top-k -> permute -> grouped GEMM + SwiGLU -> combine) over
+one batch of seeded synthetic tokens.  The default workload is the decode-sized bf16 layer
+(T=128, H=4096, 256 experts, top-6, one shared expert, I=2048), which is HBM-bound: 12.9 GB of expert
+weights are streamed every step, far more than the 126 MB L2, so no cache flush is needed between steps.
+
+Prints one JSON line: tokens/s with inputs resident in HBM (`value`), the same through the host-buffer
+entry point with the copies timed (`e2e`), the roofline of the dominant kernel, and the CPU baseline.
+With --impl reference it times the reference's own CPU ops (compiled in place under oracle/_ref, else the
+CPU oracle) on the host cores instead.
+"""
+import argparse
+import ctypes as C
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+for p in (ROOT, os.path.join(ROOT, "xstar-infer_b200")):
+    if p not in sys.path:
+        sys.path.insert(0, p)
+
+import numpy as np  # noqa: E402
+
+METRIC = "moe_layer_tokens_per_s"
+UNIT = "tokens/s"
+KERNELS_PER_STEP = 14  # router, top-k, count, scan, fill, gather, 2x(tile table, gate/up, down), shared offsets, combine
+
+
+def measured_peaks():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            p = json.load(f)
+        return float(p["hbm_gbs"]), "measured"
+    except Exception:
+        return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons while the timed region runs (read-only queries)."""
+
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index = index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.Q, "--format=csv,noheader,nounits",
+                                          "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.th = threading.Thread(target=self._read, daemon=True)
+            self.th.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        for ln in self.lines:
+            f = [s.strip() for s in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def host_cores():
+    try:
+        return len(os.sched_getaffinity(0))
+    except Exception:
+        return os.cpu_count() or 1
+
+
+# ------------------------------------------------------------------------------------------------------------
+# CPU arm: the reference's own CPU ops composed into the layer (oracle/_ref), else the CPU oracle
+# ------------------------------------------------------------------------------------------------------------
+def cpu_forward_tokens_per_s(dims, n, sample_tokens, threads, oracle):
+    """Time one CPU pass over `sample_tokens` tokens (routing over all tokens of the batch, experts for the
+    sample) and return (tokens/s, seconds, kind)."""
+    from xstar_moe import synth
+
+    K = dims["K"]
+    sub = np.arange(sample_tokens, dtype=np.int32)
+    ref = oracle.ref_lib() if dims["fmt"] == "bf16" else None
+    t0 = time.perf_counter()
+    if ref is not None:
+        xf, rwf = synth.bf16_bits_to_f32(n["x"]), synth.bf16_bits_to_f32(n["router_w"])
+        logits = oracle.ref_router_logits(xf, rwf)
+        ids, w = oracle.topk(logits, n.get("router_bias"), K)
+        counts, offsets, perm, inv = oracle.permute(ids, dims["E"])
+        routing = dict(topk_ids=ids, topk_w=w, offsets=offsets, perm=perm, inv=inv)
+        oracle.ref_experts_combine(True, n["x"], n["gate_up_w"], n["down_w"], n.get("shared_gate_up_w"), n.get("shared_down_w"),
+                                   routing, threads=threads, token_subset=sub)
+        kind = "reference"
+    else:
+        mode = {"bf16": oracle.BF16, "fp8": oracle.FP8, "fp4": oracle.FP4}[dims["fmt"]]
+        oracle.moe_forward(mode, n["x"], n["router_w"], n["gate_up_w"], n["down_w"], K, router_bias=n.get("router_bias"),
+                           gate_up_scale=n.get("gate_up_scale"), down_scale=n.get("down_scale"),
+                           shared_gate_up_w=n.get("shared_gate_up_w"), shared_down_w=n.get("shared_down_w"),
+                           shared_gate_up_scale=n.get("shared_gate_up_scale"), shared_down_scale=n.get("shared_down_scale"),
+                           threads=threads, token_subset=sub)
+        kind = "port"
+    dt = time.perf_counter() - t0
+    return sample_tokens / dt, dt, kind
+
+
+def pick_sample(dims, cores):
+    """Tokens whose expert work is roughly 10-20 s on `cores` threads at the reference's ~0.15 GMAC/s/thread."""
+    macs_per_token = (dims["K"] + dims["S"]) * 3 * dims["H"] * dims["I"]
+    rate = 0.15e9 * max(1, min(cores, dims["E"]))
+    return int(max(1, min(dims["T"], round(12.0 * rate / macs_per_token))))
+
+
+def run_reference_arm(args, dims):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    import torch
+
+    from oracle import moe_oracle as oracle
+    from xstar_moe import synth
+
+    cores = host_cores()
+    d = synth.make_inputs(dims, seed=0, device="cuda" if torch.cuda.is_available() else "cpu")
+    n = synth.to_numpy_storage(d)
+    del d
+    per_step = max(1, pick_sample(dims, cores) // 3)  # ~4 s per step keeps steps+warmup within minutes
+    kind = "port"
+    for _ in range(args.warmup):
+        _, _, kind = cpu_forward_tokens_per_s(dims, n, max(1, per_step // 4), cores, oracle)
+    t = 0.0
+    for _ in range(args.steps):
+        _, dt, kind = cpu_forward_tokens_per_s(dims, n, per_step, cores, oracle)
+        t += dt
+    value = per_step * args.steps / t
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": 1e3 * t / args.steps, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32-accumulate over bf16 storage" if dims["fmt"] == "bf16" else dims["fmt"],
+        "data": "synthetic (seeded: weights N(0,0.02), activations N(0,1))",
+        "config": dict(workload=args.workload, **{k: dims[k] for k in "THEKIS"}, format=dims["fmt"]),
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": kind,
+                         "sample": f"{per_step} of {dims['T']} tokens per step (routing over all tokens, experts for the sample)"},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------------------------------------------------
+# GPU arm
+# ------------------------------------------------------------------------------------------------------------
+def run_ours(args, dims):
+    import torch
+    import torch.distributed as dist
+
+    from xstar_moe import capi, synth
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the MoE path has no CPU fallback")
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    L = capi.lib()
+    capi.check(L.xs_moe_device_check())
+
+    T, H, E, K, I, S = (dims[k] for k in "THEKIS")
+    # every rank holds a full replica of the layer and its own batch of T tokens (weak scaling, no data-path collective)
+    d = synth.make_inputs(dims, seed=rank, device="cuda")
+    fmt = synth.FMT[dims["fmt"]]
+    cfg = capi.make_config(T, H, E, K, I, S, fmt, fmt)
+    nbytes = capi.workspace_bytes(cfg)
+    ws = torch.empty(nbytes, dtype=torch.uint8, device="cuda")
+    stream = torch.cuda.current_stream()
+    st = C.c_void_p(stream.cuda_stream)
+    capi.check(L.xs_moe_workspace_init(capi.ptr(ws), nbytes, st))
+    w = capi.make_weights(d)
+    out = torch.empty_like(d["x"])
+    x_host = d["x"].cpu().pin_memory()
+    out_host = torch.empty_like(x_host).pin_memory()
+    x_stage = torch.empty_like(d["x"])
+
+    def step():
+        capi.check(L.xs_moe_forward(C.byref(cfg), C.byref(w), capi.ptr(d["x"]), capi.ptr(out), capi.ptr(ws), nbytes, st))
+
+    def step_host():
+        capi.check(L.xs_moe_forward_host(C.byref(cfg), C.byref(w), capi.ptr(x_host), capi.ptr(out_host), capi.ptr(x_stage),
+                                         capi.ptr(out), capi.ptr(ws), nbytes, st))
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        e0.record(stream)
+        for _ in range(steps):
+            fn()
+        e1.record(stream)
+        barrier()
+        ms = torch.tensor([e0.elapsed_time(e1)], device="cuda")
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms.item())
+
+    for _ in range(max(3, args.warmup)):
+        step()
+    capi.check(L.xs_moe_check_flags(capi.ptr(ws), st))
+
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    ms = timed(step, args.steps)
+    # end-to-end through the host-buffer entry point: h2d of x and d2h of out inside the timed region
+    for _ in range(2):
+        step_host()
+    ms_e2e = timed(step_host, args.steps)
+
+    # stage times with CUDA events on the launching stream (same steps, same inputs)
+    stage = (C.c_float * 7)()
+    acc = np.zeros(7)
+    prof_steps = max(3, min(args.steps, 20))
+    for _ in range(prof_steps):
+        capi.check(L.xs_moe_forward_profile(C.byref(cfg), C.byref(w), capi.ptr(d["x"]), capi.ptr(out), capi.ptr(ws), nbytes, st, stage))
+        acc += np.array(list(stage))
+    stage_ms = acc / prof_steps
+    clocks = sampler.stop() if rank == 0 else None
+    capi.check(L.xs_moe_check_flags(capi.ptr(ws), st))
+
+    # routing of this batch -> active experts -> algorithmic bytes
+    ids = torch.empty((T, K), dtype=torch.int32, device="cuda")
+    tw = torch.empty((T, K), dtype=torch.float32, device="cuda")
+    capi.check(L.xs_moe_route(C.byref(cfg), capi.ptr(d["x"]), capi.ptr(d["router_w"]), capi.ptr(d.get("router_bias")), None,
+                              capi.ptr(ids), capi.ptr(tw), capi.ptr(ws), nbytes, st))
+    torch.cuda.synchronize()
+    active = int(torch.unique(ids).numel())
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    peak, peak_kind = measured_peaks()
+    wbytes = {"bf16": 2.0, "fp8": 1.0, "fp4": 0.5}[dims["fmt"]]
+    gate_up_bytes = active * 2 * H * I * wbytes  # the dominant kernel streams the gate and up matrices of every active expert
+    dom_ms = float(stage_ms[2])
+    layer_bytes = synth.algorithmic_bytes(dims, active)
+    roofline = {
+        "bound": "hbm", "kernel": "grouped_gemm_bf16_kernel<gate_up> (routed experts)",
+        "achieved": gate_up_bytes / (dom_ms * 1e-3) / 1e9, "peak": peak, "unit": "GB/s", "peak_kind": peak_kind,
+        "frac": gate_up_bytes / (dom_ms * 1e-3) / 1e9 / peak, "traffic": None,
+        "algorithmic_bytes_per_launch": gate_up_bytes, "ms_per_launch": dom_ms,
+        "layer": {"algorithmic_bytes": layer_bytes, "achieved": layer_bytes / (ms / args.steps * 1e-3) / 1e9,
+                  "frac": layer_bytes / (ms / args.steps * 1e-3) / 1e9 / peak},
+        "stage_ms": {k: float(v) for k, v in zip(("route", "permute_gather", "routed_gate_up", "routed_down", "shared_gate_up",
+                                                  "shared_down", "combine"), stage_ms)},
+    }
+
+    # CPU baseline on a bounded sample of the same batch
+    cpu = None
+    if not args.no_cpu:
+        from oracle import moe_oracle as oracle
+
+        cores = host_cores()
+        n = synth.to_numpy_storage(d)
+        sample = pick_sample(dims, cores)
+        v, dt, kind = cpu_forward_tokens_per_s(dims, n, sample, cores, oracle)
+        cpu = {"value": v, "unit": UNIT, "cores": cores, "kind": kind, "seconds": dt,
+               "sample": f"{sample} of {T} tokens (routing over all tokens, experts for the sample)"}
+
+    tokens = T * world * args.steps
+    line = {
+        "metric": METRIC, "value": tokens / (ms * 1e-3), "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup),
+        "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": dims["fmt"],
+        "data": "synthetic (seeded: weights N(0,0.02), activations N(0,1), rounded once to storage)",
+        "config": dict(workload=args.workload, **{k: dims[k] for k in "THEKIS"}, format=dims["fmt"], active_experts=active,
+                       parallelism=f"replicas x{world}" if world > 1 else "1 gpu",
+                       l2="inputs larger than L2: expert weights streamed per step exceed 126 MB"),
+        "e2e": {"value": tokens / (ms_e2e * 1e-3), "unit": UNIT, "h2d_bytes_per_step": T * H * 2, "d2h_bytes_per_step": T * H * 2 + 4,
+                "ms_per_step": ms_e2e / args.steps},
+        "gpu_launches": KERNELS_PER_STEP * args.steps,
+        "roofline": roofline, "cpu_baseline": cpu, "clocks": clocks,
+    }
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="decode_bf16")
+    ap.add_argument("--tokens", type=int, default=None, help="override the workload's token count")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    args = ap.parse_args()
+
+    from xstar_moe import synth
+
+    dims = dict(synth.CONFIGS[args.workload])
+    if args.tokens is not None:
+        dims["T"] = args.tokens
+    if args.impl == "reference":
+        run_reference_arm(args, dims)
+    else:
+        run_ours(args, dims)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,196 @@
+"""GPU parity tests: the CUDA path, called through the C ABI, against the CPU oracle on the same seeded
+inputs.  Index outputs (expert ids, counts, offsets, permutation) must be bit-exact; bf16 layer outputs
+must be within rel-L2 2e-3 of the oracle run with the same rounding points."""
+import ctypes as C
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from xstar_moe import capi, synth
+
+import gpu_util as gu
+
+pytestmark = pytest.mark.gpu
+
+BF16_TOL = 2e-3  # rel-L2, bf16 path vs oracle (same rounding points)
+
+
+@pytest.fixture(scope="module", autouse=True)
+def _device():
+    if not torch.cuda.is_available():
+        pytest.fail("GPU tests need a CUDA device; there is no CPU fallback")
+    capi.check(capi.lib().xs_moe_device_check())
+
+
+def _dims(**kw):
+    base = dict(T=8, H=256, E=8, K=2, I=128, S=0, fmt="bf16", bias=None)
+    base.update(kw)
+    return base
+
+
+# ---- routing: bit-exact ---------------------------------------------------------------------------------------
+@pytest.mark.parametrize("name,T", [("small_bf16", None), ("decode_bf16", None), ("decode_bf16", 1), ("decode_bf16", 37),
+                                    ("prefill_fp8", 2048)])
+def test_route_bit_exact(oracle, name, T):
+    dims = dict(synth.CONFIGS[name])
+    if T is not None:
+        dims["T"] = T
+    g = torch.Generator(device="cuda").manual_seed(21)
+    x = (torch.randn((dims["T"], dims["H"]), generator=g, device="cuda")).to(torch.bfloat16)
+    rw = (torch.randn((dims["E"], dims["H"]), generator=g, device="cuda") * 0.02).to(torch.bfloat16)
+    bias = synth.zipf_bias(dims["E"], 21).cuda() if dims["bias"] == "zipf" else None
+    d = dict(x=x, router_w=rw, router_bias=bias)
+    logits, ids, w = gu.route(dims, d)
+    xf, rwf = x.float().cpu().numpy(), rw.float().cpu().numpy()
+    ref_logits = np.zeros((dims["T"], dims["E"]), np.float32)
+    oracle.lib().xso_router_logits(C.c_void_p(xf.ctypes.data), C.c_void_p(rwf.ctypes.data), C.c_void_p(ref_logits.ctypes.data),
+                                   dims["T"], dims["H"], dims["E"])
+    assert np.array_equal(logits.cpu().numpy().view(np.uint32), ref_logits.view(np.uint32)), "router logits are not bit-exact"
+    ref_ids, ref_w = oracle.topk(ref_logits, None if bias is None else bias.cpu().numpy(), dims["K"])
+    assert np.array_equal(ids.cpu().numpy(), ref_ids)
+    assert np.allclose(w.cpu().numpy(), ref_w, atol=1e-6, rtol=0)
+
+
+def test_route_ties_and_bias(oracle):
+    """Identical router rows make exact ties: the lower expert id must win, on the device as in the oracle."""
+    dims = _dims(T=5, E=40, K=4, H=128)
+    g = torch.Generator(device="cuda").manual_seed(22)
+    x = torch.randn((5, 128), generator=g, device="cuda").to(torch.bfloat16)
+    rw = (torch.randn((40, 128), generator=g, device="cuda") * 0.02).to(torch.bfloat16)
+    rw[1::2] = rw[0::2]  # pairs of identical experts
+    bias = torch.zeros(40, device="cuda")
+    bias[33] = 5.0
+    logits, ids, w = gu.route(dims, dict(x=x, router_w=rw, router_bias=bias))
+    ref_ids, ref_w = oracle.topk(logits.cpu().numpy(), bias.cpu().numpy(), 4)
+    assert np.array_equal(ids.cpu().numpy(), ref_ids)
+    assert np.all(ids.cpu().numpy() == np.sort(ids.cpu().numpy(), axis=1))
+    assert np.all((ids.cpu().numpy() == 33).any(1))
+    assert np.allclose(w.cpu().numpy(), ref_w, atol=1e-6, rtol=0)
+
+
+# ---- permutation: bit-exact -----------------------------------------------------------------------------------
+@pytest.mark.parametrize("T,E,K", [(1, 8, 2), (64, 16, 2), (300, 256, 6), (1000, 64, 8), (4096, 256, 6)])
+def test_permute_bit_exact(oracle, T, E, K):
+    rng = np.random.default_rng(T + E)
+    p = rng.random(E) ** 3 + 1e-3  # skewed loads; some experts stay empty at small T
+    ids = np.stack([np.sort(rng.choice(E, K, replace=False, p=p / p.sum())) for _ in range(T)]).astype(np.int32)
+    dims = _dims(T=T, E=E, K=K)
+    counts, offsets, perm, inv = gu.permute(dims, torch.from_numpy(ids).cuda())
+    rc, ro, rp, ri = oracle.permute(ids, E)
+    assert np.array_equal(counts.cpu().numpy(), rc)
+    assert np.array_equal(offsets.cpu().numpy(), ro)
+    assert np.array_equal(perm.cpu().numpy(), rp)
+    assert np.array_equal(inv.cpu().numpy(), ri)
+
+
+def test_permute_all_tokens_one_expert(oracle):
+    T, E, K = 200, 8, 1
+    ids = np.full((T, K), 5, np.int32)
+    counts, offsets, perm, inv = gu.permute(_dims(T=T, E=E, K=K), torch.from_numpy(ids).cuda())
+    rc, ro, rp, ri = oracle.permute(ids, E)
+    assert np.array_equal(counts.cpu().numpy(), rc) and np.array_equal(perm.cpu().numpy(), rp)
+    assert np.array_equal(offsets.cpu().numpy(), ro) and np.array_equal(inv.cpu().numpy(), ri)
+
+
+# ---- grouped expert MLP: tensor-core kernel vs the CUDA-core cross-check vs the oracle ---------------------------
+@pytest.mark.parametrize("counts", [[3, 0, 1, 17, 2, 0, 40, 1], [1] * 8, [0, 0, 0, 130, 0, 0, 0, 0]])
+def test_grouped_mlp_tcgen05_vs_simt_vs_oracle(oracle, counts):
+    dims = _dims(E=8, H=512, I=256)
+    d = synth.make_inputs(dict(dims, T=1), seed=31, device="cuda")
+    M = sum(counts)
+    g = torch.Generator(device="cuda").manual_seed(32)
+    rows = torch.randn((M, dims["H"]), generator=g, device="cuda").to(torch.bfloat16)
+    offsets = torch.tensor(np.concatenate([[0], np.cumsum(counts)]), dtype=torch.int32, device="cuda")
+    y_tc = gu.grouped_mlp(dims, d, rows, offsets, gemm_impl=0).cpu().numpy()
+    y_simt = gu.grouped_mlp(dims, d, rows, offsets, gemm_impl=1).cpu().numpy()
+    n = synth.to_numpy_storage(d)
+    rn = rows.view(torch.uint16).cpu().numpy()
+    ref = np.zeros((M, dims["H"]), np.float32)
+    for e in range(8):
+        a, b = int(offsets[e]), int(offsets[e + 1])
+        if b > a:
+            ref[a:b] = oracle.expert_mlp(oracle.BF16, rn[a:b], n["gate_up_w"][e], n["down_w"][e])
+    assert synth.rel_l2(y_simt, ref) < 1e-3, "CUDA-core cross-check disagrees with the oracle"
+    assert synth.rel_l2(y_tc, ref) < 1e-3, "tcgen05 kernel disagrees with the oracle"
+    assert np.all(np.isfinite(y_tc))
+
+
+# ---- whole layer ---------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("impl", [0, 1])
+def test_forward_small_config(oracle, impl):
+    """T=64, H=1024, E=16, k=2, I=512, no shared expert: bf16 on the GPU against the oracle."""
+    dims = synth.CONFIGS["small_bf16"]
+    d = synth.make_inputs(dims, seed=0, device="cuda")
+    out = gu.forward(dims, d, gemm_impl=impl)
+    ref = gu.oracle_forward(oracle, dims, d)
+    rel = synth.rel_l2(gu.bf16_to_f32(out), synth.bf16_bits_to_f32(ref["out"]))
+    assert rel <= BF16_TOL, rel
+    ref32 = gu.oracle_forward(oracle, dims, d, mode=oracle.F32)
+    rel32 = synth.rel_l2(gu.bf16_to_f32(out), ref32["out"])
+    print(f"small config impl={impl}: rel-L2 vs bf16 oracle {rel:.3e}, vs f32 oracle {rel32:.3e}")
+    assert rel32 <= 3e-3, rel32  # bf16 storage of act and out alone costs ~2.3e-3 against pure f32
+
+
+@pytest.mark.parametrize("T,S,E,K", [(1, 1, 8, 2), (7, 1, 8, 3), (33, 0, 16, 4), (129, 1, 32, 6), (300, 1, 8, 2)])
+def test_forward_ragged_shapes(oracle, T, S, E, K):
+    dims = _dims(T=T, S=S, E=E, K=K, H=256, I=256)
+    d = synth.make_inputs(dims, seed=T, device="cuda")
+    out = gu.forward(dims, d)
+    ref = gu.oracle_forward(oracle, dims, d)
+    rel = synth.rel_l2(gu.bf16_to_f32(out), synth.bf16_bits_to_f32(ref["out"]))
+    assert rel <= BF16_TOL, rel
+
+
+def test_forward_empty_batch():
+    dims = _dims(T=0)
+    cfg = gu.cfg_of(dims, T=0)
+    ws = gu.new_workspace(gu.cfg_of(dims, T=8))
+    d = synth.make_inputs(dict(dims, T=1), seed=1, device="cuda")
+    w = capi.make_weights(d)
+    x = torch.empty((0, dims["H"]), dtype=torch.bfloat16, device="cuda")
+    out = torch.empty_like(x)
+    capi.check(capi.lib().xs_moe_forward(C.byref(cfg), C.byref(w), capi.ptr(d["x"]), capi.ptr(d["x"]), capi.ptr(ws), ws.numel(),
+                                         gu.stream_ptr()))
+    torch.cuda.synchronize()
+
+
+def test_forward_is_deterministic():
+    dims = _dims(T=97, S=1, E=16, K=4, H=512, I=256)
+    d = synth.make_inputs(dims, seed=3, device="cuda")
+    a = gu.forward(dims, d)
+    b = gu.forward(dims, d)
+    assert torch.equal(a, b)
+
+
+def test_forward_rejects_bad_arguments():
+    dims = _dims()
+    d = synth.make_inputs(dims, seed=1, device="cuda")
+    L = capi.lib()
+    cfg = gu.cfg_of(dims)
+    w = capi.make_weights(d)
+    out = torch.empty_like(d["x"])
+    small = torch.empty(1024, dtype=torch.uint8, device="cuda")
+    rc = L.xs_moe_forward(C.byref(cfg), C.byref(w), capi.ptr(d["x"]), capi.ptr(out), capi.ptr(small), small.numel(), None)
+    assert rc == -3 and b"workspace too small" in L.xs_moe_last_error()
+    bad = gu.cfg_of(dict(dims, K=9))
+    n = C.c_size_t(0)
+    assert L.xs_moe_workspace_bytes(C.byref(bad), C.byref(n)) == -1 and b"top_k out of range" in L.xs_moe_last_error()
+    bad = gu.cfg_of(dict(dims, H=200))
+    assert L.xs_moe_workspace_bytes(C.byref(bad), C.byref(n)) == -2 and b"shape mismatch" in L.xs_moe_last_error()
+
+
+def test_forward_decode_shape_subset(oracle):
+    """The benchmark layer (T=128, H=4096, E=256, k=6, shared expert, I=2048) at full size: routing checked on all
+    tokens, outputs on a seeded subset of tokens (rows are independent, so per-row checks are exact)."""
+    dims = synth.CONFIGS["decode_bf16"]
+    d = synth.make_inputs(dims, seed=0, device="cuda")
+    out = gu.forward(dims, d)
+    sub = np.sort(np.random.default_rng(0).choice(dims["T"], 12, replace=False)).astype(np.int32)
+    ref = gu.oracle_forward(oracle, dims, d, token_subset=sub, threads=os.cpu_count() or 8)
+    logits, ids, w = gu.route(dims, d)
+    assert np.array_equal(ids.cpu().numpy(), ref["topk_ids"])
+    got = gu.bf16_to_f32(out)[sub]
+    rel = synth.rel_l2(got, synth.bf16_bits_to_f32(ref["out"])[sub])
+    assert rel <= BF16_TOL, rel

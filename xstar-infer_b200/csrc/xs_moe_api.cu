@@ -320,10 +320,13 @@ int launch_gemm(int n_tile, const CUtensorMap &tw, const CUtensorMap &tx, const 
 // y (max_rows, H) f32.  `scratch` follows GroupedPlan.
 int run_grouped_mlp(int H, int I, int groups, int gemm_impl, const void *gate_up_w, const void *down_w, const void *rows,
                     const int32_t *offsets, int max_rows, float *y, uint8_t *scratch, const GroupedPlan &gp, int32_t *status,
-                    cudaStream_t st)
+                    cudaStream_t st, cudaEvent_t mid = nullptr)
 {
-    if (max_rows == 0)
+    if (max_rows == 0) {
+        if (mid)
+            XS_CUDA(cudaEventRecord(mid, st));
         return 0;
+    }
     void *act = scratch + gp.off_act;
     if (gemm_impl == 1) {
         dim3 grid(max_rows, 8);
@@ -331,6 +334,8 @@ int run_grouped_mlp(int H, int I, int groups, int gemm_impl, const void *gate_up
                                                                       static_cast<const __nv_bfloat16 *>(rows), offsets, groups,
                                                                       2 * I, I, H, act);
         XS_CUDA(cudaGetLastError());
+        if (mid)
+            XS_CUDA(cudaEventRecord(mid, st));
         xs::grouped_gemm_bf16_simt_kernel<false><<<grid, 256, 0, st>>>(static_cast<const __nv_bfloat16 *>(down_w),
                                                                        static_cast<const __nv_bfloat16 *>(act), offsets, groups, H,
                                                                        H, I, y);
@@ -362,6 +367,8 @@ int run_grouped_mlp(int H, int I, int groups, int gemm_impl, const void *gate_up
         return rc;
     if (int rc = launch_gemm<true>(gp.n_tile, t_wgu, t_x, offsets, tt, 2 * I, I, H, act, status, gp.max_tiles * (I / xs::kTileM), st))
         return rc;
+    if (mid)
+        XS_CUDA(cudaEventRecord(mid, st));
     if (int rc = launch_gemm<false>(gp.n_tile, t_wd, t_act, offsets, tt, H, H, I, y, status, gp.max_tiles * (H / xs::kTileM), st))
         return rc;
     return 0;
@@ -535,8 +542,14 @@ int xs_moe_combine(const XsMoeConfig *cfg, const float *y, const int32_t *inv, c
     return 0;
 }
 
-int xs_moe_forward(const XsMoeConfig *cfg, const XsMoeWeights *w, const void *x, void *out, void *ws, size_t ws_bytes, void *stream)
+static int forward_impl(const XsMoeConfig *cfg, const XsMoeWeights *w, const void *x, void *out, void *ws, size_t ws_bytes,
+                        void *stream, cudaEvent_t *ev)
 {
+#define XS_MARK(i)                                                       \
+    do {                                                                 \
+        if (ev)                                                          \
+            XS_CUDA(cudaEventRecord(ev[i], static_cast<cudaStream_t>(stream))); \
+    } while (0)
     if (int rc = check_cfg(cfg))
         return rc;
     if (!w || !x || !out || !w->router_w_dev || !w->gate_up_w_dev || !w->down_w_dev)
@@ -569,27 +582,68 @@ int xs_moe_forward(const XsMoeConfig *cfg, const XsMoeWeights *w, const void *x,
     float *y = reinterpret_cast<float *>(b + p.off_y);
     float *ysh = S ? reinterpret_cast<float *>(b + p.off_ysh) : nullptr;
 
+    XS_MARK(0);
     if (int rc = launch_route(cfg, x, w->router_w_dev, w->router_bias_dev, logits, ids, tw, st))
         return rc;
+    XS_MARK(1);
     if (int rc = launch_permute(cfg, ids, counts, offsets, perm, inv, reinterpret_cast<int32_t *>(b + p.off_chunk_counts),
                                 reinterpret_cast<int32_t *>(b + p.off_chunk_base), p.chunks, status, st))
         return rc;
     const int n_routed = T * K, n_total = T * K + S * T;
     xs::gather_rows_kernel<<<n_total, 256, 0, st>>>(static_cast<const uint8_t *>(x), perm, rows, n_routed, n_total, K, H * 2);
     XS_CUDA(cudaGetLastError());
+    XS_MARK(2);
     if (int rc = run_grouped_mlp(H, I, E, cfg->gemm_impl, w->gate_up_w_dev, w->down_w_dev, rows, offsets, n_routed, y,
-                                 b + p.off_grouped, p.routed, status, st))
+                                 b + p.off_grouped, p.routed, status, st, ev ? ev[3] : nullptr))
         return rc;
+    XS_MARK(4);
     if (S) {
         int32_t *sh_off = reinterpret_cast<int32_t *>(b + p.off_sh_offsets);
         set_two_ints_kernel<<<1, 1, 0, st>>>(sh_off, 0, T);
         XS_CUDA(cudaGetLastError());
         if (int rc = run_grouped_mlp(H, I, 1, cfg->gemm_impl, w->shared_gate_up_w_dev, w->shared_down_w_dev,
                                      rows + static_cast<size_t>(n_routed) * H * 2, sh_off, T, ysh, b + p.off_grouped_sh, p.shared,
-                                     status, st))
+                                     status, st, ev ? ev[5] : nullptr))
             return rc;
+    } else {
+        XS_MARK(5);
     }
-    return xs_moe_combine(cfg, y, inv, tw, ysh, out, stream);
+    XS_MARK(6);
+    if (int rc = xs_moe_combine(cfg, y, inv, tw, ysh, out, stream))
+        return rc;
+    XS_MARK(7);
+    return 0;
+#undef XS_MARK
+}
+
+int xs_moe_forward(const XsMoeConfig *cfg, const XsMoeWeights *w, const void *x, void *out, void *ws, size_t ws_bytes, void *stream)
+{
+    return forward_impl(cfg, w, x, out, ws, ws_bytes, stream, nullptr);
+}
+
+int xs_moe_forward_profile(const XsMoeConfig *cfg, const XsMoeWeights *w, const void *x, void *out, void *ws, size_t ws_bytes,
+                           void *stream, float *stage_ms)
+{
+    if (!stage_ms)
+        return fail(XS_MOE_ERR_INVALID_ARG, "null out-pointer");
+    cudaEvent_t ev[8];
+    for (int i = 0; i < 8; i++)
+        XS_CUDA(cudaEventCreate(&ev[i]));
+    int rc = forward_impl(cfg, w, x, out, ws, ws_bytes, stream, ev);
+    if (rc == 0 && cfg->num_tokens > 0) {
+        cudaError_t e = cudaEventSynchronize(ev[7]);
+        if (e != cudaSuccess)
+            rc = fail(XS_MOE_ERR_CUDA, "CUDA error: %s", cudaGetErrorString(e));
+        for (int i = 0; i < 7 && rc == 0; i++)
+            if (cudaEventElapsedTime(&stage_ms[i], ev[i], ev[i + 1]) != cudaSuccess)
+                rc = fail(XS_MOE_ERR_CUDA, "CUDA error: event timing failed");
+    } else {
+        for (int i = 0; i < 7; i++)
+            stage_ms[i] = 0.0f;
+    }
+    for (int i = 0; i < 8; i++)
+        cudaEventDestroy(ev[i]);
+    return rc;
 }
 
 int xs_moe_check_flags(void *ws, void *stream)
