@@ -37,6 +37,7 @@ def test_route_bit_exact(oracle, name, T):
     dims = dict(synth.CONFIGS[name])
     if T is not None:
         dims["T"] = T
+    dims["fmt"] = "bf16"  # routing does not depend on the expert weight format
     g = torch.Generator(device="cuda").manual_seed(21)
     x = (torch.randn((dims["T"], dims["H"]), generator=g, device="cuda")).to(torch.bfloat16)
     rw = (torch.randn((dims["E"], dims["H"]), generator=g, device="cuda") * 0.02).to(torch.bfloat16)

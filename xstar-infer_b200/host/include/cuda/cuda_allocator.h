@@ -1,0 +1,53 @@
+// Device memory for host-side C++: raw allocation, synchronous copies, a free-memory probe and a
+// workspace pool.  CUDA-free header: the functions forward to the C ABI of the kernel library
+// (include/xs_moe.h), so translation units compiled by g++ never see a CUDA header -- the same layering
+// as the reference's allocator wrappers (xstar_cpp/include/cuda/cuda_allocator.h:32-69), with
+// "CUDA error: ..." runtime_errors on failure like CHECK_CUDA (xstar_cpp/include/cuda/cuda_check.h:23-31).
+#pragma once
+#include <cstddef>
+#include <mutex>
+#include <vector>
+
+void *cuda_alloc(std::size_t bytes);
+void cuda_free(void *ptr) noexcept;
+void cuda_memcpy_h2d(void *dst, const void *src, std::size_t bytes);
+void cuda_memcpy_d2h(void *dst, const void *src, std::size_t bytes);
+void cuda_memcpy_d2d(void *dst, const void *src, std::size_t bytes);
+std::size_t cuda_free_bytes();
+
+// Grow-only arena for per-call scratch.  The reference allocates every temporary with cudaMalloc and frees
+// it when the Tensor dies (xstar_cpp/src/tensor.cpp:34-37); an MoE call needs a dozen temporaries, so the
+// op leases ONE buffer from this pool and carves it up.  A lease is exclusive; returning it keeps the
+// memory for the next call.  trim() gives everything back to the driver.
+class WorkspacePool
+{
+public:
+    struct Lease {
+        void *ptr = nullptr;
+        std::size_t bytes = 0;
+    };
+    static WorkspacePool &instance();
+    Lease acquire(std::size_t bytes);
+    void release(Lease lease) noexcept;
+    void trim() noexcept;
+    std::size_t cached_bytes() const;
+
+private:
+    mutable std::mutex mu_;
+    std::vector<Lease> free_;
+};
+
+// RAII lease
+class Workspace
+{
+public:
+    explicit Workspace(std::size_t bytes) : lease_(WorkspacePool::instance().acquire(bytes)) {}
+    ~Workspace() { WorkspacePool::instance().release(lease_); }
+    Workspace(const Workspace &) = delete;
+    Workspace &operator=(const Workspace &) = delete;
+    void *data() const { return lease_.ptr; }
+    std::size_t bytes() const { return lease_.bytes; }
+
+private:
+    WorkspacePool::Lease lease_;
+};
