@@ -57,7 +57,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.Q, "--format=csv,noheader,nounits",
-                                          "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                                          "-lms", "50"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.th = threading.Thread(target=self._read, daemon=True)
             self.th.start()
         except Exception:
@@ -327,6 +327,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="decode_bf16")
     ap.add_argument("--tokens", type=int, default=None, help="override the workload's token count")
+    ap.add_argument("--experts", type=int, default=None, help="override the routed expert count (small profiling cases)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     args = ap.parse_args()
 
@@ -335,6 +336,8 @@ def main():
     dims = dict(synth.CONFIGS[args.workload])
     if args.tokens is not None:
         dims["T"] = args.tokens
+    if args.experts is not None:
+        dims["E"] = args.experts
     if args.impl == "reference":
         run_reference_arm(args, dims)
     else:

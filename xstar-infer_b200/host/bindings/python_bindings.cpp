@@ -1,0 +1,130 @@
+// pybind11 module `xstar_cpp`: the Tensor bridge functions the reference's tests use
+// (reference bindings/python_bindings.cpp:60-135, 389-410: from_numpy_raw / to_numpy_raw / to_cuda / to_cpu /
+// cuda_free_bytes, DType, Device, Tensor) plus the MoE op.  Raw bytes cross the boundary; numpy dtypes carry
+// no meaning beyond their item size (bf16 travels as uint16, e4m3 / packed e2m1 / e8m0 as uint8).
+#include <pybind11/numpy.h>
+#include <pybind11/pybind11.h>
+#include <pybind11/stl.h>
+
+#include <cstring>
+
+#include "cuda/cuda_allocator.h"
+#include "ops/moe.h"
+#include "tensor.h"
+
+namespace py = pybind11;
+
+namespace {
+
+Tensor from_numpy_raw(py::array array, std::vector<std::int64_t> shape, DType dtype)
+{
+    if (static_cast<std::size_t>(array.itemsize()) != dtype_size(dtype))
+        throw std::runtime_error("itemsize mismatch: array itemsize != dtype size");
+    std::int64_t n = 1;
+    for (auto s : shape)
+        n *= s;
+    if (array.size() != n)
+        throw std::runtime_error("byte count mismatch");
+    if (!(array.flags() & py::array::c_style))
+        throw std::runtime_error("array must be C-contiguous");
+    Tensor t(std::move(shape), dtype, Device::CPU);
+    std::memcpy(t.data(), array.data(), t.nbytes());
+    return t;
+}
+
+py::array to_numpy_raw(const Tensor &t)
+{
+    if (t.device() != Device::CPU)
+        throw std::runtime_error("to_numpy_raw: tensor is not on the CPU");
+    py::array_t<std::uint8_t> out(static_cast<py::ssize_t>(t.nbytes()));
+    std::memcpy(out.mutable_data(), t.data(), t.nbytes());
+    return out;
+}
+
+const Tensor *opt(py::object o)
+{
+    return o.is_none() ? nullptr : &o.cast<const Tensor &>();
+}
+
+Tensor moe_py(const Tensor &x, const Tensor &router_weight, const Tensor &gate_up_weight, const Tensor &down_weight, std::int64_t top_k,
+              py::object router_bias, py::object gate_up_scale, py::object down_scale, py::object shared_gate_up_weight,
+              py::object shared_down_weight, py::object shared_gate_up_scale, py::object shared_down_scale)
+{
+    MoEWeights w;
+    w.router_weight = &router_weight;
+    w.router_bias = opt(router_bias);
+    w.gate_up_weight = &gate_up_weight;
+    w.gate_up_scale = opt(gate_up_scale);
+    w.down_weight = &down_weight;
+    w.down_scale = opt(down_scale);
+    w.shared_gate_up_weight = opt(shared_gate_up_weight);
+    w.shared_down_weight = opt(shared_down_weight);
+    w.shared_gate_up_scale = opt(shared_gate_up_scale);
+    w.shared_down_scale = opt(shared_down_scale);
+    MoEConfig cfg;
+    cfg.top_k = top_k;
+    py::gil_scoped_release nogil; // the device work does not touch Python state
+    return moe(x, w, cfg);
+}
+
+py::dict moe_route_py(const Tensor &x, const Tensor &router_weight, std::int64_t top_k, py::object router_bias)
+{
+    MoEConfig cfg;
+    cfg.top_k = top_k;
+    MoERouting r = moe_route(x, router_weight, opt(router_bias), cfg);
+    const py::ssize_t T = x.dim(-1) ? x.numel() / x.dim(-1) : 0, K = top_k;
+    auto ivec = [](const std::vector<std::int32_t> &v, std::vector<py::ssize_t> shape) {
+        py::array_t<std::int32_t> a(shape);
+        std::memcpy(a.mutable_data(), v.data(), v.size() * 4);
+        return a;
+    };
+    py::array_t<float> w({T, K});
+    std::memcpy(w.mutable_data(), r.topk_weights.data(), r.topk_weights.size() * 4);
+    py::dict d;
+    d["topk_ids"] = ivec(r.topk_ids, {T, K});
+    d["topk_w"] = w;
+    d["counts"] = ivec(r.counts, {(py::ssize_t)r.counts.size()});
+    d["offsets"] = ivec(r.offsets, {(py::ssize_t)r.offsets.size()});
+    d["perm"] = ivec(r.perm, {(py::ssize_t)r.perm.size()});
+    d["inv"] = ivec(r.inv, {(py::ssize_t)r.inv.size()});
+    return d;
+}
+
+} // namespace
+
+PYBIND11_MODULE(xstar_cpp, m)
+{
+    m.doc() = "Xstar MoE layer for B200: Tensor bridge + moe op";
+
+    py::enum_<DType>(m, "DType")
+        .value("Float32", DType::Float32)
+        .value("BFloat16", DType::BFloat16)
+        .value("Float8E4M3", DType::Float8E4M3)
+        .value("Float4E2M1x2", DType::Float4E2M1x2)
+        .value("UE8M0", DType::UE8M0)
+        .value("Int32", DType::Int32)
+        .export_values();
+    py::enum_<Device>(m, "Device").value("CPU", Device::CPU).value("CUDA", Device::CUDA).export_values();
+
+    py::class_<Tensor>(m, "Tensor")
+        .def(py::init<std::vector<std::int64_t>, DType, Device>(), py::arg("shape"), py::arg("dtype"), py::arg("device") = Device::CPU)
+        .def("numel", &Tensor::numel)
+        .def("nbytes", &Tensor::nbytes)
+        .def("shape", &Tensor::shape)
+        .def("dtype", &Tensor::dtype)
+        .def("device", &Tensor::device);
+
+    m.def("from_numpy_raw", &from_numpy_raw, py::arg("array"), py::arg("shape"), py::arg("dtype"));
+    m.def("to_numpy_raw", &to_numpy_raw, py::arg("tensor"));
+    m.def("to_cuda", &to_cuda, py::arg("tensor"));
+    m.def("to_cpu", &to_cpu, py::arg("tensor"));
+    m.def("cuda_free_bytes", &cuda_free_bytes);
+    m.def("workspace_cached_bytes", [] { return WorkspacePool::instance().cached_bytes(); });
+    m.def("workspace_trim", [] { WorkspacePool::instance().trim(); });
+
+    m.def("moe", &moe_py, py::arg("x"), py::arg("router_weight"), py::arg("gate_up_weight"), py::arg("down_weight"), py::arg("top_k"),
+          py::arg("router_bias") = py::none(), py::arg("gate_up_scale") = py::none(), py::arg("down_scale") = py::none(),
+          py::arg("shared_gate_up_weight") = py::none(), py::arg("shared_down_weight") = py::none(),
+          py::arg("shared_gate_up_scale") = py::none(), py::arg("shared_down_scale") = py::none());
+    m.def("moe_route", &moe_route_py, py::arg("x"), py::arg("router_weight"), py::arg("top_k"), py::arg("router_bias") = py::none());
+}

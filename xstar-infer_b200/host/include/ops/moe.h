@@ -1,0 +1,55 @@
+// Mixture-of-experts feed-forward layer: router top-k -> token permute -> per-expert SwiGLU MLP -> weighted
+// combine (+ shared expert).  It fills the slot `mlp(x, gate_up_weight, down_weight)` has in the engine's
+// transformer block (reference xstar_cpp/src/ops/transformer_block.cpp:353) and follows the same op
+// conventions (reference xstar_cpp/include/ops/mlp.h:51): free function, borrowed const inputs, optional
+// inputs as pointers, a new owned Tensor returned by value, std::runtime_error with short messages
+// ("dtype mismatch", "rank mismatch", "shape mismatch", "device mismatch") on bad arguments.
+//
+// This header is CUDA-free.  The device work is reached through the C ABI in include/xs_moe.h.
+//
+//   x                 (..., H)       bf16, leading dims collapsed to T rows
+//   router_weight     (E, H)         bf16
+//   router_bias       (E)            f32 or null; added to the logits for SELECTION only
+//   gate_up_weight    (E, 2I, H)     rows [gate; up]; bf16, or Float8E4M3 with gate_up_scale (E, 2I/128, H/128) f32
+//   down_weight       (E, H, I)      bf16, or Float8E4M3 with down_scale (E, H/128, I/128) f32
+//   shared_*          (2I, H), (H, I) one always-on expert, optional
+//   returns           same shape as x, bf16
+//
+// Numerics: router logits accumulate in ascending k in f32 (so expert choices are reproducible bit for
+// bit); the k largest logit+bias win, ties to the lower expert id; weights are the softmax over the chosen
+// logits; per expert silu(gate)*up in f32 with one rounding to the activation type, f32 accumulation in
+// both GEMMs; out = sum over slots in ascending expert id, shared expert last, one rounding to bf16.
+//
+// Device::CPU inputs are rejected ("unsupported device"): the layer has no host implementation.
+#pragma once
+#include <cstdint>
+#include <vector>
+
+#include "tensor.h"
+
+struct MoEConfig {
+    std::int64_t top_k = 1;
+};
+
+struct MoEWeights {
+    const Tensor *router_weight = nullptr;
+    const Tensor *router_bias = nullptr;
+    const Tensor *gate_up_weight = nullptr;
+    const Tensor *gate_up_scale = nullptr;
+    const Tensor *down_weight = nullptr;
+    const Tensor *down_scale = nullptr;
+    const Tensor *shared_gate_up_weight = nullptr;
+    const Tensor *shared_gate_up_scale = nullptr;
+    const Tensor *shared_down_weight = nullptr;
+    const Tensor *shared_down_scale = nullptr;
+};
+
+Tensor moe(const Tensor &x, const MoEWeights &weights, const MoEConfig &config);
+
+// Routing decisions for inspection and tests: ids (T, k) ascending per row, weights (T, k),
+// counts (E), offsets (E+1), perm (T*k), inv (T*k).  Host vectors; x and router tensors on the device.
+struct MoERouting {
+    std::vector<std::int32_t> topk_ids, counts, offsets, perm, inv;
+    std::vector<float> topk_weights;
+};
+MoERouting moe_route(const Tensor &x, const Tensor &router_weight, const Tensor *router_bias, const MoEConfig &config);
