@@ -1,0 +1,95 @@
+"""The reference-facing boundary: the `xstar_cpp` module (host C++ over the C ABI).  CPU tests cover the
+bridge and argument errors; GPU tests call xstar_cpp.moe the way the reference's tests call xstar_cpp.mlp
+(tests/ops/test_cpp_cuda_mlp.py in the reference: CUDA op against the CPU oracle)."""
+import numpy as np
+import pytest
+import torch
+
+from xstar_moe import synth
+
+from bridge import cpp_to_torch, torch_to_cpp, xstar_cpp
+
+
+def test_bridge_roundtrip_is_bit_exact():
+    g = torch.Generator().manual_seed(0)
+    for t in (torch.randn(3, 5, generator=g), torch.randn(4, 6, generator=g).to(torch.bfloat16),
+              torch.randint(-9, 9, (7,), generator=g, dtype=torch.int32)):
+        c = torch_to_cpp(t)
+        assert c.shape() == list(t.shape) and c.numel() == t.numel()
+        back = cpp_to_torch(c, t.shape)
+        assert torch.equal(back.view(torch.uint8) if back.dtype != torch.bfloat16 else back.view(torch.uint16),
+                           t.view(torch.uint8) if t.dtype != torch.bfloat16 else t.view(torch.uint16))
+    b = torch.arange(32, dtype=torch.uint8).reshape(4, 8)
+    c = torch_to_cpp(b, xstar_cpp.DType.Float8E4M3)
+    assert c.nbytes() == 32 and torch.equal(cpp_to_torch(c, (4, 8)), b)
+
+
+def test_from_numpy_raw_rejects_wrong_sizes():
+    with pytest.raises(RuntimeError, match="itemsize mismatch"):
+        xstar_cpp.from_numpy_raw(np.zeros(4, np.float32), [4], xstar_cpp.DType.BFloat16)
+    with pytest.raises(RuntimeError, match="byte count mismatch"):
+        xstar_cpp.from_numpy_raw(np.zeros(4, np.float32), [5], xstar_cpp.DType.Float32)
+
+
+def _cpu_tensors(H=128, E=4, I=128, T=3):
+    g = torch.Generator().manual_seed(1)
+    x = torch.randn(T, H, generator=g).to(torch.bfloat16)
+    rw = torch.randn(E, H, generator=g).to(torch.bfloat16)
+    gu = torch.randn(E, 2 * I, H, generator=g).to(torch.bfloat16)
+    dw = torch.randn(E, H, I, generator=g).to(torch.bfloat16)
+    return x, rw, gu, dw
+
+
+def test_moe_argument_errors_match_the_reference_vocabulary():
+    x, rw, gu, dw = _cpu_tensors()
+    X, RW, GU, DW = (torch_to_cpp(t) for t in (x, rw, gu, dw))
+    with pytest.raises(RuntimeError, match="dtype mismatch"):
+        xstar_cpp.moe(torch_to_cpp(x.float()), RW, GU, DW, 2)
+    with pytest.raises(RuntimeError, match="shape mismatch"):
+        xstar_cpp.moe(torch_to_cpp(x[:, :64].contiguous()), RW, GU, DW, 2)
+    with pytest.raises(RuntimeError, match="rank mismatch"):
+        xstar_cpp.moe(X, RW, torch_to_cpp(gu[0].contiguous()), DW, 2)
+    with pytest.raises(RuntimeError, match="top_k out of range"):
+        xstar_cpp.moe(X, RW, GU, DW, 5)
+    with pytest.raises(RuntimeError, match="expert count mismatch"):
+        xstar_cpp.moe(X, RW, torch_to_cpp(gu[:3].contiguous()), DW, 2)
+    with pytest.raises(RuntimeError, match="gate_up out must be even"):
+        xstar_cpp.moe(X, RW, torch_to_cpp(gu[:, :255].contiguous()), DW, 2)
+    with pytest.raises(RuntimeError, match="unsupported device"):  # no host implementation, no fallback
+        xstar_cpp.moe(X, RW, GU, DW, 2)
+
+
+@pytest.mark.gpu
+def test_moe_op_matches_oracle_and_does_not_leak(oracle):
+    dims = dict(T=70, H=512, E=16, K=4, I=256, S=1, fmt="bf16", bias=None)
+    d = synth.make_inputs(dims, seed=2)
+    dev = {k: xstar_cpp.to_cuda(torch_to_cpp(v)) for k, v in d.items() if v is not None}
+    kw = dict(shared_gate_up_weight=dev["shared_gate_up_w"], shared_down_weight=dev["shared_down_w"])
+    out = xstar_cpp.moe(dev["x"], dev["router_w"], dev["gate_up_w"], dev["down_w"], dims["K"], **kw)
+    assert out.shape() == [70, 512] and out.dtype() == xstar_cpp.DType.BFloat16
+    got = cpp_to_torch(xstar_cpp.to_cpu(out), (70, 512)).float().numpy()
+    n = synth.to_numpy_storage(d)
+    ref = oracle.moe_forward(oracle.BF16, n["x"], n["router_w"], n["gate_up_w"], n["down_w"], dims["K"],
+                             shared_gate_up_w=n["shared_gate_up_w"], shared_down_w=n["shared_down_w"], threads=4)
+    assert synth.rel_l2(got, synth.bf16_bits_to_f32(ref["out"])) <= 2e-3
+    r = xstar_cpp.moe_route(dev["x"], dev["router_w"], dims["K"])
+    for k in ("topk_ids", "counts", "offsets", "perm", "inv"):
+        assert np.array_equal(r[k], ref[k]), k
+    # leading dims collapse like the reference's mlp: (2, 35, H) -> same values
+    x3 = xstar_cpp.to_cuda(torch_to_cpp(d["x"].reshape(2, 35, 512)))
+    out3 = xstar_cpp.moe(x3, dev["router_w"], dev["gate_up_w"], dev["down_w"], dims["K"], **kw)
+    assert out3.shape() == [2, 35, 512]
+    assert np.array_equal(cpp_to_torch(xstar_cpp.to_cpu(out3), (70, 512)).float().numpy(), got)
+    # no-leak probe, as the reference's allocator tests do (100 iterations, 1 MiB slack)
+    before = xstar_cpp.cuda_free_bytes()
+    for _ in range(100):
+        xstar_cpp.moe(dev["x"], dev["router_w"], dev["gate_up_w"], dev["down_w"], dims["K"], **kw)
+    assert before - xstar_cpp.cuda_free_bytes() <= (1 << 20)
+
+
+@pytest.mark.gpu
+def test_moe_op_rejects_mixed_devices():
+    x, rw, gu, dw = _cpu_tensors()
+    X, RW, GU, DW = (torch_to_cpp(t) for t in (x, rw, gu, dw))
+    with pytest.raises(RuntimeError, match="device mismatch"):
+        xstar_cpp.moe(xstar_cpp.to_cuda(X), RW, GU, DW, 2)
