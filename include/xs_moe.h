@@ -140,6 +140,27 @@ int xs_moe_route(const XsMoeConfig *cfg, const void *x_dev, const void *router_w
 int xs_moe_permute(const XsMoeConfig *cfg, const int32_t *topk_ids_dev, int32_t *counts_dev, int32_t *offsets_dev,
                    int32_t *perm_dev, int32_t *inv_dev, void *workspace_dev, size_t workspace_bytes, void *stream);
 
+/* xs_moe_permute for callers that cannot allocate device memory.  No counterpart in the reference (every
+ * reference op allocates its temporaries with cudaMalloc, xstar_cpp/src/tensor.cpp:34-37).
+ *
+ * Who needs it: an engine whose start-up gave all free HBM to its KV page pool, so that a later cudaMalloc has
+ * nothing to return; a serving thread that must not stall, since cudaMalloc and cudaFree synchronise the whole
+ * device.  This call performs no cudaMalloc, cudaFree or any other allocating routine: its chunk tables live in
+ * a fixed array inside the library image (about 513 KB, held by every GPU that loads the library until the
+ * process exits).  Inputs and outputs are the caller's, exactly as for xs_moe_permute, and the results are
+ * identical.
+ *
+ * Limits: num_tokens <= 16384 and num_experts <= 1024; larger calls fail with XS_MOE_ERR_WORKSPACE and a
+ * message that names the limit.
+ * The first call on each device looks up the array's device address (one runtime query, with that device
+ * current); make that first call before any stream capture begins.
+ * All calls on a device share the array and it keeps the previous call's contents; what must start at zero
+ * is cleared on `stream` at the start of each call.  Calls that overlap on the GPU (two streams, two threads)
+ * race on it -- serialise them.  Out-of-range expert ids are skipped as in xs_moe_permute, but the flag is
+ * kept inside the library and not reported; use xs_moe_permute + xs_moe_check_flags for untrusted ids. */
+int xs_moe_permute_noalloc(const XsMoeConfig *cfg, const int32_t *topk_ids_dev, int32_t *counts_dev,
+                           int32_t *offsets_dev, int32_t *perm_dev, int32_t *inv_dev, void *stream);
+
 /* Per-expert SwiGLU MLPs over already-routed rows: rows_dev(M,H) bf16 are grouped by LOCAL expert
  * (expert e owns rows [offsets[e], offsets[e+1]), e in [0, local_expert_count)); y_dev(M,H) f32 receives
  * down(silu(gate x) * up x) per row.  Takes the role of gemm_silu_and_mul_launch + the down linear

@@ -672,6 +672,74 @@ int xs_moe_workspace_init(void *ws, size_t ws_bytes, void *stream)
     return 0;
 }
 
+// ---------------------------------------------------------------------------------------------------------
+// Permutation without any allocation.
+//
+// Some callers cannot obtain device memory at the moment they need a permutation: an engine that gave all
+// free HBM to its KV page pool at start-up has nothing left for cudaMalloc to hand out, and a serving thread
+// that must keep its latency flat cannot afford cudaMalloc / cudaFree either, because both synchronise the
+// whole device.  For them the chunk tables the permutation kernels need live in the array below, which is part
+// of the library image: every GPU that loads the library holds these ~513 KB until the process exits.
+//
+// Limits: at most kNoAllocMaxTokens tokens and kNoAllocMaxExperts experts per call.
+// The array is shared by every call on the device and keeps what the previous call left in it; the words that
+// must start at zero are cleared (on the caller's stream) at the start of each call.  Two calls that overlap
+// on the GPU -- different streams, or different host threads -- race on the array: serialise them.
+constexpr int kNoAllocMaxTokens = 16384;
+constexpr int kNoAllocMaxExperts = 1024;
+constexpr int kNoAllocStatusInts = 64; // 256 bytes: status word + padding
+constexpr size_t kNoAllocTableInts = static_cast<size_t>(kNoAllocMaxTokens / xs::kChunkTokens) * kNoAllocMaxExperts;
+static __device__ __align__(256) int32_t g_noalloc_scratch[kNoAllocStatusInts + 2 * kNoAllocTableInts];
+
+// In host code the name of a __device__ array is only a handle for the runtime, never an address a kernel may
+// be given.  The device address is looked up once per device (with that device current) and cached.
+static int noalloc_scratch_address(int32_t **out)
+{
+    static std::mutex mu;
+    static int32_t *addr[64] = {};
+    int dev = 0;
+    XS_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64)
+        return fail(XS_MOE_ERR_DEVICE, "device ordinal %d outside the supported range", dev);
+    std::lock_guard<std::mutex> g(mu);
+    if (!addr[dev]) {
+        int32_t *p = nullptr;
+        cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void **>(&p), g_noalloc_scratch);
+        if (e != cudaSuccess || !p)
+            return fail(XS_MOE_ERR_CUDA, "CUDA error: %s (cudaGetSymbolAddress of the built-in scratch)", cudaGetErrorString(e));
+        addr[dev] = p;
+    }
+    *out = addr[dev];
+    return 0;
+}
+
+int xs_moe_permute_noalloc(const XsMoeConfig *cfg, const int32_t *ids, int32_t *counts, int32_t *offsets, int32_t *perm,
+                           int32_t *inv, void *stream)
+{
+    if (int rc = check_cfg(cfg))
+        return rc;
+    if (!ids || !counts || !offsets || !perm || !inv)
+        return fail(XS_MOE_ERR_INVALID_ARG, "null tensor pointer");
+    if (cfg->num_tokens > kNoAllocMaxTokens || cfg->num_experts > kNoAllocMaxExperts)
+        return fail(XS_MOE_ERR_WORKSPACE,
+                    "built-in scratch too small: %d tokens x %d experts asked, at most %d tokens x %d experts per call "
+                    "(use xs_moe_permute with a caller workspace)",
+                    cfg->num_tokens, cfg->num_experts, kNoAllocMaxTokens, kNoAllocMaxExperts);
+    int32_t *base = nullptr;
+    if (int rc = noalloc_scratch_address(&base))
+        return rc;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    int chunks = (cfg->num_tokens + xs::kChunkTokens - 1) / xs::kChunkTokens;
+    if (chunks == 0)
+        chunks = 1;
+    // the status word is OR-ed into by the kernels, so it has to start at zero; the chunk tables are fully
+    // rewritten for the (chunks x experts) range this call reads
+    XS_CUDA(cudaMemsetAsync(base, 0, kNoAllocStatusInts * sizeof(int32_t), st));
+    int32_t *chunk_counts = base + kNoAllocStatusInts;
+    int32_t *chunk_base = chunk_counts + kNoAllocTableInts;
+    return launch_permute(cfg, ids, counts, offsets, perm, inv, chunk_counts, chunk_base, chunks, base, st);
+}
+
 int xs_moe_forward_host(const XsMoeConfig *cfg, const XsMoeWeights *w, const void *x_host, void *out_host, void *x_stage, void *out_stage,
                         void *ws, size_t ws_bytes, void *stream)
 {

@@ -40,7 +40,7 @@ EXPORTS = [
     "xs_moe_status_string", "xs_moe_last_error", "xs_moe_device_check", "xs_moe_device_alloc", "xs_moe_device_free",
     "xs_moe_memcpy_h2d", "xs_moe_memcpy_d2h", "xs_moe_memcpy_d2d", "xs_moe_device_free_bytes",
     "xs_moe_stream_synchronize", "xs_moe_workspace_bytes", "xs_moe_workspace_init", "xs_moe_forward",
-    "xs_moe_forward_host", "xs_moe_forward_profile", "xs_moe_route", "xs_moe_permute", "xs_moe_grouped_mlp_workspace_bytes",
+    "xs_moe_forward_host", "xs_moe_forward_profile", "xs_moe_route", "xs_moe_permute", "xs_moe_permute_noalloc", "xs_moe_grouped_mlp_workspace_bytes",
     "xs_moe_grouped_mlp", "xs_moe_combine", "xs_moe_check_flags",
 ]
 
@@ -74,6 +74,7 @@ def lib():
             "xs_moe_forward_profile": [cfgp, wp, vp, vp, vp, sz, vp, C.POINTER(C.c_float)],
             "xs_moe_route": [cfgp, vp, vp, vp, vp, vp, vp, vp, sz, vp],
             "xs_moe_permute": [cfgp, vp, vp, vp, vp, vp, vp, sz, vp],
+            "xs_moe_permute_noalloc": [cfgp, vp, vp, vp, vp, vp, vp],
             "xs_moe_grouped_mlp_workspace_bytes": [cfgp, i32, C.POINTER(sz)],
             "xs_moe_grouped_mlp": [cfgp, wp, vp, vp, i32, vp, vp, sz, vp],
             "xs_moe_combine": [cfgp, vp, vp, vp, vp, vp, vp],
