@@ -31,7 +31,8 @@ import numpy as np  # noqa: E402
 
 METRIC = "moe_layer_tokens_per_s"
 UNIT = "tokens/s"
-KERNELS_PER_STEP = 14  # router, top-k, count, scan, fill, gather, 2x(tile table, gate/up, down), shared offsets, combine
+# router, top-k, count, scan, fill, gather, 2x(tile table, gate/up, down), shared offsets, combine (+ quantise, scale gather for FP8)
+KERNELS_PER_STEP = {"bf16": 14, "fp8": 16, "fp4": 16}
 
 
 def measured_peaks():
@@ -279,7 +280,7 @@ def run_ours(args, dims):
     dom_ms = float(stage_ms[2])
     layer_bytes = synth.algorithmic_bytes(dims, active)
     roofline = {
-        "bound": "hbm", "kernel": "grouped_gemm_bf16_kernel<gate_up> (routed experts)",
+        "bound": "hbm", "kernel": f"grouped_gemm_{'bf16' if dims['fmt'] == 'bf16' else 'fp8'}_kernel<gate_up> (routed experts)",
         "achieved": gate_up_bytes / (dom_ms * 1e-3) / 1e9, "peak": peak, "unit": "GB/s", "peak_kind": peak_kind,
         "frac": gate_up_bytes / (dom_ms * 1e-3) / 1e9 / peak, "traffic": None,
         "algorithmic_bytes_per_launch": gate_up_bytes, "ms_per_launch": dom_ms,
@@ -311,7 +312,7 @@ def run_ours(args, dims):
                        l2="inputs larger than L2: expert weights streamed per step exceed 126 MB"),
         "e2e": {"value": tokens / (ms_e2e * 1e-3), "unit": UNIT, "h2d_bytes_per_step": T * H * 2, "d2h_bytes_per_step": T * H * 2 + 4,
                 "ms_per_step": ms_e2e / args.steps},
-        "gpu_launches": KERNELS_PER_STEP * args.steps,
+        "gpu_launches": KERNELS_PER_STEP[dims["fmt"]] * args.steps,
         "roofline": roofline, "cpu_baseline": cpu, "clocks": clocks,
     }
     print(json.dumps(line), flush=True)

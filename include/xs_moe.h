@@ -161,15 +161,22 @@ int xs_moe_permute(const XsMoeConfig *cfg, const int32_t *topk_ids_dev, int32_t 
 int xs_moe_permute_noalloc(const XsMoeConfig *cfg, const int32_t *topk_ids_dev, int32_t *counts_dev,
                            int32_t *offsets_dev, int32_t *perm_dev, int32_t *inv_dev, void *stream);
 
-/* Per-expert SwiGLU MLPs over already-routed rows: rows_dev(M,H) bf16 are grouped by LOCAL expert
+/* Per-expert SwiGLU MLPs over already-routed rows: rows_dev(M,H) (bf16, or e4m3 codes with
+ * row_scales_dev (M, H/128) f32 for FP8 experts; NULL for bf16) are grouped by LOCAL expert
  * (expert e owns rows [offsets[e], offsets[e+1]), e in [0, local_expert_count)); y_dev(M,H) f32 receives
  * down(silu(gate x) * up x) per row.  Takes the role of gemm_silu_and_mul_launch + the down linear
  * (xstar_cpp/include/ops/mlp.h:95-102, xstar_cpp/src/ops/mlp.cpp:64-70), once per expert segment.
  * max_rows is the capacity of rows_dev / y_dev (the true M is offsets[E_local], read on the device). */
 int xs_moe_grouped_mlp_workspace_bytes(const XsMoeConfig *cfg, int32_t max_rows, size_t *bytes);
 int xs_moe_grouped_mlp(const XsMoeConfig *cfg, const XsMoeWeights *w, const void *rows_dev,
-                       const int32_t *offsets_dev, int32_t max_rows, float *y_dev, void *workspace_dev,
-                       size_t workspace_bytes, void *stream);
+                       const float *row_scales_dev, const int32_t *offsets_dev, int32_t max_rows, float *y_dev,
+                       void *workspace_dev, size_t workspace_bytes, void *stream);
+
+/* Activation quantisation for FP8 experts: x (rows, cols) bf16 -> e4m3 codes (rows, cols) and one f32 scale
+ * per (row, 128 columns): s = max(amax, 1e-10) / 448, code = e4m3_rne_saturating(x / s).  No counterpart in
+ * the reference, whose DType has no 8-bit member (xstar_cpp/include/dtype.h:8-12). */
+int xs_moe_quantize_rows_fp8(const void *x_dev, int32_t rows, int32_t cols, void *codes_dev, float *scales_dev,
+                             void *stream);
 
 /* out[t] = sum_j w[t,j] * y[inv[t,j]] (+ shared[t]), slot order, shared last, f32, one RNE downcast
  * (add's contract, xstar_cpp/src/ops/add.cpp:27-49).  shared_dev (T,H) f32 may be NULL. */

@@ -65,7 +65,7 @@ def permute(dims, ids):
     return counts, offsets, perm, inv
 
 
-def grouped_mlp(dims, d, rows, offsets, gemm_impl=0):
+def grouped_mlp(dims, d, rows, offsets, gemm_impl=0, row_scales=None):
     """rows (M,H) bf16 cuda, offsets (E+1) int32 cuda -> y (M,H) f32."""
     cfg = cfg_of(dims, gemm_impl, T=1)
     M = rows.shape[0]
@@ -75,7 +75,7 @@ def grouped_mlp(dims, d, rows, offsets, gemm_impl=0):
     ws = torch.zeros(n.value, dtype=torch.uint8, device="cuda")
     y = torch.empty((M, cfg.hidden), dtype=torch.float32, device="cuda")
     w = capi.make_weights(d)
-    capi.check(L.xs_moe_grouped_mlp(C.byref(cfg), C.byref(w), capi.ptr(rows), capi.ptr(offsets), M, capi.ptr(y), capi.ptr(ws),
+    capi.check(L.xs_moe_grouped_mlp(C.byref(cfg), C.byref(w), capi.ptr(rows), capi.ptr(row_scales), capi.ptr(offsets), M, capi.ptr(y), capi.ptr(ws),
                                     ws.numel(), stream_ptr()))
     capi.check(L.xs_moe_check_flags(capi.ptr(ws), stream_ptr()))
     return y

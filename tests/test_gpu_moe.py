@@ -195,3 +195,50 @@ def test_forward_decode_shape_subset(oracle):
     got = gu.bf16_to_f32(out)[sub]
     rel = synth.rel_l2(got, synth.bf16_bits_to_f32(ref["out"])[sub])
     assert rel <= BF16_TOL, rel
+
+
+# ---- FP8 e4m3 experts with 128x128 block scales ----------------------------------------------------------------
+FP8_TOL = 1e-2  # rel-L2, FP8 path vs oracle FP8 mode (same quantisation points)
+
+
+def test_quantize_rows_fp8_bit_exact(oracle):
+    g = torch.Generator(device="cuda").manual_seed(41)
+    x = (torch.randn((37, 512), generator=g, device="cuda") * torch.rand((37, 1), generator=g, device="cuda") * 4).to(torch.bfloat16)
+    x[5, :128] = 0
+    x[6, 128:256] *= 1e-20
+    q = torch.empty((37, 512), dtype=torch.uint8, device="cuda")
+    s = torch.empty((37, 4), dtype=torch.float32, device="cuda")
+    capi.check(capi.lib().xs_moe_quantize_rows_fp8(capi.ptr(x), 37, 512, capi.ptr(q), capi.ptr(s), gu.stream_ptr()))
+    torch.cuda.synchronize()
+    rq, rs = oracle.quant_act_fp8(x.float().cpu().numpy())
+    assert np.array_equal(s.cpu().numpy().view(np.uint32), rs.view(np.uint32))
+    assert np.array_equal(q.cpu().numpy(), rq)
+
+
+@pytest.mark.parametrize("T,S,E,K,H,I", [(1, 1, 8, 2, 256, 256), (9, 1, 8, 3, 512, 256), (70, 0, 16, 4, 256, 384),
+                                         (200, 1, 8, 2, 384, 256), (333, 1, 4, 2, 256, 128)])
+def test_forward_fp8_ragged_shapes(oracle, T, S, E, K, H, I):
+    dims = _dims(T=T, S=S, E=E, K=K, H=H, I=I, fmt="fp8")
+    d = synth.make_inputs(dims, seed=T + 1, device="cuda")
+    out = gu.forward(dims, d)
+    ref = gu.oracle_forward(oracle, dims, d)
+    rel = synth.rel_l2(gu.bf16_to_f32(out), synth.bf16_bits_to_f32(ref["out"]))
+    print(f"fp8 T={T}: rel-L2 {rel:.3e}")
+    assert rel <= FP8_TOL, rel
+    assert torch.equal(out, gu.forward(dims, d)), "FP8 forward is not deterministic"
+
+
+@pytest.mark.parametrize("name,n_sub", [("decode_fp8_t1", 1), ("decode_fp8_t32", 8), ("decode_fp8_t256", 8)])
+def test_forward_fp8_decode_shapes(oracle, name, n_sub):
+    """The FP8 decode layers (H=4096, E=256, k=6, shared expert, I=2048; T=1/32/256) at full size: routing on all tokens,
+    outputs on a seeded subset of tokens."""
+    dims = synth.CONFIGS[name]
+    d = synth.make_inputs(dims, seed=0, device="cuda")
+    out = gu.forward(dims, d)
+    sub = np.sort(np.random.default_rng(1).choice(dims["T"], n_sub, replace=False)).astype(np.int32)
+    ref = gu.oracle_forward(oracle, dims, d, token_subset=sub, threads=os.cpu_count() or 8)
+    logits, ids, w = gu.route(dims, d)
+    assert np.array_equal(ids.cpu().numpy(), ref["topk_ids"])
+    rel = synth.rel_l2(gu.bf16_to_f32(out)[sub], synth.bf16_bits_to_f32(ref["out"])[sub])
+    print(f"{name}: rel-L2 {rel:.3e}")
+    assert rel <= FP8_TOL, rel

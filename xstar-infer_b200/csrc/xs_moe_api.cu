@@ -135,24 +135,28 @@ int check_cfg(const XsMoeConfig *c)
     if (c->local_expert_begin < 0 || c->local_expert_count <= 0 ||
         c->local_expert_begin + c->local_expert_count > c->num_experts)
         return fail(XS_MOE_ERR_INVALID_ARG, "expert count mismatch: local expert range outside [0, num_experts)");
-    if (c->routed_format != XS_MOE_BF16 || (c->num_shared && c->shared_format != XS_MOE_BF16))
-        return fail(XS_MOE_ERR_UNSUPPORTED, "unsupported dtype: only bf16 expert weights in this build");
+    if (c->routed_format != XS_MOE_BF16 && c->routed_format != XS_MOE_FP8_BLOCK128)
+        return fail(XS_MOE_ERR_UNSUPPORTED, "unsupported dtype: routed experts must be bf16 or FP8 e4m3 with 128x128 block scales in this build");
+    if (c->num_shared && c->shared_format != c->routed_format)
+        return fail(XS_MOE_ERR_UNSUPPORTED, "unsupported dtype: the shared expert must use the routed experts' format in this build");
     if (c->gemm_impl != 0 && c->gemm_impl != 1)
         return fail(XS_MOE_ERR_INVALID_ARG, "gemm_impl must be 0 or 1");
+    if (c->gemm_impl == 1 && c->routed_format != XS_MOE_BF16)
+        return fail(XS_MOE_ERR_UNSUPPORTED, "unsupported dtype: the CUDA-core cross-check kernels are bf16 only");
     for (int i = 0; i < 5; i++)
         if (c->reserved[i] != 0)
             return fail(XS_MOE_ERR_INVALID_ARG, "reserved fields must be zero");
     return 0;
 }
 
-int pick_n_tile(long rows, int groups)
+int pick_n_tile(long rows, int groups, int fmt)
 {
     const long avg = groups > 0 ? (rows + groups - 1) / groups : rows;
     if (avg <= 8)
         return 16;
     if (avg <= 20)
         return 32;
-    if (avg <= 48)
+    if (avg <= 48 || fmt != XS_MOE_BF16) // the FP8 epilogue keeps one f32 accumulator per token column in registers
         return 64;
     return 128;
 }
@@ -160,19 +164,20 @@ int pick_n_tile(long rows, int groups)
 // ---- workspace plans -----------------------------------------------------------------------------------
 struct GroupedPlan { // scratch of one grouped MLP over `max_rows` rows and `groups` experts
     int n_tile = 0, max_tiles = 0;
-    size_t off_tile_expert = 0, off_tile_row0 = 0, off_num_tiles = 0, off_act = 0, bytes = 0;
+    size_t off_tile_expert = 0, off_tile_row0 = 0, off_num_tiles = 0, off_act = 0, off_act_scale = 0, bytes = 0;
 };
 
-GroupedPlan plan_grouped(int max_rows, int groups, int I)
+GroupedPlan plan_grouped(int max_rows, int groups, int I, int fmt = XS_MOE_BF16)
 {
     GroupedPlan p;
-    p.n_tile = pick_n_tile(max_rows, groups);
+    p.n_tile = pick_n_tile(max_rows, groups, fmt);
     p.max_tiles = max_rows / p.n_tile + groups + 1;
     size_t o = 0;
     p.off_tile_expert = o; o = align_up(o + sizeof(int32_t) * p.max_tiles, 256);
     p.off_tile_row0 = o;   o = align_up(o + sizeof(int32_t) * p.max_tiles, 256);
     p.off_num_tiles = o;   o = align_up(o + sizeof(int32_t), 256);
-    p.off_act = o;         o = align_up(o + static_cast<size_t>(max_rows) * I * 2, 256);
+    p.off_act = o;         o = align_up(o + static_cast<size_t>(max_rows) * I * (fmt == XS_MOE_BF16 ? 2 : 1), 256);
+    p.off_act_scale = o;   o = align_up(o + (fmt == XS_MOE_BF16 ? 0 : static_cast<size_t>(max_rows) * (I / 128) * 4), 256);
     p.bytes = o;
     return p;
 }
@@ -183,7 +188,7 @@ struct ForwardPlan {
     int chunks = 0;
     size_t off_logits = 0, off_ids = 0, off_w = 0, off_counts = 0, off_offsets = 0, off_perm = 0, off_inv = 0;
     size_t off_chunk_counts = 0, off_chunk_base = 0, off_sh_offsets = 0, off_rows = 0, off_y = 0, off_ysh = 0;
-    size_t off_grouped = 0, off_grouped_sh = 0;
+    size_t off_grouped = 0, off_grouped_sh = 0, off_xq = 0, off_xs = 0, off_rows_scale = 0;
     GroupedPlan routed, shared;
     size_t bytes = 0;
 };
@@ -211,13 +216,19 @@ ForwardPlan plan_forward(const XsMoeConfig *c)
     p.off_chunk_counts = take(static_cast<size_t>(p.chunks) * E * 4);
     p.off_chunk_base = take(static_cast<size_t>(p.chunks) * E * 4);
     p.off_sh_offsets = take(2 * 4);
-    p.off_rows = take((T * K + S * T) * H * 2);
+    const bool fp8 = c->routed_format == XS_MOE_FP8_BLOCK128;
+    p.off_rows = take((T * K + S * T) * H * (fp8 ? 1 : 2));
+    if (fp8) {
+        p.off_rows_scale = take((T * K + S * T) * (H / 128) * 4);
+        p.off_xq = take(T * H);
+        p.off_xs = take(T * (H / 128) * 4);
+    }
     p.off_y = take(T * K * H * 4);
     p.off_ysh = take(S * T * H * 4);
-    p.routed = plan_grouped(static_cast<int>(T * K), static_cast<int>(E), static_cast<int>(I));
+    p.routed = plan_grouped(static_cast<int>(T * K), static_cast<int>(E), static_cast<int>(I), c->routed_format);
     p.off_grouped = take(p.routed.bytes);
     if (S) {
-        p.shared = plan_grouped(static_cast<int>(T), 1, static_cast<int>(I));
+        p.shared = plan_grouped(static_cast<int>(T), 1, static_cast<int>(I), c->shared_format);
         p.off_grouped_sh = take(p.shared.bytes);
     }
     p.bytes = o;
@@ -374,6 +385,139 @@ int run_grouped_mlp(int H, int I, int groups, int gemm_impl, const void *gate_up
     return 0;
 }
 
+
+int make_tmap_u8(CUtensorMap *m, const void *base, uint64_t rows, uint64_t cols, uint32_t box_rows)
+{
+    return make_tmap_2d(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, base, rows, cols, box_rows, xs::kBlockK8);
+}
+
+constexpr int kFp8TailBytes = 3072; // barriers (256) + amax exchange (2 x 4 x 64 floats)
+
+template <int N_TILE, bool GATE_UP>
+int launch_gemm_fp8_t(const CUtensorMap &tw, const CUtensorMap &tx, const int32_t *offsets, xs::TileTable tt, xs::Fp8Scales sc,
+                      int w_rows, int n_out, int K, void *out, int32_t *status, int max_work, cudaStream_t st)
+{
+    DeviceInfo di;
+    if (int rc = device_info(&di))
+        return rc;
+    const int stage_bytes = (GATE_UP ? 2 : 1) * xs::kTileM * xs::kBlockK8 + N_TILE * xs::kBlockK8;
+    int stages = (di.max_smem - 1024 - kFp8TailBytes) / stage_bytes;
+    if (stages > 8)
+        stages = 8;
+    if (stages < 2)
+        return fail(XS_MOE_ERR_DEVICE, "not enough shared memory for the GEMM pipeline");
+    const int smem = stages * stage_bytes + 1024 + kFp8TailBytes;
+    auto kern = xs::grouped_gemm_fp8_kernel<N_TILE, GATE_UP>;
+    static bool configured[64] = {};
+    int dev = 0;
+    XS_CUDA(cudaGetDevice(&dev));
+    if (dev >= 64 || !configured[dev]) {
+        XS_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        if (dev < 64)
+            configured[dev] = true;
+    }
+    int grid = di.sms < max_work ? di.sms : max_work;
+    if (grid < 1)
+        grid = 1;
+    kern<<<grid, xs::kGemmThreads, smem, st>>>(tw, tx, offsets, tt, sc, w_rows, n_out, K, out, status, stages);
+    XS_CUDA(cudaGetLastError());
+    return 0;
+}
+
+template <bool GATE_UP>
+int launch_gemm_fp8(int n_tile, const CUtensorMap &tw, const CUtensorMap &tx, const int32_t *offsets, xs::TileTable tt,
+                    xs::Fp8Scales sc, int w_rows, int n_out, int K, void *out, int32_t *status, int max_work, cudaStream_t st)
+{
+    switch (n_tile) {
+    case 16: return launch_gemm_fp8_t<16, GATE_UP>(tw, tx, offsets, tt, sc, w_rows, n_out, K, out, status, max_work, st);
+    case 32: return launch_gemm_fp8_t<32, GATE_UP>(tw, tx, offsets, tt, sc, w_rows, n_out, K, out, status, max_work, st);
+    case 64: return launch_gemm_fp8_t<64, GATE_UP>(tw, tx, offsets, tt, sc, w_rows, n_out, K, out, status, max_work, st);
+    }
+    return fail(XS_MOE_ERR_INVALID_ARG, "internal: bad token tile %d for FP8", n_tile);
+}
+
+// FP8 grouped SwiGLU MLP: rows (max_rows, H) e4m3 with row_scale (max_rows, H/128); weights e4m3 with 128x128 f32 scales.
+int run_grouped_mlp_fp8(int H, int I, int groups, const void *gate_up_w, const float *gate_up_scale, const void *down_w,
+                        const float *down_scale, const void *rows, const float *row_scale, const int32_t *offsets, int max_rows,
+                        float *y, uint8_t *scratch, const GroupedPlan &gp, int32_t *status, cudaStream_t st, cudaEvent_t mid = nullptr)
+{
+    if (max_rows == 0) {
+        if (mid)
+            XS_CUDA(cudaEventRecord(mid, st));
+        return 0;
+    }
+    void *act = scratch + gp.off_act;
+    float *act_scale = reinterpret_cast<float *>(scratch + gp.off_act_scale);
+    xs::TileTable tt;
+    int32_t *tile_expert = reinterpret_cast<int32_t *>(scratch + gp.off_tile_expert);
+    int32_t *tile_row0 = reinterpret_cast<int32_t *>(scratch + gp.off_tile_row0);
+    int32_t *num_tiles = reinterpret_cast<int32_t *>(scratch + gp.off_num_tiles);
+    tt.tile_expert = tile_expert;
+    tt.tile_row0 = tile_row0;
+    tt.num_tiles = num_tiles;
+    const int threads = (groups + 31) / 32 * 32;
+    xs::tile_table_kernel<<<1, threads, 0, st>>>(offsets, groups, gp.n_tile, gp.max_tiles, tile_expert, tile_row0, num_tiles, status);
+    XS_CUDA(cudaGetLastError());
+    CUtensorMap t_wgu, t_wd, t_x, t_act;
+    if (int rc = make_tmap_u8(&t_wgu, gate_up_w, static_cast<uint64_t>(groups) * 2 * I, H, xs::kTileM))
+        return rc;
+    if (int rc = make_tmap_u8(&t_wd, down_w, static_cast<uint64_t>(groups) * H, I, xs::kTileM))
+        return rc;
+    if (int rc = make_tmap_u8(&t_x, rows, max_rows, H, gp.n_tile))
+        return rc;
+    if (int rc = make_tmap_u8(&t_act, act, max_rows, I, gp.n_tile))
+        return rc;
+    xs::Fp8Scales s1{gate_up_scale, row_scale, act_scale};
+    if (int rc = launch_gemm_fp8<true>(gp.n_tile, t_wgu, t_x, offsets, tt, s1, 2 * I, I, H, act, status, gp.max_tiles * (I / xs::kTileM), st))
+        return rc;
+    if (mid)
+        XS_CUDA(cudaEventRecord(mid, st));
+    xs::Fp8Scales s2{down_scale, act_scale, nullptr};
+    if (int rc = launch_gemm_fp8<false>(gp.n_tile, t_wd, t_act, offsets, tt, s2, H, H, I, y, status, gp.max_tiles * (H / xs::kTileM), st))
+        return rc;
+    return 0;
+}
+
+// format dispatch for one grouped MLP
+int run_grouped_any(int fmt, int H, int I, int groups, int gemm_impl, const void *gate_up_w, const void *gate_up_scale,
+                    const void *down_w, const void *down_scale, const void *rows, const float *row_scale, const int32_t *offsets,
+                    int max_rows, float *y, uint8_t *scratch, const GroupedPlan &gp, int32_t *status, cudaStream_t st,
+                    cudaEvent_t mid = nullptr)
+{
+    if (fmt == XS_MOE_BF16)
+        return run_grouped_mlp(H, I, groups, gemm_impl, gate_up_w, down_w, rows, offsets, max_rows, y, scratch, gp, status, st, mid);
+    if (!gate_up_scale || !down_scale || !row_scale)
+        return fail(XS_MOE_ERR_INVALID_ARG, "missing scale");
+    return run_grouped_mlp_fp8(H, I, groups, gate_up_w, static_cast<const float *>(gate_up_scale), down_w,
+                               static_cast<const float *>(down_scale), rows, row_scale, offsets, max_rows, y, scratch, gp, status, st,
+                               mid);
+}
+
+int launch_quantize_rows(const void *x, uint8_t *q, float *scale, int rows, int cols, cudaStream_t st)
+{
+    if (rows == 0)
+        return 0;
+    const long warps = static_cast<long>(rows) * (cols / 128);
+    const int blocks = static_cast<int>((warps + 7) / 8);
+    xs::quantize_rows_fp8_kernel<<<blocks, 256, 0, st>>>(static_cast<const __nv_bfloat16 *>(x), q, scale, rows, cols);
+    XS_CUDA(cudaGetLastError());
+    return 0;
+}
+
+int launch_gather(const void *src, const int32_t *perm, void *dst, int n_routed, int n_total, int K, int row_bytes, cudaStream_t st)
+{
+    if (n_total == 0)
+        return 0;
+    if (row_bytes % 16 == 0)
+        xs::gather_rows_kernel<<<n_total, 256, 0, st>>>(static_cast<const uint8_t *>(src), perm, static_cast<uint8_t *>(dst), n_routed,
+                                                        n_total, K, row_bytes);
+    else
+        xs::gather_rows4_kernel<<<n_total, 64, 0, st>>>(static_cast<const uint32_t *>(src), perm, static_cast<uint32_t *>(dst),
+                                                        n_routed, n_total, K, row_bytes / 4);
+    XS_CUDA(cudaGetLastError());
+    return 0;
+}
+
 __global__ void set_two_ints_kernel(int32_t *p, int a, int b)
 {
     p[0] = a;
@@ -500,12 +644,12 @@ int xs_moe_grouped_mlp_workspace_bytes(const XsMoeConfig *cfg, int32_t max_rows,
         return rc;
     if (!bytes || max_rows < 0)
         return fail(XS_MOE_ERR_INVALID_ARG, "bad arguments");
-    *bytes = kStatusBytes + plan_grouped(max_rows, cfg->local_expert_count, cfg->intermediate).bytes;
+    *bytes = kStatusBytes + plan_grouped(max_rows, cfg->local_expert_count, cfg->intermediate, cfg->routed_format).bytes;
     return 0;
 }
 
-int xs_moe_grouped_mlp(const XsMoeConfig *cfg, const XsMoeWeights *w, const void *rows, const int32_t *offsets, int32_t max_rows,
-                       float *y, void *ws, size_t ws_bytes, void *stream)
+int xs_moe_grouped_mlp(const XsMoeConfig *cfg, const XsMoeWeights *w, const void *rows, const float *row_scales,
+                       const int32_t *offsets, int32_t max_rows, float *y, void *ws, size_t ws_bytes, void *stream)
 {
     if (int rc = check_cfg(cfg))
         return rc;
@@ -516,13 +660,22 @@ int xs_moe_grouped_mlp(const XsMoeConfig *cfg, const XsMoeWeights *w, const void
     if (cfg->gemm_impl == 0)
         if (int rc = xs_moe_device_check())
             return rc;
-    GroupedPlan gp = plan_grouped(max_rows, cfg->local_expert_count, cfg->intermediate);
+    GroupedPlan gp = plan_grouped(max_rows, cfg->local_expert_count, cfg->intermediate, cfg->routed_format);
     if (int rc = check_workspace(ws, ws_bytes, kStatusBytes + gp.bytes))
         return rc;
     uint8_t *b = static_cast<uint8_t *>(ws);
-    return run_grouped_mlp(cfg->hidden, cfg->intermediate, cfg->local_expert_count, cfg->gemm_impl, w->gate_up_w_dev, w->down_w_dev,
-                           rows, offsets, max_rows, y, b + kStatusBytes, gp, reinterpret_cast<int32_t *>(b),
-                           static_cast<cudaStream_t>(stream));
+    return run_grouped_any(cfg->routed_format, cfg->hidden, cfg->intermediate, cfg->local_expert_count, cfg->gemm_impl,
+                           w->gate_up_w_dev, w->gate_up_scale_dev, w->down_w_dev, w->down_scale_dev, rows, row_scales, offsets,
+                           max_rows, y, b + kStatusBytes, gp, reinterpret_cast<int32_t *>(b), static_cast<cudaStream_t>(stream));
+}
+
+int xs_moe_quantize_rows_fp8(const void *x, int32_t rows, int32_t cols, void *codes, float *scales, void *stream)
+{
+    if (!x || !codes || !scales)
+        return fail(XS_MOE_ERR_INVALID_ARG, "null tensor pointer");
+    if (rows < 0 || cols <= 0 || cols % 128 != 0)
+        return fail(XS_MOE_ERR_INVALID_ARG, "shape mismatch: columns must be a positive multiple of 128");
+    return launch_quantize_rows(x, static_cast<uint8_t *>(codes), scales, rows, cols, static_cast<cudaStream_t>(stream));
 }
 
 int xs_moe_combine(const XsMoeConfig *cfg, const float *y, const int32_t *inv, const float *topk_w, const float *shared, void *out,
@@ -590,20 +743,38 @@ static int forward_impl(const XsMoeConfig *cfg, const XsMoeWeights *w, const voi
                                 reinterpret_cast<int32_t *>(b + p.off_chunk_base), p.chunks, status, st))
         return rc;
     const int n_routed = T * K, n_total = T * K + S * T;
-    xs::gather_rows_kernel<<<n_total, 256, 0, st>>>(static_cast<const uint8_t *>(x), perm, rows, n_routed, n_total, K, H * 2);
-    XS_CUDA(cudaGetLastError());
+    const bool fp8 = cfg->routed_format == XS_MOE_FP8_BLOCK128;
+    float *rows_scale = nullptr;
+    if (fp8) {
+        // quantise x once (1x128 groups), then move codes and scales into expert order
+        uint8_t *xq = b + p.off_xq;
+        float *xs_ = reinterpret_cast<float *>(b + p.off_xs);
+        rows_scale = reinterpret_cast<float *>(b + p.off_rows_scale);
+        if (int rc = launch_quantize_rows(x, xq, xs_, T, H, st))
+            return rc;
+        if (int rc = launch_gather(xq, perm, rows, n_routed, n_total, K, H, st))
+            return rc;
+        if (int rc = launch_gather(xs_, perm, rows_scale, n_routed, n_total, K, (H / 128) * 4, st))
+            return rc;
+    } else {
+        if (int rc = launch_gather(x, perm, rows, n_routed, n_total, K, H * 2, st))
+            return rc;
+    }
+    const size_t row_bytes = static_cast<size_t>(H) * (fp8 ? 1 : 2);
     XS_MARK(2);
-    if (int rc = run_grouped_mlp(H, I, E, cfg->gemm_impl, w->gate_up_w_dev, w->down_w_dev, rows, offsets, n_routed, y,
-                                 b + p.off_grouped, p.routed, status, st, ev ? ev[3] : nullptr))
+    if (int rc = run_grouped_any(cfg->routed_format, H, I, E, cfg->gemm_impl, w->gate_up_w_dev, w->gate_up_scale_dev, w->down_w_dev,
+                                 w->down_scale_dev, rows, rows_scale, offsets, n_routed, y, b + p.off_grouped, p.routed, status, st,
+                                 ev ? ev[3] : nullptr))
         return rc;
     XS_MARK(4);
     if (S) {
         int32_t *sh_off = reinterpret_cast<int32_t *>(b + p.off_sh_offsets);
         set_two_ints_kernel<<<1, 1, 0, st>>>(sh_off, 0, T);
         XS_CUDA(cudaGetLastError());
-        if (int rc = run_grouped_mlp(H, I, 1, cfg->gemm_impl, w->shared_gate_up_w_dev, w->shared_down_w_dev,
-                                     rows + static_cast<size_t>(n_routed) * H * 2, sh_off, T, ysh, b + p.off_grouped_sh, p.shared,
-                                     status, st, ev ? ev[5] : nullptr))
+        if (int rc = run_grouped_any(cfg->shared_format, H, I, 1, cfg->gemm_impl, w->shared_gate_up_w_dev, w->shared_gate_up_scale_dev,
+                                     w->shared_down_w_dev, w->shared_down_scale_dev, rows + static_cast<size_t>(n_routed) * row_bytes,
+                                     fp8 ? rows_scale + static_cast<size_t>(n_routed) * (H / 128) : nullptr, sh_off, T, ysh,
+                                     b + p.off_grouped_sh, p.shared, status, st, ev ? ev[5] : nullptr))
             return rc;
     } else {
         XS_MARK(5);

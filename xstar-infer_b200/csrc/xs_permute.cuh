@@ -183,6 +183,19 @@ gather_rows_kernel(const uint8_t *__restrict__ x, const int32_t *__restrict__ pe
         dst[i] = src[i];
 }
 
+// same for rows that are a multiple of 4 bytes only (short scale rows)
+__global__ void __launch_bounds__(64)
+gather_rows4_kernel(const uint32_t *__restrict__ x, const int32_t *__restrict__ perm, uint32_t *__restrict__ rows_out, int n_routed,
+                    int n_total, int K, int row_words)
+{
+    const int row = blockIdx.x;
+    if (row >= n_total)
+        return;
+    const int t = row < n_routed ? perm[row] / K : row - n_routed;
+    for (int i = threadIdx.x; i < row_words; i += blockDim.x)
+        rows_out[static_cast<size_t>(row) * row_words + i] = x[static_cast<size_t>(t) * row_words + i];
+}
+
 // out[t,h] = bf16( sum_j w[t,j] * y[inv[t,j], h]  (+ shared[t,h]) ), slot order, shared last; separate
 // multiply and add (no contraction) so the sum is the same sequence of IEEE operations as the CPU's.
 // Eight outputs per thread: two 16-byte loads per row, one 16-byte store.
