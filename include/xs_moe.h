@@ -110,10 +110,11 @@ int xs_moe_workspace_init(void *workspace_dev, size_t workspace_bytes, void *str
 int xs_moe_forward(const XsMoeConfig *cfg, const XsMoeWeights *w, const void *x_dev, void *out_dev,
                    void *workspace_dev, size_t workspace_bytes, void *stream);
 
-/* xs_moe_forward with CUDA events recorded between its stages on `stream`; synchronises and returns the
- * seven stage times in milliseconds: route, permute+gather, routed gate/up GEMM, routed down GEMM,
- * shared gate/up GEMM, shared down GEMM, combine.  For benchmarks; no counterpart in the reference, whose
- * ops are timed from Python (bench/bench_splitkv.py:86-105 in the reference). */
+/* xs_moe_forward with CUDA events recorded between its stages on `stream`; synchronises and returns SIX stage
+ * times in milliseconds: router logits, selection + permutation + tile table, row scatter (+ activation
+ * quantisation for FP8), gate/up GEMM, down GEMM, combine.  The always-on expert runs inside the two GEMM
+ * launches.  For benchmarks; no counterpart in the reference, whose ops are timed from Python
+ * (bench/bench_splitkv.py:86-105 in the reference). */
 int xs_moe_forward_profile(const XsMoeConfig *cfg, const XsMoeWeights *w, const void *x_dev, void *out_dev,
                            void *workspace_dev, size_t workspace_bytes, void *stream, float *stage_ms);
 

@@ -54,9 +54,9 @@ struct TileTable {
 
 template <int N_TILE, bool GATE_UP>
 __global__ void __launch_bounds__(kGemmThreads, 1)
-grouped_gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
-                         const int32_t *__restrict__ offsets, TileTable tt, int w_rows_per_expert, int n_out, int K,
-                         void *__restrict__ out, int32_t *__restrict__ status, int stages)
+grouped_gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_w2,
+                         const __grid_constant__ CUtensorMap tmap_x, const int32_t *__restrict__ offsets, TileTable tt, int groups,
+                         int w_rows_per_expert, int n_out, int K, void *__restrict__ out, int32_t *__restrict__ status, int stages)
 {
     constexpr int A_BYTES = kTileM * kBlockK * 2;
     constexpr int B_BYTES = N_TILE * kBlockK * 2;
@@ -90,6 +90,7 @@ grouped_gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gri
         *abort_flag = 0;
         fence_mbar_init();
         prefetch_tmap(&tmap_w);
+        prefetch_tmap(&tmap_w2);
         prefetch_tmap(&tmap_x);
     }
     if (warp == 1) {
@@ -118,7 +119,9 @@ grouped_gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gri
                 const int f = w - tile * n_f_tiles;
                 const int e = tt.tile_expert[tile];
                 const int row0 = tt.tile_row0[tile];
-                const int wrow = e * w_rows_per_expert + f * kTileM;
+                // segments past `groups` belong to the always-on expert, whose weights sit behind the second map
+                const CUtensorMap *tw = e < groups ? &tmap_w : &tmap_w2;
+                const int wrow = (e < groups ? e * w_rows_per_expert : 0) + f * kTileM;
                 for (int kb = 0; kb < num_kb; kb++) {
                     if (!mbar_wait(&empty[stage], phase ^ 1, abort_flag)) {
                         ok = false;
@@ -126,9 +129,9 @@ grouped_gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gri
                     }
                     uint8_t *st = smem + static_cast<size_t>(stage) * STAGE_BYTES;
                     mbar_arrive_expect_tx(&full[stage], STAGE_BYTES);
-                    tma_load_2d(st, &tmap_w, &full[stage], kb * kBlockK, wrow, pol_w);
+                    tma_load_2d(st, tw, &full[stage], kb * kBlockK, wrow, pol_w);
                     if (GATE_UP)
-                        tma_load_2d(st + A_BYTES, &tmap_w, &full[stage], kb * kBlockK, wrow + n_out, pol_w);
+                        tma_load_2d(st + A_BYTES, tw, &full[stage], kb * kBlockK, wrow + n_out, pol_w);
                     tma_load_2d(st + (GATE_UP ? 2 : 1) * A_BYTES, &tmap_x, &full[stage], kb * kBlockK, row0, pol_x);
                     if (++stage == stages) {
                         stage = 0;
@@ -268,7 +271,7 @@ __global__ void grouped_gemm_bf16_simt_kernel(const __nv_bfloat16 *__restrict__ 
                                               const int32_t *__restrict__ offsets, int num_experts, int w_rows_per_expert,
                                               int n_out, int K, void *__restrict__ out)
 {
-    const int row = blockIdx.x;
+    const int row = offsets[0] + blockIdx.x; // offsets may point into a longer table: segment 0 starts at offsets[0]
     const int total_rows = offsets[num_experts];
     if (row >= total_rows)
         return;
@@ -342,21 +345,27 @@ __device__ __forceinline__ uint8_t f32_to_e4m3(float v)
 
 struct Fp8Scales {
     const float *w_scale;   // (groups * w_rows_per_expert / 128, K / 128)
+    const float *w_scale2;  // same for the always-on expert (segments >= groups): (w_rows_per_expert / 128, K / 128)
     const float *x_scale;   // (rows, K / 128)
     float *act_scale;       // GATE_UP only: (rows, n_out / 128) written by the epilogue
 };
 
 template <int N_TILE, bool GATE_UP>
 __global__ void __launch_bounds__(kGemmThreads, 1)
-grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
-                        const int32_t *__restrict__ offsets, TileTable tt, Fp8Scales sc, int w_rows_per_expert, int n_out, int K,
-                        void *__restrict__ out, int32_t *__restrict__ status, int stages)
+grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_w2,
+                        const __grid_constant__ CUtensorMap tmap_x, const int32_t *__restrict__ offsets, TileTable tt, Fp8Scales sc,
+                        int groups, int w_rows_per_expert, int n_out, int K, void *__restrict__ out, int32_t *__restrict__ status,
+                        int stages)
 {
     constexpr int A_BYTES = kTileM * kBlockK8;
     constexpr int B_BYTES = N_TILE * kBlockK8;
     constexpr int STAGE_BYTES = (GATE_UP ? 2 : 1) * A_BYTES + B_BYTES;
     constexpr int ACC_COLS = (GATE_UP ? 2 : 1) * N_TILE;
-    constexpr int TMEM_COLS = (2 * ACC_COLS) < 32 ? 32 : 2 * ACC_COLS;
+    // k-block accumulators in flight: enough that the tensor core keeps consuming stages while the epilogue warps
+    // finish a tile (quantise / store) -- as many as fit in the 512 TMEM columns, at most 8
+    constexpr int NBUF = (512 / ACC_COLS) < 8 ? (512 / ACC_COLS) : 8;
+    constexpr int TMEM_COLS = NBUF * ACC_COLS; // a power of two >= 32 for every instantiation (16..64 tokens)
+    static_assert((TMEM_COLS & (TMEM_COLS - 1)) == 0 && TMEM_COLS >= 32 && TMEM_COLS <= 512, "TMEM allocation must be a power of two");
     constexpr uint32_t IDESC = make_idesc(0, 0, kTileM, N_TILE); // e4m3 x e4m3 -> f32
 
     extern __shared__ uint8_t smem_raw[];
@@ -365,11 +374,11 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
     uint64_t *full = bars;
     uint64_t *empty = bars + stages;
     uint64_t *tmem_full = bars + 2 * stages;
-    uint64_t *tmem_empty = tmem_full + 2;
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(tmem_empty + 2);
+    uint64_t *tmem_empty = tmem_full + NBUF;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(tmem_empty + NBUF);
     volatile uint32_t *abort_flag = tmem_slot + 1;
-    uint64_t *xbar = tmem_empty + 3;                            // amax exchange among the four epilogue warps
-    float *amax_x = reinterpret_cast<float *>(bars) + 64;       // [2 buffers][4 warps][N_TILE], 256 bytes after the barriers
+    uint64_t *xbar = tmem_empty + NBUF + 1;                     // amax exchange among the four epilogue warps
+    float *amax_x = reinterpret_cast<float *>(bars) + 128;      // [2 buffers][4 warps][N_TILE], 512 bytes after the barriers
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -379,7 +388,7 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
             mbar_init(&full[s], 1);
             mbar_init(&empty[s], 1);
         }
-        for (int b = 0; b < 2; b++) {
+        for (int b = 0; b < NBUF; b++) {
             mbar_init(&tmem_full[b], 1);
             mbar_init(&tmem_empty[b], 4);
         }
@@ -387,6 +396,7 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
         *abort_flag = 0;
         fence_mbar_init();
         prefetch_tmap(&tmap_w);
+        prefetch_tmap(&tmap_w2);
         prefetch_tmap(&tmap_x);
     }
     if (warp == 1) {
@@ -415,7 +425,9 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
                 const int f = w - tile * n_f_tiles;
                 const int e = tt.tile_expert[tile];
                 const int row0 = tt.tile_row0[tile];
-                const int wrow = e * w_rows_per_expert + f * kTileM;
+                // segments past `groups` belong to the always-on expert, whose weights sit behind the second map
+                const CUtensorMap *tw = e < groups ? &tmap_w : &tmap_w2;
+                const int wrow = (e < groups ? e * w_rows_per_expert : 0) + f * kTileM;
                 for (int kb = 0; kb < num_kb; kb++) {
                     if (!mbar_wait(&empty[stage], phase ^ 1, abort_flag)) {
                         ok = false;
@@ -423,9 +435,9 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
                     }
                     uint8_t *st = smem + static_cast<size_t>(stage) * STAGE_BYTES;
                     mbar_arrive_expect_tx(&full[stage], STAGE_BYTES);
-                    tma_load_2d(st, &tmap_w, &full[stage], kb * kBlockK8, wrow, pol_w);
+                    tma_load_2d(st, tw, &full[stage], kb * kBlockK8, wrow, pol_w);
                     if (GATE_UP)
-                        tma_load_2d(st + A_BYTES, &tmap_w, &full[stage], kb * kBlockK8, wrow + n_out, pol_w);
+                        tma_load_2d(st + A_BYTES, tw, &full[stage], kb * kBlockK8, wrow + n_out, pol_w);
                     tma_load_2d(st + (GATE_UP ? 2 : 1) * A_BYTES, &tmap_x, &full[stage], kb * kBlockK8, row0, pol_x);
                     if (++stage == stages) {
                         stage = 0;
@@ -446,9 +458,9 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
             uint32_t g_kb = 0; // k-blocks issued so far, across tiles: selects the TMEM buffer
             for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x) {
                 for (int kb = 0; kb < num_kb; kb++, g_kb++) {
-                    const int buf = g_kb & 1;
+                    const int buf = g_kb % NBUF;
                     if (!mbar_wait(&full[stage], phase, abort_flag) ||
-                        !mbar_wait(&tmem_empty[buf], ((g_kb >> 1) & 1) ^ 1, abort_flag)) {
+                        !mbar_wait(&tmem_empty[buf], ((g_kb / NBUF) & 1) ^ 1, abort_flag)) {
                         ok = false;
                         break;
                     }
@@ -492,7 +504,8 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
             int nvalid = offsets[e + 1] - row0;
             nvalid = nvalid < N_TILE ? nvalid : N_TILE;
             const int feature = f * kTileM + q * 32 + lane;
-            const float *ws_g = sc.w_scale + static_cast<size_t>(e * (w_rows_per_expert / kTileM) + f) * kbs;
+            const float *ws_g = (e < groups ? sc.w_scale + static_cast<size_t>(e) * (w_rows_per_expert / kTileM) * kbs : sc.w_scale2) +
+                                static_cast<size_t>(f) * kbs;
             const float *ws_u = ws_g + static_cast<size_t>(n_out / kTileM) * kbs;
             float acc_g[N_TILE];
             float acc_u[GATE_UP ? N_TILE : 1];
@@ -503,39 +516,65 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
                     acc_u[c] = 0.0f;
             }
             for (int kb = 0; kb < num_kb; kb++, g_kb++) {
-                const int buf = g_kb & 1;
-                if (!mbar_wait(&tmem_full[buf], (g_kb >> 1) & 1, abort_flag)) {
+                const int buf = g_kb % NBUF;
+                // scales of this k-block first: their latency overlaps the wait for the tensor core
+                const float swg = __ldg(ws_g + kb);
+                const float swu = GATE_UP ? __ldg(ws_u + kb) : 0.0f;
+                float sxw_g[N_TILE], sxw_u[GATE_UP ? N_TILE : 1];
+#pragma unroll
+                for (int c = 0; c < N_TILE; c++) {
+                    const float sx = __ldg(sc.x_scale + static_cast<size_t>(row0 + (c < nvalid ? c : 0)) * kbs + kb);
+                    sxw_g[c] = __fmul_rn(sx, swg);
+                    if constexpr (GATE_UP)
+                        sxw_u[c] = __fmul_rn(sx, swu);
+                }
+                if (!mbar_wait(&tmem_full[buf], (g_kb / NBUF) & 1, abort_flag)) {
                     ok = false;
                     break;
                 }
                 tc_fence_after();
                 const uint32_t t0 = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(buf * ACC_COLS);
-                const float swg = __ldg(ws_g + kb);
-                const float swu = GATE_UP ? __ldg(ws_u + kb) : 0.0f;
+                if constexpr (N_TILE == 16) {
+                    // whole k-block in one round trip; the TMEM buffer is handed back before the arithmetic
+                    uint32_t g[16], u[16];
+                    tmem_ld16(t0, g);
+                    if constexpr (GATE_UP)
+                        tmem_ld16(t0 + N_TILE, u);
+                    tmem_ld_wait();
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0)
+                        mbar_arrive(&tmem_empty[buf]);
 #pragma unroll
-                for (int c0 = 0; c0 < N_TILE; c0 += 16) {
-                    if (c0 < nvalid) {
-                        uint32_t g[16];
-                        tmem_ld16(t0 + c0, g);
-                        uint32_t u[16];
+                    for (int c = 0; c < 16; c++) {
+                        acc_g[c] = __fadd_rn(acc_g[c], __fmul_rn(__uint_as_float(g[c]), sxw_g[c]));
                         if constexpr (GATE_UP)
-                            tmem_ld16(t0 + N_TILE + c0, u);
-                        tmem_ld_wait();
+                            acc_u[c] = __fadd_rn(acc_u[c], __fmul_rn(__uint_as_float(u[c]), sxw_u[c]));
+                    }
+                } else {
 #pragma unroll
-                        for (int c = 0; c < 16; c++) {
-                            const int col = c0 + c;
-                            const int row = row0 + (col < nvalid ? col : 0);
-                            const float sx = __ldg(sc.x_scale + static_cast<size_t>(row) * kbs + kb);
-                            acc_g[col] = __fadd_rn(acc_g[col], __fmul_rn(__uint_as_float(g[c]), __fmul_rn(sx, swg)));
+                    for (int c0 = 0; c0 < N_TILE; c0 += 16) {
+                        if (c0 < nvalid) {
+                            uint32_t g[16];
+                            tmem_ld16(t0 + c0, g);
+                            uint32_t u[16];
                             if constexpr (GATE_UP)
-                                acc_u[col] = __fadd_rn(acc_u[col], __fmul_rn(__uint_as_float(u[c]), __fmul_rn(sx, swu)));
+                                tmem_ld16(t0 + N_TILE + c0, u);
+                            tmem_ld_wait();
+#pragma unroll
+                            for (int c = 0; c < 16; c++) {
+                                const int col = c0 + c;
+                                acc_g[col] = __fadd_rn(acc_g[col], __fmul_rn(__uint_as_float(g[c]), sxw_g[col]));
+                                if constexpr (GATE_UP)
+                                    acc_u[col] = __fadd_rn(acc_u[col], __fmul_rn(__uint_as_float(u[c]), sxw_u[col]));
+                            }
                         }
                     }
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0)
+                        mbar_arrive(&tmem_empty[buf]);
                 }
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0)
-                    mbar_arrive(&tmem_empty[buf]);
             }
             if (!ok)
                 break;

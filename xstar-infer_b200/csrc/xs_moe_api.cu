@@ -162,16 +162,18 @@ int pick_n_tile(long rows, int groups, int fmt)
 }
 
 // ---- workspace plans -----------------------------------------------------------------------------------
-struct GroupedPlan { // scratch of one grouped MLP over `max_rows` rows and `groups` experts
+// Scratch of one grouped MLP over `max_rows` rows in `segments` expert segments (the routed experts and, when the
+// always-on expert is merged into the same launches, one more segment for its rows).
+struct GroupedPlan {
     int n_tile = 0, max_tiles = 0;
     size_t off_tile_expert = 0, off_tile_row0 = 0, off_num_tiles = 0, off_act = 0, off_act_scale = 0, bytes = 0;
 };
 
-GroupedPlan plan_grouped(int max_rows, int groups, int I, int fmt = XS_MOE_BF16)
+GroupedPlan plan_grouped(int max_rows, int routed_rows, int routed_groups, int segments, int I, int fmt)
 {
     GroupedPlan p;
-    p.n_tile = pick_n_tile(max_rows, groups, fmt);
-    p.max_tiles = max_rows / p.n_tile + groups + 1;
+    p.n_tile = pick_n_tile(routed_rows, routed_groups, fmt);
+    p.max_tiles = max_rows / p.n_tile + segments + 1;
     size_t o = 0;
     p.off_tile_expert = o; o = align_up(o + sizeof(int32_t) * p.max_tiles, 256);
     p.off_tile_row0 = o;   o = align_up(o + sizeof(int32_t) * p.max_tiles, 256);
@@ -187,9 +189,8 @@ constexpr size_t kStatusBytes = 256;
 struct ForwardPlan {
     int chunks = 0;
     size_t off_logits = 0, off_ids = 0, off_w = 0, off_counts = 0, off_offsets = 0, off_perm = 0, off_inv = 0;
-    size_t off_chunk_counts = 0, off_chunk_base = 0, off_sh_offsets = 0, off_rows = 0, off_y = 0, off_ysh = 0;
-    size_t off_grouped = 0, off_grouped_sh = 0, off_xq = 0, off_xs = 0, off_rows_scale = 0;
-    GroupedPlan routed, shared;
+    size_t off_chunk_counts = 0, off_chunk_base = 0, off_rows = 0, off_rows_scale = 0, off_y = 0, off_grouped = 0;
+    GroupedPlan grouped;
     size_t bytes = 0;
 };
 
@@ -206,31 +207,22 @@ ForwardPlan plan_forward(const XsMoeConfig *c)
         o = align_up(o + bytes, 256);
         return at;
     };
+    const bool fp8 = c->routed_format == XS_MOE_FP8_BLOCK128;
     p.off_logits = take(T * E * 4);
     p.off_ids = take(T * K * 4);
     p.off_w = take(T * K * 4);
     p.off_counts = take(E * 4);
-    p.off_offsets = take((E + 1) * 4);
+    p.off_offsets = take((E + 2) * 4);
     p.off_perm = take(T * K * 4);
     p.off_inv = take(T * K * 4);
     p.off_chunk_counts = take(static_cast<size_t>(p.chunks) * E * 4);
     p.off_chunk_base = take(static_cast<size_t>(p.chunks) * E * 4);
-    p.off_sh_offsets = take(2 * 4);
-    const bool fp8 = c->routed_format == XS_MOE_FP8_BLOCK128;
     p.off_rows = take((T * K + S * T) * H * (fp8 ? 1 : 2));
-    if (fp8) {
-        p.off_rows_scale = take((T * K + S * T) * (H / 128) * 4);
-        p.off_xq = take(T * H);
-        p.off_xs = take(T * (H / 128) * 4);
-    }
-    p.off_y = take(T * K * H * 4);
-    p.off_ysh = take(S * T * H * 4);
-    p.routed = plan_grouped(static_cast<int>(T * K), static_cast<int>(E), static_cast<int>(I), c->routed_format);
-    p.off_grouped = take(p.routed.bytes);
-    if (S) {
-        p.shared = plan_grouped(static_cast<int>(T), 1, static_cast<int>(I), c->shared_format);
-        p.off_grouped_sh = take(p.shared.bytes);
-    }
+    p.off_rows_scale = take(fp8 ? (T * K + S * T) * (H / 128) * 4 : 0);
+    p.off_y = take((T * K + S * T) * H * 4);
+    p.grouped = plan_grouped(static_cast<int>(T * K + S * T), static_cast<int>(T * K), static_cast<int>(E), static_cast<int>(E + S),
+                             static_cast<int>(I), c->routed_format);
+    p.off_grouped = take(p.grouped.bytes);
     p.bytes = o;
     return p;
 }
@@ -247,16 +239,29 @@ int check_workspace(const void *ws, size_t have, size_t need)
 }
 
 // ---- launches --------------------------------------------------------------------------------------------
-int launch_route(const XsMoeConfig *c, const void *x, const void *rw, const float *bias, float *logits, int32_t *ids, float *w,
-                 cudaStream_t st)
+int launch_logits(const XsMoeConfig *c, const void *x, const void *rw, float *logits, cudaStream_t st)
 {
-    const int T = c->num_tokens, H = c->hidden, E = c->num_experts, K = c->top_k;
+    const int T = c->num_tokens, H = c->hidden, E = c->num_experts;
     if (T == 0)
         return 0;
-    dim3 grid((E + xs::kRtExperts - 1) / xs::kRtExperts, (T + xs::kRtTokens - 1) / xs::kRtTokens);
-    xs::router_logits_kernel<<<grid, xs::kRtThreads, 0, st>>>(static_cast<const __nv_bfloat16 *>(x),
-                                                              static_cast<const __nv_bfloat16 *>(rw), logits, T, H, E);
+    const __nv_bfloat16 *xb = static_cast<const __nv_bfloat16 *>(x), *rwb = static_cast<const __nv_bfloat16 *>(rw);
+    if (T <= 1024) {
+        // decode-sized batch: one output per thread, 8 experts x 32 tokens per block, cp.async pipeline
+        dim3 grid((E + xs::kRdExperts - 1) / xs::kRdExperts, (T + xs::kRdTokens - 1) / xs::kRdTokens);
+        xs::router_logits_decode_kernel<<<grid, xs::kRdThreads, 0, st>>>(xb, rwb, logits, T, H, E);
+    } else {
+        dim3 grid((E + xs::kRtExperts - 1) / xs::kRtExperts, (T + xs::kRtTokens - 1) / xs::kRtTokens);
+        xs::router_logits_kernel<<<grid, xs::kRtThreads, 0, st>>>(xb, rwb, logits, T, H, E);
+    }
     XS_CUDA(cudaGetLastError());
+    return 0;
+}
+
+int launch_topk(const XsMoeConfig *c, const float *logits, const float *bias, int32_t *ids, float *w, cudaStream_t st)
+{
+    const int T = c->num_tokens, E = c->num_experts, K = c->top_k;
+    if (T == 0)
+        return 0;
     const int blocks = (T + 3) / 4;
     if (E <= 32)
         xs::topk_kernel<1><<<blocks, 128, 0, st>>>(logits, bias, ids, w, T, E, K);
@@ -268,24 +273,55 @@ int launch_route(const XsMoeConfig *c, const void *x, const void *rw, const floa
     return 0;
 }
 
+int launch_route(const XsMoeConfig *c, const void *x, const void *rw, const float *bias, float *logits, int32_t *ids, float *w,
+                 cudaStream_t st)
+{
+    if (int rc = launch_logits(c, x, rw, logits, st))
+        return rc;
+    return launch_topk(c, logits, bias, ids, w, st);
+}
+
+// extra_rows >= 0: the always-on expert's rows follow the routed rows and offsets gets one more entry, offsets[E+1]
 int launch_permute(const XsMoeConfig *c, const int32_t *ids, int32_t *counts, int32_t *offsets, int32_t *perm, int32_t *inv,
-                   int32_t *chunk_counts, int32_t *chunk_base, int chunks, int32_t *status, cudaStream_t st)
+                   int32_t *chunk_counts, int32_t *chunk_base, int chunks, int32_t *status, cudaStream_t st, int extra_rows = -1)
 {
     const int T = c->num_tokens, E = c->num_experts, K = c->top_k;
     const size_t smem = static_cast<size_t>(E) * xs::kChunkWords * 4;
     xs::permute_count_kernel<<<chunks, xs::kChunkTokens, smem, st>>>(ids, chunk_counts, T, E, K, status);
     XS_CUDA(cudaGetLastError());
     const int threads = (E + 31) / 32 * 32;
-    xs::permute_scan_kernel<<<1, threads, 0, st>>>(chunk_counts, counts, offsets, chunk_base, chunks, E);
+    xs::permute_scan_kernel<<<1, threads, 0, st>>>(chunk_counts, counts, offsets, chunk_base, chunks, E, extra_rows);
     XS_CUDA(cudaGetLastError());
     xs::permute_fill_kernel<<<chunks, xs::kChunkTokens, smem, st>>>(ids, chunk_base, perm, inv, T, E, K, status);
     XS_CUDA(cudaGetLastError());
     return 0;
 }
 
+struct TileBuffers {
+    int32_t *tile_expert, *tile_row0, *num_tiles;
+};
+
+TileBuffers tile_buffers(uint8_t *scratch, const GroupedPlan &gp)
+{
+    return {reinterpret_cast<int32_t *>(scratch + gp.off_tile_expert), reinterpret_cast<int32_t *>(scratch + gp.off_tile_row0),
+            reinterpret_cast<int32_t *>(scratch + gp.off_num_tiles)};
+}
+
+// Permutation + tile table for a decode-sized batch in one launch (T <= 256).
+int launch_permute_small(const XsMoeConfig *c, const int32_t *ids, int32_t *counts, int32_t *offsets, int32_t *perm, int32_t *inv,
+                         int extra_rows, const GroupedPlan &gp, TileBuffers tb, int32_t *status, cudaStream_t st)
+{
+    const int T = c->num_tokens, E = c->num_experts, K = c->top_k;
+    const size_t smem = static_cast<size_t>(E) * xs::kChunkWords * 4 + static_cast<size_t>(E) * 4;
+    xs::permute_small_kernel<<<1, xs::kChunkTokens, smem, st>>>(ids, counts, offsets, perm, inv, T, E, K, extra_rows, gp.n_tile,
+                                                                gp.max_tiles, tb.tile_expert, tb.tile_row0, tb.num_tiles, status);
+    XS_CUDA(cudaGetLastError());
+    return 0;
+}
+
 template <int N_TILE, bool GATE_UP>
-int launch_gemm_t(const CUtensorMap &tw, const CUtensorMap &tx, const int32_t *offsets, xs::TileTable tt, int w_rows, int n_out,
-                  int K, void *out, int32_t *status, int max_work, cudaStream_t st)
+int launch_gemm_t(const CUtensorMap &tw, const CUtensorMap &tw2, const CUtensorMap &tx, const int32_t *offsets, xs::TileTable tt,
+                  int groups, int w_rows, int n_out, int K, void *out, int32_t *status, int max_work, cudaStream_t st)
 {
     DeviceInfo di;
     if (int rc = device_info(&di))
@@ -309,93 +345,30 @@ int launch_gemm_t(const CUtensorMap &tw, const CUtensorMap &tx, const int32_t *o
     int grid = di.sms < max_work ? di.sms : max_work;
     if (grid < 1)
         grid = 1;
-    kern<<<grid, xs::kGemmThreads, smem, st>>>(tw, tx, offsets, tt, w_rows, n_out, K, out, status, stages);
+    kern<<<grid, xs::kGemmThreads, smem, st>>>(tw, tw2, tx, offsets, tt, groups, w_rows, n_out, K, out, status, stages);
     XS_CUDA(cudaGetLastError());
     return 0;
 }
 
 template <bool GATE_UP>
-int launch_gemm(int n_tile, const CUtensorMap &tw, const CUtensorMap &tx, const int32_t *offsets, xs::TileTable tt, int w_rows,
-                int n_out, int K, void *out, int32_t *status, int max_work, cudaStream_t st)
+int launch_gemm(int n_tile, const CUtensorMap &tw, const CUtensorMap &tw2, const CUtensorMap &tx, const int32_t *offsets,
+                xs::TileTable tt, int groups, int w_rows, int n_out, int K, void *out, int32_t *status, int max_work, cudaStream_t st)
 {
     switch (n_tile) {
-    case 16: return launch_gemm_t<16, GATE_UP>(tw, tx, offsets, tt, w_rows, n_out, K, out, status, max_work, st);
-    case 32: return launch_gemm_t<32, GATE_UP>(tw, tx, offsets, tt, w_rows, n_out, K, out, status, max_work, st);
-    case 64: return launch_gemm_t<64, GATE_UP>(tw, tx, offsets, tt, w_rows, n_out, K, out, status, max_work, st);
-    case 128: return launch_gemm_t<128, GATE_UP>(tw, tx, offsets, tt, w_rows, n_out, K, out, status, max_work, st);
+    case 16: return launch_gemm_t<16, GATE_UP>(tw, tw2, tx, offsets, tt, groups, w_rows, n_out, K, out, status, max_work, st);
+    case 32: return launch_gemm_t<32, GATE_UP>(tw, tw2, tx, offsets, tt, groups, w_rows, n_out, K, out, status, max_work, st);
+    case 64: return launch_gemm_t<64, GATE_UP>(tw, tw2, tx, offsets, tt, groups, w_rows, n_out, K, out, status, max_work, st);
+    case 128: return launch_gemm_t<128, GATE_UP>(tw, tw2, tx, offsets, tt, groups, w_rows, n_out, K, out, status, max_work, st);
     }
     return fail(XS_MOE_ERR_INVALID_ARG, "internal: bad token tile %d", n_tile);
-}
-
-// One grouped SwiGLU MLP: rows (max_rows, H) bf16 grouped by `groups` experts through offsets (groups+1);
-// y (max_rows, H) f32.  `scratch` follows GroupedPlan.
-int run_grouped_mlp(int H, int I, int groups, int gemm_impl, const void *gate_up_w, const void *down_w, const void *rows,
-                    const int32_t *offsets, int max_rows, float *y, uint8_t *scratch, const GroupedPlan &gp, int32_t *status,
-                    cudaStream_t st, cudaEvent_t mid = nullptr)
-{
-    if (max_rows == 0) {
-        if (mid)
-            XS_CUDA(cudaEventRecord(mid, st));
-        return 0;
-    }
-    void *act = scratch + gp.off_act;
-    if (gemm_impl == 1) {
-        dim3 grid(max_rows, 8);
-        xs::grouped_gemm_bf16_simt_kernel<true><<<grid, 256, 0, st>>>(static_cast<const __nv_bfloat16 *>(gate_up_w),
-                                                                      static_cast<const __nv_bfloat16 *>(rows), offsets, groups,
-                                                                      2 * I, I, H, act);
-        XS_CUDA(cudaGetLastError());
-        if (mid)
-            XS_CUDA(cudaEventRecord(mid, st));
-        xs::grouped_gemm_bf16_simt_kernel<false><<<grid, 256, 0, st>>>(static_cast<const __nv_bfloat16 *>(down_w),
-                                                                       static_cast<const __nv_bfloat16 *>(act), offsets, groups, H,
-                                                                       H, I, y);
-        XS_CUDA(cudaGetLastError());
-        return 0;
-    }
-    xs::TileTable tt;
-    int32_t *tile_expert = reinterpret_cast<int32_t *>(scratch + gp.off_tile_expert);
-    int32_t *tile_row0 = reinterpret_cast<int32_t *>(scratch + gp.off_tile_row0);
-    int32_t *num_tiles = reinterpret_cast<int32_t *>(scratch + gp.off_num_tiles);
-    tt.tile_expert = tile_expert;
-    tt.tile_row0 = tile_row0;
-    tt.num_tiles = num_tiles;
-    const int threads = (groups + 31) / 32 * 32;
-    xs::tile_table_kernel<<<1, threads, 0, st>>>(offsets, groups, gp.n_tile, gp.max_tiles, tile_expert, tile_row0, num_tiles,
-                                                 status);
-    XS_CUDA(cudaGetLastError());
-
-    CUtensorMap t_wgu, t_wd, t_x, t_act;
-    if (int rc = make_tmap_2d(&t_wgu, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, gate_up_w, static_cast<uint64_t>(groups) * 2 * I, H,
-                              xs::kTileM, xs::kBlockK))
-        return rc;
-    if (int rc = make_tmap_2d(&t_wd, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, down_w, static_cast<uint64_t>(groups) * H, I, xs::kTileM,
-                              xs::kBlockK))
-        return rc;
-    if (int rc = make_tmap_2d(&t_x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, rows, max_rows, H, gp.n_tile, xs::kBlockK))
-        return rc;
-    if (int rc = make_tmap_2d(&t_act, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, act, max_rows, I, gp.n_tile, xs::kBlockK))
-        return rc;
-    if (int rc = launch_gemm<true>(gp.n_tile, t_wgu, t_x, offsets, tt, 2 * I, I, H, act, status, gp.max_tiles * (I / xs::kTileM), st))
-        return rc;
-    if (mid)
-        XS_CUDA(cudaEventRecord(mid, st));
-    if (int rc = launch_gemm<false>(gp.n_tile, t_wd, t_act, offsets, tt, H, H, I, y, status, gp.max_tiles * (H / xs::kTileM), st))
-        return rc;
-    return 0;
-}
-
-
-int make_tmap_u8(CUtensorMap *m, const void *base, uint64_t rows, uint64_t cols, uint32_t box_rows)
-{
-    return make_tmap_2d(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, base, rows, cols, box_rows, xs::kBlockK8);
 }
 
 constexpr int kFp8TailBytes = 3072; // barriers (256) + amax exchange (2 x 4 x 64 floats)
 
 template <int N_TILE, bool GATE_UP>
-int launch_gemm_fp8_t(const CUtensorMap &tw, const CUtensorMap &tx, const int32_t *offsets, xs::TileTable tt, xs::Fp8Scales sc,
-                      int w_rows, int n_out, int K, void *out, int32_t *status, int max_work, cudaStream_t st)
+int launch_gemm_fp8_t(const CUtensorMap &tw, const CUtensorMap &tw2, const CUtensorMap &tx, const int32_t *offsets, xs::TileTable tt,
+                      xs::Fp8Scales sc, int groups, int w_rows, int n_out, int K, void *out, int32_t *status, int max_work,
+                      cudaStream_t st)
 {
     DeviceInfo di;
     if (int rc = device_info(&di))
@@ -419,78 +392,122 @@ int launch_gemm_fp8_t(const CUtensorMap &tw, const CUtensorMap &tx, const int32_
     int grid = di.sms < max_work ? di.sms : max_work;
     if (grid < 1)
         grid = 1;
-    kern<<<grid, xs::kGemmThreads, smem, st>>>(tw, tx, offsets, tt, sc, w_rows, n_out, K, out, status, stages);
+    kern<<<grid, xs::kGemmThreads, smem, st>>>(tw, tw2, tx, offsets, tt, sc, groups, w_rows, n_out, K, out, status, stages);
     XS_CUDA(cudaGetLastError());
     return 0;
 }
 
 template <bool GATE_UP>
-int launch_gemm_fp8(int n_tile, const CUtensorMap &tw, const CUtensorMap &tx, const int32_t *offsets, xs::TileTable tt,
-                    xs::Fp8Scales sc, int w_rows, int n_out, int K, void *out, int32_t *status, int max_work, cudaStream_t st)
+int launch_gemm_fp8(int n_tile, const CUtensorMap &tw, const CUtensorMap &tw2, const CUtensorMap &tx, const int32_t *offsets,
+                    xs::TileTable tt, xs::Fp8Scales sc, int groups, int w_rows, int n_out, int K, void *out, int32_t *status,
+                    int max_work, cudaStream_t st)
 {
     switch (n_tile) {
-    case 16: return launch_gemm_fp8_t<16, GATE_UP>(tw, tx, offsets, tt, sc, w_rows, n_out, K, out, status, max_work, st);
-    case 32: return launch_gemm_fp8_t<32, GATE_UP>(tw, tx, offsets, tt, sc, w_rows, n_out, K, out, status, max_work, st);
-    case 64: return launch_gemm_fp8_t<64, GATE_UP>(tw, tx, offsets, tt, sc, w_rows, n_out, K, out, status, max_work, st);
+    case 16: return launch_gemm_fp8_t<16, GATE_UP>(tw, tw2, tx, offsets, tt, sc, groups, w_rows, n_out, K, out, status, max_work, st);
+    case 32: return launch_gemm_fp8_t<32, GATE_UP>(tw, tw2, tx, offsets, tt, sc, groups, w_rows, n_out, K, out, status, max_work, st);
+    case 64: return launch_gemm_fp8_t<64, GATE_UP>(tw, tw2, tx, offsets, tt, sc, groups, w_rows, n_out, K, out, status, max_work, st);
     }
     return fail(XS_MOE_ERR_INVALID_ARG, "internal: bad token tile %d for FP8", n_tile);
 }
 
-// FP8 grouped SwiGLU MLP: rows (max_rows, H) e4m3 with row_scale (max_rows, H/128); weights e4m3 with 128x128 f32 scales.
-int run_grouped_mlp_fp8(int H, int I, int groups, const void *gate_up_w, const float *gate_up_scale, const void *down_w,
-                        const float *down_scale, const void *rows, const float *row_scale, const int32_t *offsets, int max_rows,
-                        float *y, uint8_t *scratch, const GroupedPlan &gp, int32_t *status, cudaStream_t st, cudaEvent_t mid = nullptr)
+// One grouped SwiGLU MLP over rows grouped by expert segment.  Segments 0..groups-1 use the stacked weights
+// (gu, dw); if gu2 is given, segment `groups` (the always-on expert's rows) uses (gu2, dw2) in the SAME launches, so
+// its tiles are load-balanced with the routed ones instead of running on a handful of SMs by themselves.
+struct GroupedArgs {
+    int fmt = XS_MOE_BF16, H = 0, I = 0, groups = 0, gemm_impl = 0;
+    const void *gu = nullptr, *gu_scale = nullptr, *dw = nullptr, *dw_scale = nullptr;
+    const void *gu2 = nullptr, *gu2_scale = nullptr, *dw2 = nullptr, *dw2_scale = nullptr;
+    const void *rows = nullptr;
+    const float *row_scale = nullptr;
+    const int32_t *offsets = nullptr; // groups + 1 (+ 1 with gu2) entries
+    int max_rows = 0;
+    float *y = nullptr;
+    uint8_t *scratch = nullptr;
+    GroupedPlan gp;
+    int32_t *status = nullptr;
+    bool tiles_ready = false; // the tile table was already built (fused routing kernel)
+};
+
+int run_grouped(const GroupedArgs &a, cudaStream_t st, cudaEvent_t mid = nullptr)
 {
-    if (max_rows == 0) {
+    if (a.max_rows == 0) {
         if (mid)
             XS_CUDA(cudaEventRecord(mid, st));
         return 0;
     }
-    void *act = scratch + gp.off_act;
-    float *act_scale = reinterpret_cast<float *>(scratch + gp.off_act_scale);
-    xs::TileTable tt;
-    int32_t *tile_expert = reinterpret_cast<int32_t *>(scratch + gp.off_tile_expert);
-    int32_t *tile_row0 = reinterpret_cast<int32_t *>(scratch + gp.off_tile_row0);
-    int32_t *num_tiles = reinterpret_cast<int32_t *>(scratch + gp.off_num_tiles);
-    tt.tile_expert = tile_expert;
-    tt.tile_row0 = tile_row0;
-    tt.num_tiles = num_tiles;
-    const int threads = (groups + 31) / 32 * 32;
-    xs::tile_table_kernel<<<1, threads, 0, st>>>(offsets, groups, gp.n_tile, gp.max_tiles, tile_expert, tile_row0, num_tiles, status);
-    XS_CUDA(cudaGetLastError());
-    CUtensorMap t_wgu, t_wd, t_x, t_act;
-    if (int rc = make_tmap_u8(&t_wgu, gate_up_w, static_cast<uint64_t>(groups) * 2 * I, H, xs::kTileM))
+    const int H = a.H, I = a.I, groups = a.groups;
+    const int segments = groups + (a.gu2 ? 1 : 0);
+    const bool fp8 = a.fmt == XS_MOE_FP8_BLOCK128;
+    if (fp8 && (!a.gu_scale || !a.dw_scale || !a.row_scale || (a.gu2 && (!a.gu2_scale || !a.dw2_scale))))
+        return fail(XS_MOE_ERR_INVALID_ARG, "missing scale");
+    void *act = a.scratch + a.gp.off_act;
+    if (a.gemm_impl == 1) {
+        dim3 grid(a.max_rows, 8);
+        const __nv_bfloat16 *rows = static_cast<const __nv_bfloat16 *>(a.rows);
+        xs::grouped_gemm_bf16_simt_kernel<true><<<grid, 256, 0, st>>>(static_cast<const __nv_bfloat16 *>(a.gu), rows, a.offsets, groups,
+                                                                      2 * I, I, H, act);
+        if (a.gu2)
+            xs::grouped_gemm_bf16_simt_kernel<true><<<grid, 256, 0, st>>>(static_cast<const __nv_bfloat16 *>(a.gu2), rows,
+                                                                          a.offsets + groups, 1, 2 * I, I, H, act);
+        XS_CUDA(cudaGetLastError());
+        if (mid)
+            XS_CUDA(cudaEventRecord(mid, st));
+        const __nv_bfloat16 *actb = static_cast<const __nv_bfloat16 *>(act);
+        xs::grouped_gemm_bf16_simt_kernel<false><<<grid, 256, 0, st>>>(static_cast<const __nv_bfloat16 *>(a.dw), actb, a.offsets, groups,
+                                                                       H, H, I, a.y);
+        if (a.gu2)
+            xs::grouped_gemm_bf16_simt_kernel<false><<<grid, 256, 0, st>>>(static_cast<const __nv_bfloat16 *>(a.dw2), actb,
+                                                                           a.offsets + groups, 1, H, H, I, a.y);
+        XS_CUDA(cudaGetLastError());
+        return 0;
+    }
+    TileBuffers tb = tile_buffers(a.scratch, a.gp);
+    xs::TileTable tt{tb.tile_expert, tb.tile_row0, tb.num_tiles};
+    if (!a.tiles_ready) {
+        const int threads = (segments + 31) / 32 * 32;
+        if (threads > 1024)
+            return fail(XS_MOE_ERR_UNSUPPORTED, "expert count mismatch: at most 1023 local experts next to an always-on expert");
+        xs::tile_table_kernel<<<1, threads, 0, st>>>(a.offsets, segments, a.gp.n_tile, a.gp.max_tiles, tb.tile_expert, tb.tile_row0,
+                                                     tb.num_tiles, a.status);
+        XS_CUDA(cudaGetLastError());
+    }
+    const CUtensorMapDataType dt = fp8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+    const int eb = fp8 ? 1 : 2;
+    const uint32_t box_k = fp8 ? xs::kBlockK8 : xs::kBlockK;
+    CUtensorMap t_wgu, t_wd, t_wgu2, t_wd2, t_x, t_act;
+    if (int rc = make_tmap_2d(&t_wgu, dt, eb, a.gu, static_cast<uint64_t>(groups) * 2 * I, H, xs::kTileM, box_k))
         return rc;
-    if (int rc = make_tmap_u8(&t_wd, down_w, static_cast<uint64_t>(groups) * H, I, xs::kTileM))
+    if (int rc = make_tmap_2d(&t_wd, dt, eb, a.dw, static_cast<uint64_t>(groups) * H, I, xs::kTileM, box_k))
         return rc;
-    if (int rc = make_tmap_u8(&t_x, rows, max_rows, H, gp.n_tile))
+    if (a.gu2) {
+        if (int rc = make_tmap_2d(&t_wgu2, dt, eb, a.gu2, 2 * I, H, xs::kTileM, box_k))
+            return rc;
+        if (int rc = make_tmap_2d(&t_wd2, dt, eb, a.dw2, H, I, xs::kTileM, box_k))
+            return rc;
+    } else {
+        t_wgu2 = t_wgu;
+        t_wd2 = t_wd;
+    }
+    if (int rc = make_tmap_2d(&t_x, dt, eb, a.rows, a.max_rows, H, a.gp.n_tile, box_k))
         return rc;
-    if (int rc = make_tmap_u8(&t_act, act, max_rows, I, gp.n_tile))
+    if (int rc = make_tmap_2d(&t_act, dt, eb, act, a.max_rows, I, a.gp.n_tile, box_k))
         return rc;
-    xs::Fp8Scales s1{gate_up_scale, row_scale, act_scale};
-    if (int rc = launch_gemm_fp8<true>(gp.n_tile, t_wgu, t_x, offsets, tt, s1, 2 * I, I, H, act, status, gp.max_tiles * (I / xs::kTileM), st))
+    const int work_gu = a.gp.max_tiles * (I / xs::kTileM), work_d = a.gp.max_tiles * (H / xs::kTileM);
+    if (!fp8) {
+        if (int rc = launch_gemm<true>(a.gp.n_tile, t_wgu, t_wgu2, t_x, a.offsets, tt, groups, 2 * I, I, H, act, a.status, work_gu, st))
+            return rc;
+        if (mid)
+            XS_CUDA(cudaEventRecord(mid, st));
+        return launch_gemm<false>(a.gp.n_tile, t_wd, t_wd2, t_act, a.offsets, tt, groups, H, H, I, a.y, a.status, work_d, st);
+    }
+    float *act_scale = reinterpret_cast<float *>(a.scratch + a.gp.off_act_scale);
+    xs::Fp8Scales s1{static_cast<const float *>(a.gu_scale), static_cast<const float *>(a.gu2_scale), a.row_scale, act_scale};
+    if (int rc = launch_gemm_fp8<true>(a.gp.n_tile, t_wgu, t_wgu2, t_x, a.offsets, tt, s1, groups, 2 * I, I, H, act, a.status, work_gu, st))
         return rc;
     if (mid)
         XS_CUDA(cudaEventRecord(mid, st));
-    xs::Fp8Scales s2{down_scale, act_scale, nullptr};
-    if (int rc = launch_gemm_fp8<false>(gp.n_tile, t_wd, t_act, offsets, tt, s2, H, H, I, y, status, gp.max_tiles * (H / xs::kTileM), st))
-        return rc;
-    return 0;
-}
-
-// format dispatch for one grouped MLP
-int run_grouped_any(int fmt, int H, int I, int groups, int gemm_impl, const void *gate_up_w, const void *gate_up_scale,
-                    const void *down_w, const void *down_scale, const void *rows, const float *row_scale, const int32_t *offsets,
-                    int max_rows, float *y, uint8_t *scratch, const GroupedPlan &gp, int32_t *status, cudaStream_t st,
-                    cudaEvent_t mid = nullptr)
-{
-    if (fmt == XS_MOE_BF16)
-        return run_grouped_mlp(H, I, groups, gemm_impl, gate_up_w, down_w, rows, offsets, max_rows, y, scratch, gp, status, st, mid);
-    if (!gate_up_scale || !down_scale || !row_scale)
-        return fail(XS_MOE_ERR_INVALID_ARG, "missing scale");
-    return run_grouped_mlp_fp8(H, I, groups, gate_up_w, static_cast<const float *>(gate_up_scale), down_w,
-                               static_cast<const float *>(down_scale), rows, row_scale, offsets, max_rows, y, scratch, gp, status, st,
-                               mid);
+    xs::Fp8Scales s2{static_cast<const float *>(a.dw_scale), static_cast<const float *>(a.dw2_scale), act_scale, nullptr};
+    return launch_gemm_fp8<false>(a.gp.n_tile, t_wd, t_wd2, t_act, a.offsets, tt, s2, groups, H, H, I, a.y, a.status, work_d, st);
 }
 
 int launch_quantize_rows(const void *x, uint8_t *q, float *scale, int rows, int cols, cudaStream_t st)
@@ -502,26 +519,6 @@ int launch_quantize_rows(const void *x, uint8_t *q, float *scale, int rows, int 
     xs::quantize_rows_fp8_kernel<<<blocks, 256, 0, st>>>(static_cast<const __nv_bfloat16 *>(x), q, scale, rows, cols);
     XS_CUDA(cudaGetLastError());
     return 0;
-}
-
-int launch_gather(const void *src, const int32_t *perm, void *dst, int n_routed, int n_total, int K, int row_bytes, cudaStream_t st)
-{
-    if (n_total == 0)
-        return 0;
-    if (row_bytes % 16 == 0)
-        xs::gather_rows_kernel<<<n_total, 256, 0, st>>>(static_cast<const uint8_t *>(src), perm, static_cast<uint8_t *>(dst), n_routed,
-                                                        n_total, K, row_bytes);
-    else
-        xs::gather_rows4_kernel<<<n_total, 64, 0, st>>>(static_cast<const uint32_t *>(src), perm, static_cast<uint32_t *>(dst),
-                                                        n_routed, n_total, K, row_bytes / 4);
-    XS_CUDA(cudaGetLastError());
-    return 0;
-}
-
-__global__ void set_two_ints_kernel(int32_t *p, int a, int b)
-{
-    p[0] = a;
-    p[1] = b;
 }
 
 } // namespace
@@ -638,13 +635,18 @@ int xs_moe_permute(const XsMoeConfig *cfg, const int32_t *ids, int32_t *counts, 
                           static_cast<cudaStream_t>(stream));
 }
 
+static GroupedPlan plan_grouped_stage(const XsMoeConfig *cfg, int max_rows)
+{
+    return plan_grouped(max_rows, max_rows, cfg->local_expert_count, cfg->local_expert_count, cfg->intermediate, cfg->routed_format);
+}
+
 int xs_moe_grouped_mlp_workspace_bytes(const XsMoeConfig *cfg, int32_t max_rows, size_t *bytes)
 {
     if (int rc = check_cfg(cfg))
         return rc;
     if (!bytes || max_rows < 0)
         return fail(XS_MOE_ERR_INVALID_ARG, "bad arguments");
-    *bytes = kStatusBytes + plan_grouped(max_rows, cfg->local_expert_count, cfg->intermediate, cfg->routed_format).bytes;
+    *bytes = kStatusBytes + plan_grouped_stage(cfg, max_rows).bytes;
     return 0;
 }
 
@@ -660,13 +662,28 @@ int xs_moe_grouped_mlp(const XsMoeConfig *cfg, const XsMoeWeights *w, const void
     if (cfg->gemm_impl == 0)
         if (int rc = xs_moe_device_check())
             return rc;
-    GroupedPlan gp = plan_grouped(max_rows, cfg->local_expert_count, cfg->intermediate, cfg->routed_format);
-    if (int rc = check_workspace(ws, ws_bytes, kStatusBytes + gp.bytes))
+    GroupedArgs a;
+    a.gp = plan_grouped_stage(cfg, max_rows);
+    if (int rc = check_workspace(ws, ws_bytes, kStatusBytes + a.gp.bytes))
         return rc;
     uint8_t *b = static_cast<uint8_t *>(ws);
-    return run_grouped_any(cfg->routed_format, cfg->hidden, cfg->intermediate, cfg->local_expert_count, cfg->gemm_impl,
-                           w->gate_up_w_dev, w->gate_up_scale_dev, w->down_w_dev, w->down_scale_dev, rows, row_scales, offsets,
-                           max_rows, y, b + kStatusBytes, gp, reinterpret_cast<int32_t *>(b), static_cast<cudaStream_t>(stream));
+    a.fmt = cfg->routed_format;
+    a.H = cfg->hidden;
+    a.I = cfg->intermediate;
+    a.groups = cfg->local_expert_count;
+    a.gemm_impl = cfg->gemm_impl;
+    a.gu = w->gate_up_w_dev;
+    a.gu_scale = w->gate_up_scale_dev;
+    a.dw = w->down_w_dev;
+    a.dw_scale = w->down_scale_dev;
+    a.rows = rows;
+    a.row_scale = row_scales;
+    a.offsets = offsets;
+    a.max_rows = max_rows;
+    a.y = y;
+    a.scratch = b + kStatusBytes;
+    a.status = reinterpret_cast<int32_t *>(b);
+    return run_grouped(a, static_cast<cudaStream_t>(stream));
 }
 
 int xs_moe_quantize_rows_fp8(const void *x, int32_t rows, int32_t cols, void *codes, float *scales, void *stream)
@@ -695,6 +712,8 @@ int xs_moe_combine(const XsMoeConfig *cfg, const float *y, const int32_t *inv, c
     return 0;
 }
 
+// Stage marks of xs_moe_forward_profile: logits | select + permute + tile table | scatter (+ quantise) |
+// gate/up GEMM | down GEMM | combine
 static int forward_impl(const XsMoeConfig *cfg, const XsMoeWeights *w, const void *x, void *out, void *ws, size_t ws_bytes,
                         void *stream, cudaEvent_t *ev)
 {
@@ -733,56 +752,72 @@ static int forward_impl(const XsMoeConfig *cfg, const XsMoeWeights *w, const voi
     int32_t *inv = reinterpret_cast<int32_t *>(b + p.off_inv);
     uint8_t *rows = b + p.off_rows;
     float *y = reinterpret_cast<float *>(b + p.off_y);
-    float *ysh = S ? reinterpret_cast<float *>(b + p.off_ysh) : nullptr;
-
-    XS_MARK(0);
-    if (int rc = launch_route(cfg, x, w->router_w_dev, w->router_bias_dev, logits, ids, tw, st))
-        return rc;
-    XS_MARK(1);
-    if (int rc = launch_permute(cfg, ids, counts, offsets, perm, inv, reinterpret_cast<int32_t *>(b + p.off_chunk_counts),
-                                reinterpret_cast<int32_t *>(b + p.off_chunk_base), p.chunks, status, st))
-        return rc;
     const int n_routed = T * K, n_total = T * K + S * T;
     const bool fp8 = cfg->routed_format == XS_MOE_FP8_BLOCK128;
-    float *rows_scale = nullptr;
-    if (fp8) {
-        // quantise x once (1x128 groups), then move codes and scales into expert order
-        uint8_t *xq = b + p.off_xq;
-        float *xs_ = reinterpret_cast<float *>(b + p.off_xs);
-        rows_scale = reinterpret_cast<float *>(b + p.off_rows_scale);
-        if (int rc = launch_quantize_rows(x, xq, xs_, T, H, st))
+    float *rows_scale = fp8 ? reinterpret_cast<float *>(b + p.off_rows_scale) : nullptr;
+    const int extra_rows = S ? T : -1;
+    const bool tensor_path = cfg->gemm_impl == 0;
+    uint8_t *gscratch = b + p.off_grouped;
+
+    XS_MARK(0);
+    if (int rc = launch_logits(cfg, x, w->router_w_dev, logits, st))
+        return rc;
+    XS_MARK(1);
+    bool tiles_ready = false;
+    if (T <= xs::kChunkTokens) {
+        TileBuffers tb = tile_buffers(gscratch, p.grouped);
+        if (!tensor_path)
+            tb = TileBuffers{nullptr, nullptr, nullptr};
+        if (int rc = launch_topk(cfg, logits, w->router_bias_dev, ids, tw, st))
             return rc;
-        if (int rc = launch_gather(xq, perm, rows, n_routed, n_total, K, H, st))
+        if (int rc = launch_permute_small(cfg, ids, counts, offsets, perm, inv, extra_rows, p.grouped, tb, status, st))
             return rc;
-        if (int rc = launch_gather(xs_, perm, rows_scale, n_routed, n_total, K, (H / 128) * 4, st))
-            return rc;
+        tiles_ready = tensor_path;
     } else {
-        if (int rc = launch_gather(x, perm, rows, n_routed, n_total, K, H * 2, st))
+        if (int rc = launch_topk(cfg, logits, w->router_bias_dev, ids, tw, st))
+            return rc;
+        if (int rc = launch_permute(cfg, ids, counts, offsets, perm, inv, reinterpret_cast<int32_t *>(b + p.off_chunk_counts),
+                                    reinterpret_cast<int32_t *>(b + p.off_chunk_base), p.chunks, status, st, extra_rows))
             return rc;
     }
-    const size_t row_bytes = static_cast<size_t>(H) * (fp8 ? 1 : 2);
     XS_MARK(2);
-    if (int rc = run_grouped_any(cfg->routed_format, H, I, E, cfg->gemm_impl, w->gate_up_w_dev, w->gate_up_scale_dev, w->down_w_dev,
-                                 w->down_scale_dev, rows, rows_scale, offsets, n_routed, y, b + p.off_grouped, p.routed, status, st,
-                                 ev ? ev[3] : nullptr))
-        return rc;
-    XS_MARK(4);
+    if (fp8)
+        xs::scatter_rows_kernel<true><<<T, 256, 0, st>>>(static_cast<const __nv_bfloat16 *>(x), inv, rows, rows_scale, T, H, K, n_routed, S);
+    else
+        xs::scatter_rows_kernel<false><<<T, 256, 0, st>>>(static_cast<const __nv_bfloat16 *>(x), inv, rows, nullptr, T, H, K, n_routed, S);
+    XS_CUDA(cudaGetLastError());
+    XS_MARK(3);
+    GroupedArgs a;
+    a.fmt = cfg->routed_format;
+    a.H = H;
+    a.I = I;
+    a.groups = E;
+    a.gemm_impl = cfg->gemm_impl;
+    a.gu = w->gate_up_w_dev;
+    a.gu_scale = w->gate_up_scale_dev;
+    a.dw = w->down_w_dev;
+    a.dw_scale = w->down_scale_dev;
     if (S) {
-        int32_t *sh_off = reinterpret_cast<int32_t *>(b + p.off_sh_offsets);
-        set_two_ints_kernel<<<1, 1, 0, st>>>(sh_off, 0, T);
-        XS_CUDA(cudaGetLastError());
-        if (int rc = run_grouped_any(cfg->shared_format, H, I, 1, cfg->gemm_impl, w->shared_gate_up_w_dev, w->shared_gate_up_scale_dev,
-                                     w->shared_down_w_dev, w->shared_down_scale_dev, rows + static_cast<size_t>(n_routed) * row_bytes,
-                                     fp8 ? rows_scale + static_cast<size_t>(n_routed) * (H / 128) : nullptr, sh_off, T, ysh,
-                                     b + p.off_grouped_sh, p.shared, status, st, ev ? ev[5] : nullptr))
-            return rc;
-    } else {
-        XS_MARK(5);
+        a.gu2 = w->shared_gate_up_w_dev;
+        a.gu2_scale = w->shared_gate_up_scale_dev;
+        a.dw2 = w->shared_down_w_dev;
+        a.dw2_scale = w->shared_down_scale_dev;
     }
-    XS_MARK(6);
-    if (int rc = xs_moe_combine(cfg, y, inv, tw, ysh, out, stream))
+    a.rows = rows;
+    a.row_scale = rows_scale;
+    a.offsets = offsets;
+    a.max_rows = n_total;
+    a.y = y;
+    a.scratch = gscratch;
+    a.gp = p.grouped;
+    a.status = status;
+    a.tiles_ready = tiles_ready;
+    if (int rc = run_grouped(a, st, ev ? ev[4] : nullptr))
         return rc;
-    XS_MARK(7);
+    XS_MARK(5);
+    if (int rc = xs_moe_combine(cfg, y, inv, tw, S ? y + static_cast<size_t>(n_routed) * H : nullptr, out, stream))
+        return rc;
+    XS_MARK(6);
     return 0;
 #undef XS_MARK
 }
@@ -797,22 +832,22 @@ int xs_moe_forward_profile(const XsMoeConfig *cfg, const XsMoeWeights *w, const 
 {
     if (!stage_ms)
         return fail(XS_MOE_ERR_INVALID_ARG, "null out-pointer");
-    cudaEvent_t ev[8];
-    for (int i = 0; i < 8; i++)
+    cudaEvent_t ev[7];
+    for (int i = 0; i < 7; i++)
         XS_CUDA(cudaEventCreate(&ev[i]));
     int rc = forward_impl(cfg, w, x, out, ws, ws_bytes, stream, ev);
     if (rc == 0 && cfg->num_tokens > 0) {
-        cudaError_t e = cudaEventSynchronize(ev[7]);
+        cudaError_t e = cudaEventSynchronize(ev[6]);
         if (e != cudaSuccess)
             rc = fail(XS_MOE_ERR_CUDA, "CUDA error: %s", cudaGetErrorString(e));
-        for (int i = 0; i < 7 && rc == 0; i++)
+        for (int i = 0; i < 6 && rc == 0; i++)
             if (cudaEventElapsedTime(&stage_ms[i], ev[i], ev[i + 1]) != cudaSuccess)
                 rc = fail(XS_MOE_ERR_CUDA, "CUDA error: event timing failed");
     } else {
-        for (int i = 0; i < 7; i++)
+        for (int i = 0; i < 6; i++)
             stage_ms[i] = 0.0f;
     }
-    for (int i = 0; i < 8; i++)
+    for (int i = 0; i < 7; i++)
         cudaEventDestroy(ev[i]);
     return rc;
 }

@@ -3,8 +3,11 @@
 // atomicOr (whose result does not depend on arrival order) and ranks are popcounts over them.
 #pragma once
 #include <cuda_bf16.h>
+#include <cuda_fp8.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+
+#include "xs_route.cuh"
 
 namespace xs {
 
@@ -87,7 +90,7 @@ __device__ __forceinline__ int block_exclusive_scan(int v, int *warp_sums, int *
 // first row of every (chunk, expert) group.
 __global__ void __launch_bounds__(1024)
 permute_scan_kernel(const int32_t *__restrict__ chunk_counts, int32_t *__restrict__ counts, int32_t *__restrict__ offsets,
-                    int32_t *__restrict__ chunk_base, int num_chunks, int E)
+                    int32_t *__restrict__ chunk_base, int num_chunks, int E, int extra_rows)
 {
     __shared__ int warp_sums[32];
     __shared__ int total;
@@ -106,8 +109,11 @@ permute_scan_kernel(const int32_t *__restrict__ chunk_counts, int32_t *__restric
             b += chunk_counts[static_cast<size_t>(ch) * E + e];
         }
     }
-    if (threadIdx.x == 0)
+    if (threadIdx.x == 0) {
         offsets[E] = total;
+        if (extra_rows >= 0) // rows of the always-on expert follow the routed rows: segment E
+            offsets[E + 1] = total + extra_rows;
+    }
 }
 
 // one block, blockDim.x >= E.  Token tiles of n_tile rows per expert segment, in expert order.
@@ -164,6 +170,147 @@ permute_fill_kernel(const int32_t *__restrict__ topk_ids, const int32_t *__restr
         const int row = chunk_base[static_cast<size_t>(blockIdx.x) * E + e] + rank;
         perm[row] = t * K + j;
         inv[static_cast<size_t>(t) * K + j] = row;
+    }
+}
+
+
+// Decode-sized batches (T <= 256, one chunk): permutation and the GEMM tile table in ONE launch.
+// One block of 256 threads: thread = token for the membership bitmaps / ranks, then a block scan over the experts.
+// Produces exactly what permute_count/scan/fill + tile_table_kernel produce.
+__global__ void __launch_bounds__(kChunkTokens)
+permute_small_kernel(const int32_t *__restrict__ topk_ids, int32_t *__restrict__ counts, int32_t *__restrict__ offsets,
+                     int32_t *__restrict__ perm, int32_t *__restrict__ inv, int T, int E, int K, int extra_rows, int n_tile,
+                     int max_tiles, int32_t *__restrict__ tile_expert, int32_t *__restrict__ tile_row0, int32_t *__restrict__ num_tiles,
+                     int32_t *status)
+{
+    extern __shared__ uint32_t bits[]; // E * kChunkWords words, then E ints of offsets
+    int *s_off = reinterpret_cast<int *>(bits + E * kChunkWords);
+    __shared__ int warp_sums[32];
+    __shared__ int total;
+    build_bits(bits, topk_ids, T, E, K, 0, status);
+    // counts and offsets: experts in passes of blockDim.x, carrying the running total
+    int carry = 0;
+    for (int e0 = 0; e0 < E; e0 += kChunkTokens) {
+        const int e = e0 + threadIdx.x;
+        int c = 0;
+        if (e < E) {
+#pragma unroll
+            for (int w = 0; w < kChunkWords; w++)
+                c += __popc(bits[e * kChunkWords + w]);
+        }
+        const int off = carry + block_exclusive_scan(c, warp_sums, &total);
+        if (e < E) {
+            counts[e] = c;
+            offsets[e] = off;
+            s_off[e] = off;
+        }
+        carry += total;
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) {
+        offsets[E] = carry;
+        if (extra_rows >= 0)
+            offsets[E + 1] = carry + extra_rows;
+    }
+    // ranks
+    const int t = threadIdx.x;
+    if (t < T) {
+        for (int j = 0; j < K; j++) {
+            const int e = topk_ids[static_cast<size_t>(t) * K + j];
+            if (e < 0 || e >= E)
+                continue;
+            const uint32_t *b = bits + e * kChunkWords;
+            int rank = __popc(b[t >> 5] & ((1u << (t & 31)) - 1u));
+            for (int w = 0; w < (t >> 5); w++)
+                rank += __popc(b[w]);
+            const int row = s_off[e] + rank;
+            perm[row] = t * K + j;
+            inv[static_cast<size_t>(t) * K + j] = row;
+        }
+    }
+    // tile table over E (+1 when the always-on expert's rows follow) segments
+    if (tile_expert) {
+        const int segs = E + (extra_rows >= 0 ? 1 : 0);
+        int tcarry = 0;
+        for (int e0 = 0; e0 < segs; e0 += kChunkTokens) {
+            const int e = e0 + threadIdx.x;
+            int rows = 0, start = 0;
+            if (e < E) {
+                start = s_off[e];
+                rows = (e + 1 < E ? s_off[e + 1] : carry) - start;
+            } else if (e == E && e < segs) {
+                start = carry;
+                rows = extra_rows;
+            }
+            const int nt = (rows + n_tile - 1) / n_tile;
+            const int first = tcarry + block_exclusive_scan(nt, warp_sums, &total);
+            for (int i = 0; i < nt; i++) {
+                if (first + i >= max_tiles) {
+                    atomicOr(status, 2);
+                    break;
+                }
+                tile_expert[first + i] = e;
+                tile_row0[first + i] = start + i * n_tile;
+            }
+            tcarry += total;
+            __syncthreads();
+        }
+        if (threadIdx.x == 0)
+            *num_tiles = tcarry < max_tiles ? tcarry : max_tiles;
+    }
+}
+
+// One block per token: the row of x goes to its k routed rows (inv) and, when there is an always-on expert, to
+// row n_routed + t.  bf16 rows are copied in 16-byte pieces; for FP8 experts the row is quantised on the way
+// (1x128 groups, as quantize_rows_fp8_kernel) and codes and scales are written to every destination, so x is
+// read once instead of k+1 times and no intermediate copy of the quantised x exists.
+template <bool FP8>
+__global__ void __launch_bounds__(256)
+scatter_rows_kernel(const __nv_bfloat16 *__restrict__ x, const int32_t *__restrict__ inv, uint8_t *__restrict__ rows_out,
+                    float *__restrict__ row_scales, int T, int H, int K, int n_routed, int with_shared)
+{
+    const int t = blockIdx.x;
+    if (t >= T)
+        return;
+    __shared__ int dst[33];
+    const int nd = K + (with_shared ? 1 : 0);
+    if (threadIdx.x < K)
+        dst[threadIdx.x] = inv[static_cast<size_t>(t) * K + threadIdx.x];
+    if (threadIdx.x == 0 && with_shared)
+        dst[K] = n_routed + t;
+    __syncthreads();
+    if constexpr (!FP8) {
+        const uint4 *src = reinterpret_cast<const uint4 *>(x + static_cast<size_t>(t) * H);
+        for (int i = threadIdx.x; i < H / 8; i += blockDim.x) {
+            const uint4 v = src[i];
+            for (int d = 0; d < nd; d++)
+                reinterpret_cast<uint4 *>(rows_out + static_cast<size_t>(dst[d]) * H * 2)[i] = v;
+        }
+    } else {
+        const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+        const int groups = H / 128;
+        for (int g = warp; g < groups; g += blockDim.x / 32) {
+            const uint2 raw = *reinterpret_cast<const uint2 *>(x + static_cast<size_t>(t) * H + g * 128 + lane * 4);
+            float v[4];
+            v[0] = __uint_as_float(raw.x << 16);
+            v[1] = __uint_as_float(raw.x & 0xffff0000u);
+            v[2] = __uint_as_float(raw.y << 16);
+            v[3] = __uint_as_float(raw.y & 0xffff0000u);
+            float m = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1)
+                m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+            const float s = __fdiv_rn(fmaxf(m, 1e-10f), 448.0f);
+            uint32_t packed = 0;
+#pragma unroll
+            for (int i = 0; i < 4; i++)
+                packed |= static_cast<uint32_t>(__nv_cvt_float_to_fp8(__fdiv_rn(v[i], s), __NV_SATFINITE, __NV_E4M3)) << (8 * i);
+            for (int d = 0; d < nd; d++) {
+                *reinterpret_cast<uint32_t *>(rows_out + static_cast<size_t>(dst[d]) * H + g * 128 + lane * 4) = packed;
+                if (lane == 0)
+                    row_scales[static_cast<size_t>(dst[d]) * groups + g] = s;
+            }
+        }
     }
 }
 

@@ -99,19 +99,92 @@ router_logits_kernel(const __nv_bfloat16 *__restrict__ x, const __nv_bfloat16 *_
     }
 }
 
+// Decode-sized batches.  Block = 8 experts x 32 tokens, one output per thread (warp = one expert, lanes = tokens),
+// so a batch of 128 tokens x 256 experts spreads over 128 SMs.  Operands arrive through a 4-stage cp.async
+// pipeline of 128-wide k chunks; inside a chunk each thread walks k upwards, 8 elements per 16-byte shared-memory
+// read (the router row is a warp-wide broadcast, the token rows are padded to stay bank-conflict free).
+// One accumulator per thread, touched once per k in ascending order: the contract's summation order.
+constexpr int kRdExperts = 8, kRdTokens = 32, kRdK = 128, kRdStages = 4, kRdThreads = 256;
+constexpr int kRdXStride = kRdK + 8; // bf16 elements; 272-byte rows: 16-byte aligned and conflict-free for 16-byte reads
+
+__device__ __forceinline__ void cp_async16(void *smem_dst, const void *gsrc, bool valid)
+{
+    const uint32_t d = static_cast<uint32_t>(__cvta_generic_to_shared(smem_dst));
+    const int sz = valid ? 16 : 0; // 0 source bytes => the 16 destination bytes are zero-filled
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(gsrc), "r"(sz) : "memory");
+}
+
+__global__ void __launch_bounds__(kRdThreads)
+router_logits_decode_kernel(const __nv_bfloat16 *__restrict__ x, const __nv_bfloat16 *__restrict__ rw, float *__restrict__ logits,
+                            int T, int H, int E)
+{
+    __shared__ __align__(16) __nv_bfloat16 ws[kRdStages][kRdExperts][kRdK];
+    __shared__ __align__(16) __nv_bfloat16 xsm[kRdStages][kRdTokens][kRdXStride];
+    const int tid = threadIdx.x;
+    const int el = tid >> 5, tl = tid & 31;
+    const int e0 = blockIdx.x * kRdExperts, t0 = blockIdx.y * kRdTokens;
+    const int chunks = H / kRdK;
+
+    auto issue = [&](int chunk, int stage) {
+        const int k0 = chunk * kRdK;
+        // 16-byte pieces: 8 experts x 16 + 32 tokens x 16 = 640
+        for (int p = tid; p < (kRdExperts + kRdTokens) * (kRdK / 8); p += kRdThreads) {
+            const int r = p / (kRdK / 8), c = (p - r * (kRdK / 8)) * 8;
+            if (r < kRdExperts) {
+                const int e = e0 + r;
+                const bool ok = e < E;
+                cp_async16(&ws[stage][r][c], rw + static_cast<size_t>(ok ? e : 0) * H + k0 + c, ok);
+            } else {
+                const int t = t0 + r - kRdExperts;
+                const bool ok = t < T;
+                cp_async16(&xsm[stage][r - kRdExperts][c], x + static_cast<size_t>(ok ? t : 0) * H + k0 + c, ok);
+            }
+        }
+    };
+
+#pragma unroll
+    for (int s = 0; s < kRdStages - 1; s++) {
+        if (s < chunks)
+            issue(s, s);
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    }
+    float acc = 0.0f;
+    for (int ch = 0; ch < chunks; ch++) {
+        asm volatile("cp.async.wait_group %0;" ::"n"(kRdStages - 2) : "memory");
+        __syncthreads(); // chunk ch has landed for every thread; everyone has finished chunk ch-1
+        const int nxt = ch + kRdStages - 1;
+        if (nxt < chunks)
+            issue(nxt, nxt % kRdStages);
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        const int st = ch % kRdStages;
+        const uint4 *wp = reinterpret_cast<const uint4 *>(&ws[st][el][0]);
+        const uint4 *xp = reinterpret_cast<const uint4 *>(&xsm[st][tl][0]);
+#pragma unroll 4
+        for (int i = 0; i < kRdK / 8; i++) {
+            const uint4 w = wp[i], v = xp[i];
+            acc = __fmaf_rn(__uint_as_float(v.x << 16), __uint_as_float(w.x << 16), acc);
+            acc = __fmaf_rn(__uint_as_float(v.x & 0xffff0000u), __uint_as_float(w.x & 0xffff0000u), acc);
+            acc = __fmaf_rn(__uint_as_float(v.y << 16), __uint_as_float(w.y << 16), acc);
+            acc = __fmaf_rn(__uint_as_float(v.y & 0xffff0000u), __uint_as_float(w.y & 0xffff0000u), acc);
+            acc = __fmaf_rn(__uint_as_float(v.z << 16), __uint_as_float(w.z << 16), acc);
+            acc = __fmaf_rn(__uint_as_float(v.z & 0xffff0000u), __uint_as_float(w.z & 0xffff0000u), acc);
+            acc = __fmaf_rn(__uint_as_float(v.w << 16), __uint_as_float(w.w << 16), acc);
+            acc = __fmaf_rn(__uint_as_float(v.w & 0xffff0000u), __uint_as_float(w.w & 0xffff0000u), acc);
+        }
+    }
+    const int e = e0 + el, t = t0 + tl;
+    if (e < E && t < T)
+        logits[static_cast<size_t>(t) * E + e] = acc;
+}
+
 // One warp per token.  Lane l holds experts l, l+32, l+64, ...  (NPL per lane).
 // Selection: K rounds of "largest key, ties to the lower expert id" by butterfly shuffles.
 // Output slots are in ascending expert id.  Weights: softmax over the selected unbiased logits,
 // max-shifted, summed in slot order.
 template <int NPL>
-__global__ void __launch_bounds__(128)
-topk_kernel(const float *__restrict__ logits, const float *__restrict__ bias, int32_t *__restrict__ topk_ids,
-            float *__restrict__ topk_w, int T, int E, int K)
+__device__ __forceinline__ void topk_warp(const float *__restrict__ logits, const float *__restrict__ bias,
+                                          int32_t *__restrict__ topk_ids, float *__restrict__ topk_w, int warp, int lane, int E, int K)
 {
-    const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-    const int lane = threadIdx.x & 31;
-    if (warp >= T)
-        return;
     const float *l = logits + static_cast<size_t>(warp) * E;
     float key[NPL], lg[NPL];
     uint32_t selected = 0; // bit i: expert lane + 32*i chosen
@@ -183,6 +256,18 @@ topk_kernel(const float *__restrict__ logits, const float *__restrict__ bias, in
         sum = __fadd_rn(sum, __shfl_sync(0xffffffffu, ex, j));
     if (lane < K)
         topk_w[static_cast<size_t>(warp) * K + lane] = __fdiv_rn(ex, sum);
+}
+
+template <int NPL>
+__global__ void __launch_bounds__(128)
+topk_kernel(const float *__restrict__ logits, const float *__restrict__ bias, int32_t *__restrict__ topk_ids,
+            float *__restrict__ topk_w, int T, int E, int K)
+{
+    const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (warp >= T)
+        return;
+    topk_warp<NPL>(logits, bias, topk_ids, topk_w, warp, lane, E, K);
 }
 
 } // namespace xs
