@@ -322,6 +322,105 @@ def run_ours(args, dims):
         dist.destroy_process_group()
 
 
+def run_ours_ep(args, dims):
+    """N > 1: expert parallelism.  Experts are sharded evenly over the ranks, every rank brings its own batch of T
+    tokens (weak scaling), rows travel by NCCL all-to-all each way."""
+    import torch
+    import torch.distributed as dist
+
+    from xstar_moe import capi, ep, synth
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    torch.cuda.set_device(local_rank)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    capi.check(capi.lib().xs_moe_device_check())
+    T, H, E, K, I, S = (dims[k] for k in "THEKIS")
+    x, weights, shared, bias = synth.make_ep_inputs(dims, rank, world, seed=0, device="cuda")
+    ops = ep.CudaOps(dict(dims), weights, shared, rank, world)
+    layer = ep.ExpertParallelMoE(ops, weights["router_w"], bias, E, K, S)
+    stream = torch.cuda.current_stream()
+    x_host = x.cpu().pin_memory()
+    out_host = torch.empty_like(x_host).pin_memory()
+
+    def step():
+        return layer.forward(x)
+
+    def step_host():
+        xd = x_host.to("cuda", non_blocking=True)
+        out_host.copy_(layer.forward(xd), non_blocking=True)
+        torch.cuda.synchronize()
+
+    def barrier():
+        dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        e0.record(stream)
+        for _ in range(steps):
+            fn()
+        e1.record(stream)
+        barrier()
+        ms = torch.tensor([e0.elapsed_time(e1)], device="cuda")
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms.item())
+
+    for _ in range(max(3, args.warmup)):
+        step()
+    ops.check()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    ms = timed(step, args.steps)
+    for _ in range(2):
+        step_host()
+    ms_e2e = timed(step_host, args.steps)
+    # the grouped expert MLPs of this rank, timed on their own with CUDA events
+    plan = layer.last_plan
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    payload = ops.payload(x)
+    rows = [torch.zeros((plan.n_recv, *p.shape[1:]), dtype=p.dtype, device="cuda") for p in payload]
+    off = torch.from_numpy(plan.offsets_local).cuda()
+    ops.grouped_mlp(rows, off, plan.n_recv)
+    torch.cuda.synchronize()
+    reps = 5
+    e0.record(stream)
+    for _ in range(reps):
+        ops.grouped_mlp(rows, off, plan.n_recv)
+    e1.record(stream)
+    torch.cuda.synchronize()
+    mlp_ms = e0.elapsed_time(e1) / reps
+    clocks = sampler.stop() if rank == 0 else None
+    ops.check()
+    active = int((np.diff(plan.offsets_local) > 0).sum())
+    if rank == 0:
+        peak, peak_kind = measured_peaks()
+        wbytes = {"bf16": 2.0, "fp8": 1.0, "fp4": 0.5}[dims["fmt"]]
+        mlp_bytes = active * 3 * H * I * wbytes
+        tokens = T * world * args.steps
+        line = {
+            "metric": METRIC, "value": tokens / (ms * 1e-3), "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup),
+            "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": dims["fmt"],
+            "data": "synthetic (seeded: weights N(0,0.02), activations N(0,1), rounded once to storage)",
+            "config": dict(workload=args.workload, **{k: dims[k] for k in "THEKIS"}, format=dims["fmt"], tokens_per_rank=T,
+                           experts_per_rank=E // world, parallelism=f"ep{world}: experts sharded, NCCL all-to-all dispatch/combine",
+                           l2="inputs larger than L2: expert weights streamed per step exceed 126 MB"),
+            "e2e": {"value": tokens / (ms_e2e * 1e-3), "unit": UNIT, "h2d_bytes_per_step": T * H * 2, "d2h_bytes_per_step": T * H * 2,
+                    "ms_per_step": ms_e2e / args.steps},
+            "gpu_launches": (2 + 3 + 1 + len(payload) * 2 + 3 + 1 + 3 * S + 1) * args.steps,
+            "roofline": {"bound": "hbm", "kernel": "grouped expert MLP of rank 0 (tile table + gate/up + down GEMM launches)",
+                         "achieved": mlp_bytes / (mlp_ms * 1e-3) / 1e9, "peak": peak, "unit": "GB/s", "peak_kind": peak_kind,
+                         "frac": mlp_bytes / (mlp_ms * 1e-3) / 1e9 / peak, "traffic": None, "algorithmic_bytes_per_launch": mlp_bytes,
+                         "ms_per_launch": mlp_ms, "rows_received_rank0": plan.n_recv, "active_local_experts": active},
+            "cpu_baseline": None, "clocks": clocks,
+        }
+        print(json.dumps(line), flush=True)
+    dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -343,6 +442,8 @@ def main():
         dims["E"] = args.experts
     if args.impl == "reference":
         run_reference_arm(args, dims)
+    elif int(os.environ.get("WORLD_SIZE", "1")) > 1:
+        run_ours_ep(args, dims)
     else:
         run_ours(args, dims)
 

@@ -179,6 +179,12 @@ int xs_moe_grouped_mlp(const XsMoeConfig *cfg, const XsMoeWeights *w, const void
 int xs_moe_quantize_rows_fp8(const void *x_dev, int32_t rows, int32_t cols, void *codes_dev, float *scales_dev,
                              void *stream);
 
+/* dst[r] = src[index[r]] for r < n_rows, rows of row_bytes bytes (a multiple of 4): the reference's gather
+ * (embedding_launch, xstar_cpp/include/ops/embedding.h:58-63) with int32 indices and any row type.  Used to put
+ * x into expert order (index = perm / k) and to regroup rows received from other ranks. */
+int xs_moe_gather_rows(const void *src_dev, const int32_t *index_dev, void *dst_dev, int32_t n_rows, int32_t row_bytes,
+                       void *stream);
+
 /* out[t] = sum_j w[t,j] * y[inv[t,j]] (+ shared[t]), slot order, shared last, f32, one RNE downcast
  * (add's contract, xstar_cpp/src/ops/add.cpp:27-49).  shared_dev (T,H) f32 may be NULL. */
 int xs_moe_combine(const XsMoeConfig *cfg, const float *y_dev, const int32_t *inv_dev, const float *topk_w_dev,

@@ -1,0 +1,183 @@
+"""Expert parallelism: the host-side planning on its own, the whole exchange on two CPU ranks (gloo) with a
+stand-in for the device ops, and -- where two GPUs are visible -- the real thing over NCCL."""
+import os
+import sys
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+for p in (ROOT, os.path.join(ROOT, "xstar-infer_b200"), os.path.join(ROOT, "tests")):
+    if p not in sys.path:
+        sys.path.insert(0, p)
+
+from xstar_moe import ep, synth  # noqa: E402
+
+
+# ---- planning (numpy only) --------------------------------------------------------------------------------------
+def test_plan_splits_and_maps():
+    rng = np.random.default_rng(0)
+    R, E = 4, 16
+    all_counts = rng.integers(0, 5, size=(R, E))
+    all_counts[2, 4:8] = 0  # a rank that sends nothing to rank 1
+    plans = [ep.EpPlan(all_counts, r) for r in range(R)]
+    for r, p in enumerate(plans):
+        assert p.send_splits.sum() == all_counts[r].sum()
+        for d in range(R):
+            assert p.send_splits[d] == plans[d].recv_splits[r]  # what r sends to d is what d expects from r
+        # regroup maps are inverse permutations
+        assert np.array_equal(np.sort(p.grouped_from_arrival), np.arange(p.n_recv))
+        assert np.array_equal(p.grouped_from_arrival[p.arrival_from_grouped], np.arange(p.n_recv))
+        # grouped order is (expert, source, token): label every arrival row and check
+        labels = []
+        for s in range(R):
+            for e in range(p.El):
+                labels += [(e, s, i) for i in range(int(p.recv_counts[s, e]))]
+        grouped = [labels[a] for a in p.grouped_from_arrival]
+        assert grouped == sorted(grouped)
+        assert np.array_equal(np.diff(p.offsets_local), p.recv_counts.sum(0))
+
+
+def test_plan_rejects_uneven_sharding():
+    with pytest.raises(ValueError, match="expert count mismatch"):
+        ep.EpPlan(np.zeros((3, 8), np.int64), 0)
+
+
+# ---- two CPU ranks over gloo: the exchange logic end to end ----------------------------------------------------------
+class OracleOps:
+    """Stand-in for the device ops so that the host logic of ep.ExpertParallelMoE runs on CPU ranks: each call is
+    the CPU oracle's restatement of the corresponding C-ABI stage (test infrastructure, never shipped)."""
+
+    def __init__(self, oracle, dims, d_local, shared):
+        self.o, self.dims, self.d, self.shared = oracle, dims, d_local, shared
+        self.H, self.K, self.E = dims["H"], dims["K"], dims["E"]
+
+    @staticmethod
+    def _bits(t):
+        return t.contiguous().view(torch.uint16).numpy()
+
+    def route(self, x, router_w, router_bias):
+        import ctypes as C
+        xf, rwf = x.float().numpy(), router_w.float().numpy()
+        logits = np.zeros((x.shape[0], self.E), np.float32)
+        self.o.lib().xso_router_logits(C.c_void_p(xf.ctypes.data), C.c_void_p(rwf.ctypes.data), C.c_void_p(logits.ctypes.data),
+                                       x.shape[0], self.H, self.E)
+        ids, w = self.o.topk(logits, None if router_bias is None else router_bias.numpy(), self.K)
+        return torch.from_numpy(ids), torch.from_numpy(w)
+
+    def permute(self, ids):
+        return tuple(torch.from_numpy(a) for a in self.o.permute(ids.numpy(), self.E))
+
+    def payload(self, x):
+        return [x]
+
+    def gather(self, src, index):
+        return src.index_select(0, index.long())
+
+    def grouped_mlp(self, payload, offsets_local, n_rows):
+        rows = payload[0]
+        y = torch.zeros((n_rows, self.H), dtype=torch.float32)
+        off = offsets_local.numpy()
+        gu, dw = self._bits(self.d["gate_up_w"]), self._bits(self.d["down_w"])
+        for e in range(len(off) - 1):
+            if off[e + 1] > off[e]:
+                y[off[e]:off[e + 1]] = torch.from_numpy(self.o.expert_mlp(self.o.BF16, self._bits(rows[off[e]:off[e + 1]]), gu[e], dw[e]))
+        return y
+
+    def shared_mlp(self, payload):
+        x = payload[0]
+        return torch.from_numpy(self.o.expert_mlp(self.o.BF16, self._bits(x), self._bits(self.shared["shared_gate_up_w"]),
+                                                  self._bits(self.shared["shared_down_w"])))
+
+    def combine(self, y, inv, w, shared):
+        T, K = w.shape
+        acc = np.zeros((T, self.H), np.float32)
+        yn, wn, invn = y.numpy(), w.numpy(), inv.numpy().reshape(T, K)
+        for j in range(K):
+            acc = acc + wn[:, j:j + 1] * yn[invn[:, j]]
+        if shared is not None:
+            acc = acc + shared.numpy()
+        return torch.from_numpy(acc).to(torch.bfloat16)
+
+
+def _cpu_rank(rank, world, port, dims, seed, result_dir):
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from oracle import moe_oracle as oracle
+
+        d = synth.make_inputs(dict(dims, T=dims["T"] * world), seed=seed)  # the global problem, same on every rank
+        T, El = dims["T"], dims["E"] // world
+        x_local = d["x"][rank * T:(rank + 1) * T].contiguous()
+        d_local = dict(gate_up_w=d["gate_up_w"][rank * El:(rank + 1) * El], down_w=d["down_w"][rank * El:(rank + 1) * El])
+        ops = OracleOps(oracle, dims, d_local, d)
+        layer = ep.ExpertParallelMoE(ops, d["router_w"], d["router_bias"], dims["E"], dims["K"], dims["S"])
+        out = layer.forward(x_local)
+        np.save(os.path.join(result_dir, f"out{rank}.npy"), out.view(torch.uint16).numpy())
+        np.save(os.path.join(result_dir, f"recv{rank}.npy"), np.array([layer.last_plan.n_recv]))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_ep_on_cpu_ranks_equals_single_process_oracle(oracle, tmp_path, world):
+    dims = dict(T=24, H=128, E=8, K=3, I=128, S=1, fmt="bf16", bias=None)
+    port = 29600 + world
+    mp.spawn(_cpu_rank, args=(world, port, dims, 17, str(tmp_path)), nprocs=world, join=True)
+    d = synth.make_inputs(dict(dims, T=dims["T"] * world), seed=17)
+    n = synth.to_numpy_storage(d)
+    ref = oracle.moe_forward(oracle.BF16, n["x"], n["router_w"], n["gate_up_w"], n["down_w"], dims["K"],
+                             shared_gate_up_w=n["shared_gate_up_w"], shared_down_w=n["shared_down_w"])
+    got = np.concatenate([np.load(tmp_path / f"out{r}.npy") for r in range(world)])
+    assert np.array_equal(got, ref["out"]), "expert-parallel result differs from the single-process layer"
+    total = sum(int(np.load(tmp_path / f"recv{r}.npy")[0]) for r in range(world))
+    assert total == dims["T"] * world * dims["K"]
+
+
+# ---- two GPUs over NCCL ---------------------------------------------------------------------------------------------
+def _gpu_rank(rank, world, port, dims, seed, result_dir):
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        d = synth.make_inputs(dict(dims, T=dims["T"] * world), seed=seed)  # CPU generator: identical on every rank
+        T, El = dims["T"], dims["E"] // world
+        keys = ["gate_up_w", "down_w", "gate_up_scale", "down_scale"]
+        local = {k: d[k][rank * El:(rank + 1) * El].contiguous().cuda() for k in keys if d.get(k) is not None}
+        local["router_w"] = d["router_w"].cuda()
+        shared = {k: v.cuda() for k, v in d.items() if k.startswith("shared_") and v is not None} if dims["S"] else None
+        ops = ep.CudaOps(dict(dims), local, shared, rank, world)
+        bias = d["router_bias"].cuda() if d["router_bias"] is not None else None
+        layer = ep.ExpertParallelMoE(ops, local["router_w"], bias, dims["E"], dims["K"], dims["S"])
+        x_local = d["x"][rank * T:(rank + 1) * T].contiguous().cuda()
+        out = layer.forward(x_local)
+        out2 = layer.forward(x_local)
+        ops.check()
+        torch.cuda.synchronize()
+        assert torch.equal(out, out2)
+        np.save(os.path.join(result_dir, f"out{rank}.npy"), out.cpu().view(torch.uint16).numpy())
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("fmt,tol", [("bf16", 2e-3), ("fp8", 1e-2)])
+def test_ep_on_gpus_matches_oracle(oracle, tmp_path, fmt, tol):
+    world = 2
+    if torch.cuda.device_count() < world:
+        pytest.skip("needs two GPUs on one box")
+    dims = dict(T=96, H=512, E=16, K=4, I=256, S=1, fmt=fmt, bias=None)
+    mp.spawn(_gpu_rank, args=(world, 29650 + (fmt == "fp8"), dims, 23, str(tmp_path)), nprocs=world, join=True)
+    d = synth.make_inputs(dict(dims, T=dims["T"] * world), seed=23)
+    n = synth.to_numpy_storage(d)
+    mode = oracle.BF16 if fmt == "bf16" else oracle.FP8
+    ref = oracle.moe_forward(mode, n["x"], n["router_w"], n["gate_up_w"], n["down_w"], dims["K"], gate_up_scale=n.get("gate_up_scale"),
+                             down_scale=n.get("down_scale"), shared_gate_up_w=n["shared_gate_up_w"], shared_down_w=n["shared_down_w"],
+                             shared_gate_up_scale=n.get("shared_gate_up_scale"), shared_down_scale=n.get("shared_down_scale"), threads=8)
+    got = np.concatenate([np.load(tmp_path / f"out{r}.npy") for r in range(world)])
+    rel = synth.rel_l2(synth.bf16_bits_to_f32(got), synth.bf16_bits_to_f32(ref["out"]))
+    assert rel <= tol, rel

@@ -695,6 +695,25 @@ int xs_moe_quantize_rows_fp8(const void *x, int32_t rows, int32_t cols, void *co
     return launch_quantize_rows(x, static_cast<uint8_t *>(codes), scales, rows, cols, static_cast<cudaStream_t>(stream));
 }
 
+int xs_moe_gather_rows(const void *src, const int32_t *index, void *dst, int32_t n_rows, int32_t row_bytes, void *stream)
+{
+    if (!src || !index || !dst)
+        return fail(XS_MOE_ERR_INVALID_ARG, "null tensor pointer");
+    if (n_rows < 0 || row_bytes <= 0 || row_bytes % 4 != 0)
+        return fail(XS_MOE_ERR_INVALID_ARG, "shape mismatch: row_bytes must be a positive multiple of 4");
+    if (n_rows == 0)
+        return 0;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (row_bytes % 16 == 0 && reinterpret_cast<uintptr_t>(src) % 16 == 0 && reinterpret_cast<uintptr_t>(dst) % 16 == 0)
+        xs::gather_rows_kernel<<<n_rows, 256, 0, st>>>(static_cast<const uint8_t *>(src), index, static_cast<uint8_t *>(dst), n_rows,
+                                                       n_rows, 1, row_bytes);
+    else
+        xs::gather_rows4_kernel<<<n_rows, 64, 0, st>>>(static_cast<const uint32_t *>(src), index, static_cast<uint32_t *>(dst), n_rows,
+                                                       n_rows, 1, row_bytes / 4);
+    XS_CUDA(cudaGetLastError());
+    return 0;
+}
+
 int xs_moe_combine(const XsMoeConfig *cfg, const float *y, const int32_t *inv, const float *topk_w, const float *shared, void *out,
                    void *stream)
 {

@@ -1,0 +1,220 @@
+"""Expert parallelism for the MoE layer: one process per GPU, experts sharded evenly and contiguously
+(expert e lives on rank e // (E / R)), tokens data-parallel, one all-to-all each way.
+
+    local route -> local permute (rows sorted by expert => by destination rank)
+    -> all-gather of per-expert counts (the only host synchronisation: NCCL needs split sizes on the host)
+    -> DISPATCH all-to-all of the permuted rows (payload: bf16 rows, or e4m3 codes + 1x128 scales)
+    -> regroup received rows by local expert -> grouped expert MLPs -> rows back into arrival order
+    -> COMBINE all-to-all back (f32 rows) -> local weighted combine (+ the always-on expert, computed locally)
+
+Received rows are ordered by (source rank, expert, token) -- fixed by the data, not by arrival time -- so the
+result is reproducible and equals the single-device layer bit for bit (the combine still sums each token's k
+expert outputs in slot order).
+
+This module is host logic over `torch.distributed`; all device compute goes through an `ops` object.
+`CudaOps` binds the C ABI (libxs_moe.so).  Tests drive the same host logic on CPU ranks (gloo) with a
+stand-in `ops`.
+"""
+import ctypes as C
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+from . import capi
+
+
+# ------------------------------------------------------------------------------------------------------------
+# host-side planning (pure numpy: testable without any device)
+# ------------------------------------------------------------------------------------------------------------
+class EpPlan:
+    """Split sizes and regroup maps from the (R, E) matrix of per-rank, per-expert row counts."""
+
+    def __init__(self, all_counts, rank):
+        all_counts = np.asarray(all_counts, dtype=np.int64)
+        R, E = all_counts.shape
+        if E % R != 0:
+            raise ValueError("expert count mismatch: experts must divide evenly over ranks")
+        self.R, self.E, self.rank = R, E, rank
+        self.El = El = E // R
+        mine = all_counts[rank]
+        # rows this rank sends to rank d = its rows of d's experts; rows it receives from s = s's rows of my experts
+        self.send_splits = mine.reshape(R, El).sum(1).astype(np.int64)
+        self.recv_counts = all_counts[:, rank * El:(rank + 1) * El]  # (R, El): source rank x local expert
+        self.recv_splits = self.recv_counts.sum(1).astype(np.int64)
+        self.n_recv = int(self.recv_splits.sum())
+        # grouped order: (local expert, source rank, token); arrival order: (source rank, local expert, token)
+        per_expert = self.recv_counts.sum(0)
+        self.offsets_local = np.concatenate([[0], np.cumsum(per_expert)]).astype(np.int32)
+        arrival_start = np.concatenate([[0], np.cumsum(self.recv_counts.reshape(-1))])[:-1].reshape(R, El)
+        grouped_start = self.offsets_local[:-1][None, :] + np.concatenate(
+            [np.zeros((1, El), np.int64), np.cumsum(self.recv_counts, 0)[:-1]], 0)
+        grouped_from_arrival = np.empty(self.n_recv, np.int32)  # grouped row g holds arrival row grouped_from_arrival[g]
+        for s in range(R):
+            for e in range(El):
+                n = int(self.recv_counts[s, e])
+                if n:
+                    g0, a0 = int(grouped_start[s, e]), int(arrival_start[s, e])
+                    grouped_from_arrival[g0:g0 + n] = np.arange(a0, a0 + n, dtype=np.int32)
+        self.grouped_from_arrival = grouped_from_arrival
+        arrival_from_grouped = np.empty(self.n_recv, np.int32)
+        arrival_from_grouped[grouped_from_arrival] = np.arange(self.n_recv, dtype=np.int32)
+        self.arrival_from_grouped = arrival_from_grouped
+
+
+def expert_owner(e, E, R):
+    return e // (E // R)
+
+
+# ------------------------------------------------------------------------------------------------------------
+# device ops through the C ABI
+# ------------------------------------------------------------------------------------------------------------
+class CudaOps:
+    """Stage calls of libxs_moe.so on torch CUDA tensors (torch = device memory + streams only)."""
+
+    def __init__(self, dims, weights_local, shared_weights, rank, world):
+        self.dims = dims
+        self.T, self.H, self.E, self.K, self.I, self.S = (dims[k] for k in "THEKIS")
+        self.El = self.E // world
+        self.fmt = {"bf16": capi.BF16, "fp8": capi.FP8_BLOCK128}[dims["fmt"]]
+        self.L = capi.lib()
+        self.cfg_route = capi.make_config(self.T, self.H, self.E, self.K, self.I, 0, self.fmt, self.fmt)
+        self.cfg_local = capi.make_config(self.T, self.H, self.E, self.K, self.I, 0, self.fmt, self.fmt, rank * self.El, self.El)
+        self.cfg_shared = capi.make_config(self.T, self.H, self.E, self.K, self.I, 0, self.fmt, self.fmt, 0, 1)
+        self.w_local = capi.make_weights(weights_local)
+        self.keep = (weights_local, shared_weights)
+        if shared_weights is not None:
+            sw = dict(router_w=weights_local["router_w"], gate_up_w=shared_weights["shared_gate_up_w"],
+                      down_w=shared_weights["shared_down_w"], gate_up_scale=shared_weights.get("shared_gate_up_scale"),
+                      down_scale=shared_weights.get("shared_down_scale"))
+            self.w_shared = capi.make_weights(sw)
+            self.keep += (sw,)
+        self.ws = torch.empty(capi.workspace_bytes(self.cfg_route), dtype=torch.uint8, device="cuda")
+        capi.check(self.L.xs_moe_workspace_init(capi.ptr(self.ws), self.ws.numel(), self._st()))
+        self._gws = {}
+        self.shared_offsets = torch.tensor([0, self.T], dtype=torch.int32, device="cuda")
+
+    @staticmethod
+    def _st():
+        return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+    def device(self):
+        return torch.device("cuda")
+
+    def route(self, x, router_w, router_bias):
+        T, K = self.T, self.K
+        ids = torch.empty((T, K), dtype=torch.int32, device="cuda")
+        w = torch.empty((T, K), dtype=torch.float32, device="cuda")
+        capi.check(self.L.xs_moe_route(C.byref(self.cfg_route), capi.ptr(x), capi.ptr(router_w), capi.ptr(router_bias), None,
+                                       capi.ptr(ids), capi.ptr(w), capi.ptr(self.ws), self.ws.numel(), self._st()))
+        return ids, w
+
+    def permute(self, ids):
+        T, K, E = self.T, self.K, self.E
+        counts = torch.empty(E, dtype=torch.int32, device="cuda")
+        offsets = torch.empty(E + 1, dtype=torch.int32, device="cuda")
+        perm = torch.empty(T * K, dtype=torch.int32, device="cuda")
+        inv = torch.empty(T * K, dtype=torch.int32, device="cuda")
+        capi.check(self.L.xs_moe_permute(C.byref(self.cfg_route), capi.ptr(ids), capi.ptr(counts), capi.ptr(offsets), capi.ptr(perm),
+                                         capi.ptr(inv), capi.ptr(self.ws), self.ws.numel(), self._st()))
+        return counts, offsets, perm, inv
+
+    def payload(self, x):
+        """What travels per row: [bf16 row] or [e4m3 codes, 1x128 f32 scales]."""
+        if self.fmt == capi.BF16:
+            return [x]
+        q = torch.empty(x.shape, dtype=torch.uint8, device="cuda")
+        s = torch.empty((x.shape[0], self.H // 128), dtype=torch.float32, device="cuda")
+        capi.check(self.L.xs_moe_quantize_rows_fp8(capi.ptr(x), x.shape[0], self.H, capi.ptr(q), capi.ptr(s), self._st()))
+        return [q, s]
+
+    def gather(self, src, index):
+        n = index.numel()
+        dst = torch.empty((n, *src.shape[1:]), dtype=src.dtype, device="cuda")
+        row_bytes = src[0].numel() * src.element_size() if src.shape[0] else int(np.prod(src.shape[1:])) * src.element_size()
+        capi.check(self.L.xs_moe_gather_rows(capi.ptr(src), capi.ptr(index), capi.ptr(dst), n, row_bytes, self._st()))
+        return dst
+
+    def _grouped(self, cfg, w, payload, offsets, n_rows):
+        nb = C.c_size_t(0)
+        capi.check(self.L.xs_moe_grouped_mlp_workspace_bytes(C.byref(cfg), n_rows, C.byref(nb)))
+        ws = self._gws.get(id(cfg))
+        if ws is None or ws.numel() < nb.value:  # grow-only scratch, with headroom so that routing noise does not reallocate
+            ws = torch.zeros(int(nb.value * 1.25) + 256, dtype=torch.uint8, device="cuda")
+            self._gws[id(cfg)] = ws
+        y = torch.empty((n_rows, self.H), dtype=torch.float32, device="cuda")
+        scales = payload[1] if len(payload) > 1 else None
+        capi.check(self.L.xs_moe_grouped_mlp(C.byref(cfg), C.byref(w), capi.ptr(payload[0]), capi.ptr(scales), capi.ptr(offsets),
+                                             n_rows, capi.ptr(y), capi.ptr(ws), ws.numel(), self._st()))
+        return y
+
+    def grouped_mlp(self, payload, offsets_local, n_rows):
+        return self._grouped(self.cfg_local, self.w_local, payload, offsets_local, n_rows)
+
+    def shared_mlp(self, payload):
+        return self._grouped(self.cfg_shared, self.w_shared, payload, self.shared_offsets, self.T)
+
+    def combine(self, y, inv, w, shared):
+        out = torch.empty((self.T, self.H), dtype=torch.bfloat16, device="cuda")
+        capi.check(self.L.xs_moe_combine(C.byref(self.cfg_route), capi.ptr(y), capi.ptr(inv), capi.ptr(w), capi.ptr(shared),
+                                         capi.ptr(out), self._st()))
+        return out
+
+    def check(self):
+        capi.check(self.L.xs_moe_check_flags(capi.ptr(self.ws), self._st()))
+        for ws in self._gws.values():
+            capi.check(self.L.xs_moe_check_flags(capi.ptr(ws), self._st()))
+
+
+# ------------------------------------------------------------------------------------------------------------
+# the layer
+# ------------------------------------------------------------------------------------------------------------
+class ExpertParallelMoE:
+    """forward(x_local (T,H)) -> out_local (T,H).  `ops` supplies route / permute / payload / gather / grouped_mlp /
+    shared_mlp / combine on this rank's device; `group` is the torch.distributed process group (None = world)."""
+
+    def __init__(self, ops, router_w, router_bias, num_experts, top_k, has_shared, group=None):
+        self.ops = ops
+        self.router_w, self.router_bias = router_w, router_bias
+        self.E, self.K, self.S = num_experts, top_k, has_shared
+        self.group = group
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        if self.E % self.world != 0:
+            raise ValueError("expert count mismatch: experts must divide evenly over ranks")
+        self.last_plan = None
+
+    def _all_gather_counts(self, counts):
+        if self.world == 1:
+            return counts.cpu().numpy()[None, :]
+        out = torch.empty(self.world * self.E, dtype=torch.int32, device=counts.device)
+        dist.all_gather_into_tensor(out, counts.contiguous(), group=self.group)
+        return out.view(self.world, self.E).cpu().numpy()  # the one host synchronisation of the layer
+
+    def _a2a(self, t, out_rows, in_splits, out_splits):
+        out = torch.empty((out_rows, *t.shape[1:]), dtype=t.dtype, device=t.device)
+        if self.world == 1:
+            out.copy_(t)
+            return out
+        dist.all_to_all_single(out, t.contiguous(), [int(v) for v in out_splits], [int(v) for v in in_splits], group=self.group)
+        return out
+
+    def forward(self, x):
+        ops, K = self.ops, self.K
+        ids, w = ops.route(x, self.router_w, self.router_bias)
+        counts, offsets, perm, inv = ops.permute(ids)
+        payload = ops.payload(x)
+        tok = torch.div(perm, K, rounding_mode="floor").to(torch.int32)
+        send = [ops.gather(p, tok) for p in payload]  # rows in (expert, token) order = grouped by destination rank
+        plan = EpPlan(self._all_gather_counts(counts), self.rank)
+        self.last_plan = plan
+        recv = [self._a2a(s, plan.n_recv, plan.send_splits, plan.recv_splits) for s in send]
+        dev = x.device
+        g_from_a = torch.from_numpy(plan.grouped_from_arrival).to(dev)
+        a_from_g = torch.from_numpy(plan.arrival_from_grouped).to(dev)
+        grouped = [ops.gather(r, g_from_a) for r in recv]
+        y_grouped = ops.grouped_mlp(grouped, torch.from_numpy(plan.offsets_local).to(dev), plan.n_recv)
+        y_arrival = ops.gather(y_grouped, a_from_g)
+        y_back = self._a2a(y_arrival, int(plan.send_splits.sum()), plan.recv_splits, plan.send_splits)
+        shared = ops.shared_mlp(payload) if self.S else None
+        return ops.combine(y_back, inv, w, shared)

@@ -93,6 +93,27 @@ def make_inputs(cfg, seed=0, device="cpu"):
     return d
 
 
+def make_ep_inputs(cfg, rank, world, seed=0, device="cuda"):
+    """Inputs of one expert-parallel rank: the router matrix (and bias) and the always-on expert are replicated
+    (same seed everywhere), the rank's own E/world routed experts and its own batch of T tokens are drawn from
+    rank-specific seeds.  Returns (x, weights_local, shared_weights | None, router_bias | None)."""
+    if isinstance(cfg, str):
+        cfg = CONFIGS[cfg]
+    T, H, E, K, I, S = (cfg[k] for k in "THEKIS")
+    El = E // world
+    common = make_inputs(dict(cfg, T=1, E=1, S=S), seed=seed + 3000, device=device)  # always-on expert, replicated
+    gen = torch.Generator(device=device)
+    gen.manual_seed(seed)
+    router_w = _randn_bf16((E, H), 0.02, gen, device)
+    local = make_inputs(dict(cfg, T=T, E=El, S=0, bias=None), seed=seed + 2000 + rank, device=device)
+    x = local["x"]
+    weights = {k: v for k, v in local.items() if k in ("gate_up_w", "down_w", "gate_up_scale", "down_scale") and v is not None}
+    weights["router_w"] = router_w
+    shared = {k: v for k, v in common.items() if k.startswith("shared_") and v is not None} if S else None
+    bias = zipf_bias(E, seed).to(device) if cfg.get("bias") == "zipf" else None
+    return x, weights, shared, bias
+
+
 def to_numpy_storage(d):
     """Host numpy views of the storage bytes (bf16 as uint16) for the CPU oracle."""
     out = {}
