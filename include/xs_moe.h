@@ -162,8 +162,9 @@ int xs_moe_permute(const XsMoeConfig *cfg, const int32_t *topk_ids_dev, int32_t 
 int xs_moe_permute_noalloc(const XsMoeConfig *cfg, const int32_t *topk_ids_dev, int32_t *counts_dev,
                            int32_t *offsets_dev, int32_t *perm_dev, int32_t *inv_dev, void *stream);
 
-/* Per-expert SwiGLU MLPs over already-routed rows: rows_dev(M,H) (bf16, or e4m3 codes with
- * row_scales_dev (M, H/128) f32 for FP8 experts; NULL for bf16) are grouped by LOCAL expert
+/* Per-expert SwiGLU MLPs over already-routed rows: rows_dev(M,H) (bf16; or e4m3 codes with row_scales_dev
+ * (M, H/128) f32 for FP8 experts; or e4m3 codes with row_scales_dev pointing at (M, H/32) e8m0 BYTES for FP4
+ * experts; NULL for bf16) are grouped by LOCAL expert
  * (expert e owns rows [offsets[e], offsets[e+1]), e in [0, local_expert_count)); y_dev(M,H) f32 receives
  * down(silu(gate x) * up x) per row.  Takes the role of gemm_silu_and_mul_launch + the down linear
  * (xstar_cpp/include/ops/mlp.h:95-102, xstar_cpp/src/ops/mlp.cpp:64-70), once per expert segment.
@@ -178,6 +179,12 @@ int xs_moe_grouped_mlp(const XsMoeConfig *cfg, const XsMoeWeights *w, const void
  * the reference, whose DType has no 8-bit member (xstar_cpp/include/dtype.h:8-12). */
 int xs_moe_quantize_rows_fp8(const void *x_dev, int32_t rows, int32_t cols, void *codes_dev, float *scales_dev,
                              void *stream);
+
+/* Activation quantisation for FP4 experts (MX-FP8): e4m3 codes and one e8m0 scale byte per (row, 32 columns):
+ * s = the smallest power of two >= max(amax, 1e-30) / 448, code = e4m3_rne_saturating(x / s).  No counterpart
+ * in the reference (xstar_cpp/include/dtype.h:8-12 has no 8-bit member). */
+int xs_moe_quantize_rows_mxfp8(const void *x_dev, int32_t rows, int32_t cols, void *codes_dev, uint8_t *scales_dev,
+                               void *stream);
 
 /* dst[r] = src[index[r]] for r < n_rows, rows of row_bytes bytes (a multiple of 4): the reference's gather
  * (embedding_launch, xstar_cpp/include/ops/embedding.h:58-63) with int32 indices and any row type.  Used to put

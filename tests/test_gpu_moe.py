@@ -242,3 +242,31 @@ def test_forward_fp8_decode_shapes(oracle, name, n_sub):
     rel = synth.rel_l2(gu.bf16_to_f32(out)[sub], synth.bf16_bits_to_f32(ref["out"])[sub])
     print(f"{name}: rel-L2 {rel:.3e}")
     assert rel <= FP8_TOL, rel
+
+
+# ---- FP4 e2m1 experts with e8m0 scales per 32, MX-FP8 activations ----------------------------------------------------
+def test_quantize_rows_mxfp8_bit_exact(oracle):
+    g = torch.Generator(device="cuda").manual_seed(51)
+    x = (torch.randn((29, 384), generator=g, device="cuda") * torch.rand((29, 1), generator=g, device="cuda") * 8).to(torch.bfloat16)
+    x[3, :32] = 0
+    x[4, 32:64] *= 1e-20
+    q = torch.empty((29, 384), dtype=torch.uint8, device="cuda")
+    s = torch.empty((29, 12), dtype=torch.uint8, device="cuda")
+    capi.check(capi.lib().xs_moe_quantize_rows_mxfp8(capi.ptr(x), 29, 384, capi.ptr(q), capi.ptr(s), gu.stream_ptr()))
+    torch.cuda.synchronize()
+    rq, rs = oracle.quant_act_mxfp8(x.float().cpu().numpy())
+    assert np.array_equal(s.cpu().numpy(), rs)
+    assert np.array_equal(q.cpu().numpy(), rq)
+
+
+@pytest.mark.parametrize("T,S,E,K,H,I", [(1, 0, 8, 2, 256, 256), (9, 0, 8, 3, 512, 256), (70, 1, 16, 4, 256, 384),
+                                         (200, 1, 8, 2, 384, 256), (333, 0, 4, 2, 256, 128)])
+def test_forward_fp4_ragged_shapes(oracle, T, S, E, K, H, I):
+    dims = _dims(T=T, S=S, E=E, K=K, H=H, I=I, fmt="fp4")
+    d = synth.make_inputs(dims, seed=T + 2, device="cuda")
+    out = gu.forward(dims, d)
+    ref = gu.oracle_forward(oracle, dims, d)
+    rel = synth.rel_l2(gu.bf16_to_f32(out), synth.bf16_bits_to_f32(ref["out"]))
+    print(f"fp4 T={T}: rel-L2 {rel:.3e}")
+    assert rel <= FP8_TOL, rel
+    assert torch.equal(out, gu.forward(dims, d)), "FP4 forward is not deterministic"

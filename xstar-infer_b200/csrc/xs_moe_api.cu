@@ -13,6 +13,7 @@
 #include <string>
 
 #include "xs_grouped_gemm.cuh"
+#include "xs_grouped_gemm_fp4.cuh"
 #include "xs_permute.cuh"
 #include "xs_route.cuh"
 
@@ -135,10 +136,14 @@ int check_cfg(const XsMoeConfig *c)
     if (c->local_expert_begin < 0 || c->local_expert_count <= 0 ||
         c->local_expert_begin + c->local_expert_count > c->num_experts)
         return fail(XS_MOE_ERR_INVALID_ARG, "expert count mismatch: local expert range outside [0, num_experts)");
-    if (c->routed_format != XS_MOE_BF16 && c->routed_format != XS_MOE_FP8_BLOCK128)
-        return fail(XS_MOE_ERR_UNSUPPORTED, "unsupported dtype: routed experts must be bf16 or FP8 e4m3 with 128x128 block scales in this build");
-    if (c->num_shared && c->shared_format != c->routed_format)
-        return fail(XS_MOE_ERR_UNSUPPORTED, "unsupported dtype: the shared expert must use the routed experts' format in this build");
+    if (c->routed_format != XS_MOE_BF16 && c->routed_format != XS_MOE_FP8_BLOCK128 && c->routed_format != XS_MOE_FP4_MX32)
+        return fail(XS_MOE_ERR_UNSUPPORTED, "unsupported dtype: routed experts must be bf16, FP8 e4m3 (128x128 scales) or FP4 e2m1 (e8m0/32)");
+    if (c->num_shared) {
+        const int want = c->routed_format == XS_MOE_FP4_MX32 ? XS_MOE_FP8_BLOCK128 : c->routed_format;
+        if (c->shared_format != want)
+            return fail(XS_MOE_ERR_UNSUPPORTED, "unsupported dtype: the shared expert must be bf16 next to bf16 experts and FP8 e4m3 "
+                                                "(128x128 scales) next to FP8 or FP4 experts");
+    }
     if (c->gemm_impl != 0 && c->gemm_impl != 1)
         return fail(XS_MOE_ERR_INVALID_ARG, "gemm_impl must be 0 or 1");
     if (c->gemm_impl == 1 && c->routed_format != XS_MOE_BF16)
@@ -179,7 +184,7 @@ GroupedPlan plan_grouped(int max_rows, int routed_rows, int routed_groups, int s
     p.off_tile_row0 = o;   o = align_up(o + sizeof(int32_t) * p.max_tiles, 256);
     p.off_num_tiles = o;   o = align_up(o + sizeof(int32_t), 256);
     p.off_act = o;         o = align_up(o + static_cast<size_t>(max_rows) * I * (fmt == XS_MOE_BF16 ? 2 : 1), 256);
-    p.off_act_scale = o;   o = align_up(o + (fmt == XS_MOE_BF16 ? 0 : static_cast<size_t>(max_rows) * (I / 128) * 4), 256);
+    p.off_act_scale = o;   o = align_up(o + (fmt == XS_MOE_BF16 ? 0 : static_cast<size_t>(max_rows) * (I / 128) * 4), 256); // FP4: I/32 bytes
     p.bytes = o;
     return p;
 }
@@ -190,7 +195,8 @@ struct ForwardPlan {
     int chunks = 0;
     size_t off_logits = 0, off_ids = 0, off_w = 0, off_counts = 0, off_offsets = 0, off_perm = 0, off_inv = 0;
     size_t off_chunk_counts = 0, off_chunk_base = 0, off_rows = 0, off_rows_scale = 0, off_y = 0, off_grouped = 0;
-    GroupedPlan grouped;
+    size_t off_sh_rows = 0, off_sh_scale = 0, off_sh_offsets = 0, off_sh_grouped = 0; // FP4: the FP8 always-on expert runs on its own
+    GroupedPlan grouped, sh_grouped;
     size_t bytes = 0;
 };
 
@@ -207,7 +213,8 @@ ForwardPlan plan_forward(const XsMoeConfig *c)
         o = align_up(o + bytes, 256);
         return at;
     };
-    const bool fp8 = c->routed_format == XS_MOE_FP8_BLOCK128;
+    const bool fp8 = c->routed_format == XS_MOE_FP8_BLOCK128, fp4 = c->routed_format == XS_MOE_FP4_MX32;
+    const size_t Sm = fp4 ? 0 : S; // rows of the always-on expert merged behind the routed rows
     p.off_logits = take(T * E * 4);
     p.off_ids = take(T * K * 4);
     p.off_w = take(T * K * 4);
@@ -217,12 +224,19 @@ ForwardPlan plan_forward(const XsMoeConfig *c)
     p.off_inv = take(T * K * 4);
     p.off_chunk_counts = take(static_cast<size_t>(p.chunks) * E * 4);
     p.off_chunk_base = take(static_cast<size_t>(p.chunks) * E * 4);
-    p.off_rows = take((T * K + S * T) * H * (fp8 ? 1 : 2));
-    p.off_rows_scale = take(fp8 ? (T * K + S * T) * (H / 128) * 4 : 0);
+    p.off_rows = take((T * K + Sm * T) * H * (fp8 || fp4 ? 1 : 2));
+    p.off_rows_scale = take(fp8 ? (T * K + Sm * T) * (H / 128) * 4 : (fp4 ? T * K * (H / 32) : 0));
     p.off_y = take((T * K + S * T) * H * 4);
-    p.grouped = plan_grouped(static_cast<int>(T * K + S * T), static_cast<int>(T * K), static_cast<int>(E), static_cast<int>(E + S),
+    p.grouped = plan_grouped(static_cast<int>(T * K + Sm * T), static_cast<int>(T * K), static_cast<int>(E), static_cast<int>(E + Sm),
                              static_cast<int>(I), c->routed_format);
     p.off_grouped = take(p.grouped.bytes);
+    if (fp4 && S) {
+        p.off_sh_rows = take(T * H);
+        p.off_sh_scale = take(T * (H / 128) * 4);
+        p.off_sh_offsets = take(8);
+        p.sh_grouped = plan_grouped(static_cast<int>(T), static_cast<int>(T), 1, 1, static_cast<int>(I), XS_MOE_FP8_BLOCK128);
+        p.off_sh_grouped = take(p.sh_grouped.bytes);
+    }
     p.bytes = o;
     return p;
 }
@@ -410,6 +424,73 @@ int launch_gemm_fp8(int n_tile, const CUtensorMap &tw, const CUtensorMap &tw2, c
     return fail(XS_MOE_ERR_INVALID_ARG, "internal: bad token tile %d for FP8", n_tile);
 }
 
+constexpr int kFp4TailBytes = 512;
+
+template <int N_TILE, bool GATE_UP>
+int launch_gemm_fp4_t(const CUtensorMap &tw, const CUtensorMap &tx, const int32_t *offsets, xs::TileTable tt, xs::MxScales sc, int w_rows,
+                      int n_out, int K, void *out, int32_t *status, int max_work, cudaStream_t st)
+{
+    DeviceInfo di;
+    if (int rc = device_info(&di))
+        return rc;
+    const int stage_bytes = (GATE_UP ? 2 : 1) * xs::kTileM * xs::kBlockK8 + N_TILE * xs::kBlockK8;
+    int stages = (di.max_smem - 1024 - kFp4TailBytes) / stage_bytes;
+    if (stages > 8)
+        stages = 8;
+    if (stages < 2)
+        return fail(XS_MOE_ERR_DEVICE, "not enough shared memory for the GEMM pipeline");
+    const int smem = stages * stage_bytes + 1024 + kFp4TailBytes;
+    auto kern = xs::grouped_gemm_fp4_kernel<N_TILE, GATE_UP>;
+    static bool configured[64] = {};
+    int dev = 0;
+    XS_CUDA(cudaGetDevice(&dev));
+    if (dev >= 64 || !configured[dev]) {
+        XS_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        if (dev < 64)
+            configured[dev] = true;
+    }
+    int grid = di.sms < max_work ? di.sms : max_work;
+    if (grid < 1)
+        grid = 1;
+    kern<<<grid, xs::kFp4Threads, smem, st>>>(tw, tx, offsets, tt, sc, w_rows, n_out, K, out, status, stages);
+    XS_CUDA(cudaGetLastError());
+    return 0;
+}
+
+template <bool GATE_UP>
+int launch_gemm_fp4(int n_tile, const CUtensorMap &tw, const CUtensorMap &tx, const int32_t *offsets, xs::TileTable tt, xs::MxScales sc,
+                    int w_rows, int n_out, int K, void *out, int32_t *status, int max_work, cudaStream_t st)
+{
+    switch (n_tile) {
+    case 16: return launch_gemm_fp4_t<16, GATE_UP>(tw, tx, offsets, tt, sc, w_rows, n_out, K, out, status, max_work, st);
+    case 32: return launch_gemm_fp4_t<32, GATE_UP>(tw, tx, offsets, tt, sc, w_rows, n_out, K, out, status, max_work, st);
+    case 64: return launch_gemm_fp4_t<64, GATE_UP>(tw, tx, offsets, tt, sc, w_rows, n_out, K, out, status, max_work, st);
+    }
+    return fail(XS_MOE_ERR_INVALID_ARG, "internal: bad token tile %d for FP4", n_tile);
+}
+
+// Packed e2m1 matrix (rows, K elements = K/2 bytes per row): the TMA unit expands each 16 codes (8 bytes) to a 16-byte
+// shared-memory piece, the form the f8f6f4 MMA kinds read.  Box = 128 elements x box_rows, 128-byte swizzle.
+int make_tmap_fp4(CUtensorMap *m, const void *base, uint64_t rows, uint64_t k_elems, uint32_t box_rows)
+{
+    EncodeTiledFn fn = get_encode_fn();
+    if (!fn)
+        return fail(XS_MOE_ERR_CUDA, "CUDA error: cuTensorMapEncodeTiled entry point not available");
+    if (reinterpret_cast<uintptr_t>(base) % 32 != 0 || (k_elems / 2) % 32 != 0)
+        return fail(XS_MOE_ERR_INVALID_ARG, "packed FP4 operand must be 32-byte aligned with a 32-byte multiple row pitch");
+    cuuint64_t dims[2] = {k_elems, rows};
+    cuuint64_t strides[1] = {k_elems / 2};
+    cuuint32_t box[2] = {128, box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B, 2, const_cast<void *>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS)
+        return fail(XS_MOE_ERR_CUDA, "CUDA error: cuTensorMapEncodeTiled (packed FP4) failed with code %d (rows=%llu k=%llu)", (int)r,
+                    (unsigned long long)rows, (unsigned long long)k_elems);
+    return 0;
+}
+
 // One grouped SwiGLU MLP over rows grouped by expert segment.  Segments 0..groups-1 use the stacked weights
 // (gu, dw); if gu2 is given, segment `groups` (the always-on expert's rows) uses (gu2, dw2) in the SAME launches, so
 // its tiles are load-balanced with the routed ones instead of running on a handful of SMs by themselves.
@@ -437,7 +518,9 @@ int run_grouped(const GroupedArgs &a, cudaStream_t st, cudaEvent_t mid = nullptr
     }
     const int H = a.H, I = a.I, groups = a.groups;
     const int segments = groups + (a.gu2 ? 1 : 0);
-    const bool fp8 = a.fmt == XS_MOE_FP8_BLOCK128;
+    const bool fp8 = a.fmt == XS_MOE_FP8_BLOCK128, fp4 = a.fmt == XS_MOE_FP4_MX32;
+    if (fp4 && (a.gu2 || !a.gu_scale || !a.dw_scale || !a.row_scale))
+        return fail(XS_MOE_ERR_INVALID_ARG, "missing scale");
     if (fp8 && (!a.gu_scale || !a.dw_scale || !a.row_scale || (a.gu2 && (!a.gu2_scale || !a.dw2_scale))))
         return fail(XS_MOE_ERR_INVALID_ARG, "missing scale");
     void *act = a.scratch + a.gp.off_act;
@@ -470,6 +553,27 @@ int run_grouped(const GroupedArgs &a, cudaStream_t st, cudaEvent_t mid = nullptr
         xs::tile_table_kernel<<<1, threads, 0, st>>>(a.offsets, segments, a.gp.n_tile, a.gp.max_tiles, tb.tile_expert, tb.tile_row0,
                                                      tb.num_tiles, a.status);
         XS_CUDA(cudaGetLastError());
+    }
+    if (fp4) {
+        CUtensorMap t_wgu, t_wd, t_x, t_act;
+        if (int rc = make_tmap_fp4(&t_wgu, a.gu, static_cast<uint64_t>(groups) * 2 * I, H, xs::kTileM))
+            return rc;
+        if (int rc = make_tmap_fp4(&t_wd, a.dw, static_cast<uint64_t>(groups) * H, I, xs::kTileM))
+            return rc;
+        if (int rc = make_tmap_2d(&t_x, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a.rows, a.max_rows, H, a.gp.n_tile, xs::kBlockK8))
+            return rc;
+        if (int rc = make_tmap_2d(&t_act, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, act, a.max_rows, I, a.gp.n_tile, xs::kBlockK8))
+            return rc;
+        uint8_t *act_scale = a.scratch + a.gp.off_act_scale;
+        xs::MxScales s1{static_cast<const uint8_t *>(a.gu_scale), reinterpret_cast<const uint8_t *>(a.row_scale), act_scale, a.max_rows};
+        if (int rc = launch_gemm_fp4<true>(a.gp.n_tile, t_wgu, t_x, a.offsets, tt, s1, 2 * I, I, H, act, a.status,
+                                           a.gp.max_tiles * (I / xs::kTileM), st))
+            return rc;
+        if (mid)
+            XS_CUDA(cudaEventRecord(mid, st));
+        xs::MxScales s2{static_cast<const uint8_t *>(a.dw_scale), act_scale, nullptr, a.max_rows};
+        return launch_gemm_fp4<false>(a.gp.n_tile, t_wd, t_act, a.offsets, tt, s2, H, H, I, a.y, a.status,
+                                      a.gp.max_tiles * (H / xs::kTileM), st);
     }
     const CUtensorMapDataType dt = fp8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
     const int eb = fp8 ? 1 : 2;
@@ -508,6 +612,21 @@ int run_grouped(const GroupedArgs &a, cudaStream_t st, cudaEvent_t mid = nullptr
         XS_CUDA(cudaEventRecord(mid, st));
     xs::Fp8Scales s2{static_cast<const float *>(a.dw_scale), static_cast<const float *>(a.dw2_scale), act_scale, nullptr};
     return launch_gemm_fp8<false>(a.gp.n_tile, t_wd, t_wd2, t_act, a.offsets, tt, s2, groups, H, H, I, a.y, a.status, work_d, st);
+}
+
+__global__ void set_two_ints_kernel(int32_t *p, int a, int b)
+{
+    p[0] = a;
+    p[1] = b;
+}
+
+int launch_quantize_rows_mx(const void *x, const int32_t *dst, int nd, uint8_t *q, uint8_t *scale, int rows, int cols, cudaStream_t st)
+{
+    if (rows == 0)
+        return 0;
+    xs::quantize_rows_mxfp8_kernel<<<rows, 256, 0, st>>>(static_cast<const __nv_bfloat16 *>(x), dst, nd, q, scale, rows, cols);
+    XS_CUDA(cudaGetLastError());
+    return 0;
 }
 
 int launch_quantize_rows(const void *x, uint8_t *q, float *scale, int rows, int cols, cudaStream_t st)
@@ -695,6 +814,15 @@ int xs_moe_quantize_rows_fp8(const void *x, int32_t rows, int32_t cols, void *co
     return launch_quantize_rows(x, static_cast<uint8_t *>(codes), scales, rows, cols, static_cast<cudaStream_t>(stream));
 }
 
+int xs_moe_quantize_rows_mxfp8(const void *x, int32_t rows, int32_t cols, void *codes, uint8_t *scales, void *stream)
+{
+    if (!x || !codes || !scales)
+        return fail(XS_MOE_ERR_INVALID_ARG, "null tensor pointer");
+    if (rows < 0 || cols <= 0 || cols % 128 != 0)
+        return fail(XS_MOE_ERR_INVALID_ARG, "shape mismatch: columns must be a positive multiple of 128");
+    return launch_quantize_rows_mx(x, nullptr, 1, static_cast<uint8_t *>(codes), scales, rows, cols, static_cast<cudaStream_t>(stream));
+}
+
 int xs_moe_gather_rows(const void *src, const int32_t *index, void *dst, int32_t n_rows, int32_t row_bytes, void *stream)
 {
     if (!src || !index || !dst)
@@ -772,9 +900,9 @@ static int forward_impl(const XsMoeConfig *cfg, const XsMoeWeights *w, const voi
     uint8_t *rows = b + p.off_rows;
     float *y = reinterpret_cast<float *>(b + p.off_y);
     const int n_routed = T * K, n_total = T * K + S * T;
-    const bool fp8 = cfg->routed_format == XS_MOE_FP8_BLOCK128;
-    float *rows_scale = fp8 ? reinterpret_cast<float *>(b + p.off_rows_scale) : nullptr;
-    const int extra_rows = S ? T : -1;
+    const bool fp8 = cfg->routed_format == XS_MOE_FP8_BLOCK128, fp4 = cfg->routed_format == XS_MOE_FP4_MX32;
+    float *rows_scale = (fp8 || fp4) ? reinterpret_cast<float *>(b + p.off_rows_scale) : nullptr;
+    const int extra_rows = (S && !fp4) ? T : -1; // FP4 experts: the FP8 always-on expert runs in its own launches
     const bool tensor_path = cfg->gemm_impl == 0;
     uint8_t *gscratch = b + p.off_grouped;
 
@@ -800,7 +928,10 @@ static int forward_impl(const XsMoeConfig *cfg, const XsMoeWeights *w, const voi
             return rc;
     }
     XS_MARK(2);
-    if (fp8)
+    if (fp4) {
+        if (int rc = launch_quantize_rows_mx(x, inv, K, rows, reinterpret_cast<uint8_t *>(rows_scale), T, H, st))
+            return rc;
+    } else if (fp8)
         xs::scatter_rows_kernel<true><<<T, 256, 0, st>>>(static_cast<const __nv_bfloat16 *>(x), inv, rows, rows_scale, T, H, K, n_routed, S);
     else
         xs::scatter_rows_kernel<false><<<T, 256, 0, st>>>(static_cast<const __nv_bfloat16 *>(x), inv, rows, nullptr, T, H, K, n_routed, S);
@@ -816,7 +947,7 @@ static int forward_impl(const XsMoeConfig *cfg, const XsMoeWeights *w, const voi
     a.gu_scale = w->gate_up_scale_dev;
     a.dw = w->down_w_dev;
     a.dw_scale = w->down_scale_dev;
-    if (S) {
+    if (S && !fp4) {
         a.gu2 = w->shared_gate_up_w_dev;
         a.gu2_scale = w->shared_gate_up_scale_dev;
         a.dw2 = w->shared_down_w_dev;
@@ -825,7 +956,7 @@ static int forward_impl(const XsMoeConfig *cfg, const XsMoeWeights *w, const voi
     a.rows = rows;
     a.row_scale = rows_scale;
     a.offsets = offsets;
-    a.max_rows = n_total;
+    a.max_rows = fp4 ? n_routed : n_total;
     a.y = y;
     a.scratch = gscratch;
     a.gp = p.grouped;
@@ -833,6 +964,35 @@ static int forward_impl(const XsMoeConfig *cfg, const XsMoeWeights *w, const voi
     a.tiles_ready = tiles_ready;
     if (int rc = run_grouped(a, st, ev ? ev[4] : nullptr))
         return rc;
+    if (fp4 && S) {
+        // always-on expert in FP8 (128x128 scales): quantise x per 1x128 and run it as a one-segment grouped MLP
+        uint8_t *xq = b + p.off_sh_rows;
+        float *xs_ = reinterpret_cast<float *>(b + p.off_sh_scale);
+        int32_t *sh_off = reinterpret_cast<int32_t *>(b + p.off_sh_offsets);
+        if (int rc = launch_quantize_rows(x, xq, xs_, T, H, st))
+            return rc;
+        set_two_ints_kernel<<<1, 1, 0, st>>>(sh_off, 0, T);
+        XS_CUDA(cudaGetLastError());
+        GroupedArgs sa;
+        sa.fmt = XS_MOE_FP8_BLOCK128;
+        sa.H = H;
+        sa.I = I;
+        sa.groups = 1;
+        sa.gu = w->shared_gate_up_w_dev;
+        sa.gu_scale = w->shared_gate_up_scale_dev;
+        sa.dw = w->shared_down_w_dev;
+        sa.dw_scale = w->shared_down_scale_dev;
+        sa.rows = xq;
+        sa.row_scale = xs_;
+        sa.offsets = sh_off;
+        sa.max_rows = T;
+        sa.y = y + static_cast<size_t>(n_routed) * H;
+        sa.scratch = b + p.off_sh_grouped;
+        sa.gp = p.sh_grouped;
+        sa.status = status;
+        if (int rc = run_grouped(sa, st))
+            return rc;
+    }
     XS_MARK(5);
     if (int rc = xs_moe_combine(cfg, y, inv, tw, S ? y + static_cast<size_t>(n_routed) * H : nullptr, out, stream))
         return rc;

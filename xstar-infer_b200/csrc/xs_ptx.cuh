@@ -197,3 +197,39 @@ __device__ __forceinline__ void tmem_ld_wait()
 }
 
 } // namespace xs
+
+namespace xs {
+
+// Instruction descriptor for block-scaled MMA (kind::mxf8f6f4, one ue8m0 scale per 32 elements of K):
+// bits [4,6) B scale id, [7,10) A format, [10,13) B format, [17,23) N>>3, [23] scale format (1 = ue8m0),
+// [24,29) M>>4, [29,31) A scale id.  A scale id selects which byte of the 32-bit TMEM scale column is used.
+__host__ __device__ constexpr uint32_t make_idesc_mx(uint32_t a_fmt, uint32_t b_fmt, uint32_t m, uint32_t n, uint32_t sf_id)
+{
+    return (sf_id << 4) | (a_fmt << 7) | (b_fmt << 10) | ((n >> 3) << 17) | (1u << 23) | ((m >> 4) << 24) | (sf_id << 29);
+}
+
+__device__ __forceinline__ void mma_mxf8f6f4(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t tmem_sfa,
+                                             uint32_t tmem_sfb, uint32_t accumulate)
+{
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n\t"
+        "}\n"
+        :
+        : "r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(tmem_sfa), "r"(tmem_sfb)
+        : "memory");
+}
+
+// registers -> TMEM: this warp's 32 lanes x 4 (or 1) consecutive 32-bit columns
+__device__ __forceinline__ void tmem_st4(uint32_t taddr, uint32_t a, uint32_t b, uint32_t c, uint32_t d)
+{
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x4.b32 [%0], {%1, %2, %3, %4};" ::"r"(taddr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait()
+{
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+
+} // namespace xs

@@ -62,6 +62,30 @@ def _fp8_block128(shape, std, gen, device):
     return codes, scales
 
 
+_E2M1_MID = [0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0]
+
+
+def _fp4_mx32(shape, std, gen, device):
+    """Packed e2m1 codes (two per byte, low nibble = even k) + one e8m0 scale per 32 elements of the last dim:
+    scale = smallest power of two >= amax / 6, code = nearest e2m1 value of w / scale."""
+    *lead, R, C = shape
+    codes = torch.empty((*lead, R, C // 2), dtype=torch.uint8, device=device)
+    scales = torch.empty((*lead, R, C // 32), dtype=torch.uint8, device=device)
+    flat_c = codes.view(-1, R, C // 2)
+    flat_s = scales.view(-1, R, C // 32)
+    mid = torch.tensor(_E2M1_MID, device=device)
+    for i in range(flat_c.shape[0]):
+        w = (torch.randn((R, C), generator=gen, device=device, dtype=torch.float32) * std).view(R, C // 32, 32)
+        amax = w.abs().amax(-1, keepdim=True).clamp_min(1e-30)
+        ex = torch.ceil(torch.log2(amax / 6.0)).clamp(-127, 127)
+        q = w / torch.exp2(ex)
+        idx = torch.bucketize(q.abs(), mid).to(torch.uint8)  # 0..7
+        code = (idx | ((q < 0).to(torch.uint8) << 3)).view(R, C)
+        flat_c[i] = code[:, 0::2] | (code[:, 1::2] << 4)
+        flat_s[i] = (ex.view(R, C // 32) + 127).to(torch.uint8)
+    return codes, scales
+
+
 def make_inputs(cfg, seed=0, device="cpu"):
     """Returns a dict of torch tensors in storage form:
        x (T,H) bf16, router_w (E,H) bf16, router_bias (E) f32 | None,
@@ -86,6 +110,12 @@ def make_inputs(cfg, seed=0, device="cpu"):
         d["gate_up_w"], d["gate_up_scale"] = _fp8_block128((E, 2 * I, H), 0.02, gen, device)
         d["down_w"], d["down_scale"] = _fp8_block128((E, H, I), 0.02, gen, device)
         if S:
+            d["shared_gate_up_w"], d["shared_gate_up_scale"] = _fp8_block128((2 * I, H), 0.02, gen, device)
+            d["shared_down_w"], d["shared_down_scale"] = _fp8_block128((H, I), 0.02, gen, device)
+    elif fmt == "fp4":
+        d["gate_up_w"], d["gate_up_scale"] = _fp4_mx32((E, 2 * I, H), 0.02, gen, device)
+        d["down_w"], d["down_scale"] = _fp4_mx32((E, H, I), 0.02, gen, device)
+        if S:  # the always-on expert is FP8 with 128x128 scales next to FP4 routed experts
             d["shared_gate_up_w"], d["shared_gate_up_scale"] = _fp8_block128((2 * I, H), 0.02, gen, device)
             d["shared_down_w"], d["shared_down_scale"] = _fp8_block128((H, I), 0.02, gen, device)
     else:
