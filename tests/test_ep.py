@@ -87,8 +87,7 @@ class OracleOps:
                 y[off[e]:off[e + 1]] = torch.from_numpy(self.o.expert_mlp(self.o.BF16, self._bits(rows[off[e]:off[e + 1]]), gu[e], dw[e]))
         return y
 
-    def shared_mlp(self, payload):
-        x = payload[0]
+    def shared_mlp(self, x, payload):
         return torch.from_numpy(self.o.expert_mlp(self.o.BF16, self._bits(x), self._bits(self.shared["shared_gate_up_w"]),
                                                   self._bits(self.shared["shared_down_w"])))
 
@@ -165,16 +164,16 @@ def _gpu_rank(rank, world, port, dims, seed, result_dir):
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("fmt,tol", [("bf16", 2e-3), ("fp8", 1e-2)])
+@pytest.mark.parametrize("fmt,tol", [("bf16", 2e-3), ("fp8", 1e-2), ("fp4", 1e-2)])
 def test_ep_on_gpus_matches_oracle(oracle, tmp_path, fmt, tol):
     world = 2
     if torch.cuda.device_count() < world:
         pytest.skip("needs two GPUs on one box")
     dims = dict(T=96, H=512, E=16, K=4, I=256, S=1, fmt=fmt, bias=None)
-    mp.spawn(_gpu_rank, args=(world, 29650 + (fmt == "fp8"), dims, 23, str(tmp_path)), nprocs=world, join=True)
+    mp.spawn(_gpu_rank, args=(world, 29650 + ["bf16", "fp8", "fp4"].index(fmt), dims, 23, str(tmp_path)), nprocs=world, join=True)
     d = synth.make_inputs(dict(dims, T=dims["T"] * world), seed=23)
     n = synth.to_numpy_storage(d)
-    mode = oracle.BF16 if fmt == "bf16" else oracle.FP8
+    mode = {"bf16": oracle.BF16, "fp8": oracle.FP8, "fp4": oracle.FP4}[fmt]
     ref = oracle.moe_forward(mode, n["x"], n["router_w"], n["gate_up_w"], n["down_w"], dims["K"], gate_up_scale=n.get("gate_up_scale"),
                              down_scale=n.get("down_scale"), shared_gate_up_w=n["shared_gate_up_w"], shared_down_w=n["shared_down_w"],
                              shared_gate_up_scale=n.get("shared_gate_up_scale"), shared_down_scale=n.get("shared_down_scale"), threads=8)

@@ -3,7 +3,7 @@
 
     local route -> local permute (rows sorted by expert => by destination rank)
     -> all-gather of per-expert counts (the only host synchronisation: NCCL needs split sizes on the host)
-    -> DISPATCH all-to-all of the permuted rows (payload: bf16 rows, or e4m3 codes + 1x128 scales)
+    -> DISPATCH all-to-all of the permuted rows (payload: bf16 rows, or e4m3 codes + 1x128 f32 / 1x32 e8m0 scales)
     -> regroup received rows by local expert -> grouped expert MLPs -> rows back into arrival order
     -> COMBINE all-to-all back (f32 rows) -> local weighted combine (+ the always-on expert, computed locally)
 
@@ -76,11 +76,12 @@ class CudaOps:
         self.dims = dims
         self.T, self.H, self.E, self.K, self.I, self.S = (dims[k] for k in "THEKIS")
         self.El = self.E // world
-        self.fmt = {"bf16": capi.BF16, "fp8": capi.FP8_BLOCK128}[dims["fmt"]]
+        self.fmt = {"bf16": capi.BF16, "fp8": capi.FP8_BLOCK128, "fp4": capi.FP4_MX32}[dims["fmt"]]
+        self.fmt_shared = capi.FP8_BLOCK128 if self.fmt == capi.FP4_MX32 else self.fmt  # FP8 always-on expert next to FP4 experts
         self.L = capi.lib()
-        self.cfg_route = capi.make_config(self.T, self.H, self.E, self.K, self.I, 0, self.fmt, self.fmt)
-        self.cfg_local = capi.make_config(self.T, self.H, self.E, self.K, self.I, 0, self.fmt, self.fmt, rank * self.El, self.El)
-        self.cfg_shared = capi.make_config(self.T, self.H, self.E, self.K, self.I, 0, self.fmt, self.fmt, 0, 1)
+        self.cfg_route = capi.make_config(self.T, self.H, self.E, self.K, self.I, 0, self.fmt, self.fmt_shared)
+        self.cfg_local = capi.make_config(self.T, self.H, self.E, self.K, self.I, 0, self.fmt, self.fmt_shared, rank * self.El, self.El)
+        self.cfg_shared = capi.make_config(self.T, self.H, self.E, self.K, self.I, 0, self.fmt_shared, self.fmt_shared, 0, 1)
         self.w_local = capi.make_weights(weights_local)
         self.keep = (weights_local, shared_weights)
         if shared_weights is not None:
@@ -119,14 +120,22 @@ class CudaOps:
                                          capi.ptr(inv), capi.ptr(self.ws), self.ws.numel(), self._st()))
         return counts, offsets, perm, inv
 
-    def payload(self, x):
-        """What travels per row: [bf16 row] or [e4m3 codes, 1x128 f32 scales]."""
-        if self.fmt == capi.BF16:
+    def _payload(self, x, fmt):
+        if fmt == capi.BF16:
             return [x]
         q = torch.empty(x.shape, dtype=torch.uint8, device="cuda")
-        s = torch.empty((x.shape[0], self.H // 128), dtype=torch.float32, device="cuda")
-        capi.check(self.L.xs_moe_quantize_rows_fp8(capi.ptr(x), x.shape[0], self.H, capi.ptr(q), capi.ptr(s), self._st()))
+        if fmt == capi.FP8_BLOCK128:
+            s = torch.empty((x.shape[0], self.H // 128), dtype=torch.float32, device="cuda")
+            capi.check(self.L.xs_moe_quantize_rows_fp8(capi.ptr(x), x.shape[0], self.H, capi.ptr(q), capi.ptr(s), self._st()))
+        else:
+            s = torch.empty((x.shape[0], self.H // 32), dtype=torch.uint8, device="cuda")
+            capi.check(self.L.xs_moe_quantize_rows_mxfp8(capi.ptr(x), x.shape[0], self.H, capi.ptr(q), capi.ptr(s), self._st()))
         return [q, s]
+
+    def payload(self, x):
+        """What travels per row: [bf16 row], [e4m3 codes, 1x128 f32 scales] (FP8 experts) or
+        [e4m3 codes, 1x32 e8m0 scales] (FP4 experts)."""
+        return self._payload(x, self.fmt)
 
     def gather(self, src, index):
         n = index.numel()
@@ -151,7 +160,9 @@ class CudaOps:
     def grouped_mlp(self, payload, offsets_local, n_rows):
         return self._grouped(self.cfg_local, self.w_local, payload, offsets_local, n_rows)
 
-    def shared_mlp(self, payload):
+    def shared_mlp(self, x, payload):
+        if self.fmt_shared != self.fmt:
+            payload = self._payload(x, self.fmt_shared)
         return self._grouped(self.cfg_shared, self.w_shared, payload, self.shared_offsets, self.T)
 
     def combine(self, y, inv, w, shared):
@@ -216,5 +227,5 @@ class ExpertParallelMoE:
         y_grouped = ops.grouped_mlp(grouped, torch.from_numpy(plan.offsets_local).to(dev), plan.n_recv)
         y_arrival = ops.gather(y_grouped, a_from_g)
         y_back = self._a2a(y_arrival, int(plan.send_splits.sum()), plan.recv_splits, plan.send_splits)
-        shared = ops.shared_mlp(payload) if self.S else None
+        shared = ops.shared_mlp(x, payload) if self.S else None
         return ops.combine(y_back, inv, w, shared)
