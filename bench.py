@@ -205,7 +205,7 @@ def run_ours(args, dims):
     # every rank holds a full replica of the layer and its own batch of T tokens (weak scaling, no data-path collective)
     d = synth.make_inputs(dims, seed=rank, device="cuda")
     fmt = synth.FMT[dims["fmt"]]
-    cfg = capi.make_config(T, H, E, K, I, S, fmt, fmt)
+    cfg = capi.make_config(T, H, E, K, I, S, fmt, capi.FP8_BLOCK128 if fmt == capi.FP4_MX32 else fmt)
     nbytes = capi.workspace_bytes(cfg)
     ws = torch.empty(nbytes, dtype=torch.uint8, device="cuda")
     stream = torch.cuda.current_stream()
@@ -282,11 +282,11 @@ def run_ours(args, dims):
     peak, peak_kind = measured_peaks()
     wbytes = {"bf16": 2.0, "fp8": 1.0, "fp4": 0.5}[dims["fmt"]]
     # the dominant kernel streams the gate and up matrices of every active expert and of the always-on expert
-    gate_up_bytes = (active + S) * 2 * H * I * wbytes
+    gate_up_bytes = (active + (S if dims["fmt"] != "fp4" else 0)) * 2 * H * I * wbytes
     dom_ms = float(stage_ms[3])
     layer_bytes = synth.algorithmic_bytes(dims, active)
     roofline = {
-        "bound": "hbm", "kernel": f"grouped_gemm_{'bf16' if dims['fmt'] == 'bf16' else 'fp8'}_kernel<gate_up> (routed + always-on experts)",
+        "bound": "hbm", "kernel": f"grouped_gemm_{dims['fmt']}_kernel<gate_up> (routed" + (" + always-on experts)" if dims["fmt"] != "fp4" else " experts)"),
         "achieved": gate_up_bytes / (dom_ms * 1e-3) / 1e9, "peak": peak, "unit": "GB/s", "peak_kind": peak_kind,
         "frac": gate_up_bytes / (dom_ms * 1e-3) / 1e9 / peak, "traffic": None,
         "algorithmic_bytes_per_launch": gate_up_bytes, "ms_per_launch": dom_ms,

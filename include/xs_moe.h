@@ -197,6 +197,13 @@ int xs_moe_gather_rows(const void *src_dev, const int32_t *index_dev, void *dst_
 int xs_moe_combine(const XsMoeConfig *cfg, const float *y_dev, const int32_t *inv_dev, const float *topk_w_dev,
                    const float *shared_dev, void *out_dev, void *stream);
 
+/* Role profile of the warp-specialised GEMM kernels that ran on this workspace since the last call: eight
+ * 64-bit cycle counters summed over CTAs (0 producer blocked on a free stage, 1 MMA issuer blocked on operands,
+ * 2 on scales, 3 on a free accumulator, 4 scale writers blocked on a free slot, 5 epilogue blocked on an
+ * accumulator, 6 CTA lifetime, 7 CTAs).  Reads and clears; synchronises.  A tuning aid with no counterpart in
+ * the reference. */
+int xs_moe_debug_counters(void *workspace_dev, unsigned long long *out8, void *stream);
+
 /* Reads and clears the device-side status word the kernels of the last calls on this workspace wrote
  * (bounded waits that gave up, index checks that failed).  Synchronises the stream. */
 int xs_moe_check_flags(void *workspace_dev, void *stream);

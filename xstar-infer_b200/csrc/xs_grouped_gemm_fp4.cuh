@@ -9,17 +9,20 @@
 //
 // Scale factors live in TMEM.  For an MMA of K = 32 each operand row has one scale byte; a 32-bit TMEM column
 // carries the bytes of FOUR consecutive 32-blocks (the instruction descriptor's scale id picks the byte), and
-// row r of the operand sits in lane r % 32, column r / 32, replicated in all four lane quarters.  Four scale
-// warps copy them from global memory with one 32-bit load per row and tcgen05.st, one ring slot per
-// shared-memory stage.
+// row r of the operand sits in lane r % 32, column r / 32, replicated in all four lane quarters.  One scale warp
+// fetches them from global memory (one 32-bit load per row, issued a few k-blocks ahead) into a 512-byte block
+// per operand tile in shared memory -- lane i writes the 16 bytes {rows i, 32+i, 64+i, 96+i} -- and the MMA
+// thread moves each block into TMEM with tcgen05.cp (32x128b, replicated x4) right before the MMAs that use it,
+// so no thread ever waits for a TMEM store.
 //
-// Warps: 0 TMA producer | 1 MMA issuer, TMEM owner | 2..5 epilogue | 6..9 scale writers.
+// Warps: 0 TMA producer | 1 MMA issuer, TMEM owner | 2..5 epilogue | 6 scale loader.
 #pragma once
 #include "xs_grouped_gemm.cuh"
 
 namespace xs {
 
-constexpr int kFp4Threads = 320;
+constexpr int kFp4Threads = 224;
+constexpr int kFp4SfBytesPerStage = 1536; // three 512-byte scale blocks: gate rows, up rows, tokens
 
 struct MxScales {
     const uint8_t *w_scale; // (groups * w_rows_per_expert, K / 32) e8m0
@@ -68,15 +71,20 @@ grouped_gemm_fp4_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
     uint64_t *tmem_empty = tmem_full + 2;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(tmem_empty + 2);
     volatile uint32_t *abort_flag = tmem_slot + 1;
+    uint8_t *sf_smem = reinterpret_cast<uint8_t *>(bars) + 512; // [stages][kFp4SfBytesPerStage], 16-byte aligned
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
+    // role profile: cycles each role spent blocked, summed over CTAs into eight 64-bit counters behind the status word
+    unsigned long long *prof = reinterpret_cast<unsigned long long *>(status + 16);
+    const long long t_start = clock64();
+    long long w0 = 0, w1 = 0, w2 = 0;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < stages; s++) {
             mbar_init(&full[s], 1);
             mbar_init(&empty[s], 1);
-            mbar_init(&sf_full[s], 4);
+            mbar_init(&sf_full[s], 1);
         }
         for (int b = 0; b < 2; b++) {
             mbar_init(&tmem_full[b], 1);
@@ -117,7 +125,7 @@ grouped_gemm_fp4_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
                 const int row0 = tt.tile_row0[tile];
                 const int wrow = e * w_rows_per_expert + f * kTileM;
                 for (int kb = 0; kb < num_kb; kb++) {
-                    if (!mbar_wait(&empty[stage], phase ^ 1, abort_flag)) {
+                    if (!mbar_wait_t(&empty[stage], phase ^ 1, abort_flag, w0)) {
                         ok = false;
                         break;
                     }
@@ -137,6 +145,9 @@ grouped_gemm_fp4_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
                 *abort_flag = 1;
                 atomicOr(status, kStatusWaitTimeout);
             }
+            atomicAdd(&prof[0], static_cast<unsigned long long>(w0));
+            atomicAdd(&prof[6], static_cast<unsigned long long>(clock64() - t_start));
+            atomicAdd(&prof[7], 1ull);
         }
     } else if (warp == 1) {
         if (lane == 0) {
@@ -147,14 +158,14 @@ grouped_gemm_fp4_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
             for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x, it++) {
                 const int buf = it & 1;
                 const uint32_t use = static_cast<uint32_t>(it >> 1);
-                if (!mbar_wait(&tmem_empty[buf], (use & 1) ^ 1, abort_flag)) {
+                if (!mbar_wait_t(&tmem_empty[buf], (use & 1) ^ 1, abort_flag, w2)) {
                     ok = false;
                     break;
                 }
                 tc_fence_after();
                 const uint32_t d0 = tmem_base + static_cast<uint32_t>(buf * ACC_COLS);
                 for (int kb = 0; kb < num_kb; kb++) {
-                    if (!mbar_wait(&full[stage], phase, abort_flag) || !mbar_wait(&sf_full[stage], phase, abort_flag)) {
+                    if (!mbar_wait_t(&full[stage], phase, abort_flag, w0) || !mbar_wait_t(&sf_full[stage], phase, abort_flag, w1)) {
                         ok = false;
                         break;
                     }
@@ -165,6 +176,11 @@ grouped_gemm_fp4_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
                     const uint64_t db = make_desc_sw128(sa + (GATE_UP ? 2 : 1) * A_BYTES);
                     const uint32_t sfw = sf_base + static_cast<uint32_t>(stage * SF_COLS);
                     const uint32_t sfx = sfw + SF_W_COLS;
+                    const uint32_t sfs = smem_u32(sf_smem + static_cast<size_t>(stage) * kFp4SfBytesPerStage);
+                    tmem_cp_32x128b_x4(sfw, make_desc_rows16(sfs));
+                    if (GATE_UP)
+                        tmem_cp_32x128b_x4(sfw + 4, make_desc_rows16(sfs + 512));
+                    tmem_cp_32x128b_x4(sfx, make_desc_rows16(sfs + 1024));
 #pragma unroll
                     for (int kk = 0; kk < kBlockK8 / kUmmaK8; kk++) {
                         const uint32_t idesc = make_idesc_mx(5, 0, kTileM, N_TILE, kk); // A = e2m1, B = e4m3, scale byte kk
@@ -186,45 +202,82 @@ grouped_gemm_fp4_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
                 *abort_flag = 1;
                 atomicOr(status, kStatusWaitTimeout);
             }
+            atomicAdd(&prof[1], static_cast<unsigned long long>(w0));
+            atomicAdd(&prof[2], static_cast<unsigned long long>(w1));
+            atomicAdd(&prof[3], static_cast<unsigned long long>(w2));
         }
-    } else if (warp >= 6) {
-        // scale writers: each of the four warps fills its own lane quarter with the same 32 x SF_COLS cells
-        const int q = warp & 3;
+    } else if (warp == 6) {
+        // Scale loader.  The global loads run kSfAhead k-blocks ahead of the shared-memory stores (a register ring),
+        // so their latency is off the per-stage critical path.
+        constexpr int kSfAhead = 3;
+        struct Cursor {
+            int w, kb, row0;
+            size_t wrow;
+            bool valid;
+        };
+        auto locate = [&](Cursor &c) {
+            c.valid = c.w < total_work;
+            if (c.valid) {
+                const int tile = c.w / n_f_tiles;
+                const int f = c.w - tile * n_f_tiles;
+                c.row0 = tt.tile_row0[tile];
+                c.wrow = static_cast<size_t>(tt.tile_expert[tile]) * w_rows_per_expert + f * kTileM;
+            }
+        };
+        auto advance = [&](Cursor &c) {
+            if (++c.kb == num_kb) {
+                c.kb = 0;
+                c.w += gridDim.x;
+                locate(c);
+            }
+        };
+        auto fetch = [&](const Cursor &c, uint32_t (&r)[SF_COLS]) {
+            if (!c.valid)
+                return;
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                r[i] = __ldg(reinterpret_cast<const uint32_t *>(sc.w_scale + (c.wrow + i * 32 + lane) * kbs + c.kb * 4));
+                if constexpr (GATE_UP)
+                    r[4 + i] = __ldg(reinterpret_cast<const uint32_t *>(sc.w_scale + (c.wrow + n_out + i * 32 + lane) * kbs + c.kb * 4));
+            }
+#pragma unroll
+            for (int i = 0; i < SF_X_COLS; i++) {
+                int row = c.row0 + i * 32 + lane;
+                row = row < sc.max_rows ? row : sc.max_rows - 1;
+                r[SF_W_COLS + i] =
+                    (i * 32 < N_TILE) ? __ldg(reinterpret_cast<const uint32_t *>(sc.x_scale + static_cast<size_t>(row) * kbs + c.kb * 4)) : 0u;
+            }
+        };
+        uint32_t ring[kSfAhead + 1][SF_COLS];
+        Cursor ld{static_cast<int>(blockIdx.x), 0, 0, 0, false}, stc = ld;
+        locate(ld);
+        locate(stc);
+#pragma unroll
+        for (int j = 0; j < kSfAhead; j++) {
+            fetch(ld, ring[j]);
+            advance(ld);
+        }
         int stage = 0;
         uint32_t phase = 0;
         bool ok = true;
-        for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x) {
-            const int tile = w / n_f_tiles;
-            const int f = w - tile * n_f_tiles;
-            const int e = tt.tile_expert[tile];
-            const int row0 = tt.tile_row0[tile];
-            const size_t wrow = static_cast<size_t>(e) * w_rows_per_expert + f * kTileM;
-            for (int kb = 0; kb < num_kb; kb++) {
-                uint32_t rw[SF_W_COLS], rx[SF_X_COLS];
+        while (stc.valid && ok) {
 #pragma unroll
-                for (int c = 0; c < 4; c++) {
-                    rw[c] = __ldg(reinterpret_cast<const uint32_t *>(sc.w_scale + (wrow + c * 32 + lane) * kbs + kb * 4));
-                    if constexpr (GATE_UP)
-                        rw[4 + c] = __ldg(reinterpret_cast<const uint32_t *>(sc.w_scale + (wrow + n_out + c * 32 + lane) * kbs + kb * 4));
-                }
-#pragma unroll
-                for (int c = 0; c < SF_X_COLS; c++) {
-                    int row = row0 + c * 32 + lane;
-                    row = row < sc.max_rows ? row : sc.max_rows - 1;
-                    rx[c] = (c * 32 < N_TILE) ? __ldg(reinterpret_cast<const uint32_t *>(sc.x_scale + static_cast<size_t>(row) * kbs + kb * 4)) : 0u;
-                }
-                if (!mbar_wait(&empty[stage], phase ^ 1, abort_flag)) {
+            for (int j = 0; j <= kSfAhead; j++) {
+                if (!stc.valid)
+                    break;
+                fetch(ld, ring[(j + kSfAhead) % (kSfAhead + 1)]);
+                advance(ld);
+                if (!mbar_wait_t(&empty[stage], phase ^ 1, abort_flag, w0)) {
                     ok = false;
                     break;
                 }
-                tc_fence_after();
-                const uint32_t slot = sf_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(stage * SF_COLS);
-                tmem_st4(slot, rw[0], rw[1], rw[2], rw[3]);
+                const uint32_t (&r)[SF_COLS] = ring[j];
+                uint8_t *blk = sf_smem + static_cast<size_t>(stage) * kFp4SfBytesPerStage + lane * 16;
+                *reinterpret_cast<uint4 *>(blk) = make_uint4(r[0], r[1], r[2], r[3]);
                 if constexpr (GATE_UP)
-                    tmem_st4(slot + 4, rw[4], rw[5], rw[6], rw[7]);
-                tmem_st4(slot + SF_W_COLS, rx[0], rx[1], rx[2], rx[3]);
-                tmem_st_wait();
-                tc_fence_before();
+                    *reinterpret_cast<uint4 *>(blk + 512) = make_uint4(r[4], r[5], r[6], r[7]);
+                *reinterpret_cast<uint4 *>(blk + 1024) = make_uint4(r[SF_W_COLS], r[SF_W_COLS + 1], r[SF_W_COLS + 2], r[SF_W_COLS + 3]);
+                fence_proxy_async_smem(); // the tensor-core copy engine reads these bytes through the async proxy
                 __syncwarp();
                 if (lane == 0)
                     mbar_arrive(&sf_full[stage]);
@@ -232,12 +285,15 @@ grouped_gemm_fp4_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
                     stage = 0;
                     phase ^= 1;
                 }
+                advance(stc);
             }
         }
         if (!ok && lane == 0) {
             *abort_flag = 1;
             atomicOr(status, kStatusWaitTimeout);
         }
+        if (warp == 6 && lane == 0)
+            atomicAdd(&prof[4], static_cast<unsigned long long>(w0));
     } else {
         const int q = warp & 3;
         bool ok = true;
@@ -251,7 +307,7 @@ grouped_gemm_fp4_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
             nvalid = nvalid < N_TILE ? nvalid : N_TILE;
             const int buf = it & 1;
             const uint32_t use = static_cast<uint32_t>(it >> 1);
-            if (!mbar_wait(&tmem_full[buf], use & 1, abort_flag)) {
+            if (!mbar_wait_t(&tmem_full[buf], use & 1, abort_flag, w0)) {
                 ok = false;
                 break;
             }
@@ -303,6 +359,8 @@ grouped_gemm_fp4_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
             *abort_flag = 1;
             atomicOr(status, kStatusWaitTimeout);
         }
+        if (warp == 2 && lane == 0)
+            atomicAdd(&prof[5], static_cast<unsigned long long>(w0));
     }
 
     __syncwarp();

@@ -424,7 +424,7 @@ int launch_gemm_fp8(int n_tile, const CUtensorMap &tw, const CUtensorMap &tw2, c
     return fail(XS_MOE_ERR_INVALID_ARG, "internal: bad token tile %d for FP8", n_tile);
 }
 
-constexpr int kFp4TailBytes = 512;
+constexpr int kFp4TailBytes = 512 + 8 * xs::kFp4SfBytesPerStage; // barriers + per-stage scale blocks
 
 template <int N_TILE, bool GATE_UP>
 int launch_gemm_fp4_t(const CUtensorMap &tw, const CUtensorMap &tx, const int32_t *offsets, xs::TileTable tt, xs::MxScales sc, int w_rows,
@@ -1046,6 +1046,18 @@ int xs_moe_check_flags(void *ws, void *stream)
             return fail(XS_MOE_ERR_KERNEL_TIMEOUT, "a kernel gave up a bounded wait (status word 0x%x)", flags);
         return fail(XS_MOE_ERR_INVALID_ARG, "a kernel met an out-of-range index (status word 0x%x)", flags);
     }
+    return 0;
+}
+
+int xs_moe_debug_counters(void *ws, unsigned long long *out8, void *stream)
+{
+    if (!ws || !out8)
+        return fail(XS_MOE_ERR_INVALID_ARG, "null pointer");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    uint8_t *p = static_cast<uint8_t *>(ws) + 64;
+    XS_CUDA(cudaMemcpyAsync(out8, p, 64, cudaMemcpyDeviceToHost, st));
+    XS_CUDA(cudaMemsetAsync(p, 0, 64, st));
+    XS_CUDA(cudaStreamSynchronize(st));
     return 0;
 }
 

@@ -77,6 +77,17 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volati
     return false;
 }
 
+// Same wait, adding the cycles spent to `acc` (role profiling: who waits for whom inside a warp-specialised kernel).
+__device__ __forceinline__ bool mbar_wait_t(uint64_t *bar, uint32_t parity, volatile uint32_t *abort_flag, long long &acc)
+{
+    if (mbar_try_wait(bar, parity))
+        return true;
+    const long long t0 = clock64();
+    const bool ok = mbar_wait(bar, parity, abort_flag);
+    acc += clock64() - t0;
+    return ok;
+}
+
 // ---- TMA ----------------------------------------------------------------------------------------------
 __device__ __forceinline__ void prefetch_tmap(const CUtensorMap *m)
 {
@@ -220,6 +231,29 @@ __device__ __forceinline__ void mma_mxf8f6f4(uint32_t tmem_d, uint64_t desc_a, u
         :
         : "r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(tmem_sfa), "r"(tmem_sfb)
         : "memory");
+}
+
+// Shared-memory descriptor of an unswizzled block of 16-byte rows stored back to back (row r at r * 16): groups of
+// 8 rows are 128 bytes apart.  Used as the source of tcgen05.cp.
+__device__ __forceinline__ uint64_t make_desc_rows16(uint32_t smem_addr)
+{
+    uint64_t d = 0;
+    d |= static_cast<uint64_t>((smem_addr & 0x3FFFF) >> 4);
+    d |= static_cast<uint64_t>(16 >> 4) << 16;  // leading offset (unused: one 16-byte column)
+    d |= static_cast<uint64_t>(128 >> 4) << 32; // stride between 8-row groups
+    d |= static_cast<uint64_t>(1) << 46;
+    return d;
+}
+// shared memory -> TMEM: 32 rows x 128 bits land in lanes 0..31 of FOUR consecutive columns and are replicated into
+// all four lane quarters.  Ordered with the tcgen05.mma instructions the same thread issues afterwards.
+__device__ __forceinline__ void tmem_cp_32x128b_x4(uint32_t taddr, uint64_t sdesc)
+{
+    asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
+}
+// make generic-proxy writes to shared memory visible to the async proxy (TMA, tcgen05 reads of shared memory)
+__device__ __forceinline__ void fence_proxy_async_smem()
+{
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
 
 // registers -> TMEM: this warp's 32 lanes x 4 (or 1) consecutive 32-bit columns

@@ -19,6 +19,8 @@ CONFIGS = {
     "decode_fp8_t32": dict(T=32, H=4096, E=256, K=6, I=2048, S=1, fmt="fp8", bias=None),
     "decode_fp8_t256": dict(T=256, H=4096, E=256, K=6, I=2048, S=1, fmt="fp8", bias=None),
     "prefill_fp8": dict(T=8192, H=4096, E=256, K=6, I=2048, S=1, fmt="fp8", bias="zipf"),
+    "decode_fp4": dict(T=128, H=4096, E=256, K=6, I=2048, S=1, fmt="fp4", bias=None),
+    "prefill_fp4": dict(T=8192, H=4096, E=256, K=6, I=2048, S=1, fmt="fp4", bias="zipf"),
     "ep_fp4": dict(T=16384, H=4096, E=256, K=6, I=2048, S=1, fmt="fp4", bias=None),
 }
 
