@@ -284,11 +284,16 @@ def run_ours(args, dims):
     # the dominant kernel streams the gate and up matrices of every active expert and of the always-on expert
     gate_up_bytes = (active + (S if dims["fmt"] != "fp4" else 0)) * 2 * H * I * wbytes
     dom_ms = float(stage_ms[3])
+    # DRAM traffic of the gate/up launch: dram__bytes_read + dram__bytes_write from the ncu capture of a small case
+    # (32 experts' weights, 16 tokens; profiles/), which grows in proportion to the experts streamed
+    per_expert = {"bf16": (1.074722e9 + 4.153856e6) / 32, "fp8": (537.667072e6 + 3.838208e6) / 32}.get(dims["fmt"])
+    traffic = per_expert * (active + S) * (H * I) / (4096 * 2048) if per_expert else None
     layer_bytes = synth.algorithmic_bytes(dims, active)
     roofline = {
         "bound": "hbm", "kernel": f"grouped_gemm_{dims['fmt']}_kernel<gate_up> (routed" + (" + always-on experts)" if dims["fmt"] != "fp4" else " experts)"),
         "achieved": gate_up_bytes / (dom_ms * 1e-3) / 1e9, "peak": peak, "unit": "GB/s", "peak_kind": peak_kind,
-        "frac": gate_up_bytes / (dom_ms * 1e-3) / 1e9 / peak, "traffic": None,
+        "frac": gate_up_bytes / (dom_ms * 1e-3) / 1e9 / peak, "traffic": traffic,
+        "traffic_source": "ncu capture of a 32-expert case of the same kernel, scaled by experts streamed (profiles/)" if traffic else None,
         "algorithmic_bytes_per_launch": gate_up_bytes, "ms_per_launch": dom_ms,
         "layer": {"algorithmic_bytes": layer_bytes, "achieved": layer_bytes / (ms / args.steps * 1e-3) / 1e9,
                   "frac": layer_bytes / (ms / args.steps * 1e-3) / 1e9 / peak},

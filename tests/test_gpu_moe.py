@@ -270,3 +270,33 @@ def test_forward_fp4_ragged_shapes(oracle, T, S, E, K, H, I):
     print(f"fp4 T={T}: rel-L2 {rel:.3e}")
     assert rel <= FP8_TOL, rel
     assert torch.equal(out, gu.forward(dims, d)), "FP4 forward is not deterministic"
+
+
+# ---- prefill-sized batches: many tokens per expert -> the N = 256 prefill kernel for FP8 ------------------------------
+@pytest.mark.parametrize("T,S,E,K,H,I", [(600, 1, 4, 2, 512, 256), (1500, 0, 8, 3, 256, 384), (130, 1, 2, 1, 256, 128)])
+def test_forward_fp8_many_tokens_per_expert(oracle, T, S, E, K, H, I):
+    dims = _dims(T=T, S=S, E=E, K=K, H=H, I=I, fmt="fp8")
+    d = synth.make_inputs(dims, seed=T + 3, device="cuda")
+    out = gu.forward(dims, d)
+    ref = gu.oracle_forward(oracle, dims, d)
+    rel = synth.rel_l2(gu.bf16_to_f32(out), synth.bf16_bits_to_f32(ref["out"]))
+    print(f"fp8 prefill-shaped T={T}: rel-L2 {rel:.3e}")
+    assert rel <= FP8_TOL, rel
+    assert torch.equal(out, gu.forward(dims, d))
+
+
+def test_forward_prefill_fp8_full_size_subset(oracle):
+    """Config 'prefill_fp8' (T=8192, H=4096, E=256, k=6, shared expert, I=2048, Zipf router bias) at full size: expert ids
+    of all tokens bit-exact, outputs on a seeded subset of tokens."""
+    dims = synth.CONFIGS["prefill_fp8"]
+    d = synth.make_inputs(dims, seed=0, device="cuda")
+    out = gu.forward(dims, d)
+    sub = np.sort(np.random.default_rng(2).choice(dims["T"], 6, replace=False)).astype(np.int32)
+    ref = gu.oracle_forward(oracle, dims, d, token_subset=sub, threads=os.cpu_count() or 8)
+    logits, ids, w = gu.route(dims, d)
+    assert np.array_equal(ids.cpu().numpy(), ref["topk_ids"])
+    counts = ref["counts"]
+    print(f"prefill loads: min {counts.min()} max {counts.max()} mean {counts.mean():.0f}")
+    rel = synth.rel_l2(gu.bf16_to_f32(out)[sub], synth.bf16_bits_to_f32(ref["out"])[sub])
+    print(f"prefill_fp8: rel-L2 {rel:.3e}")
+    assert rel <= FP8_TOL, rel

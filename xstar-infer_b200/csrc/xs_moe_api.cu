@@ -14,6 +14,7 @@
 
 #include "xs_grouped_gemm.cuh"
 #include "xs_grouped_gemm_fp4.cuh"
+#include "xs_prefill_fp8.cuh"
 #include "xs_permute.cuh"
 #include "xs_route.cuh"
 
@@ -154,16 +155,23 @@ int check_cfg(const XsMoeConfig *c)
     return 0;
 }
 
-int pick_n_tile(long rows, int groups, int fmt)
+// Rows per token tile.  bf16: 16..128 tokens as the N of a 128-weight-row MMA.  FP8/FP4: up to 64 in that shape (the
+// FP8 epilogue keeps one f32 accumulator per token column in registers); FP8 batches with many tokens per expert use
+// the prefill kernel instead, whose tiles are 128 tokens as the M of an N = 256 MMA (needs hidden % 256 == 0).
+int pick_n_tile(long rows, int groups, int fmt, int hidden)
 {
     const long avg = groups > 0 ? (rows + groups - 1) / groups : rows;
     if (avg <= 8)
         return 16;
     if (avg <= 20)
         return 32;
-    if (avg <= 48 || fmt != XS_MOE_BF16) // the FP8 epilogue keeps one f32 accumulator per token column in registers
+    if (avg <= 48)
         return 64;
-    return 128;
+    if (fmt == XS_MOE_BF16)
+        return 128;
+    if (fmt == XS_MOE_FP8_BLOCK128 && hidden % 256 == 0)
+        return 128;
+    return 64;
 }
 
 // ---- workspace plans -----------------------------------------------------------------------------------
@@ -174,10 +182,10 @@ struct GroupedPlan {
     size_t off_tile_expert = 0, off_tile_row0 = 0, off_num_tiles = 0, off_act = 0, off_act_scale = 0, bytes = 0;
 };
 
-GroupedPlan plan_grouped(int max_rows, int routed_rows, int routed_groups, int segments, int I, int fmt)
+GroupedPlan plan_grouped(int max_rows, int routed_rows, int routed_groups, int segments, int I, int fmt, int H)
 {
     GroupedPlan p;
-    p.n_tile = pick_n_tile(routed_rows, routed_groups, fmt);
+    p.n_tile = pick_n_tile(routed_rows, routed_groups, fmt, H);
     p.max_tiles = max_rows / p.n_tile + segments + 1;
     size_t o = 0;
     p.off_tile_expert = o; o = align_up(o + sizeof(int32_t) * p.max_tiles, 256);
@@ -228,13 +236,14 @@ ForwardPlan plan_forward(const XsMoeConfig *c)
     p.off_rows_scale = take(fp8 ? (T * K + Sm * T) * (H / 128) * 4 : (fp4 ? T * K * (H / 32) : 0));
     p.off_y = take((T * K + S * T) * H * 4);
     p.grouped = plan_grouped(static_cast<int>(T * K + Sm * T), static_cast<int>(T * K), static_cast<int>(E), static_cast<int>(E + Sm),
-                             static_cast<int>(I), c->routed_format);
+                             static_cast<int>(I), c->routed_format, static_cast<int>(H));
     p.off_grouped = take(p.grouped.bytes);
     if (fp4 && S) {
         p.off_sh_rows = take(T * H);
         p.off_sh_scale = take(T * (H / 128) * 4);
         p.off_sh_offsets = take(8);
-        p.sh_grouped = plan_grouped(static_cast<int>(T), static_cast<int>(T), 1, 1, static_cast<int>(I), XS_MOE_FP8_BLOCK128);
+        p.sh_grouped = plan_grouped(static_cast<int>(T), static_cast<int>(T), 1, 1, static_cast<int>(I), XS_MOE_FP8_BLOCK128,
+                                    static_cast<int>(H));
         p.off_sh_grouped = take(p.sh_grouped.bytes);
     }
     p.bytes = o;
@@ -424,6 +433,37 @@ int launch_gemm_fp8(int n_tile, const CUtensorMap &tw, const CUtensorMap &tw2, c
     return fail(XS_MOE_ERR_INVALID_ARG, "internal: bad token tile %d for FP8", n_tile);
 }
 
+template <bool GATE_UP>
+int launch_prefill_fp8(const CUtensorMap &tw, const CUtensorMap &tw2, const CUtensorMap &tx, const int32_t *offsets, xs::TileTable tt,
+                       xs::Fp8Scales sc, int groups, int w_rows, int n_out, int K, void *out, int32_t *status, int max_work,
+                       cudaStream_t st)
+{
+    DeviceInfo di;
+    if (int rc = device_info(&di))
+        return rc;
+    int stages = (di.max_smem - 1024 - xs::kPfTailBytes) / xs::kPfStageBytes;
+    if (stages > 6)
+        stages = 6;
+    if (stages < 2)
+        return fail(XS_MOE_ERR_DEVICE, "not enough shared memory for the GEMM pipeline");
+    const int smem = stages * xs::kPfStageBytes + 1024 + xs::kPfTailBytes;
+    auto kern = xs::prefill_gemm_fp8_kernel<GATE_UP>;
+    static bool configured[64] = {};
+    int dev = 0;
+    XS_CUDA(cudaGetDevice(&dev));
+    if (dev >= 64 || !configured[dev]) {
+        XS_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        if (dev < 64)
+            configured[dev] = true;
+    }
+    int grid = di.sms < max_work ? di.sms : max_work;
+    if (grid < 1)
+        grid = 1;
+    kern<<<grid, xs::kPfThreads, smem, st>>>(tw, tw2, tx, offsets, tt, sc, groups, w_rows, n_out, K, out, status, stages);
+    XS_CUDA(cudaGetLastError());
+    return 0;
+}
+
 constexpr int kFp4TailBytes = 512 + 8 * xs::kFp4SfBytesPerStage; // barriers + per-stage scale blocks
 
 template <int N_TILE, bool GATE_UP>
@@ -605,6 +645,18 @@ int run_grouped(const GroupedArgs &a, cudaStream_t st, cudaEvent_t mid = nullptr
         return launch_gemm<false>(a.gp.n_tile, t_wd, t_wd2, t_act, a.offsets, tt, groups, H, H, I, a.y, a.status, work_d, st);
     }
     float *act_scale = reinterpret_cast<float *>(a.scratch + a.gp.off_act_scale);
+    if (a.gp.n_tile == 128) {
+        // many tokens per expert: tokens as the M of N = 256 MMAs (prefill kernel); the maps above already use 128-row boxes
+        xs::Fp8Scales p1{static_cast<const float *>(a.gu_scale), static_cast<const float *>(a.gu2_scale), a.row_scale, act_scale};
+        if (int rc = launch_prefill_fp8<true>(t_wgu, t_wgu2, t_x, a.offsets, tt, p1, groups, 2 * I, I, H, act, a.status,
+                                              a.gp.max_tiles * (I / 128), st))
+            return rc;
+        if (mid)
+            XS_CUDA(cudaEventRecord(mid, st));
+        xs::Fp8Scales p2{static_cast<const float *>(a.dw_scale), static_cast<const float *>(a.dw2_scale), act_scale, nullptr};
+        return launch_prefill_fp8<false>(t_wd, t_wd2, t_act, a.offsets, tt, p2, groups, H, H, I, a.y, a.status,
+                                         a.gp.max_tiles * (H / 256), st);
+    }
     xs::Fp8Scales s1{static_cast<const float *>(a.gu_scale), static_cast<const float *>(a.gu2_scale), a.row_scale, act_scale};
     if (int rc = launch_gemm_fp8<true>(a.gp.n_tile, t_wgu, t_wgu2, t_x, a.offsets, tt, s1, groups, 2 * I, I, H, act, a.status, work_gu, st))
         return rc;
@@ -756,7 +808,8 @@ int xs_moe_permute(const XsMoeConfig *cfg, const int32_t *ids, int32_t *counts, 
 
 static GroupedPlan plan_grouped_stage(const XsMoeConfig *cfg, int max_rows)
 {
-    return plan_grouped(max_rows, max_rows, cfg->local_expert_count, cfg->local_expert_count, cfg->intermediate, cfg->routed_format);
+    return plan_grouped(max_rows, max_rows, cfg->local_expert_count, cfg->local_expert_count, cfg->intermediate, cfg->routed_format,
+                        cfg->hidden);
 }
 
 int xs_moe_grouped_mlp_workspace_bytes(const XsMoeConfig *cfg, int32_t max_rows, size_t *bytes)
