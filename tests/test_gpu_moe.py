@@ -300,3 +300,15 @@ def test_forward_prefill_fp8_full_size_subset(oracle):
     rel = synth.rel_l2(gu.bf16_to_f32(out)[sub], synth.bf16_bits_to_f32(ref["out"])[sub])
     print(f"prefill_fp8: rel-L2 {rel:.3e}")
     assert rel <= FP8_TOL, rel
+
+
+@pytest.mark.parametrize("T,S,E,K,H,I", [(600, 1, 4, 2, 512, 256), (1500, 0, 8, 3, 256, 384), (130, 0, 2, 1, 256, 128)])
+def test_forward_fp4_many_tokens_per_expert(oracle, T, S, E, K, H, I):
+    dims = _dims(T=T, S=S, E=E, K=K, H=H, I=I, fmt="fp4")
+    d = synth.make_inputs(dims, seed=T + 4, device="cuda")
+    out = gu.forward(dims, d)
+    ref = gu.oracle_forward(oracle, dims, d)
+    rel = synth.rel_l2(gu.bf16_to_f32(out), synth.bf16_bits_to_f32(ref["out"]))
+    print(f"fp4 prefill-shaped T={T}: rel-L2 {rel:.3e}")
+    assert rel <= FP8_TOL, rel
+    assert torch.equal(out, gu.forward(dims, d))

@@ -34,6 +34,14 @@ __device__ __forceinline__ float silu_f32(float x)
     return x * s;
 }
 
+// SiLU for the quantised (FP8 / FP4) paths, where the result is rounded to e4m3 right away: hardware exp2-based
+// exponential and reciprocal (a few ulp from the IEEE form, far below half an e4m3 step).  exp(-x) overflowing to
+// +inf for very negative x gives x * 0 = -0, the right limit.
+__device__ __forceinline__ float silu_fast(float x)
+{
+    return x * __frcp_rn(1.0f + __expf(-x));
+}
+
 struct GemmSmemLayout {
     int stage_bytes;
     int stages;
@@ -586,7 +594,7 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
                 float *ax = amax_x + (it & 1) * 4 * N_TILE;
 #pragma unroll
                 for (int c = 0; c < N_TILE; c++) {
-                    const float a = silu_f32(acc_g[c]) * acc_u[c];
+                    const float a = silu_fast(acc_g[c]) * acc_u[c];
                     acc_g[c] = a;
                     float m = fabsf(a);
 #pragma unroll

@@ -328,7 +328,7 @@ grouped_gemm_fp4_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
 #pragma unroll
                     for (int c = 0; c < 16; c++) {
                         // the 32 features of this warp are one MX group of the token: amax by shuffles
-                        const float a = silu_f32(__uint_as_float(g[c])) * __uint_as_float(u[c]);
+                        const float a = silu_fast(__uint_as_float(g[c])) * __uint_as_float(u[c]);
                         float m = fabsf(a);
 #pragma unroll
                         for (int o = 16; o > 0; o >>= 1)

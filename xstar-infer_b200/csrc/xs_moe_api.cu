@@ -15,6 +15,7 @@
 #include "xs_grouped_gemm.cuh"
 #include "xs_grouped_gemm_fp4.cuh"
 #include "xs_prefill_fp8.cuh"
+#include "xs_prefill_fp4.cuh"
 #include "xs_permute.cuh"
 #include "xs_route.cuh"
 
@@ -169,7 +170,7 @@ int pick_n_tile(long rows, int groups, int fmt, int hidden)
         return 64;
     if (fmt == XS_MOE_BF16)
         return 128;
-    if (fmt == XS_MOE_FP8_BLOCK128 && hidden % 256 == 0)
+    if ((fmt == XS_MOE_FP8_BLOCK128 || fmt == XS_MOE_FP4_MX32) && hidden % 256 == 0)
         return 128;
     return 64;
 }
@@ -509,6 +510,36 @@ int launch_gemm_fp4(int n_tile, const CUtensorMap &tw, const CUtensorMap &tx, co
     return fail(XS_MOE_ERR_INVALID_ARG, "internal: bad token tile %d for FP4", n_tile);
 }
 
+template <bool GATE_UP>
+int launch_prefill_fp4(const CUtensorMap &tw, const CUtensorMap &tx, const int32_t *offsets, xs::TileTable tt, xs::MxScales sc, int w_rows,
+                       int n_out, int K, void *out, int32_t *status, int max_work, cudaStream_t st)
+{
+    DeviceInfo di;
+    if (int rc = device_info(&di))
+        return rc;
+    int stages = (di.max_smem - 1024 - xs::kPf4TailBytes) / xs::kPfStageBytes;
+    if (stages > 6)
+        stages = 6;
+    if (stages < 2)
+        return fail(XS_MOE_ERR_DEVICE, "not enough shared memory for the GEMM pipeline");
+    const int smem = stages * xs::kPfStageBytes + 1024 + xs::kPf4TailBytes;
+    auto kern = xs::prefill_gemm_fp4_kernel<GATE_UP>;
+    static bool configured[64] = {};
+    int dev = 0;
+    XS_CUDA(cudaGetDevice(&dev));
+    if (dev >= 64 || !configured[dev]) {
+        XS_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        if (dev < 64)
+            configured[dev] = true;
+    }
+    int grid = di.sms < max_work ? di.sms : max_work;
+    if (grid < 1)
+        grid = 1;
+    kern<<<grid, xs::kPf4Threads, smem, st>>>(tw, tx, offsets, tt, sc, w_rows, n_out, K, out, status, stages);
+    XS_CUDA(cudaGetLastError());
+    return 0;
+}
+
 // Packed e2m1 matrix (rows, K elements = K/2 bytes per row): the TMA unit expands each 16 codes (8 bytes) to a 16-byte
 // shared-memory piece, the form the f8f6f4 MMA kinds read.  Box = 128 elements x box_rows, 128-byte swizzle.
 int make_tmap_fp4(CUtensorMap *m, const void *base, uint64_t rows, uint64_t k_elems, uint32_t box_rows)
@@ -605,6 +636,16 @@ int run_grouped(const GroupedArgs &a, cudaStream_t st, cudaEvent_t mid = nullptr
         if (int rc = make_tmap_2d(&t_act, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, act, a.max_rows, I, a.gp.n_tile, xs::kBlockK8))
             return rc;
         uint8_t *act_scale = a.scratch + a.gp.off_act_scale;
+        if (a.gp.n_tile == 128) {
+            // many tokens per expert: tokens as the M of N = 256 block-scaled MMAs
+            xs::MxScales p1{static_cast<const uint8_t *>(a.gu_scale), reinterpret_cast<const uint8_t *>(a.row_scale), act_scale, a.max_rows};
+            if (int rc = launch_prefill_fp4<true>(t_wgu, t_x, a.offsets, tt, p1, 2 * I, I, H, act, a.status, a.gp.max_tiles * (I / 128), st))
+                return rc;
+            if (mid)
+                XS_CUDA(cudaEventRecord(mid, st));
+            xs::MxScales p2{static_cast<const uint8_t *>(a.dw_scale), act_scale, nullptr, a.max_rows};
+            return launch_prefill_fp4<false>(t_wd, t_act, a.offsets, tt, p2, H, H, I, a.y, a.status, a.gp.max_tiles * (H / 256), st);
+        }
         xs::MxScales s1{static_cast<const uint8_t *>(a.gu_scale), reinterpret_cast<const uint8_t *>(a.row_scale), act_scale, a.max_rows};
         if (int rc = launch_gemm_fp4<true>(a.gp.n_tile, t_wgu, t_x, a.offsets, tt, s1, 2 * I, I, H, act, a.status,
                                            a.gp.max_tiles * (I / xs::kTileM), st))

@@ -53,6 +53,10 @@ prefill_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
+    // role profile (see xs_moe_debug_counters): cycles each role spent blocked, summed over CTAs
+    unsigned long long *prof = reinterpret_cast<unsigned long long *>(status + 16);
+    const long long t_start = clock64();
+    long long w0 = 0, w1 = 0;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < stages; s++) {
@@ -100,7 +104,7 @@ prefill_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
                 const int wbase = (e < groups ? e * w_rows_per_expert : 0) + nt * N_PER_TILE;
                 const int wrow2 = GATE_UP ? wbase + n_out : wbase + 128; // up block of the same features | next 128 rows
                 for (int kb = 0; kb < num_kb; kb++) {
-                    if (!mbar_wait(&empty[stage], phase ^ 1, abort_flag)) {
+                    if (!mbar_wait_t(&empty[stage], phase ^ 1, abort_flag, w0)) {
                         ok = false;
                         break;
                     }
@@ -119,6 +123,9 @@ prefill_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
                 *abort_flag = 1;
                 atomicOr(status, kStatusWaitTimeout);
             }
+            atomicAdd(&prof[0], static_cast<unsigned long long>(w0));
+            atomicAdd(&prof[6], static_cast<unsigned long long>(clock64() - t_start));
+            atomicAdd(&prof[7], 1ull);
         }
     } else if (warp == 1) {
         if (lane == 0) {
@@ -129,8 +136,8 @@ prefill_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
             for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x) {
                 for (int kb = 0; kb < num_kb; kb++, g_kb++) {
                     const int buf = g_kb & 1;
-                    if (!mbar_wait(&full[stage], phase, abort_flag) ||
-                        !mbar_wait(&tmem_empty[buf], ((g_kb >> 1) & 1) ^ 1, abort_flag)) {
+                    if (!mbar_wait_t(&full[stage], phase, abort_flag, w0) ||
+                        !mbar_wait_t(&tmem_empty[buf], ((g_kb >> 1) & 1) ^ 1, abort_flag, w1)) {
                         ok = false;
                         break;
                     }
@@ -154,6 +161,8 @@ prefill_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
                 *abort_flag = 1;
                 atomicOr(status, kStatusWaitTimeout);
             }
+            atomicAdd(&prof[1], static_cast<unsigned long long>(w0));
+            atomicAdd(&prof[3], static_cast<unsigned long long>(w1));
         }
     } else {
 #include "xs_prefill_fp8_epilogue.inl"

@@ -31,22 +31,27 @@
             const float sx = __ldg(xs_row + kb);
             const float sa = __fmul_rn(sx, __ldg(ws_a + kb));
             const float sb = __fmul_rn(sx, __ldg(ws_b + kb));
-            if (!mbar_wait(&tmem_full[buf], (g_kb >> 1) & 1, abort_flag)) {
+            if (!mbar_wait_t(&tmem_full[buf], (g_kb >> 1) & 1, abort_flag, w0)) {
                 ok = false;
                 break;
             }
             tc_fence_after();
             const uint32_t t0 = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(buf * kPfCols);
+            // four rounds of 2 x 16 columns; the loads of round i+1 are in flight while round i is accumulated
+            uint32_t pa[2][16], pb[2][16];
+            tmem_ld16(t0 + col_a, pa[0]);
+            tmem_ld16(t0 + col_b, pb[0]);
 #pragma unroll
-            for (int c0 = 0; c0 < 64; c0 += 16) {
-                uint32_t pa[16], pb[16];
-                tmem_ld16(t0 + col_a + c0, pa);
-                tmem_ld16(t0 + col_b + c0, pb);
-                tmem_ld_wait();
+            for (int i = 0; i < 4; i++) {
+                tmem_ld_wait_for(pa[i & 1], pb[i & 1]);
+                if (i < 3) {
+                    tmem_ld16(t0 + col_a + (i + 1) * 16, pa[(i + 1) & 1]);
+                    tmem_ld16(t0 + col_b + (i + 1) * 16, pb[(i + 1) & 1]);
+                }
 #pragma unroll
                 for (int c = 0; c < 16; c++) {
-                    acc[c0 + c] = __fmaf_rn(__uint_as_float(pa[c]), sa, acc[c0 + c]);
-                    acc[64 + c0 + c] = __fmaf_rn(__uint_as_float(pb[c]), sb, acc[64 + c0 + c]);
+                    acc[i * 16 + c] = __fmaf_rn(__uint_as_float(pa[i & 1][c]), sa, acc[i * 16 + c]);
+                    acc[64 + i * 16 + c] = __fmaf_rn(__uint_as_float(pb[i & 1][c]), sb, acc[64 + i * 16 + c]);
                 }
             }
             tc_fence_before();
@@ -61,7 +66,7 @@
             float m = 0.0f;
 #pragma unroll
             for (int c = 0; c < 64; c++) {
-                acc[c] = silu_f32(acc[c]) * acc[64 + c];
+                acc[c] = silu_fast(acc[c]) * acc[64 + c];
                 m = fmaxf(m, fabsf(acc[c]));
             }
             float *ax = amax_x + (it & 1) * 256;
@@ -105,4 +110,6 @@
         *abort_flag = 1;
         atomicOr(status, kStatusWaitTimeout);
     }
+    if (warp == 2 && lane == 0)
+        atomicAdd(&prof[5], static_cast<unsigned long long>(w0));
 }
