@@ -274,8 +274,16 @@ int launch_logits(const XsMoeConfig *c, const void *x, const void *rw, float *lo
         dim3 grid((E + xs::kRdExperts - 1) / xs::kRdExperts, (T + xs::kRdTokens - 1) / xs::kRdTokens);
         xs::router_logits_decode_kernel<<<grid, xs::kRdThreads, 0, st>>>(xb, rwb, logits, T, H, E);
     } else {
-        dim3 grid((E + xs::kRtExperts - 1) / xs::kRtExperts, (T + xs::kRtTokens - 1) / xs::kRtTokens);
-        xs::router_logits_kernel<<<grid, xs::kRtThreads, 0, st>>>(xb, rwb, logits, T, H, E);
+        dim3 grid((E + xs::kRbExperts - 1) / xs::kRbExperts, (T + xs::kRbTokens - 1) / xs::kRbTokens);
+        static bool configured[64] = {};
+        int dev = 0;
+        XS_CUDA(cudaGetDevice(&dev));
+        if (dev >= 64 || !configured[dev]) {
+            XS_CUDA(cudaFuncSetAttribute(xs::router_logits_big_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, xs::kRbSmemBytes));
+            if (dev < 64)
+                configured[dev] = true;
+        }
+        xs::router_logits_big_kernel<<<grid, xs::kRbThreads, xs::kRbSmemBytes, st>>>(xb, rwb, logits, T, H, E);
     }
     XS_CUDA(cudaGetLastError());
     return 0;

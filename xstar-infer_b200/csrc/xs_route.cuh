@@ -99,6 +99,104 @@ router_logits_kernel(const __nv_bfloat16 *__restrict__ x, const __nv_bfloat16 *_
     }
 }
 
+// Large batches: 64 tokens x 128 experts per block, 4 x 8 outputs per thread.  Operands are widened to f32 while they are
+// staged in shared memory, so the inner loop is 12 16-byte shared loads per 128 FMAs and no conversions; k chunks of
+// 32 are double-buffered.  Same contract: every accumulator sees k = 0, 1, 2, ... in order.
+constexpr int kRbTokens = 64, kRbExperts = 128, kRbK = 32, kRbThreads = 256, kRbStride = kRbK + 4;
+constexpr int kRbSmemBytes = 2 * (kRbTokens + kRbExperts) * kRbStride * 4;
+__global__ void __launch_bounds__(kRbThreads, 2)
+router_logits_big_kernel(const __nv_bfloat16 *__restrict__ x, const __nv_bfloat16 *__restrict__ rw, float *__restrict__ logits,
+                         int T, int H, int E)
+{
+    extern __shared__ __align__(16) float rb_smem[]; // kRbSmemBytes
+    float (*xs)[kRbTokens][kRbStride] = reinterpret_cast<float (*)[kRbTokens][kRbStride]>(rb_smem);
+    float (*ws)[kRbExperts][kRbStride] = reinterpret_cast<float (*)[kRbExperts][kRbStride]>(rb_smem + 2 * kRbTokens * kRbStride);
+    const int tid = threadIdx.x;
+    const int tx = tid & 15, ty = tid >> 4;
+    const int t0 = blockIdx.y * kRbTokens, e0 = blockIdx.x * kRbExperts;
+    // staging: (64 + 128) rows x 32 k = 192 rows x 4 pieces of 8 bf16; 768 pieces over 256 threads = 3 each
+    uint4 stage_regs[3];
+    auto fetch = [&](int k0) {
+#pragma unroll
+        for (int i = 0; i < 3; i++) {
+            const int p = tid + i * kRbThreads;
+            const int r = p >> 2, c = (p & 3) * 8;
+            uint4 v = make_uint4(0, 0, 0, 0);
+            if (r < kRbTokens) {
+                if (t0 + r < T)
+                    v = __ldg(reinterpret_cast<const uint4 *>(x + static_cast<size_t>(t0 + r) * H + k0 + c));
+            } else if (e0 + r - kRbTokens < E) {
+                v = __ldg(reinterpret_cast<const uint4 *>(rw + static_cast<size_t>(e0 + r - kRbTokens) * H + k0 + c));
+            }
+            stage_regs[i] = v;
+        }
+    };
+    auto stash = [&](int buf) {
+#pragma unroll
+        for (int i = 0; i < 3; i++) {
+            const int p = tid + i * kRbThreads;
+            const int r = p >> 2, c = (p & 3) * 8;
+            const uint4 v = stage_regs[i];
+            float *dst = r < kRbTokens ? &xs[buf][r][c] : &ws[buf][r - kRbTokens][c];
+            *reinterpret_cast<float4 *>(dst) = make_float4(__uint_as_float(v.x << 16), __uint_as_float(v.x & 0xffff0000u),
+                                                            __uint_as_float(v.y << 16), __uint_as_float(v.y & 0xffff0000u));
+            *reinterpret_cast<float4 *>(dst + 4) = make_float4(__uint_as_float(v.z << 16), __uint_as_float(v.z & 0xffff0000u),
+                                                                __uint_as_float(v.w << 16), __uint_as_float(v.w & 0xffff0000u));
+        }
+    };
+    float acc[4][8];
+#pragma unroll
+    for (int i = 0; i < 4; i++)
+#pragma unroll
+        for (int j = 0; j < 8; j++)
+            acc[i][j] = 0.0f;
+    fetch(0);
+    stash(0);
+    __syncthreads();
+    const int chunks = H / kRbK;
+    for (int ch = 0; ch < chunks; ch++) {
+        const int buf = ch & 1;
+        if (ch + 1 < chunks)
+            fetch((ch + 1) * kRbK);
+#pragma unroll
+        for (int k = 0; k < kRbK; k += 4) {
+            float4 xv[4], wv[8];
+#pragma unroll
+            for (int i = 0; i < 4; i++)
+                xv[i] = *reinterpret_cast<const float4 *>(&xs[buf][ty + 16 * i][k]);
+#pragma unroll
+            for (int j = 0; j < 8; j++)
+                wv[j] = *reinterpret_cast<const float4 *>(&ws[buf][tx + 16 * j][k]);
+#pragma unroll
+            for (int i = 0; i < 4; i++)
+#pragma unroll
+                for (int j = 0; j < 8; j++) {
+                    float a = acc[i][j];
+                    a = __fmaf_rn(xv[i].x, wv[j].x, a);
+                    a = __fmaf_rn(xv[i].y, wv[j].y, a);
+                    a = __fmaf_rn(xv[i].z, wv[j].z, a);
+                    a = __fmaf_rn(xv[i].w, wv[j].w, a);
+                    acc[i][j] = a;
+                }
+        }
+        if (ch + 1 < chunks)
+            stash(buf ^ 1);
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        const int t = t0 + ty + 16 * i;
+        if (t >= T)
+            continue;
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            const int e = e0 + tx + 16 * j;
+            if (e < E)
+                logits[static_cast<size_t>(t) * E + e] = acc[i][j];
+        }
+    }
+}
+
 // Decode-sized batches.  Block = 8 experts x 32 tokens, one output per thread (warp = one expert, lanes = tokens),
 // so a batch of 128 tokens x 256 experts spreads over 128 SMs.  Operands arrive through a 4-stage cp.async
 // pipeline of 128-wide k chunks; inside a chunk each thread walks k upwards, 8 elements per 16-byte shared-memory
