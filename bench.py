@@ -430,6 +430,11 @@ def run_ours_ep(args, dims):
     mlp_ms = e0.elapsed_time(e1) / reps
     clocks = sampler.stop() if rank == 0 else None
     ops.check()
+    # phase times of one more step (CUDA events on the launching stream; host-side gaps show up in the phase that follows them)
+    marks = []
+    layer.forward(x, marks)
+    torch.cuda.synchronize()
+    phases = {marks[i][0]: marks[i - 1][1].elapsed_time(marks[i][1]) for i in range(1, len(marks))}
     active = int((np.diff(plan.offsets_local) > 0).sum())
     if rank == 0:
         peak, peak_kind = measured_peaks()
@@ -449,7 +454,8 @@ def run_ours_ep(args, dims):
             "roofline": {"bound": "hbm", "kernel": "grouped expert MLP of rank 0 (tile table + gate/up + down GEMM launches)",
                          "achieved": mlp_bytes / (mlp_ms * 1e-3) / 1e9, "peak": peak, "unit": "GB/s", "peak_kind": peak_kind,
                          "frac": mlp_bytes / (mlp_ms * 1e-3) / 1e9 / peak, "traffic": None, "algorithmic_bytes_per_launch": mlp_bytes,
-                         "ms_per_launch": mlp_ms, "rows_received_rank0": plan.n_recv, "active_local_experts": active},
+                         "ms_per_launch": mlp_ms, "rows_received_rank0": plan.n_recv, "active_local_experts": active,
+                         "phase_ms_rank0": phases},
             "cpu_baseline": None, "clocks": clocks,
         }
         print(json.dumps(line), flush=True)

@@ -197,6 +197,14 @@ int xs_moe_gather_rows(const void *src_dev, const int32_t *index_dev, void *dst_
 int xs_moe_combine(const XsMoeConfig *cfg, const float *y_dev, const int32_t *inv_dev, const float *topk_w_dev,
                    const float *shared_dev, void *out_dev, void *stream);
 
+/* Expert-parallel return trip with bf16 rows on the wire (used for the quantised formats, whose tolerance allows
+ * it): gather + round f32 expert outputs into arrival order, and the combine that reads bf16 rows.  Same contracts as
+ * xs_moe_gather_rows / xs_moe_combine otherwise (add_launch, xstar_cpp/include/ops/add.h:38). */
+int xs_moe_gather_rows_f32_to_bf16(const float *src_dev, const int32_t *index_dev, void *dst_bf16_dev, int32_t n_rows,
+                                   int32_t cols, void *stream);
+int xs_moe_combine_bf16_rows(const XsMoeConfig *cfg, const void *y_bf16_dev, const int32_t *inv_dev,
+                             const float *topk_w_dev, const float *shared_dev, void *out_dev, void *stream);
+
 /* Role profile of the warp-specialised GEMM kernels that ran on this workspace since the last call: eight
  * 64-bit cycle counters summed over CTAs (0 producer blocked on a free stage, 1 MMA issuer blocked on operands,
  * 2 on scales, 3 on a free accumulator, 4 scale writers blocked on a free slot, 5 epilogue blocked on an

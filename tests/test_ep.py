@@ -77,6 +77,9 @@ class OracleOps:
     def gather(self, src, index):
         return src.index_select(0, index.long())
 
+    def return_rows(self, y_grouped, index):
+        return self.gather(y_grouped, index)
+
     def grouped_mlp(self, payload, offsets_local, n_rows):
         rows = payload[0]
         y = torch.zeros((n_rows, self.H), dtype=torch.float32)

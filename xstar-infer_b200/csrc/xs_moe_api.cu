@@ -955,8 +955,39 @@ int xs_moe_combine(const XsMoeConfig *cfg, const float *y, const int32_t *inv, c
     if (T == 0)
         return 0;
     int gy = (H + 1023) / 1024;
-    xs::combine_kernel<<<dim3(T, gy), 128, 0, static_cast<cudaStream_t>(stream)>>>(y, inv, topk_w, shared,
-                                                                                  static_cast<__nv_bfloat16 *>(out), T, H, K);
+    xs::combine_kernel<float><<<dim3(T, gy), 128, 0, static_cast<cudaStream_t>(stream)>>>(y, inv, topk_w, shared,
+                                                                                         static_cast<__nv_bfloat16 *>(out), T, H, K);
+    XS_CUDA(cudaGetLastError());
+    return 0;
+}
+
+int xs_moe_combine_bf16_rows(const XsMoeConfig *cfg, const void *y_bf16, const int32_t *inv, const float *topk_w, const float *shared,
+                             void *out, void *stream)
+{
+    if (int rc = check_cfg(cfg))
+        return rc;
+    if (!y_bf16 || !inv || !topk_w || !out)
+        return fail(XS_MOE_ERR_INVALID_ARG, "null tensor pointer");
+    const int T = cfg->num_tokens, H = cfg->hidden, K = cfg->top_k;
+    if (T == 0)
+        return 0;
+    int gy = (H + 1023) / 1024;
+    xs::combine_kernel<__nv_bfloat16><<<dim3(T, gy), 128, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const __nv_bfloat16 *>(y_bf16), inv, topk_w, shared, static_cast<__nv_bfloat16 *>(out), T, H, K);
+    XS_CUDA(cudaGetLastError());
+    return 0;
+}
+
+int xs_moe_gather_rows_f32_to_bf16(const float *src, const int32_t *index, void *dst_bf16, int32_t n_rows, int32_t cols, void *stream)
+{
+    if (!src || !index || !dst_bf16)
+        return fail(XS_MOE_ERR_INVALID_ARG, "null tensor pointer");
+    if (n_rows < 0 || cols <= 0 || cols % 8 != 0)
+        return fail(XS_MOE_ERR_INVALID_ARG, "shape mismatch: columns must be a positive multiple of 8");
+    if (n_rows == 0)
+        return 0;
+    xs::gather_rows_f32_to_bf16_kernel<<<n_rows, 256, 0, static_cast<cudaStream_t>(stream)>>>(src, index, static_cast<__nv_bfloat16 *>(dst_bf16),
+                                                                                             n_rows, cols);
     XS_CUDA(cudaGetLastError());
     return 0;
 }

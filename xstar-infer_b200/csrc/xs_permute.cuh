@@ -345,9 +345,25 @@ gather_rows4_kernel(const uint32_t *__restrict__ x, const int32_t *__restrict__ 
 
 // out[t,h] = bf16( sum_j w[t,j] * y[inv[t,j], h]  (+ shared[t,h]) ), slot order, shared last; separate
 // multiply and add (no contraction) so the sum is the same sequence of IEEE operations as the CPU's.
-// Eight outputs per thread: two 16-byte loads per row, one 16-byte store.
+// Eight outputs per thread: 16-byte loads, one 16-byte store.  YB16: y rows are bf16 (expert-parallel return rows of
+// the quantised formats travel as bf16); the always-on expert's rows stay f32.
+__device__ __forceinline__ void load8(const float *p, float (&v)[8])
+{
+    const float4 a = reinterpret_cast<const float4 *>(p)[0], b = reinterpret_cast<const float4 *>(p)[1];
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+__device__ __forceinline__ void load8(const __nv_bfloat16 *p, float (&v)[8])
+{
+    const uint4 r = *reinterpret_cast<const uint4 *>(p);
+    v[0] = __uint_as_float(r.x << 16); v[1] = __uint_as_float(r.x & 0xffff0000u);
+    v[2] = __uint_as_float(r.y << 16); v[3] = __uint_as_float(r.y & 0xffff0000u);
+    v[4] = __uint_as_float(r.z << 16); v[5] = __uint_as_float(r.z & 0xffff0000u);
+    v[6] = __uint_as_float(r.w << 16); v[7] = __uint_as_float(r.w & 0xffff0000u);
+}
+
+template <typename YT>
 __global__ void __launch_bounds__(128)
-combine_kernel(const float *__restrict__ y, const int32_t *__restrict__ inv, const float *__restrict__ topk_w,
+combine_kernel(const YT *__restrict__ y, const int32_t *__restrict__ inv, const float *__restrict__ topk_w,
                const float *__restrict__ shared, __nv_bfloat16 *__restrict__ out, int T, int H, int K)
 {
     const int t = blockIdx.x;
@@ -366,31 +382,46 @@ combine_kernel(const float *__restrict__ y, const int32_t *__restrict__ inv, con
         for (int i = 0; i < 8; i++)
             acc[i] = 0.0f;
         for (int j = 0; j < K; j++) {
-            const float4 *p = reinterpret_cast<const float4 *>(y + static_cast<size_t>(s_row[j]) * H + h0);
-            const float4 a = p[0], b = p[1];
+            float v[8];
+            load8(y + static_cast<size_t>(s_row[j]) * H + h0, v);
             const float w = s_w[j];
-            acc[0] = __fadd_rn(acc[0], __fmul_rn(w, a.x));
-            acc[1] = __fadd_rn(acc[1], __fmul_rn(w, a.y));
-            acc[2] = __fadd_rn(acc[2], __fmul_rn(w, a.z));
-            acc[3] = __fadd_rn(acc[3], __fmul_rn(w, a.w));
-            acc[4] = __fadd_rn(acc[4], __fmul_rn(w, b.x));
-            acc[5] = __fadd_rn(acc[5], __fmul_rn(w, b.y));
-            acc[6] = __fadd_rn(acc[6], __fmul_rn(w, b.z));
-            acc[7] = __fadd_rn(acc[7], __fmul_rn(w, b.w));
+#pragma unroll
+            for (int i = 0; i < 8; i++)
+                acc[i] = __fadd_rn(acc[i], __fmul_rn(w, v[i]));
         }
         if (shared) {
-            const float4 *p = reinterpret_cast<const float4 *>(shared + static_cast<size_t>(t) * H + h0);
-            const float4 a = p[0], b = p[1];
-            acc[0] = __fadd_rn(acc[0], a.x); acc[1] = __fadd_rn(acc[1], a.y);
-            acc[2] = __fadd_rn(acc[2], a.z); acc[3] = __fadd_rn(acc[3], a.w);
-            acc[4] = __fadd_rn(acc[4], b.x); acc[5] = __fadd_rn(acc[5], b.y);
-            acc[6] = __fadd_rn(acc[6], b.z); acc[7] = __fadd_rn(acc[7], b.w);
+            float v[8];
+            load8(shared + static_cast<size_t>(t) * H + h0, v);
+#pragma unroll
+            for (int i = 0; i < 8; i++)
+                acc[i] = __fadd_rn(acc[i], v[i]);
         }
         __nv_bfloat162 o[4];
 #pragma unroll
         for (int i = 0; i < 4; i++)
             o[i] = __floats2bfloat162_rn(acc[2 * i], acc[2 * i + 1]);
         *reinterpret_cast<uint4 *>(out + static_cast<size_t>(t) * H + h0) = *reinterpret_cast<uint4 *>(o);
+    }
+}
+
+// dst[r] = bf16(src[index[r]]) for f32 rows of `cols` columns (cols % 8 == 0): gather and round in one pass
+__global__ void __launch_bounds__(256)
+gather_rows_f32_to_bf16_kernel(const float *__restrict__ src, const int32_t *__restrict__ index, __nv_bfloat16 *__restrict__ dst,
+                               int n_rows, int cols)
+{
+    const int row = blockIdx.x;
+    if (row >= n_rows)
+        return;
+    const float *s = src + static_cast<size_t>(index[row]) * cols;
+    __nv_bfloat16 *d = dst + static_cast<size_t>(row) * cols;
+    for (int c = threadIdx.x * 8; c < cols; c += blockDim.x * 8) {
+        float v[8];
+        load8(s + c, v);
+        __nv_bfloat162 o[4];
+#pragma unroll
+        for (int i = 0; i < 4; i++)
+            o[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+        *reinterpret_cast<uint4 *>(d + c) = *reinterpret_cast<uint4 *>(o);
     }
 }
 

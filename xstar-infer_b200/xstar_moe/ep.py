@@ -5,7 +5,7 @@
     -> all-gather of per-expert counts (the only host synchronisation: NCCL needs split sizes on the host)
     -> DISPATCH all-to-all of the permuted rows (payload: bf16 rows, or e4m3 codes + 1x128 f32 / 1x32 e8m0 scales)
     -> regroup received rows by local expert -> grouped expert MLPs -> rows back into arrival order
-    -> COMBINE all-to-all back (f32 rows) -> local weighted combine (+ the always-on expert, computed locally)
+    -> COMBINE all-to-all back (f32 rows; bf16 rows for the quantised formats) -> local weighted combine (+ the always-on expert, computed locally)
 
 Received rows are ordered by (source rank, expert, token) -- fixed by the data, not by arrival time -- so the
 result is reproducible and equals the single-device layer bit for bit (the combine still sums each token's k
@@ -46,20 +46,16 @@ class EpPlan:
         # grouped order: (local expert, source rank, token); arrival order: (source rank, local expert, token)
         per_expert = self.recv_counts.sum(0)
         self.offsets_local = np.concatenate([[0], np.cumsum(per_expert)]).astype(np.int32)
-        arrival_start = np.concatenate([[0], np.cumsum(self.recv_counts.reshape(-1))])[:-1].reshape(R, El)
-        grouped_start = self.offsets_local[:-1][None, :] + np.concatenate(
-            [np.zeros((1, El), np.int64), np.cumsum(self.recv_counts, 0)[:-1]], 0)
-        grouped_from_arrival = np.empty(self.n_recv, np.int32)  # grouped row g holds arrival row grouped_from_arrival[g]
-        for s in range(R):
-            for e in range(El):
-                n = int(self.recv_counts[s, e])
-                if n:
-                    g0, a0 = int(grouped_start[s, e]), int(arrival_start[s, e])
-                    grouped_from_arrival[g0:g0 + n] = np.arange(a0, a0 + n, dtype=np.int32)
-        self.grouped_from_arrival = grouped_from_arrival
+        # arrival rows carry (source, expert) labels in source-major order; a stable sort by expert gives the grouped order
+        expert_of_row = np.repeat(np.tile(np.arange(El, dtype=np.int32), R), self.recv_counts.reshape(-1))
+        self.grouped_from_arrival = np.argsort(expert_of_row, kind="stable").astype(np.int32)  # grouped row g <- arrival row
         arrival_from_grouped = np.empty(self.n_recv, np.int32)
-        arrival_from_grouped[grouped_from_arrival] = np.arange(self.n_recv, dtype=np.int32)
+        arrival_from_grouped[self.grouped_from_arrival] = np.arange(self.n_recv, dtype=np.int32)
         self.arrival_from_grouped = arrival_from_grouped
+
+    def packed_maps(self):
+        """offsets_local | grouped_from_arrival | arrival_from_grouped in one int32 array (one host-to-device copy)."""
+        return np.concatenate([self.offsets_local, self.grouped_from_arrival, self.arrival_from_grouped])
 
 
 def expert_owner(e, E, R):
@@ -165,10 +161,20 @@ class CudaOps:
             payload = self._payload(x, self.fmt_shared)
         return self._grouped(self.cfg_shared, self.w_shared, payload, self.shared_offsets, self.T)
 
+    def return_rows(self, y_grouped, index):
+        """Expert outputs back into arrival order for the return trip: f32 rows for bf16 experts (bit-identical to the
+        single-device layer), bf16 rows for the quantised formats (half the NVLink bytes, inside their tolerance)."""
+        if self.fmt == capi.BF16:
+            return self.gather(y_grouped, index)
+        n = index.numel()
+        dst = torch.empty((n, self.H), dtype=torch.bfloat16, device="cuda")
+        capi.check(self.L.xs_moe_gather_rows_f32_to_bf16(capi.ptr(y_grouped), capi.ptr(index), capi.ptr(dst), n, self.H, self._st()))
+        return dst
+
     def combine(self, y, inv, w, shared):
         out = torch.empty((self.T, self.H), dtype=torch.bfloat16, device="cuda")
-        capi.check(self.L.xs_moe_combine(C.byref(self.cfg_route), capi.ptr(y), capi.ptr(inv), capi.ptr(w), capi.ptr(shared),
-                                         capi.ptr(out), self._st()))
+        fn = self.L.xs_moe_combine if y.dtype == torch.float32 else self.L.xs_moe_combine_bf16_rows
+        capi.check(fn(C.byref(self.cfg_route), capi.ptr(y), capi.ptr(inv), capi.ptr(w), capi.ptr(shared), capi.ptr(out), self._st()))
         return out
 
     def check(self):
@@ -210,22 +216,41 @@ class ExpertParallelMoE:
         dist.all_to_all_single(out, t.contiguous(), [int(v) for v in out_splits], [int(v) for v in in_splits], group=self.group)
         return out
 
-    def forward(self, x):
+    def forward(self, x, marks=None):
+        """marks: optional list; when given, (name, cuda event) pairs are appended after each phase (device ops only)."""
         ops, K = self.ops, self.K
+
+        def mark(name):
+            if marks is not None:
+                ev = torch.cuda.Event(enable_timing=True)
+                ev.record()
+                marks.append((name, ev))
+
+        mark("start")
         ids, w = ops.route(x, self.router_w, self.router_bias)
         counts, offsets, perm, inv = ops.permute(ids)
+        mark("route+permute")
         payload = ops.payload(x)
         tok = torch.div(perm, K, rounding_mode="floor").to(torch.int32)
         send = [ops.gather(p, tok) for p in payload]  # rows in (expert, token) order = grouped by destination rank
+        mark("quantise+pack")
         plan = EpPlan(self._all_gather_counts(counts), self.rank)
         self.last_plan = plan
+        mark("counts exchange + plan (host sync)")
         recv = [self._a2a(s, plan.n_recv, plan.send_splits, plan.recv_splits) for s in send]
-        dev = x.device
-        g_from_a = torch.from_numpy(plan.grouped_from_arrival).to(dev)
-        a_from_g = torch.from_numpy(plan.arrival_from_grouped).to(dev)
+        mark("dispatch all-to-all")
+        maps = torch.from_numpy(plan.packed_maps()).to(x.device, non_blocking=True)
+        n_off = plan.El + 1
+        off_local, g_from_a, a_from_g = maps[:n_off], maps[n_off:n_off + plan.n_recv], maps[n_off + plan.n_recv:]
         grouped = [ops.gather(r, g_from_a) for r in recv]
-        y_grouped = ops.grouped_mlp(grouped, torch.from_numpy(plan.offsets_local).to(dev), plan.n_recv)
-        y_arrival = ops.gather(y_grouped, a_from_g)
+        mark("regroup")
+        y_grouped = ops.grouped_mlp(grouped, off_local, plan.n_recv)
+        mark("grouped expert MLP")
+        y_arrival = ops.return_rows(y_grouped, a_from_g)
         y_back = self._a2a(y_arrival, int(plan.send_splits.sum()), plan.recv_splits, plan.send_splits)
+        mark("combine all-to-all")
         shared = ops.shared_mlp(x, payload) if self.S else None
-        return ops.combine(y_back, inv, w, shared)
+        mark("always-on expert")
+        out = ops.combine(y_back, inv, w, shared)
+        mark("combine")
+        return out
