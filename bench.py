@@ -462,6 +462,28 @@ def run_ours_ep(args, dims):
     dist.destroy_process_group()
 
 
+def run_mma_rate():
+    """Table of tcgen05.mma rates (M = 128) by kind and N: cycles per instruction and whole-chip TFLOP/s."""
+    import torch
+
+    from xstar_moe import capi
+
+    torch.cuda.set_device(0)
+    L = capi.lib()
+    ws = torch.zeros(4096, dtype=torch.uint8, device="cuda")
+    rows = []
+    for kind, name in ((0, "bf16 K=16"), (1, "e4m3 K=32"), (2, "e4m3 x e2m1 block-scaled K=32")):
+        for n in (16, 64, 128, 256):
+            for chains in (1, 2) if n <= 128 else (1,):
+                cyc, iss, tf = C.c_double(), C.c_double(), C.c_double()
+                for _ in range(2):  # second run is warm
+                    capi.check(L.xs_moe_probe_mma_rate(kind, n, 4000, chains, capi.ptr(ws), ws.numel(), C.byref(cyc), C.byref(iss),
+                                                       C.byref(tf), None))
+                rows.append({"kind": name, "n": n, "chains": chains, "cycles_per_mma": round(cyc.value, 1),
+                             "issue_cycles_per_mma": round(iss.value, 1), "tflops": round(tf.value, 1)})
+    print(json.dumps({"mma_rate": rows}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -473,7 +495,10 @@ def main():
     ap.add_argument("--experts", type=int, default=None, help="override the routed expert count (small profiling cases)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--graph", default="auto", choices=["auto", "on", "off"], help="replay the step as a CUDA graph (auto: T <= 1024)")
+    ap.add_argument("--mma-rate", action="store_true", help="print the tensor-pipe rate probe table and exit")
     args = ap.parse_args()
+    if args.mma_rate:
+        return run_mma_rate()
 
     from xstar_moe import synth
 

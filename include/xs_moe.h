@@ -205,6 +205,15 @@ int xs_moe_gather_rows_f32_to_bf16(const float *src_dev, const int32_t *index_de
 int xs_moe_combine_bf16_rows(const XsMoeConfig *cfg, const void *y_bf16_dev, const int32_t *inv_dev,
                              const float *topk_w_dev, const float *shared_dev, void *out_dev, void *stream);
 
+/* Tensor-pipe rate probe (a tuning aid; no counterpart in the reference): every SM issues `iters` tcgen05.mma of
+ * M = 128, N = n (16..256) on zeroed shared memory, round-robin over `chains` independent TMEM accumulators
+ * (chains * n <= 480).  kind 0 = bf16 (K = 16), 1 = e4m3 (K = 32), 2 = block-scaled e4m3 x e2m1 (K = 32).
+ * Returns cycles per MMA until completion, cycles per MMA spent issuing, and whole-chip TFLOP/s by CUDA events.
+ * Needs a workspace of at least 256 bytes (status block).  Synchronises. */
+int xs_moe_probe_mma_rate(int32_t kind, int32_t n, int32_t iters, int32_t chains, void *workspace_dev,
+                          size_t workspace_bytes, double *cycles_per_mma, double *issue_cycles_per_mma, double *tflops,
+                          void *stream);
+
 /* Role profile of the warp-specialised GEMM kernels that ran on this workspace since the last call: eight
  * 64-bit cycle counters summed over CTAs (0 producer blocked on a free stage, 1 MMA issuer blocked on operands,
  * 2 on scales, 3 on a free accumulator, 4 scale writers blocked on a free slot, 5 epilogue blocked on an

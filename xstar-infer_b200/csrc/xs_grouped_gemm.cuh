@@ -390,6 +390,9 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
+    unsigned long long *prof = reinterpret_cast<unsigned long long *>(status + 16); // role profile, see xs_moe_debug_counters
+    const long long t_start = clock64();
+    long long w0 = 0, w1 = 0;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < stages; s++) {
@@ -437,7 +440,7 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
                 const CUtensorMap *tw = e < groups ? &tmap_w : &tmap_w2;
                 const int wrow = (e < groups ? e * w_rows_per_expert : 0) + f * kTileM;
                 for (int kb = 0; kb < num_kb; kb++) {
-                    if (!mbar_wait(&empty[stage], phase ^ 1, abort_flag)) {
+                    if (!mbar_wait_t(&empty[stage], phase ^ 1, abort_flag, w0)) {
                         ok = false;
                         break;
                     }
@@ -457,6 +460,9 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
                 *abort_flag = 1;
                 atomicOr(status, kStatusWaitTimeout);
             }
+            atomicAdd(&prof[0], static_cast<unsigned long long>(w0));
+            atomicAdd(&prof[6], static_cast<unsigned long long>(clock64() - t_start));
+            atomicAdd(&prof[7], 1ull);
         }
     } else if (warp == 1) {
         if (lane == 0) {
@@ -467,8 +473,8 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
             for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x) {
                 for (int kb = 0; kb < num_kb; kb++, g_kb++) {
                     const int buf = g_kb % NBUF;
-                    if (!mbar_wait(&full[stage], phase, abort_flag) ||
-                        !mbar_wait(&tmem_empty[buf], ((g_kb / NBUF) & 1) ^ 1, abort_flag)) {
+                    if (!mbar_wait_t(&full[stage], phase, abort_flag, w0) ||
+                        !mbar_wait_t(&tmem_empty[buf], ((g_kb / NBUF) & 1) ^ 1, abort_flag, w1)) {
                         ok = false;
                         break;
                     }
@@ -496,6 +502,8 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
                 *abort_flag = 1;
                 atomicOr(status, kStatusWaitTimeout);
             }
+            atomicAdd(&prof[1], static_cast<unsigned long long>(w0));
+            atomicAdd(&prof[3], static_cast<unsigned long long>(w1));
         }
     } else {
         const int q = warp & 3;
@@ -536,7 +544,7 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
                     if constexpr (GATE_UP)
                         sxw_u[c] = __fmul_rn(sx, swu);
                 }
-                if (!mbar_wait(&tmem_full[buf], (g_kb / NBUF) & 1, abort_flag)) {
+                if (!mbar_wait_t(&tmem_full[buf], (g_kb / NBUF) & 1, abort_flag, w0)) {
                     ok = false;
                     break;
                 }
@@ -632,6 +640,8 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
             *abort_flag = 1;
             atomicOr(status, kStatusWaitTimeout);
         }
+        if (warp == 2 && lane == 0)
+            atomicAdd(&prof[5], static_cast<unsigned long long>(w0));
     }
 
     __syncwarp();

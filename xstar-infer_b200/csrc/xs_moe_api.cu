@@ -16,6 +16,7 @@
 #include "xs_grouped_gemm_fp4.cuh"
 #include "xs_prefill_fp8.cuh"
 #include "xs_prefill_fp4.cuh"
+#include "xs_mma_rate.cuh"
 #include "xs_permute.cuh"
 #include "xs_route.cuh"
 
@@ -1180,6 +1181,58 @@ int xs_moe_check_flags(void *ws, void *stream)
         return fail(XS_MOE_ERR_INVALID_ARG, "a kernel met an out-of-range index (status word 0x%x)", flags);
     }
     return 0;
+}
+
+int xs_moe_probe_mma_rate(int32_t kind, int32_t n, int32_t iters, int32_t chains, void *ws, size_t ws_bytes, double *cycles_per_mma,
+                          double *issue_cycles_per_mma, double *tflops, void *stream)
+{
+    if (int rc = xs_moe_device_check())
+        return rc;
+    if (kind < 0 || kind > 2 || n < 16 || n > 256 || n % 16 != 0 || iters < 1 || chains < 1 || chains * n > 480)
+        return fail(XS_MOE_ERR_INVALID_ARG, "bad probe arguments");
+    if (int rc = check_workspace(ws, ws_bytes, kStatusBytes))
+        return rc;
+    DeviceInfo di;
+    if (int rc = device_info(&di))
+        return rc;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    uint8_t *b = static_cast<uint8_t *>(ws);
+    unsigned long long *ctr = reinterpret_cast<unsigned long long *>(b + 64);
+    XS_CUDA(cudaMemsetAsync(ctr, 0, 64, st));
+    const int smem = (128 + 256) * 128 + 1536 + 1024;
+    static bool configured[64] = {};
+    int dev = 0;
+    XS_CUDA(cudaGetDevice(&dev));
+    if (dev >= 64 || !configured[dev]) {
+        XS_CUDA(cudaFuncSetAttribute(xs::mma_rate_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        if (dev < 64)
+            configured[dev] = true;
+    }
+    cudaEvent_t e0, e1;
+    XS_CUDA(cudaEventCreate(&e0));
+    XS_CUDA(cudaEventCreate(&e1));
+    XS_CUDA(cudaEventRecord(e0, st));
+    xs::mma_rate_kernel<<<di.sms, 64, smem, st>>>(kind, n, iters, chains, ctr, reinterpret_cast<int32_t *>(b));
+    XS_CUDA(cudaGetLastError());
+    XS_CUDA(cudaEventRecord(e1, st));
+    XS_CUDA(cudaEventSynchronize(e1));
+    float ms = 0;
+    XS_CUDA(cudaEventElapsedTime(&ms, e0, e1));
+    cudaEventDestroy(e0);
+    cudaEventDestroy(e1);
+    unsigned long long h[3];
+    XS_CUDA(cudaMemcpy(h, ctr, sizeof(h), cudaMemcpyDeviceToHost));
+    XS_CUDA(cudaMemsetAsync(ctr, 0, 64, st));
+    const double ctas = h[2] ? static_cast<double>(h[2]) : 1.0;
+    if (cycles_per_mma)
+        *cycles_per_mma = static_cast<double>(h[0]) / ctas / iters;
+    if (issue_cycles_per_mma)
+        *issue_cycles_per_mma = static_cast<double>(h[1]) / ctas / iters;
+    if (tflops) {
+        const double k = kind == 0 ? 16.0 : 32.0;
+        *tflops = 2.0 * 128.0 * n * k * iters * di.sms / (ms * 1e-3) / 1e12;
+    }
+    return xs_moe_check_flags(ws, stream);
 }
 
 int xs_moe_debug_counters(void *ws, unsigned long long *out8, void *stream)
