@@ -20,7 +20,9 @@
         }
         tc_fence_after();
         const uint32_t t0 = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
-        if constexpr (GATE_UP) {
+        if (q * 32 >= nvalid) {
+            // no valid token in this warp's lane quarter (decode-sized segments): nothing to read or store
+        } else if constexpr (GATE_UP) {
             // features nt*128 + [0,128): gate in columns [0,128), up in [128,256); MX groups of 32 features = 2 chunks
             uint8_t *arow = static_cast<uint8_t *>(out) + static_cast<size_t>(row0 + r) * n_out + nt * 128;
             uint8_t *srow = sc.act_scale + static_cast<size_t>(row0 + r) * (n_out / 32) + nt * 4;
