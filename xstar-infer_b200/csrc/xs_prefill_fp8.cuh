@@ -9,21 +9,23 @@
 //
 // Block scales: each 128-deep k-block is accumulated on its own and promoted by the epilogue warps,
 //     acc += partial * (s_token[kb] * s_weight_block[kb]),
-// with one scalar token scale per TMEM lane and one scalar weight scale per 128 columns.  Two epilogue warpgroups share
-// the 256 columns (128 accumulator registers per thread): for gate/up each takes 64 gate + the matching 64 up columns
-// so that SwiGLU needs no exchange; only the 1x128 amax of the re-quantised activations crosses the warpgroups.
+// with one scalar token scale per TMEM lane and one scalar weight scale per 128 columns.  The promotion is bound by the
+// latency of the TMEM reads, so FOUR epilogue warpgroups (16 warps, 4 per scheduler) share the 256 columns, 64
+// accumulator registers per thread: for gate/up each takes 32 gate + the matching 32 up columns so that SwiGLU needs no
+// exchange; only the 1x128 amax of the re-quantised activations crosses the warpgroups.
 //
-// Warps: 0 TMA producer | 1 MMA issuer, TMEM owner | 2..5 epilogue group 0 | 6..9 epilogue group 1.
+// Warps: 0 TMA producer | 1 MMA issuer, TMEM owner | 2..17 epilogue (group = (warp - 2) / 4, lane quarter = warp % 4).
 #pragma once
 #include "xs_grouped_gemm.cuh"
 
 namespace xs {
 
-constexpr int kPfThreads = 320;
+constexpr int kPfGroups = 4;                     // epilogue warpgroups sharing the 256 columns
+constexpr int kPfThreads = 64 + kPfGroups * 128;
 constexpr int kPfTokens = 128;  // MMA M
 constexpr int kPfCols = 256;    // MMA N
 constexpr int kPfStageBytes = (kPfTokens + kPfCols) * kBlockK8; // 48 KB
-constexpr int kPfTailBytes = 3072; // barriers (512) + amax exchange (2 tile parities x 2 groups x 128 floats)
+constexpr int kPfTailBytes = 512 + 2 * kPfGroups * 128 * 4; // barriers + amax exchange (2 tile parities x groups x 128 floats)
 
 template <bool GATE_UP>
 __global__ void __launch_bounds__(kPfThreads, 1)
@@ -49,7 +51,7 @@ prefill_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
     uint64_t *xbar = tmem_empty + NBUF;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(xbar + 1);
     volatile uint32_t *abort_flag = tmem_slot + 1;
-    float *amax_x = reinterpret_cast<float *>(bars) + 128; // [2 tile parities][2 groups][128 rows]
+    float *amax_x = reinterpret_cast<float *>(bars) + 128; // [2 tile parities][groups][128 rows]
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -65,9 +67,9 @@ prefill_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
         }
         for (int b = 0; b < NBUF; b++) {
             mbar_init(&tmem_full[b], 1);
-            mbar_init(&tmem_empty[b], 8); // one arrival per epilogue warp
+            mbar_init(&tmem_empty[b], 4 * kPfGroups); // one arrival per epilogue warp
         }
-        mbar_init(xbar, 8);
+        mbar_init(xbar, 4 * kPfGroups);
         *abort_flag = 0;
         fence_mbar_init();
         prefetch_tmap(&tmap_w);

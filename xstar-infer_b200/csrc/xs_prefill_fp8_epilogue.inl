@@ -1,6 +1,8 @@
-// Epilogue of prefill_gemm_fp8_kernel (included inside the kernel body; warps 2..9).
-// Group g = 0/1, TMEM lane quarter q: this thread owns token row r = q*32 + lane of the tile and 128 of its 256 columns.
+// Epilogue of prefill_gemm_fp8_kernel (included inside the kernel body; warps 2..17).
+// Group g = 0..3, TMEM lane quarter q: this thread owns token row r = q*32 + lane of the tile and 64 of its 256 columns.
 {
+    constexpr int CPT = 256 / kPfGroups; // columns per thread (64)
+    constexpr int HALF = CPT / 2;        // gate/up: 32 gate + 32 up columns
     const int g = (warp - 2) >> 2;
     const int q = warp & 3;
     const int r = q * 32 + lane;
@@ -17,14 +19,15 @@
         const bool valid = r < nvalid;
         const float *xs_row = sc.x_scale + static_cast<size_t>(row0 + (valid ? r : 0)) * kbs;
         const float *wbase = e < groups ? sc.w_scale + static_cast<size_t>(e) * (w_rows_per_expert / 128) * kbs : sc.w_scale2;
-        const float *ws_a = wbase + static_cast<size_t>(GATE_UP ? nt : nt * 2 + g) * kbs;
+        // gate/up: gate block nt and up block nt; down: the 128-column block this group's columns fall into
+        const float *ws_a = wbase + static_cast<size_t>(GATE_UP ? nt : nt * 2 + (g * CPT) / 128) * kbs;
         const float *ws_b = GATE_UP ? wbase + static_cast<size_t>(n_out / 128 + nt) * kbs : ws_a;
-        // columns of this thread: gate/up -> gate [64g, 64g+64) and up [128+64g, 128+64g+64); down -> [128g, 128g+128)
-        const uint32_t col_a = GATE_UP ? 64u * g : 128u * g;
-        const uint32_t col_b = GATE_UP ? 128u + 64u * g : 128u * g + 64u;
-        float acc[128];
+        // columns of this thread: gate/up -> gate [32g, 32g+32) and up [128+32g, 128+32g+32); down -> [64g, 64g+64)
+        const uint32_t col_a = GATE_UP ? static_cast<uint32_t>(HALF * g) : static_cast<uint32_t>(CPT * g);
+        const uint32_t col_b = GATE_UP ? 128u + static_cast<uint32_t>(HALF * g) : static_cast<uint32_t>(CPT * g + HALF);
+        float acc[CPT];
 #pragma unroll
-        for (int c = 0; c < 128; c++)
+        for (int c = 0; c < CPT; c++)
             acc[c] = 0.0f;
         for (int kb = 0; kb < num_kb; kb++, g_kb++) {
             const int buf = g_kb & 1;
@@ -37,21 +40,16 @@
             }
             tc_fence_after();
             const uint32_t t0 = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(buf * kPfCols);
-            // four rounds of 2 x 16 columns; the loads of round i+1 are in flight while round i is accumulated
-            uint32_t pa[2][16], pb[2][16];
-            tmem_ld16(t0 + col_a, pa[0]);
-            tmem_ld16(t0 + col_b, pb[0]);
 #pragma unroll
-            for (int i = 0; i < 4; i++) {
-                tmem_ld_wait_for(pa[i & 1], pb[i & 1]);
-                if (i < 3) {
-                    tmem_ld16(t0 + col_a + (i + 1) * 16, pa[(i + 1) & 1]);
-                    tmem_ld16(t0 + col_b + (i + 1) * 16, pb[(i + 1) & 1]);
-                }
+            for (int i = 0; i < HALF / 16; i++) {
+                uint32_t pa[16], pb[16];
+                tmem_ld16(t0 + col_a + i * 16, pa);
+                tmem_ld16(t0 + col_b + i * 16, pb);
+                tmem_ld_wait_for(pa, pb);
 #pragma unroll
                 for (int c = 0; c < 16; c++) {
-                    acc[i * 16 + c] = __fmaf_rn(__uint_as_float(pa[i & 1][c]), sa, acc[i * 16 + c]);
-                    acc[64 + i * 16 + c] = __fmaf_rn(__uint_as_float(pb[i & 1][c]), sb, acc[64 + i * 16 + c]);
+                    acc[i * 16 + c] = __fmaf_rn(__uint_as_float(pa[c]), sa, acc[i * 16 + c]);
+                    acc[HALF + i * 16 + c] = __fmaf_rn(__uint_as_float(pb[c]), sb, acc[HALF + i * 16 + c]);
                 }
             }
             tc_fence_before();
@@ -62,14 +60,14 @@
         if (!ok)
             break;
         if constexpr (GATE_UP) {
-            // act = silu(gate) * up for this thread's 64 features; the 1x128 group spans both warpgroups
+            // act = silu(gate) * up for this thread's 32 features; the 1x128 group spans the four warpgroups
             float m = 0.0f;
 #pragma unroll
-            for (int c = 0; c < 64; c++) {
-                acc[c] = silu_fast(acc[c]) * acc[64 + c];
+            for (int c = 0; c < HALF; c++) {
+                acc[c] = silu_fast(acc[c]) * acc[HALF + c];
                 m = fmaxf(m, fabsf(acc[c]));
             }
-            float *ax = amax_x + (it & 1) * 256;
+            float *ax = amax_x + (it & 1) * (kPfGroups * 128);
             ax[g * 128 + r] = m;
             __syncwarp();
             if (lane == 0)
@@ -78,12 +76,14 @@
                 ok = false;
                 break;
             }
-            m = fmaxf(ax[r], ax[128 + r]);
+#pragma unroll
+            for (int j = 0; j < kPfGroups; j++)
+                m = fmaxf(m, ax[j * 128 + r]);
             const float s = __fdiv_rn(fmaxf(m, 1e-10f), 448.0f);
             if (valid) {
-                uint8_t *dst = static_cast<uint8_t *>(out) + static_cast<size_t>(row0 + r) * n_out + nt * 128 + 64 * g;
+                uint8_t *dst = static_cast<uint8_t *>(out) + static_cast<size_t>(row0 + r) * n_out + nt * 128 + HALF * g;
 #pragma unroll
-                for (int v = 0; v < 4; v++) {
+                for (int v = 0; v < HALF / 16; v++) {
                     uint32_t pk[4];
 #pragma unroll
                     for (int j = 0; j < 4; j++) {
@@ -99,9 +99,9 @@
             }
         } else {
             if (valid) {
-                float *dst = static_cast<float *>(out) + static_cast<size_t>(row0 + r) * n_out + nt * 256 + 128 * g;
+                float *dst = static_cast<float *>(out) + static_cast<size_t>(row0 + r) * n_out + nt * 256 + CPT * g;
 #pragma unroll
-                for (int v = 0; v < 32; v++)
+                for (int v = 0; v < CPT / 4; v++)
                     *reinterpret_cast<float4 *>(dst + v * 4) = make_float4(acc[v * 4], acc[v * 4 + 1], acc[v * 4 + 2], acc[v * 4 + 3]);
             }
         }
