@@ -13,19 +13,6 @@ __device__ __forceinline__ uint32_t smem_u32(const void *p)
     return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }
 
-__device__ __forceinline__ uint32_t elect_one()
-{
-    uint32_t pred = 0;
-    asm volatile(
-        "{\n\t"
-        ".reg .pred P;\n\t"
-        "elect.sync _|P, 0xffffffff;\n\t"
-        "selp.u32 %0, 1, 0, P;\n\t"
-        "}\n"
-        : "=r"(pred));
-    return pred;
-}
-
 // ---- mbarrier -----------------------------------------------------------------------------------------
 __device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count)
 {
@@ -266,16 +253,6 @@ __device__ __forceinline__ void tmem_cp_32x128b_x4(uint32_t taddr, uint64_t sdes
 __device__ __forceinline__ void fence_proxy_async_smem()
 {
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-}
-
-// registers -> TMEM: this warp's 32 lanes x 4 (or 1) consecutive 32-bit columns
-__device__ __forceinline__ void tmem_st4(uint32_t taddr, uint32_t a, uint32_t b, uint32_t c, uint32_t d)
-{
-    asm volatile("tcgen05.st.sync.aligned.32x32b.x4.b32 [%0], {%1, %2, %3, %4};" ::"r"(taddr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
-}
-__device__ __forceinline__ void tmem_st_wait()
-{
-    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
 
 } // namespace xs

@@ -8,97 +8,6 @@
 
 namespace xs {
 
-constexpr int kRtTokens = 16;  // tokens per block
-constexpr int kRtExperts = 64; // experts per block
-constexpr int kRtK = 64;       // k elements staged per step
-constexpr int kRtThreads = 128;
-constexpr int kRtPad = 4;      // bf16 elements of row padding: row stride 136 B keeps 8-byte reads conflict-free
-
-// Products of two bf16 values are exact in f32, so fma(x, w, acc) rounds once exactly like the CPU's
-// separate multiply and add; only the ORDER of the additions matters and it is ascending k here:
-// every accumulator is touched once per k, k = 0, 1, 2, ...
-__global__ void __launch_bounds__(kRtThreads)
-router_logits_kernel(const __nv_bfloat16 *__restrict__ x, const __nv_bfloat16 *__restrict__ rw, float *__restrict__ logits,
-                     int T, int H, int E)
-{
-    __shared__ __align__(16) __nv_bfloat16 xs[kRtTokens][kRtK + kRtPad];
-    __shared__ __align__(16) __nv_bfloat16 ws[kRtExperts][kRtK + kRtPad];
-
-    const int tid = threadIdx.x;
-    const int tx = tid & 15; // expert lane: experts j*16 + tx, j = 0..3
-    const int ty = tid >> 4; // token pair: tokens 2*ty, 2*ty+1
-    const int t0 = blockIdx.y * kRtTokens;
-    const int e0 = blockIdx.x * kRtExperts;
-
-    float acc[2][4];
-#pragma unroll
-    for (int i = 0; i < 2; i++)
-#pragma unroll
-        for (int j = 0; j < 4; j++)
-            acc[i][j] = 0.0f;
-
-    for (int k0 = 0; k0 < H; k0 += kRtK) {
-        // stage x (16 rows x 64) and w (64 rows x 64): 8-byte pieces
-        for (int p = tid; p < (kRtTokens + kRtExperts) * (kRtK / 4); p += kRtThreads) {
-            const int r = p / (kRtK / 4);
-            const int c = (p - r * (kRtK / 4)) * 4;
-            uint2 v = make_uint2(0u, 0u);
-            if (r < kRtTokens) {
-                const int t = t0 + r;
-                if (t < T)
-                    v = *reinterpret_cast<const uint2 *>(x + static_cast<size_t>(t) * H + k0 + c);
-                *reinterpret_cast<uint2 *>(&xs[r][c]) = v;
-            } else {
-                const int e = e0 + r - kRtTokens;
-                if (e < E)
-                    v = *reinterpret_cast<const uint2 *>(rw + static_cast<size_t>(e) * H + k0 + c);
-                *reinterpret_cast<uint2 *>(&ws[r - kRtTokens][c]) = v;
-            }
-        }
-        __syncthreads();
-#pragma unroll 4
-        for (int k = 0; k < kRtK; k += 4) {
-            float xv[2][4], wv[4][4];
-#pragma unroll
-            for (int i = 0; i < 2; i++) {
-                const uint2 v = *reinterpret_cast<const uint2 *>(&xs[2 * ty + i][k]);
-                xv[i][0] = __uint_as_float(v.x << 16);
-                xv[i][1] = __uint_as_float(v.x & 0xffff0000u);
-                xv[i][2] = __uint_as_float(v.y << 16);
-                xv[i][3] = __uint_as_float(v.y & 0xffff0000u);
-            }
-#pragma unroll
-            for (int j = 0; j < 4; j++) {
-                const uint2 v = *reinterpret_cast<const uint2 *>(&ws[j * 16 + tx][k]);
-                wv[j][0] = __uint_as_float(v.x << 16);
-                wv[j][1] = __uint_as_float(v.x & 0xffff0000u);
-                wv[j][2] = __uint_as_float(v.y << 16);
-                wv[j][3] = __uint_as_float(v.y & 0xffff0000u);
-            }
-#pragma unroll
-            for (int kk = 0; kk < 4; kk++)
-#pragma unroll
-                for (int i = 0; i < 2; i++)
-#pragma unroll
-                    for (int j = 0; j < 4; j++)
-                        acc[i][j] = __fmaf_rn(xv[i][kk], wv[j][kk], acc[i][j]);
-        }
-        __syncthreads();
-    }
-#pragma unroll
-    for (int i = 0; i < 2; i++) {
-        const int t = t0 + 2 * ty + i;
-        if (t >= T)
-            continue;
-#pragma unroll
-        for (int j = 0; j < 4; j++) {
-            const int e = e0 + j * 16 + tx;
-            if (e < E)
-                logits[static_cast<size_t>(t) * E + e] = acc[i][j];
-        }
-    }
-}
-
 // Large batches: 64 tokens x 128 experts per block, 4 x 8 outputs per thread.  Operands are widened to f32 while they are
 // staged in shared memory, so the inner loop is 12 16-byte shared loads per 128 FMAs and no conversions; k chunks of
 // 32 are double-buffered.  Same contract: every accumulator sees k = 0, 1, 2, ... in order.

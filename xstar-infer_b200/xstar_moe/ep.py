@@ -58,10 +58,6 @@ class EpPlan:
         return np.concatenate([self.offsets_local, self.grouped_from_arrival, self.arrival_from_grouped])
 
 
-def expert_owner(e, E, R):
-    return e // (E // R)
-
-
 # ------------------------------------------------------------------------------------------------------------
 # device ops through the C ABI
 # ------------------------------------------------------------------------------------------------------------
