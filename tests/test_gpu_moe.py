@@ -312,3 +312,50 @@ def test_forward_fp4_many_tokens_per_expert(oracle, T, S, E, K, H, I):
     print(f"fp4 prefill-shaped T={T}: rel-L2 {rel:.3e}")
     assert rel <= FP8_TOL, rel
     assert torch.equal(out, gu.forward(dims, d))
+
+
+# ---- small stage entry points ----------------------------------------------------------------------------------
+def test_gather_rows_and_bf16_return_rows():
+    g = torch.Generator(device="cuda").manual_seed(61)
+    L = capi.lib()
+    for dtype, cols in ((torch.float32, 96), (torch.uint8, 132), (torch.bfloat16, 256)):
+        src = (torch.randn((50, cols), generator=g, device="cuda") * 50).to(dtype)
+        idx = torch.randint(0, 50, (77,), generator=g, device="cuda", dtype=torch.int32)
+        dst = torch.empty((77, cols), dtype=dtype, device="cuda")
+        capi.check(L.xs_moe_gather_rows(capi.ptr(src), capi.ptr(idx), capi.ptr(dst), 77, cols * src.element_size(), gu.stream_ptr()))
+        torch.cuda.synchronize()
+        assert torch.equal(dst, src[idx.long()])
+    src = torch.randn((40, 512), generator=g, device="cuda")
+    idx = torch.randperm(40, generator=g, device="cuda").to(torch.int32)
+    dst = torch.empty((40, 512), dtype=torch.bfloat16, device="cuda")
+    capi.check(L.xs_moe_gather_rows_f32_to_bf16(capi.ptr(src), capi.ptr(idx), capi.ptr(dst), 40, 512, gu.stream_ptr()))
+    torch.cuda.synchronize()
+    assert torch.equal(dst, src[idx.long()].to(torch.bfloat16))
+
+
+def test_combine_with_bf16_rows_matches_f32_combine_on_rounded_rows():
+    T, K, H = 33, 4, 512
+    g = torch.Generator(device="cuda").manual_seed(62)
+    y = torch.randn((T * K, H), generator=g, device="cuda")
+    yb = y.to(torch.bfloat16)
+    inv = torch.randperm(T * K, generator=g, device="cuda").to(torch.int32)
+    w = torch.rand((T, K), generator=g, device="cuda")
+    shared = torch.randn((T, H), generator=g, device="cuda")
+    cfg = capi.make_config(T, H, 8, K, 128, 0)
+    a = torch.empty((T, H), dtype=torch.bfloat16, device="cuda")
+    b = torch.empty_like(a)
+    L = capi.lib()
+    capi.check(L.xs_moe_combine(C.byref(cfg), capi.ptr(yb.float()), capi.ptr(inv), capi.ptr(w), capi.ptr(shared), capi.ptr(a), gu.stream_ptr()))
+    capi.check(L.xs_moe_combine_bf16_rows(C.byref(cfg), capi.ptr(yb), capi.ptr(inv), capi.ptr(w), capi.ptr(shared), capi.ptr(b), gu.stream_ptr()))
+    torch.cuda.synchronize()
+    assert torch.equal(a, b)
+    ref = (w[:, :, None] * y[inv.long()].view(T, K, H)).sum(1) + shared
+    assert synth.rel_l2(b.float().cpu().numpy(), ref.cpu().numpy()) < 5e-3
+
+
+def test_mma_rate_probe_runs_and_reports():
+    ws = torch.zeros(4096, dtype=torch.uint8, device="cuda")
+    cyc, iss, tf = C.c_double(), C.c_double(), C.c_double()
+    capi.check(capi.lib().xs_moe_probe_mma_rate(1, 64, 200, 2, capi.ptr(ws), ws.numel(), C.byref(cyc), C.byref(iss), C.byref(tf), None))
+    assert 10 < cyc.value < 5000 and tf.value > 1.0
+    assert capi.lib().xs_moe_probe_mma_rate(1, 24, 200, 1, capi.ptr(ws), ws.numel(), C.byref(cyc), C.byref(iss), C.byref(tf), None) == -1

@@ -93,3 +93,24 @@ def test_moe_op_rejects_mixed_devices():
     X, RW, GU, DW = (torch_to_cpp(t) for t in (x, rw, gu, dw))
     with pytest.raises(RuntimeError, match="device mismatch"):
         xstar_cpp.moe(xstar_cpp.to_cuda(X), RW, GU, DW, 2)
+
+
+@pytest.mark.gpu
+def test_moe_op_fp8_experts_through_the_binding(oracle):
+    """FP8 e4m3 experts with 128x128 block scales enter as byte tensors tagged Float8E4M3 plus Float32 scale tensors."""
+    dims = dict(T=40, H=512, E=8, K=2, I=256, S=1, fmt="fp8", bias=None)
+    d = synth.make_inputs(dims, seed=4)
+    tag = {"gate_up_w": xstar_cpp.DType.Float8E4M3, "down_w": xstar_cpp.DType.Float8E4M3,
+           "shared_gate_up_w": xstar_cpp.DType.Float8E4M3, "shared_down_w": xstar_cpp.DType.Float8E4M3}
+    dev = {k: xstar_cpp.to_cuda(torch_to_cpp(v, tag.get(k))) for k, v in d.items() if v is not None}
+    out = xstar_cpp.moe(dev["x"], dev["router_w"], dev["gate_up_w"], dev["down_w"], dims["K"], gate_up_scale=dev["gate_up_scale"],
+                        down_scale=dev["down_scale"], shared_gate_up_weight=dev["shared_gate_up_w"], shared_down_weight=dev["shared_down_w"],
+                        shared_gate_up_scale=dev["shared_gate_up_scale"], shared_down_scale=dev["shared_down_scale"])
+    got = cpp_to_torch(xstar_cpp.to_cpu(out), (40, 512)).float().numpy()
+    n = synth.to_numpy_storage(d)
+    ref = oracle.moe_forward(oracle.FP8, n["x"], n["router_w"], n["gate_up_w"], n["down_w"], dims["K"], gate_up_scale=n["gate_up_scale"],
+                             down_scale=n["down_scale"], shared_gate_up_w=n["shared_gate_up_w"], shared_down_w=n["shared_down_w"],
+                             shared_gate_up_scale=n["shared_gate_up_scale"], shared_down_scale=n["shared_down_scale"], threads=4)
+    assert synth.rel_l2(got, synth.bf16_bits_to_f32(ref["out"])) <= 1e-2
+    with pytest.raises(RuntimeError, match="missing scale"):
+        xstar_cpp.moe(dev["x"], dev["router_w"], dev["gate_up_w"], dev["down_w"], dims["K"])
