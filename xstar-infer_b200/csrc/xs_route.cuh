@@ -8,54 +8,66 @@
 
 namespace xs {
 
-// Large batches: 64 tokens x 128 experts per block, 4 x 8 outputs per thread.  Operands are widened to f32 while they are
-// staged in shared memory, so the inner loop is 12 16-byte shared loads per 128 FMAs and no conversions; k chunks of
-// 32 are double-buffered.  Same contract: every accumulator sees k = 0, 1, 2, ... in order.
-constexpr int kRbTokens = 64, kRbExperts = 128, kRbK = 32, kRbThreads = 256, kRbStride = kRbK + 4;
-constexpr int kRbSmemBytes = 2 * (kRbTokens + kRbExperts) * kRbStride * 4;
+// Large batches: (16 * TPT) tokens x 128 experts per block, TPT x 8 outputs per thread (TPT = 4, or 2 when the batch is
+// too small to fill the SMs with 64-token tiles).  Operands are widened to f32 while they are staged in shared memory,
+// so the inner loop is (TPT + 8) 16-byte shared loads per 32 * TPT FMAs and no conversions; k chunks of 32 are
+// double-buffered.  Same contract: every accumulator sees k = 0, 1, 2, ... in order.
+constexpr int kRbExperts = 128, kRbK = 32, kRbThreads = 256, kRbStride = kRbK + 4;
+template <int TPT>
+constexpr int rb_smem_bytes()
+{
+    return 2 * (16 * TPT + kRbExperts) * kRbStride * 4;
+}
+template <int TPT>
 __global__ void __launch_bounds__(kRbThreads, 2)
 router_logits_big_kernel(const __nv_bfloat16 *__restrict__ x, const __nv_bfloat16 *__restrict__ rw, float *__restrict__ logits,
                          int T, int H, int E)
 {
-    extern __shared__ __align__(16) float rb_smem[]; // kRbSmemBytes
-    float (*xs)[kRbTokens][kRbStride] = reinterpret_cast<float (*)[kRbTokens][kRbStride]>(rb_smem);
-    float (*ws)[kRbExperts][kRbStride] = reinterpret_cast<float (*)[kRbExperts][kRbStride]>(rb_smem + 2 * kRbTokens * kRbStride);
+    constexpr int TOK = 16 * TPT;
+    constexpr int PIECES = (TOK + kRbExperts) * 4; // 16-byte pieces (8 bf16) per k chunk
+    constexpr int PPT = (PIECES + kRbThreads - 1) / kRbThreads;
+    extern __shared__ __align__(16) float rb_smem[];
+    float (*xs)[TOK][kRbStride] = reinterpret_cast<float (*)[TOK][kRbStride]>(rb_smem);
+    float (*ws)[kRbExperts][kRbStride] = reinterpret_cast<float (*)[kRbExperts][kRbStride]>(rb_smem + 2 * TOK * kRbStride);
     const int tid = threadIdx.x;
     const int tx = tid & 15, ty = tid >> 4;
-    const int t0 = blockIdx.y * kRbTokens, e0 = blockIdx.x * kRbExperts;
-    // staging: (64 + 128) rows x 32 k = 192 rows x 4 pieces of 8 bf16; 768 pieces over 256 threads = 3 each
-    uint4 stage_regs[3];
+    const int t0 = blockIdx.y * TOK, e0 = blockIdx.x * kRbExperts;
+    uint4 stage_regs[PPT];
     auto fetch = [&](int k0) {
 #pragma unroll
-        for (int i = 0; i < 3; i++) {
+        for (int i = 0; i < PPT; i++) {
             const int p = tid + i * kRbThreads;
             const int r = p >> 2, c = (p & 3) * 8;
             uint4 v = make_uint4(0, 0, 0, 0);
-            if (r < kRbTokens) {
-                if (t0 + r < T)
-                    v = __ldg(reinterpret_cast<const uint4 *>(x + static_cast<size_t>(t0 + r) * H + k0 + c));
-            } else if (e0 + r - kRbTokens < E) {
-                v = __ldg(reinterpret_cast<const uint4 *>(rw + static_cast<size_t>(e0 + r - kRbTokens) * H + k0 + c));
+            if (p < PIECES) {
+                if (r < TOK) {
+                    if (t0 + r < T)
+                        v = __ldg(reinterpret_cast<const uint4 *>(x + static_cast<size_t>(t0 + r) * H + k0 + c));
+                } else if (e0 + r - TOK < E) {
+                    v = __ldg(reinterpret_cast<const uint4 *>(rw + static_cast<size_t>(e0 + r - TOK) * H + k0 + c));
+                }
             }
             stage_regs[i] = v;
         }
     };
     auto stash = [&](int buf) {
 #pragma unroll
-        for (int i = 0; i < 3; i++) {
+        for (int i = 0; i < PPT; i++) {
             const int p = tid + i * kRbThreads;
+            if (p >= PIECES)
+                continue;
             const int r = p >> 2, c = (p & 3) * 8;
             const uint4 v = stage_regs[i];
-            float *dst = r < kRbTokens ? &xs[buf][r][c] : &ws[buf][r - kRbTokens][c];
+            float *dst = r < TOK ? &xs[buf][r][c] : &ws[buf][r - TOK][c];
             *reinterpret_cast<float4 *>(dst) = make_float4(__uint_as_float(v.x << 16), __uint_as_float(v.x & 0xffff0000u),
                                                             __uint_as_float(v.y << 16), __uint_as_float(v.y & 0xffff0000u));
             *reinterpret_cast<float4 *>(dst + 4) = make_float4(__uint_as_float(v.z << 16), __uint_as_float(v.z & 0xffff0000u),
                                                                 __uint_as_float(v.w << 16), __uint_as_float(v.w & 0xffff0000u));
         }
     };
-    float acc[4][8];
+    float acc[TPT][8];
 #pragma unroll
-    for (int i = 0; i < 4; i++)
+    for (int i = 0; i < TPT; i++)
 #pragma unroll
         for (int j = 0; j < 8; j++)
             acc[i][j] = 0.0f;
@@ -69,15 +81,15 @@ router_logits_big_kernel(const __nv_bfloat16 *__restrict__ x, const __nv_bfloat1
             fetch((ch + 1) * kRbK);
 #pragma unroll
         for (int k = 0; k < kRbK; k += 4) {
-            float4 xv[4], wv[8];
+            float4 xv[TPT], wv[8];
 #pragma unroll
-            for (int i = 0; i < 4; i++)
+            for (int i = 0; i < TPT; i++)
                 xv[i] = *reinterpret_cast<const float4 *>(&xs[buf][ty + 16 * i][k]);
 #pragma unroll
             for (int j = 0; j < 8; j++)
                 wv[j] = *reinterpret_cast<const float4 *>(&ws[buf][tx + 16 * j][k]);
 #pragma unroll
-            for (int i = 0; i < 4; i++)
+            for (int i = 0; i < TPT; i++)
 #pragma unroll
                 for (int j = 0; j < 8; j++) {
                     float a = acc[i][j];
@@ -93,7 +105,7 @@ router_logits_big_kernel(const __nv_bfloat16 *__restrict__ x, const __nv_bfloat1
         __syncthreads();
     }
 #pragma unroll
-    for (int i = 0; i < 4; i++) {
+    for (int i = 0; i < TPT; i++) {
         const int t = t0 + ty + 16 * i;
         if (t >= T)
             continue;

@@ -86,6 +86,7 @@ class CudaOps:
         capi.check(self.L.xs_moe_workspace_init(capi.ptr(self.ws), self.ws.numel(), self._st()))
         self._gws = {}
         self.shared_offsets = torch.tensor([0, self.T], dtype=torch.int32, device="cuda")
+        self.side_stream = torch.cuda.Stream()
 
     @staticmethod
     def _st():
@@ -153,7 +154,7 @@ class CudaOps:
         return self._grouped(self.cfg_local, self.w_local, payload, offsets_local, n_rows)
 
     def shared_mlp(self, x, payload):
-        if self.fmt_shared != self.fmt:
+        if payload is None or self.fmt_shared != self.fmt:
             payload = self._payload(x, self.fmt_shared)
         return self._grouped(self.cfg_shared, self.w_shared, payload, self.shared_offsets, self.T)
 
@@ -197,12 +198,15 @@ class ExpertParallelMoE:
             raise ValueError("expert count mismatch: experts must divide evenly over ranks")
         self.last_plan = None
 
-    def _all_gather_counts(self, counts):
+    def _all_gather_counts_start(self, counts):
         if self.world == 1:
-            return counts.cpu().numpy()[None, :]
+            return counts
         out = torch.empty(self.world * self.E, dtype=torch.int32, device=counts.device)
         dist.all_gather_into_tensor(out, counts.contiguous(), group=self.group)
-        return out.view(self.world, self.E).cpu().numpy()  # the one host synchronisation of the layer
+        return out
+
+    def _all_gather_counts_finish(self, gathered):
+        return gathered.view(self.world, self.E).cpu().numpy()  # the one host synchronisation of the layer
 
     def _a2a(self, t, out_rows, in_splits, out_splits):
         out = torch.empty((out_rows, *t.shape[1:]), dtype=t.dtype, device=t.device)
@@ -223,14 +227,22 @@ class ExpertParallelMoE:
                 marks.append((name, ev))
 
         mark("start")
+        side = getattr(ops, "side_stream", None)
+        shared = None
+        if self.S and side is not None:
+            # the always-on expert needs only x: it runs on a second stream next to routing and the exchange
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                shared = ops.shared_mlp(x, None)
         ids, w = ops.route(x, self.router_w, self.router_bias)
         counts, offsets, perm, inv = ops.permute(ids)
         mark("route+permute")
+        gathered = self._all_gather_counts_start(counts)  # in flight while the rows are quantised and packed
         payload = ops.payload(x)
         tok = torch.div(perm, K, rounding_mode="floor").to(torch.int32)
         send = [ops.gather(p, tok) for p in payload]  # rows in (expert, token) order = grouped by destination rank
         mark("quantise+pack")
-        plan = EpPlan(self._all_gather_counts(counts), self.rank)
+        plan = EpPlan(self._all_gather_counts_finish(gathered), self.rank)
         self.last_plan = plan
         mark("counts exchange + plan (host sync)")
         recv = [self._a2a(s, plan.n_recv, plan.send_splits, plan.recv_splits) for s in send]
@@ -245,7 +257,11 @@ class ExpertParallelMoE:
         y_arrival = ops.return_rows(y_grouped, a_from_g)
         y_back = self._a2a(y_arrival, int(plan.send_splits.sum()), plan.recv_splits, plan.send_splits)
         mark("combine all-to-all")
-        shared = ops.shared_mlp(x, payload) if self.S else None
+        if self.S and side is None:
+            shared = ops.shared_mlp(x, payload)
+        elif self.S:
+            torch.cuda.current_stream().wait_stream(side)
+            shared.record_stream(torch.cuda.current_stream())  # allocated on the side stream, consumed here
         mark("always-on expert")
         out = ops.combine(y_back, inv, w, shared)
         mark("combine")
