@@ -273,7 +273,15 @@ int launch_logits(const XsMoeConfig *c, const void *x, const void *rw, float *lo
     if (T <= 1024) {
         // decode-sized batch: one output per thread, 8 experts x 32 tokens per block, cp.async pipeline
         dim3 grid((E + xs::kRdExperts - 1) / xs::kRdExperts, (T + xs::kRdTokens - 1) / xs::kRdTokens);
-        xs::router_logits_decode_kernel<<<grid, xs::kRdThreads, 0, st>>>(xb, rwb, logits, T, H, E);
+        static bool configured_rd[64] = {};
+        int dev_rd = 0;
+        XS_CUDA(cudaGetDevice(&dev_rd));
+        if (dev_rd >= 64 || !configured_rd[dev_rd]) {
+            XS_CUDA(cudaFuncSetAttribute(xs::router_logits_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, xs::kRdSmemBytes));
+            if (dev_rd < 64)
+                configured_rd[dev_rd] = true;
+        }
+        xs::router_logits_decode_kernel<<<grid, xs::kRdThreads, xs::kRdSmemBytes, st>>>(xb, rwb, logits, T, H, E);
     } else {
         static bool configured[64] = {};
         int dev = 0;

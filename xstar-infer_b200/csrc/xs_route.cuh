@@ -119,12 +119,15 @@ router_logits_big_kernel(const __nv_bfloat16 *__restrict__ x, const __nv_bfloat1
 }
 
 // Decode-sized batches.  Block = 8 experts x 32 tokens, one output per thread (warp = one expert, lanes = tokens),
-// so a batch of 128 tokens x 256 experts spreads over 128 SMs.  Operands arrive through a 4-stage cp.async
+// so a batch of 128 tokens x 256 experts spreads over 128 SMs.  Operands arrive through an 8-stage cp.async
 // pipeline of 128-wide k chunks; inside a chunk each thread walks k upwards, 8 elements per 16-byte shared-memory
 // read (the router row is a warp-wide broadcast, the token rows are padded to stay bank-conflict free).
-// One accumulator per thread, touched once per k in ascending order: the contract's summation order.
-constexpr int kRdExperts = 8, kRdTokens = 32, kRdK = 128, kRdStages = 4, kRdThreads = 256;
+// One accumulator per thread, touched once per k in ascending order: the contract's summation order -- which makes the
+// H dependent FMAs the floor of this kernel; the pipeline is eight chunks deep because at decode sizes the kernel is
+// otherwise bound by the latency of fetching its operands.
+constexpr int kRdExperts = 8, kRdTokens = 32, kRdK = 128, kRdStages = 8, kRdThreads = 256;
 constexpr int kRdXStride = kRdK + 8; // bf16 elements; 272-byte rows: 16-byte aligned and conflict-free for 16-byte reads
+constexpr int kRdSmemBytes = kRdStages * (kRdExperts * kRdK + kRdTokens * kRdXStride) * 2;
 
 __device__ __forceinline__ void cp_async16(void *smem_dst, const void *gsrc, bool valid)
 {
@@ -137,8 +140,10 @@ __global__ void __launch_bounds__(kRdThreads)
 router_logits_decode_kernel(const __nv_bfloat16 *__restrict__ x, const __nv_bfloat16 *__restrict__ rw, float *__restrict__ logits,
                             int T, int H, int E)
 {
-    __shared__ __align__(16) __nv_bfloat16 ws[kRdStages][kRdExperts][kRdK];
-    __shared__ __align__(16) __nv_bfloat16 xsm[kRdStages][kRdTokens][kRdXStride];
+    extern __shared__ __align__(16) uint8_t rd_smem[]; // kRdSmemBytes
+    __nv_bfloat16 (*ws)[kRdExperts][kRdK] = reinterpret_cast<__nv_bfloat16 (*)[kRdExperts][kRdK]>(rd_smem);
+    __nv_bfloat16 (*xsm)[kRdTokens][kRdXStride] =
+        reinterpret_cast<__nv_bfloat16 (*)[kRdTokens][kRdXStride]>(rd_smem + kRdStages * kRdExperts * kRdK * 2);
     const int tid = threadIdx.x;
     const int el = tid >> 5, tl = tid & 31;
     const int e0 = blockIdx.x * kRdExperts, t0 = blockIdx.y * kRdTokens;
