@@ -378,13 +378,21 @@ def run_ours_ep(args, dims):
     stream = torch.cuda.current_stream()
     x_host = x.cpu().pin_memory()
     out_host = torch.empty_like(x_host).pin_memory()
+    peer = args.exchange == "peer"
+    px = None
+    if peer:
+        px = ep.PeerExchange(dims, rank, world)
+        px.connect_ipc()
+
+    def forward(xd, marks=None):
+        return layer.forward_peer(xd, px, marks) if peer else layer.forward(xd, marks)
 
     def step():
-        return layer.forward(x)
+        return forward(x)
 
     def step_host():
         xd = x_host.to("cuda", non_blocking=True)
-        out_host.copy_(layer.forward(xd), non_blocking=True)
+        out_host.copy_(forward(xd), non_blocking=True)
         torch.cuda.synchronize()
 
     def barrier():
@@ -414,7 +422,12 @@ def run_ours_ep(args, dims):
         step_host()
     ms_e2e = timed(step_host, args.steps)
     # the grouped expert MLPs of this rank, timed on their own with CUDA events
-    plan = layer.last_plan
+    if peer:
+        counts_now = torch.empty(world * E, dtype=torch.int32, device="cuda")
+        dist.all_gather_into_tensor(counts_now, ops.permute(ops.route(x, weights["router_w"], bias)[0])[0])
+        plan = ep.EpPlan(counts_now.view(world, E).cpu().numpy(), rank)
+    else:
+        plan = layer.last_plan
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     payload = ops.payload(x)
     rows = [torch.zeros((plan.n_recv, *p.shape[1:]), dtype=p.dtype, device="cuda") for p in payload]
@@ -432,7 +445,7 @@ def run_ours_ep(args, dims):
     ops.check()
     # phase times of one more step (CUDA events on the launching stream; host-side gaps show up in the phase that follows them)
     marks = []
-    layer.forward(x, marks)
+    forward(x, marks)
     torch.cuda.synchronize()
     phases = {marks[i][0]: marks[i - 1][1].elapsed_time(marks[i][1]) for i in range(1, len(marks))}
     active = int((np.diff(plan.offsets_local) > 0).sum())
@@ -446,11 +459,12 @@ def run_ours_ep(args, dims):
             "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong" if strong else "weak", "vs_baseline": None,
             "dtype": dims["fmt"], "data": "synthetic (seeded: weights N(0,0.02), activations N(0,1), rounded once to storage)",
             "config": dict(workload=args.workload, **{k: dims[k] for k in "THEKIS"}, format=dims["fmt"], tokens_per_rank=T,
-                           experts_per_rank=E // world, parallelism=f"ep{world}: experts sharded, NCCL all-to-all dispatch/combine",
+                           experts_per_rank=E // world, parallelism=f"ep{world}: experts sharded, " + ("dispatch/return by peer-memory stores over NVLink, no host synchronisation"
+                                                                           if peer else "NCCL all-to-all dispatch/combine"),
                            l2="inputs larger than L2: expert weights streamed per step exceed 126 MB"),
             "e2e": {"value": tokens / (ms_e2e * 1e-3), "unit": UNIT, "h2d_bytes_per_step": T * H * 2, "d2h_bytes_per_step": T * H * 2,
                     "ms_per_step": ms_e2e / args.steps},
-            "gpu_launches": (2 + 3 + 1 + len(payload) * 2 + 3 + 1 + 3 * S + 1) * args.steps,
+            "gpu_launches": ((2 + 3 + 1 + 1 + 3 + 1 + 3 * S + 1) if peer else (2 + 3 + 1 + len(payload) * 2 + 3 + 1 + 3 * S + 1)) * args.steps,
             "roofline": {"bound": "hbm", "kernel": "grouped expert MLP of rank 0 (tile table + gate/up + down GEMM launches)",
                          "achieved": mlp_bytes / (mlp_ms * 1e-3) / 1e9, "peak": peak, "unit": "GB/s", "peak_kind": peak_kind,
                          "frac": mlp_bytes / (mlp_ms * 1e-3) / 1e9 / peak, "traffic": None, "algorithmic_bytes_per_launch": mlp_bytes,
@@ -459,6 +473,10 @@ def run_ours_ep(args, dims):
             "cpu_baseline": None, "clocks": clocks,
         }
         print(json.dumps(line), flush=True)
+    if px is not None:
+        torch.cuda.synchronize()
+        dist.barrier()
+        px.close()
     dist.destroy_process_group()
 
 
@@ -495,6 +513,8 @@ def main():
     ap.add_argument("--experts", type=int, default=None, help="override the routed expert count (small profiling cases)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--graph", default="auto", choices=["auto", "on", "off"], help="replay the step as a CUDA graph (auto: T <= 1024)")
+    ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
+                    help="N > 1: rows travel by peer-memory stores from the dispatch/return kernels (default) or by NCCL all-to-all")
     ap.add_argument("--mma-rate", action="store_true", help="print the tensor-pipe rate probe table and exit")
     args = ap.parse_args()
     if args.mma_rate:

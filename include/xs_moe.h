@@ -205,6 +205,43 @@ int xs_moe_gather_rows_f32_to_bf16(const float *src_dev, const int32_t *index_de
 int xs_moe_combine_bf16_rows(const XsMoeConfig *cfg, const void *y_bf16_dev, const int32_t *inv_dev,
                              const float *topk_w_dev, const float *shared_dev, void *out_dev, void *stream);
 
+/* ---- expert parallelism over peer memory (no counterpart in the reference: the expert all-to-all is a roadmap
+ * row there, README.md:30, with no code behind it) ---------------------------------------------------------------
+ * The dispatch and return trips of an expert-parallel layer as kernels that store each row straight into the buffer
+ * of the rank that needs it, over NVLink peer mappings.  Every address is computed on the device from the (ranks,
+ * experts) matrix of row counts, so the layer needs no host synchronisation; no kernel waits for another GPU, the
+ * caller puts a barrier collective between the stores and their first reader. */
+
+#define XS_MOE_IPC_HANDLE_BYTES 64
+/* Peer mappings of buffers from xs_moe_device_alloc: export a handle here, import it in the other process of the
+ * same box (enables peer access on first use), close it before the owner frees the buffer. */
+int xs_moe_ipc_export(void *ptr_dev, uint8_t *handle64);
+int xs_moe_ipc_import(const uint8_t *handle64, void **ptr_dev);
+int xs_moe_ipc_close(void *ptr_dev);
+
+/* From all_counts (ranks, experts) int32: dest_base[e] = first row of THIS rank's rows of expert e inside the
+ * grouped buffer of e's owner (rows grouped by local expert, then source rank, then source order);
+ * offsets_local[experts/ranks + 1] = segment offsets of this rank's own grouped buffer; src_offsets (ranks, experts) =
+ * every rank's exclusive prefix of its counts (its permuted-row offsets). */
+int xs_moe_ep_plan(const int32_t *all_counts_dev, int32_t ranks, int32_t num_experts, int32_t rank, int32_t *dest_base_dev,
+                   int32_t *offsets_local_dev, int32_t *src_offsets_dev, void *stream);
+
+/* Quantise (per cfg->routed_format: bf16 rows | e4m3 + 1x128 f32 scales | e4m3 + 1x32 e8m0 scales) each local token
+ * once and store it for each of its k experts into row dest_base[e] + (inv[t,j] - my_offsets[e]) of the owner's
+ * buffers.  peer_rows_dev / peer_scales_dev: device arrays of `ranks` pointers (this rank's own buffer included).
+ * Rows outside [0, capacity_rows) are skipped and flagged in the workspace status word. */
+int xs_moe_ep_dispatch(const XsMoeConfig *cfg, int32_t ranks, const void *x_dev, const int32_t *topk_ids_dev,
+                       const int32_t *inv_dev, const int32_t *my_offsets_dev, const int32_t *dest_base_dev,
+                       void *const *peer_rows_dev, void *const *peer_scales_dev, int32_t capacity_rows, void *workspace_dev,
+                       void *stream);
+
+/* Expert outputs (grouped rows, f32) back to row src_offsets[s][e] + j of their source rank's return buffer, as f32
+ * or rounded to bf16 (wire_bf16 != 0).  The row count is read on the device from offsets_local. */
+int xs_moe_ep_return(const XsMoeConfig *cfg, int32_t ranks, int32_t rank, const float *y_grouped_dev,
+                     const int32_t *all_counts_dev, const int32_t *offsets_local_dev, const int32_t *src_offsets_dev,
+                     void *const *peer_back_dev, int32_t back_capacity_rows, int32_t wire_bf16, void *workspace_dev,
+                     void *stream);
+
 /* Tensor-pipe rate probe (a tuning aid; no counterpart in the reference): every SM issues `iters` tcgen05.mma of
  * M = 128, N = n (16..256) on zeroed shared memory, round-robin over `chains` independent TMEM accumulators
  * (chains * n <= 480).  kind 0 = bf16 (K = 16), 1 = e4m3 (K = 32), 2 = block-scaled e4m3 x e2m1 (K = 32).

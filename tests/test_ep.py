@@ -183,3 +183,144 @@ def test_ep_on_gpus_matches_oracle(oracle, tmp_path, fmt, tol):
     got = np.concatenate([np.load(tmp_path / f"out{r}.npy") for r in range(world)])
     rel = synth.rel_l2(synth.bf16_bits_to_f32(got), synth.bf16_bits_to_f32(ref["out"]))
     assert rel <= tol, rel
+
+
+# ---- the exchange over peer memory ------------------------------------------------------------------------------------
+def _oracle_ref(oracle, dims, d):
+    n = synth.to_numpy_storage(d)
+    mode = {"bf16": oracle.BF16, "fp8": oracle.FP8, "fp4": oracle.FP4}[dims["fmt"]]
+    return oracle.moe_forward(mode, n["x"], n["router_w"], n["gate_up_w"], n["down_w"], dims["K"], gate_up_scale=n.get("gate_up_scale"),
+                              down_scale=n.get("down_scale"), shared_gate_up_w=n["shared_gate_up_w"], shared_down_w=n["shared_down_w"],
+                              shared_gate_up_scale=n.get("shared_gate_up_scale"), shared_down_scale=n.get("shared_down_scale"), threads=8)
+
+
+def _virtual_ranks(dims, R, seed, capacity=None):
+    """R expert-parallel ranks inside one process on one GPU: every rank has its own ops, buffers and index tables, and
+    the 'peer' pointers are simply the other ranks' buffers on the same device.  Exercises every kernel and all the
+    index arithmetic of the peer exchange without a second GPU; phases run rank after rank on one stream, which is
+    what the barriers between them guarantee on real ranks."""
+    d = synth.make_inputs(dict(dims, T=dims["T"] * R), seed=seed)
+    T, El = dims["T"], dims["E"] // R
+    keys = ["gate_up_w", "down_w", "gate_up_scale", "down_scale"]
+    shared = {k: v.cuda() for k, v in d.items() if k.startswith("shared_") and v is not None}
+    router_w = d["router_w"].cuda()
+    ranks = []
+    for r in range(R):
+        local = {k: d[k][r * El:(r + 1) * El].contiguous().cuda() for k in keys if d.get(k) is not None}
+        local["router_w"] = router_w
+        ops = ep.CudaOps(dict(dims), local, shared, r, R)
+        px = ep.PeerExchange(dims, r, R, capacity)
+        ranks.append(dict(ops=ops, px=px, x=d["x"][r * T:(r + 1) * T].contiguous().cuda()))
+    for k in ranks:
+        k["px"].connect([q["px"].rows.data_ptr() for q in ranks], [q["px"].scales.data_ptr() for q in ranks],
+                        [q["px"].back.data_ptr() for q in ranks])
+    return d, ranks
+
+
+def _run_virtual(ranks):
+    for k in ranks:
+        k["ids"], k["w"] = k["ops"].route(k["x"], k["ops"].keep[0]["router_w"], None)
+        k["counts"], k["offsets"], k["perm"], k["inv"] = k["ops"].permute(k["ids"])
+    all_counts = torch.cat([k["counts"] for k in ranks])
+    for k in ranks:
+        k["px"].plan(all_counts)
+        k["px"].dispatch(k["x"], k["ids"], k["inv"], k["offsets"], k["ops"].ws)
+    for k in ranks:
+        px = k["px"]
+        y = k["ops"].grouped_mlp([px.rows, px.scales if px.fmt != 0 else None], px.offsets_local, px.capacity)
+        px.give_back(y, all_counts, k["ops"].ws)
+    outs = []
+    for k in ranks:
+        sh = k["ops"].shared_mlp(k["x"], None)
+        outs.append(k["ops"].combine(k["px"].back, k["inv"], k["w"], sh))
+    return all_counts, outs
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("fmt,tol", [("bf16", 2e-3), ("fp8", 1e-2), ("fp4", 1e-2)])
+def test_peer_exchange_virtual_ranks_match_oracle(oracle, fmt, tol):
+    R = 4
+    dims = dict(T=40, H=512, E=16, K=4, I=256, S=1, fmt=fmt, bias=None)
+    d, ranks = _virtual_ranks(dims, R, seed=31)
+    try:
+        all_counts, outs = _run_virtual(ranks)
+        for k in ranks:
+            k["ops"].check()
+        torch.cuda.synchronize()
+        # the device-side plan equals the host-side one
+        ac = all_counts.view(R, dims["E"]).cpu().numpy()
+        for r, k in enumerate(ranks):
+            assert np.array_equal(k["px"].offsets_local.cpu().numpy(), ep.EpPlan(ac, r).offsets_local)
+        got = torch.cat(outs).cpu().view(torch.uint16).numpy()
+        ref = _oracle_ref(oracle, dims, d)
+        rel = synth.rel_l2(synth.bf16_bits_to_f32(got), synth.bf16_bits_to_f32(ref["out"]))
+        assert rel <= tol, rel
+    finally:
+        torch.cuda.synchronize()
+        for k in ranks:
+            k["px"].close()
+
+
+@pytest.mark.gpu
+def test_peer_exchange_flags_a_buffer_that_is_too_small(oracle):
+    R = 2
+    dims = dict(T=32, H=256, E=8, K=2, I=128, S=1, fmt="bf16", bias=None)
+    d, ranks = _virtual_ranks(dims, R, seed=5, capacity=8)  # far fewer rows than the routing sends
+    try:
+        _run_virtual(ranks)
+        with pytest.raises(RuntimeError, match="out-of-range index"):
+            for k in ranks:
+                k["ops"].check()
+    finally:
+        torch.cuda.synchronize()
+        for k in ranks:
+            k["px"].close()
+
+
+def _gpu_rank_peer(rank, world, port, dims, seed, result_dir):
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    px = None
+    try:
+        d = synth.make_inputs(dict(dims, T=dims["T"] * world), seed=seed)
+        T, El = dims["T"], dims["E"] // world
+        keys = ["gate_up_w", "down_w", "gate_up_scale", "down_scale"]
+        local = {k: d[k][rank * El:(rank + 1) * El].contiguous().cuda() for k in keys if d.get(k) is not None}
+        local["router_w"] = d["router_w"].cuda()
+        shared = {k: v.cuda() for k, v in d.items() if k.startswith("shared_") and v is not None}
+        ops = ep.CudaOps(dict(dims), local, shared, rank, world)
+        layer = ep.ExpertParallelMoE(ops, local["router_w"], None, dims["E"], dims["K"], dims["S"])
+        px = ep.PeerExchange(dims, rank, world)
+        px.connect_ipc()
+        x_local = d["x"][rank * T:(rank + 1) * T].contiguous().cuda()
+        via_nccl = layer.forward(x_local)
+        out = layer.forward_peer(x_local, px)
+        out2 = layer.forward_peer(x_local, px)
+        ops.check()
+        torch.cuda.synchronize()
+        assert torch.equal(out, out2)
+        assert torch.equal(out, via_nccl), "peer-memory exchange and all-to-all exchange disagree"
+        np.save(os.path.join(result_dir, f"out{rank}.npy"), out.cpu().view(torch.uint16).numpy())
+    finally:
+        torch.cuda.synchronize()
+        dist.barrier()
+        if px is not None:
+            px.close()
+        dist.destroy_process_group()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("fmt,tol", [("bf16", 2e-3), ("fp8", 1e-2), ("fp4", 1e-2)])
+def test_ep_peer_exchange_on_gpus_matches_oracle(oracle, tmp_path, fmt, tol):
+    world = 2
+    if torch.cuda.device_count() < world:
+        pytest.skip("needs two GPUs on one box")
+    dims = dict(T=96, H=512, E=16, K=4, I=256, S=1, fmt=fmt, bias=None)
+    mp.spawn(_gpu_rank_peer, args=(world, 29660 + ["bf16", "fp8", "fp4"].index(fmt), dims, 23, str(tmp_path)), nprocs=world, join=True)
+    d = synth.make_inputs(dict(dims, T=dims["T"] * world), seed=23)
+    ref = _oracle_ref(oracle, dims, d)
+    got = np.concatenate([np.load(tmp_path / f"out{r}.npy") for r in range(world)])
+    rel = synth.rel_l2(synth.bf16_bits_to_f32(got), synth.bf16_bits_to_f32(ref["out"]))
+    assert rel <= tol, rel

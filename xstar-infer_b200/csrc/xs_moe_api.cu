@@ -19,6 +19,7 @@
 #include "xs_mma_rate.cuh"
 #include "xs_permute.cuh"
 #include "xs_route.cuh"
+#include "xs_ep.cuh"
 
 namespace {
 
@@ -870,7 +871,11 @@ int xs_moe_permute(const XsMoeConfig *cfg, const int32_t *ids, int32_t *counts, 
 
 static GroupedPlan plan_grouped_stage(const XsMoeConfig *cfg, int max_rows)
 {
-    return plan_grouped(max_rows, max_rows, cfg->local_expert_count, cfg->local_expert_count, cfg->intermediate, cfg->routed_format,
+    // max_rows is a capacity (the expert-parallel buffers are sized for the worst routing); the tile shape follows the rows
+    // this rank expects, tokens x top_k, when that is smaller
+    const long expect = static_cast<long>(cfg->num_tokens) * cfg->top_k;
+    const int rows = expect > 0 && expect < max_rows ? static_cast<int>(expect) : max_rows;
+    return plan_grouped(max_rows, rows, cfg->local_expert_count, cfg->local_expert_count, cfg->intermediate, cfg->routed_format,
                         cfg->hidden);
 }
 
@@ -1350,6 +1355,124 @@ int xs_moe_forward_host(const XsMoeConfig *cfg, const XsMoeWeights *w, const voi
     XS_CUDA(cudaMemcpyAsync(out_host, out_stage, bytes, cudaMemcpyDeviceToHost, st));
     XS_CUDA(cudaStreamSynchronize(st));
     return xs_moe_check_flags(ws, stream);
+}
+
+// ---- expert parallelism over peer memory ---------------------------------------------------------------------------
+
+int xs_moe_ipc_export(void *ptr, uint8_t *handle)
+{
+    static_assert(sizeof(cudaIpcMemHandle_t) == XS_MOE_IPC_HANDLE_BYTES, "handle size");
+    if (!ptr || !handle)
+        return fail(XS_MOE_ERR_INVALID_ARG, "null pointer");
+    cudaIpcMemHandle_t h;
+    XS_CUDA(cudaIpcGetMemHandle(&h, ptr));
+    memcpy(handle, &h, sizeof(h));
+    return 0;
+}
+
+int xs_moe_ipc_import(const uint8_t *handle, void **ptr)
+{
+    if (!ptr || !handle)
+        return fail(XS_MOE_ERR_INVALID_ARG, "null pointer");
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle, sizeof(h));
+    void *p = nullptr;
+    XS_CUDA(cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess));
+    *ptr = p;
+    return 0;
+}
+
+int xs_moe_ipc_close(void *ptr)
+{
+    if (ptr)
+        XS_CUDA(cudaIpcCloseMemHandle(ptr));
+    return 0;
+}
+
+static int check_ep(int32_t ranks, int32_t rank, int32_t experts)
+{
+    if (ranks < 1 || ranks > 32 || rank < 0 || rank >= ranks)
+        return fail(XS_MOE_ERR_INVALID_ARG, "bad rank %d of %d (at most 32 ranks)", rank, ranks);
+    if (experts < 1 || experts > 1024 || experts % ranks != 0)
+        return fail(XS_MOE_ERR_INVALID_ARG, "expert count mismatch: %d experts must divide evenly over %d ranks (at most 1024)", experts,
+                    ranks);
+    return 0;
+}
+
+int xs_moe_ep_plan(const int32_t *all_counts, int32_t ranks, int32_t experts, int32_t rank, int32_t *dest_base, int32_t *offsets_local,
+                   int32_t *src_offsets, void *stream)
+{
+    if (int rc = check_ep(ranks, rank, experts))
+        return rc;
+    if (!all_counts || !dest_base || !offsets_local || !src_offsets)
+        return fail(XS_MOE_ERR_INVALID_ARG, "null tensor pointer");
+    int threads = ((experts > ranks ? experts : ranks) + 31) / 32 * 32;
+    xs::ep_plan_kernel<<<1, threads, 0, static_cast<cudaStream_t>(stream)>>>(all_counts, ranks, experts, rank, dest_base, offsets_local,
+                                                                            src_offsets);
+    XS_CUDA(cudaGetLastError());
+    return 0;
+}
+
+int xs_moe_ep_dispatch(const XsMoeConfig *cfg, int32_t ranks, const void *x, const int32_t *ids, const int32_t *inv,
+                       const int32_t *my_offsets, const int32_t *dest_base, void *const *peer_rows, void *const *peer_scales,
+                       int32_t capacity_rows, void *ws, void *stream)
+{
+    if (int rc = check_cfg(cfg))
+        return rc;
+    if (int rc = check_ep(ranks, 0, cfg->num_experts))
+        return rc;
+    if (!x || !ids || !inv || !my_offsets || !dest_base || !peer_rows || !ws || (cfg->routed_format != XS_MOE_BF16 && !peer_scales))
+        return fail(XS_MOE_ERR_INVALID_ARG, "null tensor pointer");
+    if (cfg->top_k > 32 || capacity_rows < 0 || cfg->hidden % 128 != 0)
+        return fail(XS_MOE_ERR_INVALID_ARG, "shape mismatch: top_k <= 32 and hidden a multiple of 128 are required");
+    if (cfg->num_tokens == 0)
+        return 0;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    auto rows = reinterpret_cast<uint8_t *const *>(peer_rows);
+    auto scales = reinterpret_cast<uint8_t *const *>(peer_scales);
+    auto xb = static_cast<const __nv_bfloat16 *>(x);
+    int32_t *status = static_cast<int32_t *>(ws);
+    const int T = cfg->num_tokens, H = cfg->hidden, K = cfg->top_k, E = cfg->num_experts;
+    if (cfg->routed_format == XS_MOE_BF16)
+        xs::ep_dispatch_kernel<0><<<T, 256, 0, st>>>(xb, ids, inv, my_offsets, dest_base, rows, scales, T, H, K, E, ranks, capacity_rows,
+                                                     status);
+    else if (cfg->routed_format == XS_MOE_FP8_BLOCK128)
+        xs::ep_dispatch_kernel<1><<<T, 256, 0, st>>>(xb, ids, inv, my_offsets, dest_base, rows, scales, T, H, K, E, ranks, capacity_rows,
+                                                     status);
+    else
+        xs::ep_dispatch_kernel<2><<<T, 256, 0, st>>>(xb, ids, inv, my_offsets, dest_base, rows, scales, T, H, K, E, ranks, capacity_rows,
+                                                     status);
+    XS_CUDA(cudaGetLastError());
+    return 0;
+}
+
+int xs_moe_ep_return(const XsMoeConfig *cfg, int32_t ranks, int32_t rank, const float *y_grouped, const int32_t *all_counts,
+                     const int32_t *offsets_local, const int32_t *src_offsets, void *const *peer_back, int32_t back_capacity_rows,
+                     int32_t wire_bf16, void *ws, void *stream)
+{
+    if (int rc = check_cfg(cfg))
+        return rc;
+    if (int rc = check_ep(ranks, rank, cfg->num_experts))
+        return rc;
+    if (!y_grouped || !all_counts || !offsets_local || !src_offsets || !peer_back || !ws)
+        return fail(XS_MOE_ERR_INVALID_ARG, "null tensor pointer");
+    if (back_capacity_rows < 0 || cfg->hidden % 8 != 0)
+        return fail(XS_MOE_ERR_INVALID_ARG, "shape mismatch");
+    DeviceInfo di;
+    if (int rc = device_info(&di))
+        return rc;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    auto back = reinterpret_cast<uint8_t *const *>(peer_back);
+    int32_t *status = static_cast<int32_t *>(ws);
+    const int grid = di.sms * 8;
+    if (wire_bf16)
+        xs::ep_return_kernel<true><<<grid, 256, 0, st>>>(y_grouped, all_counts, offsets_local, src_offsets, back, cfg->hidden,
+                                                         cfg->num_experts, ranks, rank, back_capacity_rows, status);
+    else
+        xs::ep_return_kernel<false><<<grid, 256, 0, st>>>(y_grouped, all_counts, offsets_local, src_offsets, back, cfg->hidden,
+                                                          cfg->num_experts, ranks, rank, back_capacity_rows, status);
+    XS_CUDA(cudaGetLastError());
+    return 0;
 }
 
 } // extern "C"

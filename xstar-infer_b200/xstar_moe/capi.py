@@ -36,12 +36,15 @@ class XsMoeWeights(C.Structure):
         "shared_gate_up_w_dev", "shared_gate_up_scale_dev", "shared_down_w_dev", "shared_down_scale_dev")]
 
 
+IPC_HANDLE_BYTES = 64
+
 EXPORTS = [
     "xs_moe_status_string", "xs_moe_last_error", "xs_moe_device_check", "xs_moe_device_alloc", "xs_moe_device_free",
     "xs_moe_memcpy_h2d", "xs_moe_memcpy_d2h", "xs_moe_memcpy_d2d", "xs_moe_device_free_bytes",
     "xs_moe_stream_synchronize", "xs_moe_workspace_bytes", "xs_moe_workspace_init", "xs_moe_forward",
     "xs_moe_forward_host", "xs_moe_forward_profile", "xs_moe_route", "xs_moe_permute", "xs_moe_permute_noalloc", "xs_moe_grouped_mlp_workspace_bytes",
     "xs_moe_grouped_mlp", "xs_moe_quantize_rows_fp8", "xs_moe_quantize_rows_mxfp8", "xs_moe_gather_rows", "xs_moe_combine", "xs_moe_combine_bf16_rows", "xs_moe_gather_rows_f32_to_bf16", "xs_moe_check_flags", "xs_moe_debug_counters", "xs_moe_probe_mma_rate",
+    "xs_moe_ipc_export", "xs_moe_ipc_import", "xs_moe_ipc_close", "xs_moe_ep_plan", "xs_moe_ep_dispatch", "xs_moe_ep_return",
 ]
 
 _lib = None
@@ -86,6 +89,12 @@ def lib():
             "xs_moe_check_flags": [vp, vp],
             "xs_moe_probe_mma_rate": [i32, i32, i32, i32, vp, sz, C.POINTER(C.c_double), C.POINTER(C.c_double), C.POINTER(C.c_double), vp],
             "xs_moe_debug_counters": [vp, C.POINTER(C.c_ulonglong), vp],
+            "xs_moe_ipc_export": [vp, vp],
+            "xs_moe_ipc_import": [vp, C.POINTER(vp)],
+            "xs_moe_ipc_close": [vp],
+            "xs_moe_ep_plan": [vp, i32, i32, i32, vp, vp, vp, vp],
+            "xs_moe_ep_dispatch": [cfgp, i32, vp, vp, vp, vp, vp, vp, vp, i32, vp, vp],
+            "xs_moe_ep_return": [cfgp, i32, i32, vp, vp, vp, vp, vp, i32, i32, vp, vp],
         }
         for name, args in sig.items():
             fn = getattr(L, name)

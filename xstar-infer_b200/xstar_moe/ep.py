@@ -181,6 +181,106 @@ class CudaOps:
 
 
 # ------------------------------------------------------------------------------------------------------------
+# exchange over peer memory (NVLink stores from the dispatch / return kernels; no host synchronisation)
+# ------------------------------------------------------------------------------------------------------------
+class DeviceBuffer:
+    """Raw device memory from the library's allocator: exportable to the other processes of the box, which a block
+    of torch's pooled allocator is not."""
+
+    def __init__(self, nbytes, dtype=torch.uint8):
+        self.nbytes, self.dtype = int(nbytes), dtype
+        p = C.c_void_p()
+        capi.check(capi.lib().xs_moe_device_alloc(C.byref(p), max(self.nbytes, 256)))
+        self._ptr = p.value
+
+    def data_ptr(self):
+        return self._ptr
+
+    def free(self):
+        if self._ptr:
+            capi.check(capi.lib().xs_moe_device_free(C.c_void_p(self._ptr)))
+            self._ptr = 0
+
+
+class PeerExchange:
+    """This rank's side of the peer-memory exchange: its receive buffers (grouped rows + scales, sized for the worst
+    routing: every token of every rank choosing this rank's experts), its return buffer (one row per local (token, slot)),
+    the small index tables, and the pointer tables of all ranks' buffers."""
+
+    def __init__(self, dims, rank, world, capacity=None):
+        T, H, E, K = (dims[k] for k in "THEK")
+        self.T, self.H, self.E, self.K, self.R, self.rank = T, H, E, K, world, rank
+        self.El = E // world
+        self.fmt = {"bf16": capi.BF16, "fp8": capi.FP8_BLOCK128, "fp4": capi.FP4_MX32}[dims["fmt"]]
+        self.capacity = int(capacity) if capacity is not None else world * T * K
+        self.back_rows = T * K
+        self.wire_bf16 = self.fmt != capi.BF16
+        row_bytes = H * 2 if self.fmt == capi.BF16 else H
+        scale_bytes = {capi.BF16: 0, capi.FP8_BLOCK128: (H // 128) * 4, capi.FP4_MX32: H // 32}[self.fmt]
+        self.rows = DeviceBuffer(self.capacity * row_bytes)
+        self.scales = DeviceBuffer(self.capacity * scale_bytes, torch.float32 if self.fmt == capi.FP8_BLOCK128 else torch.uint8)
+        self.back = DeviceBuffer(self.back_rows * H * (2 if self.wire_bf16 else 4), torch.bfloat16 if self.wire_bf16 else torch.float32)
+        self.dest_base = torch.zeros(E, dtype=torch.int32, device="cuda")
+        self.offsets_local = torch.zeros(self.El + 1, dtype=torch.int32, device="cuda")
+        self.src_offsets = torch.zeros(world * E, dtype=torch.int32, device="cuda")
+        self.cfg = capi.make_config(T, H, E, K, dims["I"], 0, self.fmt, self.fmt)
+        self.L = capi.lib()
+        self._imported = []
+        self.tables = None
+
+    def connect(self, rows_ptrs, scales_ptrs, back_ptrs):
+        """Addresses of every rank's buffers as this process sees them (index = rank)."""
+        self.tables = torch.tensor([rows_ptrs, scales_ptrs, back_ptrs], dtype=torch.int64, device="cuda")
+
+    def connect_ipc(self, group=None):
+        """Exchange handles with the other processes of the box and map their buffers."""
+        mine = torch.zeros(3, capi.IPC_HANDLE_BYTES, dtype=torch.uint8)
+        for i, b in enumerate((self.rows, self.scales, self.back)):
+            capi.check(self.L.xs_moe_ipc_export(C.c_void_p(b.data_ptr()), C.c_void_p(mine[i].data_ptr())))
+        every = torch.empty(self.R, 3, capi.IPC_HANDLE_BYTES, dtype=torch.uint8, device="cuda")
+        dist.all_gather_into_tensor(every.view(-1), mine.cuda().view(-1), group=group)
+        every = every.cpu()
+        ptrs = [[0] * self.R for _ in range(3)]
+        for r in range(self.R):
+            for i, b in enumerate((self.rows, self.scales, self.back)):
+                if r == self.rank:
+                    ptrs[i][r] = b.data_ptr()
+                else:
+                    p = C.c_void_p()
+                    h = every[r, i].contiguous()
+                    capi.check(self.L.xs_moe_ipc_import(C.c_void_p(h.data_ptr()), C.byref(p)))
+                    self._imported.append(p.value)
+                    ptrs[i][r] = p.value
+        self.connect(*ptrs)
+
+    @staticmethod
+    def _st():
+        return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+    def plan(self, all_counts):
+        capi.check(self.L.xs_moe_ep_plan(capi.ptr(all_counts), self.R, self.E, self.rank, capi.ptr(self.dest_base),
+                                         capi.ptr(self.offsets_local), capi.ptr(self.src_offsets), self._st()))
+
+    def dispatch(self, x, ids, inv, offsets, ws):
+        capi.check(self.L.xs_moe_ep_dispatch(C.byref(self.cfg), self.R, capi.ptr(x), capi.ptr(ids), capi.ptr(inv), capi.ptr(offsets),
+                                             capi.ptr(self.dest_base), capi.ptr(self.tables[0]), capi.ptr(self.tables[1]),
+                                             self.capacity, capi.ptr(ws), self._st()))
+
+    def give_back(self, y_grouped, all_counts, ws):
+        capi.check(self.L.xs_moe_ep_return(C.byref(self.cfg), self.R, self.rank, capi.ptr(y_grouped), capi.ptr(all_counts),
+                                           capi.ptr(self.offsets_local), capi.ptr(self.src_offsets), capi.ptr(self.tables[2]),
+                                           self.back_rows, int(self.wire_bf16), capi.ptr(ws), self._st()))
+
+    def close(self):
+        """Unmap the peers' buffers and free this rank's (call on every rank, after a barrier)."""
+        for p in self._imported:
+            capi.check(self.L.xs_moe_ipc_close(C.c_void_p(p)))
+        self._imported = []
+        for b in (self.rows, self.scales, self.back):
+            b.free()
+
+
+# ------------------------------------------------------------------------------------------------------------
 # the layer
 # ------------------------------------------------------------------------------------------------------------
 class ExpertParallelMoE:
@@ -215,6 +315,52 @@ class ExpertParallelMoE:
             return out
         dist.all_to_all_single(out, t.contiguous(), [int(v) for v in out_splits], [int(v) for v in in_splits], group=self.group)
         return out
+
+    def forward_peer(self, x, px, marks=None):
+        """The layer with both exchanges as peer-memory kernels (`px`: this rank's connected PeerExchange).  Nothing
+        here synchronises with the host; the two barriers are one-element all-reduces on the stream."""
+        ops = self.ops
+
+        def mark(name):
+            if marks is not None:
+                ev = torch.cuda.Event(enable_timing=True)
+                ev.record()
+                marks.append((name, ev))
+
+        mark("start")
+        side = ops.side_stream
+        shared = None
+        if self.S:
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                shared = ops.shared_mlp(x, None)
+        ids, w = ops.route(x, self.router_w, self.router_bias)
+        counts, offsets, perm, inv = ops.permute(ids)
+        mark("route+permute")
+        all_counts = self._all_gather_counts_start(counts)
+        px.plan(all_counts)
+        mark("counts exchange + plan (device)")
+        px.dispatch(x, ids, inv, offsets, ops.ws)
+        self._barrier()
+        mark("dispatch (peer stores) + barrier")
+        y_grouped = ops.grouped_mlp([px.rows, px.scales if px.fmt != capi.BF16 else None], px.offsets_local, px.capacity)
+        mark("grouped expert MLP")
+        px.give_back(y_grouped, all_counts, ops.ws)
+        self._barrier()
+        mark("return (peer stores) + barrier")
+        if self.S:
+            torch.cuda.current_stream().wait_stream(side)
+            shared.record_stream(torch.cuda.current_stream())
+        mark("always-on expert")
+        out = ops.combine(px.back, inv, w, shared)
+        mark("combine")
+        return out
+
+    def _barrier(self):
+        if self.world > 1:
+            if not hasattr(self, "_token"):
+                self._token = torch.zeros(1, dtype=torch.int32, device="cuda")
+            dist.all_reduce(self._token, group=self.group)
 
     def forward(self, x, marks=None):
         """marks: optional list; when given, (name, cuda event) pairs are appended after each phase (device ops only)."""
