@@ -15,6 +15,7 @@ CPU oracle) on the host cores instead.
 """
 import argparse
 import ctypes as C
+import datetime
 import json
 import os
 import subprocess
@@ -366,7 +367,7 @@ def run_ours_ep(args, dims):
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     torch.cuda.set_device(local_rank)
-    dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank), timeout=datetime.timedelta(seconds=180))
     capi.check(capi.lib().xs_moe_device_check())
     strong = args.workload == "ep_fp4"  # this workload fixes the GLOBAL batch (16384 tokens) and splits it over the ranks
     if strong:
@@ -387,13 +388,28 @@ def run_ours_ep(args, dims):
     def forward(xd, marks=None):
         return layer.forward_peer(xd, px, marks) if peer else layer.forward(xd, marks)
 
-    def step():
-        return forward(x)
+    use_graph = peer and (args.graph == "on" or (args.graph == "auto" and T <= 1024))
+    if use_graph:
+        x_static = x.clone()
+        graph, out_static = layer.capture_peer(x_static, px)
 
-    def step_host():
-        xd = x_host.to("cuda", non_blocking=True)
-        out_host.copy_(forward(xd), non_blocking=True)
-        torch.cuda.synchronize()
+        def step():
+            graph.replay()
+            return out_static
+
+        def step_host():
+            x_static.copy_(x_host, non_blocking=True)
+            graph.replay()
+            out_host.copy_(out_static, non_blocking=True)
+            torch.cuda.synchronize()
+    else:
+        def step():
+            return forward(x)
+
+        def step_host():
+            xd = x_host.to("cuda", non_blocking=True)
+            out_host.copy_(forward(xd), non_blocking=True)
+            torch.cuda.synchronize()
 
     def barrier():
         dist.barrier()
@@ -460,7 +476,7 @@ def run_ours_ep(args, dims):
             "dtype": dims["fmt"], "data": "synthetic (seeded: weights N(0,0.02), activations N(0,1), rounded once to storage)",
             "config": dict(workload=args.workload, **{k: dims[k] for k in "THEKIS"}, format=dims["fmt"], tokens_per_rank=T,
                            experts_per_rank=E // world, parallelism=f"ep{world}: experts sharded, " + ("dispatch/return by peer-memory stores over NVLink, no host synchronisation"
-                                                                           if peer else "NCCL all-to-all dispatch/combine"),
+                                                                           if peer else "NCCL all-to-all dispatch/combine"), cuda_graph=bool(use_graph),
                            l2="inputs larger than L2: expert weights streamed per step exceed 126 MB"),
             "e2e": {"value": tokens / (ms_e2e * 1e-3), "unit": UNIT, "h2d_bytes_per_step": T * H * 2, "d2h_bytes_per_step": T * H * 2,
                     "ms_per_step": ms_e2e / args.steps},
@@ -473,8 +489,10 @@ def run_ours_ep(args, dims):
             "cpu_baseline": None, "clocks": clocks,
         }
         print(json.dumps(line), flush=True)
+    torch.cuda.synchronize()
+    if use_graph:
+        graph.reset()  # a live graph holds the communicator; destroy_process_group would block on it
     if px is not None:
-        torch.cuda.synchronize()
         dist.barrier()
         px.close()
     dist.destroy_process_group()

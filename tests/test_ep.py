@@ -1,5 +1,6 @@
 """Expert parallelism: the host-side planning on its own, the whole exchange on two CPU ranks (gloo) with a
 stand-in for the device ops, and -- where two GPUs are visible -- the real thing over NCCL."""
+import datetime
 import os
 import sys
 
@@ -144,7 +145,8 @@ def _gpu_rank(rank, world, port, dims, seed, result_dir):
     os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
     os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
     torch.cuda.set_device(rank)
-    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank),
+                            timeout=datetime.timedelta(seconds=90))
     try:
         d = synth.make_inputs(dict(dims, T=dims["T"] * world), seed=seed)  # CPU generator: identical on every rank
         T, El = dims["T"], dims["E"] // world
@@ -277,12 +279,41 @@ def test_peer_exchange_flags_a_buffer_that_is_too_small(oracle):
             k["px"].close()
 
 
+@pytest.mark.gpu
+@pytest.mark.parametrize("fmt", ["bf16", "fp4"])
+def test_peer_step_replays_as_cuda_graph_on_one_rank(oracle, fmt):
+    """World size 1 (no collective): the whole step -- route, permute, plan, dispatch, grouped MLP, return, always-on
+    expert on its side stream, combine -- captured once and replayed on new inputs."""
+    dims = dict(T=48, H=512, E=16, K=4, I=256, S=1, fmt=fmt, bias=None)
+    d, ranks = _virtual_ranks(dims, 1, seed=41)
+    k = ranks[0]
+    try:
+        layer = ep.ExpertParallelMoE(k["ops"], k["ops"].keep[0]["router_w"], None, dims["E"], dims["K"], dims["S"])
+        eager = layer.forward_peer(k["x"], k["px"])
+        x_static = k["x"].clone()
+        graph, out_static = layer.capture_peer(x_static, k["px"])
+        graph.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(out_static, eager)
+        x2 = torch.roll(k["x"], 7, dims=0).contiguous()  # other tokens, other routing counts
+        x_static.copy_(x2)
+        graph.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(out_static, layer.forward_peer(x2, k["px"]))
+        k["ops"].check()
+    finally:
+        torch.cuda.synchronize()
+        k["px"].close()
+
+
 def _gpu_rank_peer(rank, world, port, dims, seed, result_dir):
     os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
     os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
     torch.cuda.set_device(rank)
-    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank),
+                            timeout=datetime.timedelta(seconds=90))
     px = None
+    done = False
     try:
         d = synth.make_inputs(dict(dims, T=dims["T"] * world), seed=seed)
         T, El = dims["T"], dims["E"] // world
@@ -302,13 +333,25 @@ def _gpu_rank_peer(rank, world, port, dims, seed, result_dir):
         torch.cuda.synchronize()
         assert torch.equal(out, out2)
         assert torch.equal(out, via_nccl), "peer-memory exchange and all-to-all exchange disagree"
+        # the same step captured once and replayed as a CUDA graph
+        x_static = x_local.clone()
+        graph, out_static = layer.capture_peer(x_static, px)
+        for _ in range(2):
+            out_static.zero_()
+            graph.replay()
+            torch.cuda.synchronize()
+            assert torch.equal(out_static, out)
+        ops.check()
+        graph.reset()  # a live graph holds the communicator: release it before the process group goes away
+        del graph
         np.save(os.path.join(result_dir, f"out{rank}.npy"), out.cpu().view(torch.uint16).numpy())
+        done = True
     finally:
         torch.cuda.synchronize()
-        dist.barrier()
-        if px is not None:
+        if done:  # a rank that failed leaves without a collective: the other one must not wait for it
+            dist.barrier()
             px.close()
-        dist.destroy_process_group()
+            dist.destroy_process_group()
 
 
 @pytest.mark.gpu

@@ -356,6 +356,24 @@ class ExpertParallelMoE:
         mark("combine")
         return out
 
+    def capture_peer(self, x_static, px):
+        """forward_peer(x_static, px) as a CUDA graph -- possible because nothing in it returns to the host: every
+        size the kernels and the collectives need is fixed (buffers sized for the worst routing), every count is read
+        on the device.  Returns (graph, out_static); refill x_static, replay, read out_static.  Collective: every
+        rank captures, and later replays, the same number of times.  The graph holds the communicator: call
+        graph.reset() before the process group is destroyed, or the destroy blocks."""
+        warm = torch.cuda.Stream()
+        warm.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(warm):
+            for _ in range(2):
+                self.forward_peer(x_static, px)
+        torch.cuda.current_stream().wait_stream(warm)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            out = self.forward_peer(x_static, px)
+        return graph, out
+
     def _barrier(self):
         if self.world > 1:
             if not hasattr(self, "_token"):
