@@ -380,10 +380,15 @@ def run_ours_ep(args, dims):
     x_host = x.cpu().pin_memory()
     out_host = torch.empty_like(x_host).pin_memory()
     peer = args.exchange == "peer"
-    px = None
+    px, fallback = None, None
     if peer:
         px = ep.PeerExchange(dims, rank, world)
-        px.connect_ipc()
+        try:
+            px.connect_ipc()
+        except RuntimeError as e:  # agreed on by all ranks: no peer mappings on this box -> all-to-all exchange everywhere
+            fallback = str(e)
+            px.close()
+            px, peer = None, False
 
     def forward(xd, marks=None):
         return layer.forward_peer(xd, px, marks) if peer else layer.forward(xd, marks)
@@ -476,7 +481,7 @@ def run_ours_ep(args, dims):
             "dtype": dims["fmt"], "data": "synthetic (seeded: weights N(0,0.02), activations N(0,1), rounded once to storage)",
             "config": dict(workload=args.workload, **{k: dims[k] for k in "THEKIS"}, format=dims["fmt"], tokens_per_rank=T,
                            experts_per_rank=E // world, parallelism=f"ep{world}: experts sharded, " + ("dispatch/return by peer-memory stores over NVLink, no host synchronisation"
-                                                                           if peer else "NCCL all-to-all dispatch/combine"), cuda_graph=bool(use_graph),
+                                                                           if peer else "NCCL all-to-all dispatch/combine"), cuda_graph=bool(use_graph), exchange_fallback=fallback,
                            l2="inputs larger than L2: expert weights streamed per step exceed 126 MB"),
             "e2e": {"value": tokens / (ms_e2e * 1e-3), "unit": UNIT, "h2d_bytes_per_step": T * H * 2, "d2h_bytes_per_step": T * H * 2,
                     "ms_per_step": ms_e2e / args.steps},

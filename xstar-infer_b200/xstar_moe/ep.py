@@ -233,24 +233,37 @@ class PeerExchange:
         self.tables = torch.tensor([rows_ptrs, scales_ptrs, back_ptrs], dtype=torch.int64, device="cuda")
 
     def connect_ipc(self, group=None):
-        """Exchange handles with the other processes of the box and map their buffers."""
+        """Exchange handles with the other processes of the box and map their buffers.  Collective; the ranks agree on
+        the outcome before any of them raises, so a caller may fall back to the all-to-all exchange on every rank."""
+        err = None
         mine = torch.zeros(3, capi.IPC_HANDLE_BYTES, dtype=torch.uint8)
-        for i, b in enumerate((self.rows, self.scales, self.back)):
-            capi.check(self.L.xs_moe_ipc_export(C.c_void_p(b.data_ptr()), C.c_void_p(mine[i].data_ptr())))
+        try:
+            for i, b in enumerate((self.rows, self.scales, self.back)):
+                capi.check(self.L.xs_moe_ipc_export(C.c_void_p(b.data_ptr()), C.c_void_p(mine[i].data_ptr())))
+        except RuntimeError as e:
+            err = e
         every = torch.empty(self.R, 3, capi.IPC_HANDLE_BYTES, dtype=torch.uint8, device="cuda")
         dist.all_gather_into_tensor(every.view(-1), mine.cuda().view(-1), group=group)
         every = every.cpu()
         ptrs = [[0] * self.R for _ in range(3)]
-        for r in range(self.R):
-            for i, b in enumerate((self.rows, self.scales, self.back)):
-                if r == self.rank:
-                    ptrs[i][r] = b.data_ptr()
-                else:
-                    p = C.c_void_p()
-                    h = every[r, i].contiguous()
-                    capi.check(self.L.xs_moe_ipc_import(C.c_void_p(h.data_ptr()), C.byref(p)))
-                    self._imported.append(p.value)
-                    ptrs[i][r] = p.value
+        try:
+            for r in range(self.R if err is None else 0):
+                for i, b in enumerate((self.rows, self.scales, self.back)):
+                    if r == self.rank:
+                        ptrs[i][r] = b.data_ptr()
+                    else:
+                        p = C.c_void_p()
+                        h = every[r, i].contiguous()
+                        capi.check(self.L.xs_moe_ipc_import(C.c_void_p(h.data_ptr()), C.byref(p)))
+                        self._imported.append(p.value)
+                        ptrs[i][r] = p.value
+        except RuntimeError as e:
+            err = e
+        ok = torch.tensor([0 if err is not None else 1], dtype=torch.int32, device="cuda")
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=group)
+        if int(ok.item()) == 0:
+            self._unmap()
+            raise RuntimeError(f"peer mapping failed on at least one rank ({err if err is not None else 'another rank'})")
         self.connect(*ptrs)
 
     @staticmethod
@@ -273,11 +286,14 @@ class PeerExchange:
 
     def close(self):
         """Unmap the peers' buffers and free this rank's (call on every rank, after a barrier)."""
+        self._unmap()
+        for b in (self.rows, self.scales, self.back):
+            b.free()
+
+    def _unmap(self):
         for p in self._imported:
             capi.check(self.L.xs_moe_ipc_close(C.c_void_p(p)))
         self._imported = []
-        for b in (self.rows, self.scales, self.back):
-            b.free()
 
 
 # ------------------------------------------------------------------------------------------------------------
