@@ -8,6 +8,7 @@
 
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 #include <string>
@@ -265,13 +266,26 @@ int check_workspace(const void *ws, size_t have, size_t need)
 }
 
 // ---- launches --------------------------------------------------------------------------------------------
+constexpr int kRouterSmallTokens = 32;
+
 int launch_logits(const XsMoeConfig *c, const void *x, const void *rw, float *logits, cudaStream_t st)
 {
     const int T = c->num_tokens, H = c->hidden, E = c->num_experts;
     if (T == 0)
         return 0;
     const __nv_bfloat16 *xb = static_cast<const __nv_bfloat16 *>(x), *rwb = static_cast<const __nv_bfloat16 *>(rw);
-    if (T <= 1024) {
+    if (T <= kRouterSmallTokens) {
+        // a few tokens per SM at most: one warp per block, lane = expert, one token per block
+        static bool configured_rs[64] = {};
+        int dev_rs = 0;
+        XS_CUDA(cudaGetDevice(&dev_rs));
+        if (dev_rs >= 64 || !configured_rs[dev_rs]) {
+            XS_CUDA(cudaFuncSetAttribute(xs::router_logits_small_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, xs::rs_smem_bytes<1>()));
+            if (dev_rs < 64)
+                configured_rs[dev_rs] = true;
+        }
+        xs::router_logits_small_kernel<1><<<dim3((E + 31) / 32, T), 32, xs::rs_smem_bytes<1>(), st>>>(xb, rwb, logits, T, H, E);
+    } else if (T <= 1024) {
         // decode-sized batch: one output per thread, 8 experts x 32 tokens per block, cp.async pipeline
         dim3 grid((E + xs::kRdExperts - 1) / xs::kRdExperts, (T + xs::kRdTokens - 1) / xs::kRdTokens);
         static bool configured_rd[64] = {};
@@ -288,16 +302,16 @@ int launch_logits(const XsMoeConfig *c, const void *x, const void *rw, float *lo
         int dev = 0;
         XS_CUDA(cudaGetDevice(&dev));
         if (dev >= 64 || !configured[dev]) {
-            XS_CUDA(cudaFuncSetAttribute(xs::router_logits_pair_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, xs::rp_smem_bytes<4>()));
-            XS_CUDA(cudaFuncSetAttribute(xs::router_logits_pair_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, xs::rp_smem_bytes<2>()));
+            XS_CUDA(cudaFuncSetAttribute(xs::router_logits_big_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, xs::rb_smem_bytes<4>()));
+            XS_CUDA(cudaFuncSetAttribute(xs::router_logits_big_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, xs::rb_smem_bytes<2>()));
             if (dev < 64)
                 configured[dev] = true;
         }
         const int eg = (E + xs::kRbExperts - 1) / xs::kRbExperts;
         if (static_cast<long>(eg) * ((T + 63) / 64) >= 256)
-            xs::router_logits_pair_kernel<4><<<dim3(eg, (T + 63) / 64), xs::kRbThreads, xs::rp_smem_bytes<4>(), st>>>(xb, rwb, logits, T, H, E);
+            xs::router_logits_big_kernel<4><<<dim3(eg, (T + 63) / 64), xs::kRbThreads, xs::rb_smem_bytes<4>(), st>>>(xb, rwb, logits, T, H, E);
         else // 32-token tiles keep more SMs busy on medium batches
-            xs::router_logits_pair_kernel<2><<<dim3(eg, (T + 31) / 32), xs::kRbThreads, xs::rp_smem_bytes<2>(), st>>>(xb, rwb, logits, T, H, E);
+            xs::router_logits_big_kernel<2><<<dim3(eg, (T + 31) / 32), xs::kRbThreads, xs::rb_smem_bytes<2>(), st>>>(xb, rwb, logits, T, H, E);
     }
     XS_CUDA(cudaGetLastError());
     return 0;

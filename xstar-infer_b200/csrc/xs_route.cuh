@@ -118,138 +118,6 @@ router_logits_big_kernel(const __nv_bfloat16 *__restrict__ x, const __nv_bfloat1
     }
 }
 
-// The same tile with the f32 FMAs issued two at a time (fma.rn.f32x2: two independent IEEE FMAs per instruction, so
-// every accumulator still sees k = 0, 1, 2, ... one rounding per step).  For that the operands sit k-major in shared
-// memory -- sm[k][token columns | expert columns] -- so that one 16-byte read yields four neighbouring experts (two
-// packed operands) at one k; a thread owns TPT consecutive tokens and experts {4 tx .. 4 tx + 3, 64 + 4 tx .. 64 + 4 tx + 3}.
-// Per k and thread: 3 shared reads, 4 * TPT packed FMAs.  The transposing stores of the staging step are conflict-free
-// because consecutive lanes stage consecutive rows.
-__device__ __forceinline__ void fma2(float2 &acc, const float2 a, const float2 b)
-{
-    unsigned long long &c = reinterpret_cast<unsigned long long &>(acc);
-    asm("fma.rn.f32x2 %0, %1, %2, %0;"
-        : "+l"(c)
-        : "l"(reinterpret_cast<const unsigned long long &>(a)), "l"(reinterpret_cast<const unsigned long long &>(b)));
-}
-
-template <int TPT>
-constexpr int rp_smem_bytes()
-{
-    return 2 * kRbK * (16 * TPT + kRbExperts) * 4;
-}
-template <int TPT>
-__global__ void __launch_bounds__(kRbThreads, 2)
-router_logits_pair_kernel(const __nv_bfloat16 *__restrict__ x, const __nv_bfloat16 *__restrict__ rw, float *__restrict__ logits,
-                          int T, int H, int E)
-{
-    constexpr int TOK = 16 * TPT;
-    constexpr int ROWS = TOK + kRbExperts;
-    constexpr int PIECES = ROWS * 4; // 16-byte pieces (8 bf16 along k) per k chunk of 32
-    constexpr int PPT = (PIECES + kRbThreads - 1) / kRbThreads;
-    extern __shared__ __align__(16) float rp_smem[];
-    float (*sm)[kRbK][ROWS] = reinterpret_cast<float (*)[kRbK][ROWS]>(rp_smem);
-    const int tid = threadIdx.x;
-    const int tx = tid & 15, ty = tid >> 4;
-    const int t0 = blockIdx.y * TOK, e0 = blockIdx.x * kRbExperts;
-    uint4 stage_regs[PPT];
-    auto fetch = [&](int k0) {
-#pragma unroll
-        for (int i = 0; i < PPT; i++) {
-            const int p = tid + i * kRbThreads;
-            const int r = p % ROWS, c = (p / ROWS) * 8;
-            uint4 v = make_uint4(0, 0, 0, 0);
-            if (p < PIECES) {
-                if (r < TOK) {
-                    if (t0 + r < T)
-                        v = __ldg(reinterpret_cast<const uint4 *>(x + static_cast<size_t>(t0 + r) * H + k0 + c));
-                } else if (e0 + r - TOK < E) {
-                    v = __ldg(reinterpret_cast<const uint4 *>(rw + static_cast<size_t>(e0 + r - TOK) * H + k0 + c));
-                }
-            }
-            stage_regs[i] = v;
-        }
-    };
-    auto stash = [&](int buf) {
-#pragma unroll
-        for (int i = 0; i < PPT; i++) {
-            const int p = tid + i * kRbThreads;
-            if (p >= PIECES)
-                continue;
-            const int r = p % ROWS, c = (p / ROWS) * 8;
-            const uint4 v = stage_regs[i];
-            sm[buf][c + 0][r] = __uint_as_float(v.x << 16);
-            sm[buf][c + 1][r] = __uint_as_float(v.x & 0xffff0000u);
-            sm[buf][c + 2][r] = __uint_as_float(v.y << 16);
-            sm[buf][c + 3][r] = __uint_as_float(v.y & 0xffff0000u);
-            sm[buf][c + 4][r] = __uint_as_float(v.z << 16);
-            sm[buf][c + 5][r] = __uint_as_float(v.z & 0xffff0000u);
-            sm[buf][c + 6][r] = __uint_as_float(v.w << 16);
-            sm[buf][c + 7][r] = __uint_as_float(v.w & 0xffff0000u);
-        }
-    };
-    float2 acc[TPT][4];
-#pragma unroll
-    for (int i = 0; i < TPT; i++)
-#pragma unroll
-        for (int j = 0; j < 4; j++)
-            acc[i][j] = make_float2(0.0f, 0.0f);
-    fetch(0);
-    stash(0);
-    __syncthreads();
-    const int chunks = H / kRbK;
-    for (int ch = 0; ch < chunks; ch++) {
-        const int buf = ch & 1;
-        if (ch + 1 < chunks)
-            fetch((ch + 1) * kRbK);
-#pragma unroll 8
-        for (int k = 0; k < kRbK; k++) {
-            float xv[TPT];
-            if constexpr (TPT == 4) {
-                const float4 v = *reinterpret_cast<const float4 *>(&sm[buf][k][ty * 4]);
-                xv[0] = v.x, xv[1] = v.y, xv[2] = v.z, xv[3] = v.w;
-            } else {
-                const float2 v = *reinterpret_cast<const float2 *>(&sm[buf][k][ty * 2]);
-                xv[0] = v.x, xv[1] = v.y;
-            }
-            const float4 wa = *reinterpret_cast<const float4 *>(&sm[buf][k][TOK + tx * 4]);
-            const float4 wb = *reinterpret_cast<const float4 *>(&sm[buf][k][TOK + 64 + tx * 4]);
-            const float2 w0 = make_float2(wa.x, wa.y), w1 = make_float2(wa.z, wa.w);
-            const float2 w2 = make_float2(wb.x, wb.y), w3 = make_float2(wb.z, wb.w);
-#pragma unroll
-            for (int i = 0; i < TPT; i++) {
-                const float2 xx = make_float2(xv[i], xv[i]);
-                fma2(acc[i][0], xx, w0);
-                fma2(acc[i][1], xx, w1);
-                fma2(acc[i][2], xx, w2);
-                fma2(acc[i][3], xx, w3);
-            }
-        }
-        if (ch + 1 < chunks)
-            stash(buf ^ 1);
-        __syncthreads();
-    }
-#pragma unroll
-    for (int i = 0; i < TPT; i++) {
-        const int t = t0 + ty * TPT + i;
-        if (t >= T)
-            continue;
-#pragma unroll
-        for (int h = 0; h < 2; h++) {
-            const int e = e0 + 64 * h + tx * 4;
-            float *dst = logits + static_cast<size_t>(t) * E + e;
-            const float2 a = acc[i][2 * h], b = acc[i][2 * h + 1];
-            if (e + 3 < E && (E & 3) == 0) {
-                *reinterpret_cast<float4 *>(dst) = make_float4(a.x, a.y, b.x, b.y);
-            } else {
-                const float v[4] = {a.x, a.y, b.x, b.y};
-                for (int j = 0; j < 4; j++)
-                    if (e + j < E)
-                        dst[j] = v[j];
-            }
-        }
-    }
-}
-
 // Decode-sized batches.  Block = 8 experts x 32 tokens, one output per thread (warp = one expert, lanes = tokens),
 // so a batch of 128 tokens x 256 experts spreads over 128 SMs.  Operands arrive through an 8-stage cp.async
 // pipeline of 128-wide k chunks; inside a chunk each thread walks k upwards, 8 elements per 16-byte shared-memory
@@ -331,6 +199,118 @@ router_logits_decode_kernel(const __nv_bfloat16 *__restrict__ x, const __nv_bflo
     const int e = e0 + el, t = t0 + tl;
     if (e < E && t < T)
         logits[static_cast<size_t>(t) * E + e] = acc;
+}
+
+// The smallest batches (a few tokens per SM at most): the floor of the router is the chain of H dependent FMAs of one
+// output (about 10 us at H = 4096), so the kernel is built to keep that chain fed and nothing else in its way.  One WARP
+// per block: lane = expert (32 experts per block), TPW tokens per lane (the launcher uses 1: one token per block; more
+// chains per lane measured slower).  Router rows arrive through a 4-stage
+// cp.async pipeline of 128-wide k chunks and are widened on the fly (one ALU operation per k); the token rows are widened
+// ONCE per chunk by the whole warp into an f32 buffer (so the per-lane cost of a token operand is a broadcast shared
+// read, not a conversion), one chunk ahead of the FMAs that use it.  With a single warp there is no block barrier;
+// __syncwarp orders the hand-overs.  Same contract: every accumulator sees k = 0, 1, 2, ... in order.
+constexpr int kRsK = 128, kRsStages = 4, kRsWStride = kRsK + 8; // bf16 elements; 272-byte rows are conflict-free for 16-byte reads
+template <int TPW>
+constexpr int rs_smem_bytes()
+{
+    return kRsStages * (32 * kRsWStride + TPW * kRsK) * 2 + 2 * TPW * kRsK * 4;
+}
+template <int TPW>
+__global__ void __launch_bounds__(32)
+router_logits_small_kernel(const __nv_bfloat16 *__restrict__ x, const __nv_bfloat16 *__restrict__ rw, float *__restrict__ logits,
+                           int T, int H, int E)
+{
+    extern __shared__ __align__(16) uint8_t rs_smem[];
+    __nv_bfloat16 (*wsm)[32][kRsWStride] = reinterpret_cast<__nv_bfloat16 (*)[32][kRsWStride]>(rs_smem);
+    __nv_bfloat16 (*xsm)[TPW][kRsK] =
+        reinterpret_cast<__nv_bfloat16 (*)[TPW][kRsK]>(rs_smem + kRsStages * 32 * kRsWStride * 2);
+    float (*xf)[TPW][kRsK] = reinterpret_cast<float (*)[TPW][kRsK]>(rs_smem + kRsStages * (32 * kRsWStride + TPW * kRsK) * 2);
+    const int lane = threadIdx.x;
+    const int e0 = blockIdx.x * 32, t0 = blockIdx.y * TPW;
+    const int chunks = H / kRsK;
+
+    auto issue = [&](int ch, int st) {
+        const int k0 = ch * kRsK;
+#pragma unroll
+        for (int i = 0; i < 16; i++) { // 32 router rows x 16 pieces of 8 bf16
+            const int p = lane + 32 * i;
+            const int r = p >> 4, c = (p & 15) * 8;
+            const bool ok = e0 + r < E;
+            cp_async16(&wsm[st][r][c], rw + static_cast<size_t>(ok ? e0 + r : 0) * H + k0 + c, ok);
+        }
+#pragma unroll
+        for (int i = 0; i < (TPW * 16 + 31) / 32; i++) {
+            const int p = lane + 32 * i;
+            if (p < TPW * 16) {
+                const int r = p >> 4, c = (p & 15) * 8;
+                const bool ok = t0 + r < T;
+                cp_async16(&xsm[st][r][c], x + static_cast<size_t>(ok ? t0 + r : 0) * H + k0 + c, ok);
+            }
+        }
+    };
+    auto widen = [&](int st, int buf) { // token rows of one chunk: bf16 -> f32, 4 elements per lane and token
+#pragma unroll
+        for (int j = 0; j < TPW; j++) {
+            const uint2 v = *reinterpret_cast<const uint2 *>(&xsm[st][j][lane * 4]);
+            *reinterpret_cast<float4 *>(&xf[buf][j][lane * 4]) =
+                make_float4(__uint_as_float(v.x << 16), __uint_as_float(v.x & 0xffff0000u), __uint_as_float(v.y << 16),
+                            __uint_as_float(v.y & 0xffff0000u));
+        }
+    };
+
+#pragma unroll
+    for (int s = 0; s < kRsStages - 1; s++) {
+        if (s < chunks)
+            issue(s, s);
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    }
+    asm volatile("cp.async.wait_group %0;" ::"n"(kRsStages - 2) : "memory");
+    __syncwarp();
+    widen(0, 0);
+    float acc[TPW];
+#pragma unroll
+    for (int j = 0; j < TPW; j++)
+        acc[j] = 0.0f;
+    for (int ch = 0; ch < chunks; ch++) {
+        asm volatile("cp.async.wait_group %0;" ::"n"(kRsStages - 3) : "memory"); // chunk ch + 1 has landed
+        __syncwarp(); // ... for every lane; every lane has finished chunk ch - 1; xf[ch & 1] is written
+        const int nxt = ch + kRsStages - 1;
+        if (nxt < chunks)
+            issue(nxt, nxt % kRsStages);
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        if (ch + 1 < chunks)
+            widen((ch + 1) % kRsStages, (ch + 1) & 1);
+        const int st = ch % kRsStages, buf = ch & 1;
+        const uint4 *wp = reinterpret_cast<const uint4 *>(&wsm[st][lane][0]);
+#pragma unroll 4
+        for (int i = 0; i < kRsK / 8; i++) {
+            const uint4 w = wp[i];
+            const float w0 = __uint_as_float(w.x << 16), w1 = __uint_as_float(w.x & 0xffff0000u);
+            const float w2 = __uint_as_float(w.y << 16), w3 = __uint_as_float(w.y & 0xffff0000u);
+            const float w4 = __uint_as_float(w.z << 16), w5 = __uint_as_float(w.z & 0xffff0000u);
+            const float w6 = __uint_as_float(w.w << 16), w7 = __uint_as_float(w.w & 0xffff0000u);
+#pragma unroll
+            for (int j = 0; j < TPW; j++) {
+                const float4 a = *reinterpret_cast<const float4 *>(&xf[buf][j][i * 8]);
+                const float4 b = *reinterpret_cast<const float4 *>(&xf[buf][j][i * 8 + 4]);
+                float c = acc[j];
+                c = __fmaf_rn(a.x, w0, c);
+                c = __fmaf_rn(a.y, w1, c);
+                c = __fmaf_rn(a.z, w2, c);
+                c = __fmaf_rn(a.w, w3, c);
+                c = __fmaf_rn(b.x, w4, c);
+                c = __fmaf_rn(b.y, w5, c);
+                c = __fmaf_rn(b.z, w6, c);
+                c = __fmaf_rn(b.w, w7, c);
+                acc[j] = c;
+            }
+        }
+    }
+    const int e = e0 + lane;
+#pragma unroll
+    for (int j = 0; j < TPW; j++)
+        if (e < E && t0 + j < T)
+            logits[static_cast<size_t>(t0 + j) * E + e] = acc[j];
 }
 
 // One warp per token.  Lane l holds experts l, l+32, l+64, ...  (NPL per lane).
