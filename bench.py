@@ -465,6 +465,8 @@ def run_ours_ep(args, dims):
     clocks = sampler.stop() if rank == 0 else None
     ops.check()
     # phase times of one more step (CUDA events on the launching stream; host-side gaps show up in the phase that follows them)
+    forward(x)  # the marked step runs eagerly: warm its allocations first when the timed steps were graph replays
+    torch.cuda.synchronize()
     marks = []
     forward(x, marks)
     torch.cuda.synchronize()
