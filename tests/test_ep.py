@@ -191,7 +191,8 @@ def test_ep_on_gpus_matches_oracle(oracle, tmp_path, fmt, tol):
 def _oracle_ref(oracle, dims, d):
     n = synth.to_numpy_storage(d)
     mode = {"bf16": oracle.BF16, "fp8": oracle.FP8, "fp4": oracle.FP4}[dims["fmt"]]
-    return oracle.moe_forward(mode, n["x"], n["router_w"], n["gate_up_w"], n["down_w"], dims["K"], gate_up_scale=n.get("gate_up_scale"),
+    return oracle.moe_forward(mode, n["x"], n["router_w"], n["gate_up_w"], n["down_w"], dims["K"], router_bias=n.get("router_bias"),
+                              gate_up_scale=n.get("gate_up_scale"),
                               down_scale=n.get("down_scale"), shared_gate_up_w=n["shared_gate_up_w"], shared_down_w=n["shared_down_w"],
                               shared_gate_up_scale=n.get("shared_gate_up_scale"), shared_down_scale=n.get("shared_down_scale"), threads=8)
 
@@ -212,7 +213,8 @@ def _virtual_ranks(dims, R, seed, capacity=None):
         local["router_w"] = router_w
         ops = ep.CudaOps(dict(dims), local, shared, r, R)
         px = ep.PeerExchange(dims, r, R, capacity)
-        ranks.append(dict(ops=ops, px=px, x=d["x"][r * T:(r + 1) * T].contiguous().cuda()))
+        bias = d["router_bias"].cuda() if d.get("router_bias") is not None else None
+        ranks.append(dict(ops=ops, px=px, x=d["x"][r * T:(r + 1) * T].contiguous().cuda(), bias=bias))
     for k in ranks:
         k["px"].connect([q["px"].rows.data_ptr() for q in ranks], [q["px"].scales.data_ptr() for q in ranks],
                         [q["px"].back.data_ptr() for q in ranks])
@@ -221,7 +223,7 @@ def _virtual_ranks(dims, R, seed, capacity=None):
 
 def _run_virtual(ranks):
     for k in ranks:
-        k["ids"], k["w"] = k["ops"].route(k["x"], k["ops"].keep[0]["router_w"], None)
+        k["ids"], k["w"] = k["ops"].route(k["x"], k["ops"].keep[0]["router_w"], k["bias"])
         k["counts"], k["offsets"], k["perm"], k["inv"] = k["ops"].permute(k["ids"])
     all_counts = torch.cat([k["counts"] for k in ranks])
     for k in ranks:
@@ -257,6 +259,33 @@ def test_peer_exchange_virtual_ranks_match_oracle(oracle, fmt, tol):
         ref = _oracle_ref(oracle, dims, d)
         rel = synth.rel_l2(synth.bf16_bits_to_f32(got), synth.bf16_bits_to_f32(ref["out"]))
         assert rel <= tol, rel
+    finally:
+        torch.cuda.synchronize()
+        for k in ranks:
+            k["px"].close()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("R,dims", [
+    (8, dict(T=16, H=256, E=32, K=6, I=128, S=1, fmt="fp8", bias="zipf")),   # skewed routing: experts (and ranks) with no rows at all
+    (2, dict(T=33, H=256, E=8, K=1, I=128, S=1, fmt="bf16", bias="zipf")),   # top-1, ragged token count
+    (4, dict(T=1, H=512, E=16, K=4, I=256, S=1, fmt="fp4", bias=None)),      # one token per rank
+    (8, dict(T=8, H=256, E=8, K=2, I=128, S=1, fmt="bf16", bias=None)),      # one expert per rank
+])
+def test_peer_exchange_virtual_ranks_edge_cases(oracle, R, dims):
+    d, ranks = _virtual_ranks(dims, R, seed=77)
+    try:
+        all_counts, outs = _run_virtual(ranks)
+        for k in ranks:
+            k["ops"].check()
+        torch.cuda.synchronize()
+        ac = all_counts.view(R, dims["E"]).cpu().numpy()
+        assert ac.sum() == R * dims["T"] * dims["K"]
+        got = torch.cat(outs).cpu().view(torch.uint16).numpy()
+        ref = _oracle_ref(oracle, dims, d)
+        assert np.array_equal(torch.cat([k["ids"] for k in ranks]).cpu().numpy(), ref["topk_ids"]), "routing differs from the oracle"
+        rel = synth.rel_l2(synth.bf16_bits_to_f32(got), synth.bf16_bits_to_f32(ref["out"]))
+        assert rel <= (2e-3 if dims["fmt"] == "bf16" else 1e-2), rel
     finally:
         torch.cuda.synchronize()
         for k in ranks:
