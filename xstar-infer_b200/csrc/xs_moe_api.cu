@@ -303,7 +303,7 @@ int launch_logits(const XsMoeConfig *c, const void *x, const void *rw, float *lo
         XS_CUDA(cudaGetDevice(&dev));
         if (dev >= 64 || !configured[dev]) {
             XS_CUDA(cudaFuncSetAttribute(xs::router_logits_big_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, xs::rb_smem_bytes<4>()));
-            XS_CUDA(cudaFuncSetAttribute(xs::router_logits_big_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, xs::rb_smem_bytes<2>()));
+            XS_CUDA(cudaFuncSetAttribute(xs::router_logits_mid_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, xs::rm_smem_bytes<2>()));
             if (dev < 64)
                 configured[dev] = true;
         }
@@ -311,7 +311,7 @@ int launch_logits(const XsMoeConfig *c, const void *x, const void *rw, float *lo
         if (static_cast<long>(eg) * ((T + 63) / 64) >= 256)
             xs::router_logits_big_kernel<4><<<dim3(eg, (T + 63) / 64), xs::kRbThreads, xs::rb_smem_bytes<4>(), st>>>(xb, rwb, logits, T, H, E);
         else // 32-token tiles keep more SMs busy on medium batches
-            xs::router_logits_big_kernel<2><<<dim3(eg, (T + 31) / 32), xs::kRbThreads, xs::rb_smem_bytes<2>(), st>>>(xb, rwb, logits, T, H, E);
+            xs::router_logits_mid_kernel<2><<<dim3(eg, (T + 31) / 32), xs::kRbThreads, xs::rm_smem_bytes<2>(), st>>>(xb, rwb, logits, T, H, E);
     }
     XS_CUDA(cudaGetLastError());
     return 0;

@@ -201,6 +201,123 @@ router_logits_decode_kernel(const __nv_bfloat16 *__restrict__ x, const __nv_bflo
         logits[static_cast<size_t>(t) * E + e] = acc;
 }
 
+// Medium batches (too few 64-token tiles to fill the SMs): 32 tokens x 128 experts per block, 2 x 8 outputs per thread.
+// With that small a register tile the f32-staged kernel above is bound by shared-memory wavefronts (profile: shared pipe
+// at 76 % of peak, FMA pipe at 36 %), so here the operands stay bf16 in shared memory -- a 16-byte read carries 8 k
+// instead of 4 -- and are widened in registers, one ALU operation each on a pipe that is otherwise idle.  (With the 4 x 8
+// tile the extra instructions cost more than the wavefronts saved, which is why both kernels exist.)  Same contract: every
+// accumulator sees k = 0, 1, 2, ... in order.
+constexpr int kRmStride = kRbK + 8; // bf16 elements; 80-byte rows: conflict-free 16-byte reads
+template <int TPT>
+constexpr int rm_smem_bytes()
+{
+    return 2 * (16 * TPT + kRbExperts) * kRmStride * 2;
+}
+__device__ __forceinline__ float bf16_at(const uint4 &v, int k) // element k (0..7) of eight packed bf16, widened
+{
+    const uint32_t w = k < 2 ? v.x : (k < 4 ? v.y : (k < 6 ? v.z : v.w));
+    return (k & 1) ? __uint_as_float(w & 0xffff0000u) : __uint_as_float(w << 16);
+}
+template <int TPT>
+__global__ void __launch_bounds__(kRbThreads, 2)
+router_logits_mid_kernel(const __nv_bfloat16 *__restrict__ x, const __nv_bfloat16 *__restrict__ rw, float *__restrict__ logits,
+                         int T, int H, int E)
+{
+    constexpr int TOK = 16 * TPT;
+    constexpr int PIECES = (TOK + kRbExperts) * 4; // 16-byte pieces (8 bf16) per k chunk
+    constexpr int PPT = (PIECES + kRbThreads - 1) / kRbThreads;
+    extern __shared__ __align__(16) uint16_t rm_smem[];
+    uint16_t (*xs)[TOK][kRmStride] = reinterpret_cast<uint16_t (*)[TOK][kRmStride]>(rm_smem);
+    uint16_t (*ws)[kRbExperts][kRmStride] = reinterpret_cast<uint16_t (*)[kRbExperts][kRmStride]>(rm_smem + 2 * TOK * kRmStride);
+    const int tid = threadIdx.x;
+    const int tx = tid & 15, ty = tid >> 4;
+    const int t0 = blockIdx.y * TOK, e0 = blockIdx.x * kRbExperts;
+    uint4 stage_regs[PPT];
+    auto fetch = [&](int k0) {
+#pragma unroll
+        for (int i = 0; i < PPT; i++) {
+            const int p = tid + i * kRbThreads;
+            const int r = p >> 2, c = (p & 3) * 8;
+            uint4 v = make_uint4(0, 0, 0, 0);
+            if (p < PIECES) {
+                if (r < TOK) {
+                    if (t0 + r < T)
+                        v = __ldg(reinterpret_cast<const uint4 *>(x + static_cast<size_t>(t0 + r) * H + k0 + c));
+                } else if (e0 + r - TOK < E) {
+                    v = __ldg(reinterpret_cast<const uint4 *>(rw + static_cast<size_t>(e0 + r - TOK) * H + k0 + c));
+                }
+            }
+            stage_regs[i] = v;
+        }
+    };
+    auto stash = [&](int buf) {
+#pragma unroll
+        for (int i = 0; i < PPT; i++) {
+            const int p = tid + i * kRbThreads;
+            if (p >= PIECES)
+                continue;
+            const int r = p >> 2, c = (p & 3) * 8;
+            uint16_t *dst = r < TOK ? &xs[buf][r][c] : &ws[buf][r - TOK][c];
+            *reinterpret_cast<uint4 *>(dst) = stage_regs[i];
+        }
+    };
+    float acc[TPT][8];
+#pragma unroll
+    for (int i = 0; i < TPT; i++)
+#pragma unroll
+        for (int j = 0; j < 8; j++)
+            acc[i][j] = 0.0f;
+    fetch(0);
+    stash(0);
+    __syncthreads();
+    const int chunks = H / kRbK;
+    for (int ch = 0; ch < chunks; ch++) {
+        const int buf = ch & 1;
+        if (ch + 1 < chunks)
+            fetch((ch + 1) * kRbK);
+#pragma unroll
+        for (int k = 0; k < kRbK; k += 8) {
+            uint4 xv[TPT], wv[8];
+#pragma unroll
+            for (int i = 0; i < TPT; i++)
+                xv[i] = *reinterpret_cast<const uint4 *>(&xs[buf][ty + 16 * i][k]);
+#pragma unroll
+            for (int j = 0; j < 8; j++)
+                wv[j] = *reinterpret_cast<const uint4 *>(&ws[buf][tx + 16 * j][k]);
+#pragma unroll
+            for (int kk = 0; kk < 8; kk++) {
+                float xf[TPT], wf[8];
+#pragma unroll
+                for (int i = 0; i < TPT; i++)
+                    xf[i] = bf16_at(xv[i], kk);
+#pragma unroll
+                for (int j = 0; j < 8; j++)
+                    wf[j] = bf16_at(wv[j], kk);
+#pragma unroll
+                for (int i = 0; i < TPT; i++)
+#pragma unroll
+                    for (int j = 0; j < 8; j++)
+                        acc[i][j] = __fmaf_rn(xf[i], wf[j], acc[i][j]);
+            }
+        }
+        if (ch + 1 < chunks)
+            stash(buf ^ 1);
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < TPT; i++) {
+        const int t = t0 + ty + 16 * i;
+        if (t >= T)
+            continue;
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            const int e = e0 + tx + 16 * j;
+            if (e < E)
+                logits[static_cast<size_t>(t) * E + e] = acc[i][j];
+        }
+    }
+}
+
 // The smallest batches (a few tokens per SM at most): the floor of the router is the chain of H dependent FMAs of one
 // output (about 10 us at H = 4096), so the kernel is built to keep that chain fed and nothing else in its way.  One WARP
 // per block: lane = expert (32 experts per block), TPW tokens per lane (the launcher uses 1: one token per block; more
