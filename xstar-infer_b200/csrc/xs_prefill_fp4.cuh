@@ -7,14 +7,15 @@
 // rows); the accumulator is single-buffered, the epilogue of a tile (about a tenth of its main loop) is not overlapped.
 //
 // Warps: 0 TMA producer | 1 MMA issuer (+ tcgen05.cp of the scales), TMEM owner | 2..5 and 7..10 epilogue (two warps per
-// TMEM lane quarter, each taking half of the columns) | 6 scale loader.
+// TMEM lane quarter, each taking half of the columns) | 6 and 11 scale loaders (alternate k-blocks).
 #pragma once
 #include "xs_grouped_gemm_fp4.cuh"
 #include "xs_prefill_fp8.cuh"
 
 namespace xs {
 
-constexpr int kPf4Threads = 352;
+constexpr int kPf4Loaders = 2;                      // scale-loader warps: 6, 11, 12, ...
+constexpr int kPf4Threads = 352 + 32 * (kPf4Loaders - 1);
 constexpr int kPf4SfBytesPerStage = 1536; // tokens | weight rows 0..127 | weight rows 128..255
 constexpr int kPf4TailBytes = 512 + 8 * kPf4SfBytesPerStage;
 
@@ -164,7 +165,7 @@ prefill_gemm_fp4_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
             atomicAdd(&prof[2], static_cast<unsigned long long>(w1));
             atomicAdd(&prof[3], static_cast<unsigned long long>(w2));
         }
-    } else if (warp == 6) {
+    } else if (warp == 6 || warp >= 11) {
 #include "xs_prefill_fp4_scales.inl"
     } else {
 #include "xs_prefill_fp4_epilogue.inl"

@@ -20,68 +20,87 @@
         }
         tc_fence_after();
         const uint32_t t0 = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
-        if (q * 32 >= nvalid) {
-            // no valid token in this warp's lane quarter (decode-sized segments): nothing to read or store
-        } else if constexpr (GATE_UP) {
-            // features nt*128 + [0,128): gate in columns [0,128), up in [128,256); MX groups of 32 features = 2 chunks
-            uint8_t *arow = static_cast<uint8_t *>(out) + static_cast<size_t>(row0 + r) * n_out + nt * 128;
-            uint8_t *srow = sc.act_scale + static_cast<size_t>(row0 + r) * (n_out / 32) + nt * 4;
-#pragma unroll 1
-            for (int grp = 2 * half; grp < 2 * half + 2; grp++) {
-                float a[32];
+        // The accumulators leave TMEM first (for gate/up already folded to silu(gate) * up) and the accumulator is handed
+        // back to the MMA thread BEFORE the quantisation and the global stores, which then overlap the next tile's main loop.
+        const bool active = q * 32 < nvalid; // no valid token in this warp's lane quarter: nothing to read or store
+        if constexpr (GATE_UP) {
+            // features nt*128 + [0,128): gate in columns [0,128), up in [128,256); this thread: groups 2*half, 2*half + 1
+            float a[2][32];
+            if (active) {
 #pragma unroll
-                for (int h = 0; h < 2; h++) {
-                    uint32_t pg[16], pu[16];
-                    tmem_ld16(t0 + grp * 32 + h * 16, pg);
-                    tmem_ld16(t0 + 128 + grp * 32 + h * 16, pu);
-                    tmem_ld_wait_for(pg, pu);
+                for (int g = 0; g < 2; g++) {
+                    const int grp = 2 * half + g;
+                    uint32_t pg[2][16], pu[2][16]; // all four reads of the group in flight before the first wait
 #pragma unroll
-                    for (int c = 0; c < 16; c++)
-                        a[h * 16 + c] = silu_fast(__uint_as_float(pg[c])) * __uint_as_float(pu[c]);
-                }
-                float m = 0.0f;
-#pragma unroll
-                for (int c = 0; c < 32; c++)
-                    m = fmaxf(m, fabsf(a[c]));
-                const uint32_t se = e8m0_ceil(__fdiv_rn(fmaxf(m, 1e-30f), 448.0f));
-                const float inv = __uint_as_float((254u - se) << 23);
-                if (valid) {
-#pragma unroll
-                    for (int v = 0; v < 2; v++) {
-                        uint32_t pk[4];
-#pragma unroll
-                        for (int j = 0; j < 4; j++) {
-                            pk[j] = 0;
-#pragma unroll
-                            for (int b = 0; b < 4; b++)
-                                pk[j] |= static_cast<uint32_t>(f32_to_e4m3(__fmul_rn(a[v * 16 + j * 4 + b], inv))) << (8 * b);
-                        }
-                        *reinterpret_cast<uint4 *>(arow + grp * 32 + v * 16) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+                    for (int h = 0; h < 2; h++) {
+                        tmem_ld16(t0 + grp * 32 + h * 16, pg[h]);
+                        tmem_ld16(t0 + 128 + grp * 32 + h * 16, pu[h]);
                     }
-                    srow[grp] = static_cast<uint8_t>(se);
+#pragma unroll
+                    for (int h = 0; h < 2; h++) {
+                        tmem_ld_wait_for(pg[h], pu[h]);
+#pragma unroll
+                        for (int c = 0; c < 16; c++)
+                            a[g][h * 16 + c] = silu_fast(__uint_as_float(pg[h][c])) * __uint_as_float(pu[h][c]);
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0)
+                mbar_arrive(tmem_empty);
+            if (active) {
+                uint8_t *arow = static_cast<uint8_t *>(out) + static_cast<size_t>(row0 + r) * n_out + nt * 128;
+                uint8_t *srow = sc.act_scale + static_cast<size_t>(row0 + r) * (n_out / 32) + nt * 4;
+#pragma unroll
+                for (int g = 0; g < 2; g++) {
+                    const int grp = 2 * half + g; // one MX group of 32 features
+                    float m = 0.0f;
+#pragma unroll
+                    for (int c = 0; c < 32; c++)
+                        m = fmaxf(m, fabsf(a[g][c]));
+                    const uint32_t se = e8m0_ceil(__fdiv_rn(fmaxf(m, 1e-30f), 448.0f));
+                    const float inv = __uint_as_float((254u - se) << 23);
+                    if (valid) {
+#pragma unroll
+                        for (int v = 0; v < 2; v++) {
+                            uint32_t pk[4];
+#pragma unroll
+                            for (int j = 0; j < 4; j++) {
+                                pk[j] = 0;
+#pragma unroll
+                                for (int b = 0; b < 4; b++)
+                                    pk[j] |= static_cast<uint32_t>(f32_to_e4m3(__fmul_rn(a[g][v * 16 + j * 4 + b], inv))) << (8 * b);
+                            }
+                            *reinterpret_cast<uint4 *>(arow + grp * 32 + v * 16) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+                        }
+                        srow[grp] = static_cast<uint8_t>(se);
+                    }
                 }
             }
         } else {
-            float *yrow = static_cast<float *>(out) + static_cast<size_t>(row0 + r) * n_out + nt * 256;
-#pragma unroll 1
-            for (int c0 = 128 * half; c0 < 128 * half + 128; c0 += 32) {
-                uint32_t pa[16], pb[16];
-                tmem_ld16(t0 + c0, pa);
-                tmem_ld16(t0 + c0 + 16, pb);
-                tmem_ld_wait_for(pa, pb);
-                if (valid) {
+            uint32_t y[8][16]; // this thread's 128 columns
+            if (active) {
 #pragma unroll
-                    for (int v = 0; v < 4; v++) {
-                        *reinterpret_cast<uint4 *>(yrow + c0 + v * 4) = make_uint4(pa[v * 4], pa[v * 4 + 1], pa[v * 4 + 2], pa[v * 4 + 3]);
-                        *reinterpret_cast<uint4 *>(yrow + c0 + 16 + v * 4) = make_uint4(pb[v * 4], pb[v * 4 + 1], pb[v * 4 + 2], pb[v * 4 + 3]);
-                    }
-                }
+                for (int i = 0; i < 8; i++)
+                    tmem_ld16(t0 + 128 * half + i * 16, y[i]);
+#pragma unroll
+                for (int i = 0; i < 4; i++)
+                    tmem_ld_wait_for(y[2 * i], y[2 * i + 1]);
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0)
+                mbar_arrive(tmem_empty);
+            if (valid) {
+                float *yrow = static_cast<float *>(out) + static_cast<size_t>(row0 + r) * n_out + nt * 256 + 128 * half;
+#pragma unroll
+                for (int i = 0; i < 8; i++)
+#pragma unroll
+                    for (int v = 0; v < 4; v++)
+                        *reinterpret_cast<uint4 *>(yrow + i * 16 + v * 4) = make_uint4(y[i][v * 4], y[i][v * 4 + 1], y[i][v * 4 + 2], y[i][v * 4 + 3]);
             }
         }
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0)
-            mbar_arrive(tmem_empty);
     }
     if (!ok && lane == 0) {
         *abort_flag = 1;

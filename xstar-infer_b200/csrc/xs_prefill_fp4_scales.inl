@@ -1,9 +1,11 @@
-// Scale loader of prefill_gemm_fp4_kernel (warp 6; included inside the kernel body).
+// Scale loaders of prefill_gemm_fp4_kernel (warps 6 and 11; included inside the kernel body).
 // Per k-block: three 512-byte blocks -- e8m0 scales of the 128 token rows, of weight rows 0..127 and of weight rows
-// 128..255 of the tile -- lane i writing the 16 bytes {rows i, 32+i, 64+i, 96+i}.  Global loads run kSfAhead k-blocks
-// ahead of the shared-memory stores.
+// 128..255 of the tile -- lane i writing the 16 bytes {rows i, 32+i, 64+i, 96+i}.  Global loads run kSfAhead of the
+// warp's k-blocks ahead of the shared-memory stores.  The kPf4Loaders warps take k-blocks round-robin of the CTA's sequence (one
+// warp alone was the kernel's bottleneck: it never once waited for a free slot while the MMA thread waited for scales).
 {
     constexpr int kSfAhead = 3;
+    const int loader = warp == 6 ? 0 : warp - 10; // warps 6, 11, 12, ...
     struct Cursor {
         int w, kb, row0;
         size_t wrow, wrow2;
@@ -42,13 +44,19 @@
     Cursor ld{static_cast<int>(blockIdx.x), 0, 0, 0, 0, false}, stc = ld;
     locate(ld);
     locate(stc);
+    uint32_t seq = loader; // index of this warp's next k-block in the CTA's sequence: slot = seq % stages
+    for (int i = 0; i < loader && ld.valid; i++) {
+        advance(ld);
+        advance(stc);
+    }
 #pragma unroll
     for (int j = 0; j < kSfAhead; j++) {
         fetch(ld, ring[j]);
-        advance(ld);
+#pragma unroll
+        for (int i = 0; i < kPf4Loaders; i++)
+            if (ld.valid)
+                advance(ld);
     }
-    int stage = 0;
-    uint32_t phase = 0;
     bool ok = true;
     while (stc.valid && ok) {
 #pragma unroll
@@ -56,7 +64,12 @@
             if (!stc.valid)
                 break;
             fetch(ld, ring[(j + kSfAhead) % (kSfAhead + 1)]);
-            advance(ld);
+#pragma unroll
+            for (int i = 0; i < kPf4Loaders; i++)
+                if (ld.valid)
+                    advance(ld);
+            const int stage = static_cast<int>(seq % static_cast<uint32_t>(stages));
+            const uint32_t phase = (seq / static_cast<uint32_t>(stages)) & 1u;
             if (!mbar_wait_t(&empty[stage], phase ^ 1, abort_flag, w0)) {
                 ok = false;
                 break;
@@ -70,17 +83,17 @@
             __syncwarp();
             if (lane == 0)
                 mbar_arrive(&sf_full[stage]);
-            if (++stage == stages) {
-                stage = 0;
-                phase ^= 1;
-            }
-            advance(stc);
+            seq += kPf4Loaders;
+#pragma unroll
+            for (int i = 0; i < kPf4Loaders; i++)
+                if (stc.valid)
+                    advance(stc);
         }
     }
     if (!ok && lane == 0) {
         *abort_flag = 1;
         atomicOr(status, kStatusWaitTimeout);
     }
-    if (lane == 0)
+    if (lane == 0 && loader == 0)
         atomicAdd(&prof[4], static_cast<unsigned long long>(w0));
 }
