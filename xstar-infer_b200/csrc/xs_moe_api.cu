@@ -880,6 +880,9 @@ int xs_moe_permute(const XsMoeConfig *cfg, const int32_t *ids, int32_t *counts, 
     if (int rc = check_workspace(ws, ws_bytes, p.off_chunk_base + static_cast<size_t>(p.chunks) * cfg->num_experts * 4))
         return rc;
     uint8_t *b = static_cast<uint8_t *>(ws);
+    if (cfg->num_tokens > 0 && cfg->num_tokens <= xs::kChunkTokens) // one block does it all (no tile table asked for here)
+        return launch_permute_small(cfg, ids, counts, offsets, perm, inv, -1, GroupedPlan{}, TileBuffers{},
+                                    reinterpret_cast<int32_t *>(b), static_cast<cudaStream_t>(stream));
     return launch_permute(cfg, ids, counts, offsets, perm, inv, reinterpret_cast<int32_t *>(b + p.off_chunk_counts),
                           reinterpret_cast<int32_t *>(b + p.off_chunk_base), p.chunks, reinterpret_cast<int32_t *>(b),
                           static_cast<cudaStream_t>(stream));
