@@ -8,10 +8,10 @@
 
 namespace xs {
 
-// Large batches: (16 * TPT) tokens x 128 experts per block, TPT x 8 outputs per thread (TPT = 4, or 2 when the batch is
-// too small to fill the SMs with 64-token tiles).  Operands are widened to f32 while they are staged in shared memory,
-// so the inner loop is (TPT + 8) 16-byte shared loads per 32 * TPT FMAs and no conversions; k chunks of 32 are
-// double-buffered.  Same contract: every accumulator sees k = 0, 1, 2, ... in order.
+// Large batches: (16 * TPT) tokens x 128 experts per block, TPT x 8 outputs per thread (launched with TPT = 4: 64-token
+// tiles, once there are enough of them to fill the SMs; smaller batches take router_logits_mid_kernel below).  Operands are
+// widened to f32 while they are staged in shared memory, so the inner loop is (TPT + 8) 16-byte shared loads per 32 * TPT
+// FMAs and no conversions; k chunks of 32 are double-buffered.  Same contract: every accumulator sees k = 0, 1, 2, ... in order.
 constexpr int kRbExperts = 128, kRbK = 32, kRbThreads = 256, kRbStride = kRbK + 4;
 template <int TPT>
 constexpr int rb_smem_bytes()
