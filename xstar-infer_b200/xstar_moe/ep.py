@@ -1,15 +1,23 @@
 """Expert parallelism for the MoE layer: one process per GPU, experts sharded evenly and contiguously
-(expert e lives on rank e // (E / R)), tokens data-parallel, one all-to-all each way.
+(expert e lives on rank e // (E / R)), tokens data-parallel, one exchange each way.  Two transports:
 
+`forward_peer` (default in bench.py) -- rows travel by peer-memory stores from kernels of the library:
+    local route -> local permute -> all-gather of per-expert counts (stays on the device) -> plan kernel
+    -> DISPATCH kernel: each token quantised once and stored into the grouped buffer of the owner of each of its experts
+    -> barrier -> grouped expert MLPs straight on that buffer -> RETURN kernel: results stored into the source rank's
+    return buffer at their permuted row -> barrier -> local weighted combine (+ the always-on expert, computed locally)
+  Nothing returns to the host, so the step can be captured as one CUDA graph (`capture_peer`).
+
+`forward` -- rows travel by NCCL all-to-all (portable baseline; what the CPU/gloo tests drive):
     local route -> local permute (rows sorted by expert => by destination rank)
-    -> all-gather of per-expert counts (the only host synchronisation: NCCL needs split sizes on the host)
+    -> all-gather of per-expert counts (the one host synchronisation: NCCL needs split sizes on the host)
     -> DISPATCH all-to-all of the permuted rows (payload: bf16 rows, or e4m3 codes + 1x128 f32 / 1x32 e8m0 scales)
     -> regroup received rows by local expert -> grouped expert MLPs -> rows back into arrival order
-    -> COMBINE all-to-all back (f32 rows; bf16 rows for the quantised formats) -> local weighted combine (+ the always-on expert, computed locally)
+    -> COMBINE all-to-all back (f32 rows; bf16 rows for the quantised formats) -> local weighted combine
 
-Received rows are ordered by (source rank, expert, token) -- fixed by the data, not by arrival time -- so the
-result is reproducible and equals the single-device layer bit for bit (the combine still sums each token's k
-expert outputs in slot order).
+Received rows are ordered by (expert, source rank, source order) in both -- fixed by the data, not by arrival time --
+so the result is reproducible, the two transports agree bit for bit, and with bf16 experts the layer equals the
+single-device layer bit for bit (the combine still sums each token's k expert outputs in slot order).
 
 This module is host logic over `torch.distributed`; all device compute goes through an `ops` object.
 `CudaOps` binds the C ABI (libxs_moe.so).  Tests drive the same host logic on CPU ranks (gloo) with a
