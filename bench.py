@@ -396,7 +396,18 @@ def run_ours_ep(args, dims):
     use_graph = peer and args.graph != "off"  # nothing in the peer step touches the host: replay it whole at any size
     if use_graph:
         x_static = x.clone()
-        graph, out_static = layer.capture_peer(x_static, px)
+        graph = None
+        try:
+            graph, out_static = layer.capture_peer(x_static, px)
+        except RuntimeError as e:
+            print(f"rank {rank}: graph capture failed ({e}); launching the step eagerly", file=sys.stderr, flush=True)
+        agreed = torch.tensor([1 if graph is not None else 0], dtype=torch.int32, device="cuda")
+        dist.all_reduce(agreed, op=dist.ReduceOp.MIN)  # every rank replays, or none does
+        if int(agreed.item()) == 0:
+            if graph is not None:
+                graph.reset()
+            use_graph = False
+    if use_graph:
 
         def step():
             graph.replay()
