@@ -498,7 +498,10 @@ def run_ours_ep(args, dims):
                            l2="inputs larger than L2: expert weights streamed per step exceed 126 MB"),
             "e2e": {"value": tokens / (ms_e2e * 1e-3), "unit": UNIT, "h2d_bytes_per_step": T * H * 2, "d2h_bytes_per_step": T * H * 2,
                     "ms_per_step": ms_e2e / args.steps},
-            "gpu_launches": ((2 + 3 + 1 + 1 + 3 + 1 + 3 * S + 1) if peer else (2 + 3 + 1 + len(payload) * 2 + 3 + 1 + 3 * S + 1)) * args.steps,
+            # route 2 | permute 1 or 3 | [peer: plan, dispatch, return | all-to-all: quantise, 2 gathers per payload tensor, return gather]
+            # | grouped MLP 3 | always-on expert 3 (+ its own quantise next to FP4 experts) | combine 1
+            "gpu_launches": (2 + (1 if T <= 256 else 3) + (3 if peer else 1 + len(payload) * 2 + 1) + 3
+                             + S * (4 if dims["fmt"] == "fp4" else 3) + 1) * args.steps,
             "roofline": {"bound": "hbm", "kernel": "grouped expert MLP of rank 0 (tile table + gate/up + down GEMM launches)",
                          "achieved": mlp_bytes / (mlp_ms * 1e-3) / 1e9, "peak": peak, "unit": "GB/s", "peak_kind": peak_kind,
                          "frac": mlp_bytes / (mlp_ms * 1e-3) / 1e9 / peak, "traffic": None, "algorithmic_bytes_per_launch": mlp_bytes,
