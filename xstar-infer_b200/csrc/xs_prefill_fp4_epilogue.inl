@@ -20,35 +20,40 @@
         }
         tc_fence_after();
         const uint32_t t0 = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
-        // The accumulators leave TMEM first (for gate/up already folded to silu(gate) * up) and the accumulator is handed
-        // back to the MMA thread BEFORE the quantisation and the global stores, which then overlap the next tile's main loop.
+        // The raw accumulators leave TMEM first and the accumulator is handed back to the MMA thread BEFORE SwiGLU, the
+        // quantisation and the global stores, which then overlap the next tile's main loop.
         const bool active = q * 32 < nvalid; // no valid token in this warp's lane quarter: nothing to read or store
         if constexpr (GATE_UP) {
             // features nt*128 + [0,128): gate in columns [0,128), up in [128,256); this thread: groups 2*half, 2*half + 1
-            float a[2][32];
+            uint32_t pg[2][2][16], pu[2][2][16]; // raw gate / up accumulators of this thread's two groups
             if (active) {
 #pragma unroll
-                for (int g = 0; g < 2; g++) {
-                    const int grp = 2 * half + g;
-                    uint32_t pg[2][16], pu[2][16]; // all four reads of the group in flight before the first wait
+                for (int g = 0; g < 2; g++)
 #pragma unroll
                     for (int h = 0; h < 2; h++) {
-                        tmem_ld16(t0 + grp * 32 + h * 16, pg[h]);
-                        tmem_ld16(t0 + 128 + grp * 32 + h * 16, pu[h]);
+                        tmem_ld16(t0 + (2 * half + g) * 32 + h * 16, pg[g][h]);
+                        tmem_ld16(t0 + 128 + (2 * half + g) * 32 + h * 16, pu[g][h]);
                     }
 #pragma unroll
-                    for (int h = 0; h < 2; h++) {
-                        tmem_ld_wait_for(pg[h], pu[h]);
+                for (int g = 0; g < 2; g++)
 #pragma unroll
-                        for (int c = 0; c < 16; c++)
-                            a[g][h * 16 + c] = silu_fast(__uint_as_float(pg[h][c])) * __uint_as_float(pu[h][c]);
-                    }
-                }
+                    for (int h = 0; h < 2; h++)
+                        tmem_ld_wait_for(pg[g][h], pu[g][h]);
             }
             tc_fence_before();
             __syncwarp();
             if (lane == 0)
                 mbar_arrive(tmem_empty);
+            float a[2][32];
+            if (active) {
+#pragma unroll
+                for (int g = 0; g < 2; g++)
+#pragma unroll
+                    for (int h = 0; h < 2; h++)
+#pragma unroll
+                        for (int c = 0; c < 16; c++)
+                            a[g][h * 16 + c] = silu_fast(__uint_as_float(pg[g][h][c])) * __uint_as_float(pu[g][h][c]);
+            }
             if (active) {
                 uint8_t *arow = static_cast<uint8_t *>(out) + static_cast<size_t>(row0 + r) * n_out + nt * 128;
                 uint8_t *srow = sc.act_scale + static_cast<size_t>(row0 + r) * (n_out / 32) + nt * 4;
