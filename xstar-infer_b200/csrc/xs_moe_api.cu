@@ -556,9 +556,7 @@ int launch_prefill_fp4(const CUtensorMap &tw, const CUtensorMap &tx, const int32
     int stages = (di.max_smem - 1024 - xs::kPf4TailBytes) / xs::kPfStageBytes;
     if (stages > 6)
         stages = 6;
-    // the scale-loader warps take k-blocks round-robin: a parity wait on a slot is unambiguous only while no loader can be
-    // two uses of that slot ahead of the MMA thread, i.e. with at least as many slots as loaders
-    if (stages < 2 || stages < xs::kPf4Loaders)
+    if (stages < 2)
         return fail(XS_MOE_ERR_DEVICE, "not enough shared memory for the GEMM pipeline");
     const int smem = stages * xs::kPfStageBytes + 1024 + xs::kPf4TailBytes;
     auto kern = xs::prefill_gemm_fp4_kernel<GATE_UP>;

@@ -17,7 +17,8 @@ namespace xs {
 constexpr int kPf4Loaders = 2;                      // scale-loader warps: 6, 11, 12, ...
 constexpr int kPf4Threads = 352 + 32 * (kPf4Loaders - 1);
 constexpr int kPf4SfBytesPerStage = 1536; // tokens | weight rows 0..127 | weight rows 128..255
-constexpr int kPf4TailBytes = 512 + 8 * kPf4SfBytesPerStage;
+constexpr int kPf4SfSlots = 8;            // shared-memory ring of scale blocks (barriers of its own)
+constexpr int kPf4TailBytes = 512 + kPf4SfSlots * kPf4SfBytesPerStage;
 
 template <bool GATE_UP>
 __global__ void __launch_bounds__(kPf4Threads, 1)
@@ -37,8 +38,9 @@ prefill_gemm_fp4_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
     uint64_t *bars = reinterpret_cast<uint64_t *>(smem + static_cast<size_t>(stages) * kPfStageBytes);
     uint64_t *full = bars;
     uint64_t *empty = bars + stages;
-    uint64_t *sf_full = bars + 2 * stages;
-    uint64_t *tmem_full = bars + 3 * stages;
+    uint64_t *sf_full = bars + 2 * stages;  // scale slots: a ring of kPf4SfSlots of its own, not tied to the operand stages
+    uint64_t *sf_empty = sf_full + kPf4SfSlots;
+    uint64_t *tmem_full = sf_empty + kPf4SfSlots;
     uint64_t *tmem_empty = tmem_full + 1;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(tmem_empty + 1);
     volatile uint32_t *abort_flag = tmem_slot + 1;
@@ -54,7 +56,10 @@ prefill_gemm_fp4_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
         for (int s = 0; s < stages; s++) {
             mbar_init(&full[s], 1);
             mbar_init(&empty[s], 1);
+        }
+        for (int s = 0; s < kPf4SfSlots; s++) {
             mbar_init(&sf_full[s], 1);
+            mbar_init(&sf_empty[s], 1);
         }
         mbar_init(tmem_full, 1);
         mbar_init(tmem_empty, 8);
@@ -121,15 +126,17 @@ prefill_gemm_fp4_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
-            uint32_t it = 0;
+            uint32_t it = 0, n = 0; // n: k-blocks issued so far; its scales sit in slot n % kPf4SfSlots
             for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x, it++) {
                 if (!mbar_wait_t(tmem_empty, (it & 1) ^ 1, abort_flag, w2)) { // previous tile drained by the epilogue
                     ok = false;
                     break;
                 }
                 tc_fence_after();
-                for (int kb = 0; kb < num_kb; kb++) {
-                    if (!mbar_wait_t(&full[stage], phase, abort_flag, w0) || !mbar_wait_t(&sf_full[stage], phase, abort_flag, w1)) {
+                for (int kb = 0; kb < num_kb; kb++, n++) {
+                    const uint32_t slot = n % kPf4SfSlots;
+                    if (!mbar_wait_t(&full[stage], phase, abort_flag, w0) ||
+                        !mbar_wait_t(&sf_full[slot], (n / kPf4SfSlots) & 1u, abort_flag, w1)) {
                         ok = false;
                         break;
                     }
@@ -139,7 +146,7 @@ prefill_gemm_fp4_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
                     const uint64_t dw = make_desc_sw128(sa + X_BYTES);
                     const uint32_t sfx = sf_base + static_cast<uint32_t>(stage * SF_COLS);
                     const uint32_t sfw = sfx + 4;
-                    const uint32_t sfs = smem_u32(sf_smem + static_cast<size_t>(stage) * kPf4SfBytesPerStage);
+                    const uint32_t sfs = smem_u32(sf_smem + static_cast<size_t>(slot) * kPf4SfBytesPerStage);
                     tmem_cp_32x128b_x4(sfx, make_desc_rows16(sfs));
                     tmem_cp_32x128b_x4(sfw, make_desc_rows16(sfs + 512));
                     tmem_cp_32x128b_x4(sfw + 4, make_desc_rows16(sfs + 1024));
@@ -149,6 +156,7 @@ prefill_gemm_fp4_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
                         mma_mxf8f6f4(tmem_base, dx + 2 * kk, dw + 2 * kk, idesc, sfx, sfw, (kb | kk) ? 1u : 0u);
                     }
                     tc_commit(&empty[stage]);
+                    tc_commit(&sf_empty[slot]);
                     if (++stage == stages) {
                         stage = 0;
                         phase ^= 1;
