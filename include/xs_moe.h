@@ -254,7 +254,8 @@ int xs_moe_probe_mma_rate(int32_t kind, int32_t n, int32_t iters, int32_t chains
 /* Role profile of the warp-specialised GEMM kernels that ran on this workspace since the last call: eight
  * 64-bit cycle counters summed over CTAs (0 producer blocked on a free stage, 1 MMA issuer blocked on operands,
  * 2 on scales, 3 on a free accumulator, 4 scale writers blocked on a free slot, 5 epilogue blocked on an
- * accumulator, 6 CTA lifetime, 7 CTAs).  Reads and clears; synchronises.  A tuning aid with no counterpart in
+ * accumulator, 6 CTA lifetime, 7 CTAs).  A wait that the first poll of its barrier already satisfies is not
+ * counted, so the figures are lower bounds.  Reads and clears; synchronises.  A tuning aid with no counterpart in
  * the reference. */
 int xs_moe_debug_counters(void *workspace_dev, unsigned long long *out8, void *stream);
 
