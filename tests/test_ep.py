@@ -47,6 +47,47 @@ def test_plan_rejects_uneven_sharding():
         ep.EpPlan(np.zeros((3, 8), np.int64), 0)
 
 
+def test_peer_layout_formulas_agree_with_the_plan():
+    """The peer-memory exchange addresses rows by closed formulas over the (R, E) count matrix (csrc/xs_ep.cuh):
+        row in the owner's buffer  = offsets_local_owner[e mod El] + sum_{s' < s} counts[s'][e] + j
+        row in the source's buffer = exclusive prefix of counts[s] at e + j
+    Restated here in numpy and checked against EpPlan's regroup maps: both describe the same grouped order."""
+    rng = np.random.default_rng(3)
+    R, E = 4, 16
+    El = E // R
+    counts = rng.integers(0, 6, size=(R, E))
+    counts[1, :] = 0          # a rank without tokens
+    counts[:, 5] = 0          # an expert nobody chose
+    col = counts.sum(0)
+    for d in range(R):
+        plan = ep.EpPlan(counts, d)
+        offsets_local = np.concatenate([[0], np.cumsum(col[d * El:(d + 1) * El])])
+        assert np.array_equal(offsets_local, plan.offsets_local)
+        # label every arrival row (all-to-all order: source, expert, j) and map it through the formula
+        grouped_of = []
+        for s in range(R):
+            for el in range(El):
+                e = d * El + el
+                for j in range(int(counts[s, e])):
+                    grouped_of.append(offsets_local[el] + counts[:s, e].sum() + j)
+        grouped_of = np.array(grouped_of, dtype=np.int64)
+        assert np.array_equal(np.sort(grouped_of), np.arange(plan.n_recv))  # a bijection onto the buffer's rows
+        # plan.arrival_from_grouped[a] is the grouped row of arrival row a (the inverse of grouped_from_arrival)
+        assert np.array_equal(grouped_of, plan.arrival_from_grouped), "formula and regroup map disagree"
+    # the way back: row g of the owner's buffer returns to (source s, row prefix_s[e] + j)
+    prefix = np.concatenate([np.zeros((R, 1), np.int64), np.cumsum(counts, 1)[:, :-1]], 1)
+    seen = [np.zeros(int(counts[s].sum()), bool) for s in range(R)]
+    for d in range(R):
+        for el in range(El):
+            e = d * El + el
+            for s in range(R):
+                for j in range(int(counts[s, e])):
+                    row = prefix[s, e] + j
+                    assert not seen[s][row]
+                    seen[s][row] = True
+    assert all(v.all() for v in seen)  # every permuted row of every source gets exactly one result
+
+
 # ---- two CPU ranks over gloo: the exchange logic end to end ----------------------------------------------------------
 class OracleOps:
     """Stand-in for the device ops so that the host logic of ep.ExpertParallelMoE runs on CPU ranks: each call is
