@@ -266,7 +266,7 @@ int check_workspace(const void *ws, size_t have, size_t need)
 }
 
 // ---- launches --------------------------------------------------------------------------------------------
-constexpr int kRouterSmallTokens = 32;
+constexpr int kRouterSmallTokens = 64;
 
 int launch_logits(const XsMoeConfig *c, const void *x, const void *rw, float *logits, cudaStream_t st)
 {
@@ -275,7 +275,8 @@ int launch_logits(const XsMoeConfig *c, const void *x, const void *rw, float *lo
         return 0;
     const __nv_bfloat16 *xb = static_cast<const __nv_bfloat16 *>(x), *rwb = static_cast<const __nv_bfloat16 *>(rw);
     if (T <= kRouterSmallTokens) {
-        // a few tokens per SM at most: one warp per block, lane = expert, one token per block
+        // a few tokens per SM at most: one warp per block, lane = expert, one token per block (measured faster than the
+        // 8 x 32 tile up to 64 tokens, level at 96, slower beyond)
         static bool configured_rs[64] = {};
         int dev_rs = 0;
         XS_CUDA(cudaGetDevice(&dev_rs));
