@@ -520,7 +520,9 @@ def run_ours_ep(args, dims):
 
 
 def run_mma_rate():
-    """Table of tcgen05.mma rates (M = 128) by kind and N: cycles per instruction and whole-chip TFLOP/s."""
+    """Tables of hardware rates the tile shapes rest on: tcgen05.mma (M = 128) by kind, N and number of independent
+    accumulators (cycles per instruction, whole-chip TFLOP/s), and TMEM -> register reads by load shape and warp count
+    (bytes per cycle per SM), alone and beside a stream of N = 256 FP8 MMAs."""
     import torch
 
     from xstar_moe import capi
@@ -531,7 +533,9 @@ def run_mma_rate():
     rows = []
     for kind, name in ((0, "bf16 K=16"), (1, "e4m3 K=32"), (2, "e4m3 x e2m1 block-scaled K=32")):
         for n in (16, 64, 128, 256):
-            for chains in (1, 2) if n <= 128 else (1,):
+            for chains in (1, 2, 4):
+                if chains * n > (496 if kind == 2 else 512):
+                    continue
                 cyc, iss, tf = C.c_double(), C.c_double(), C.c_double()
                 for _ in range(2):  # second run is warm
                     capi.check(L.xs_moe_probe_mma_rate(kind, n, 4000, chains, capi.ptr(ws), ws.numel(), C.byref(cyc), C.byref(iss),
@@ -539,6 +543,18 @@ def run_mma_rate():
                 rows.append({"kind": name, "n": n, "chains": chains, "cycles_per_mma": round(cyc.value, 1),
                              "issue_cycles_per_mma": round(iss.value, 1), "tflops": round(tf.value, 1)})
     print(json.dumps({"mma_rate": rows}), flush=True)
+    shapes = {0: "2 x (2 x .x16, wait)", 1: "4 x .x16, wait", 2: "2 x .x32, wait", 3: ".x64, wait"}
+    rows = []
+    for with_mma in (0, 1):
+        for shape, sname in shapes.items():
+            for warps in (4, 8, 16):
+                bpc, mcyc = C.c_double(), C.c_double()
+                for _ in range(2):
+                    capi.check(L.xs_moe_probe_tmem_ld_rate(shape, warps, 2000, with_mma, capi.ptr(ws), ws.numel(), C.byref(bpc),
+                                                           C.byref(mcyc), None))
+                rows.append({"loads": sname, "warps": warps, "beside_mma": bool(with_mma), "bytes_per_cycle_per_sm": round(bpc.value, 1),
+                             "mma_cycles_per_mma": round(mcyc.value, 1)})
+    print(json.dumps({"tmem_ld_rate": rows}), flush=True)
 
 
 def main():

@@ -82,6 +82,12 @@ const char *xs_moe_last_error(void);
 /* 0 if the current device can run this library (compute capability 10.x), else XS_MOE_ERR_DEVICE. */
 int xs_moe_device_check(void);
 
+/* Device selection for the calling host thread (the reference's ops run on device 0 implicitly,
+ * xstar_cpp/src/ops/add.cu:26; an expert-parallel host drives one device per thread). */
+int xs_moe_device_count(int32_t *count);
+int xs_moe_set_device(int32_t device);
+int xs_moe_current_device(int32_t *device);
+
 /* Allocator wrappers with the reference's meaning (xstar_cpp/include/cuda/cuda_allocator.h:32-69):
  * raw device allocation, synchronous copies, free-memory probe. */
 int xs_moe_device_alloc(void **ptr_dev, size_t bytes);
@@ -128,12 +134,18 @@ int xs_moe_forward_host(const XsMoeConfig *cfg, const XsMoeWeights *w, const voi
 
 /* Router logits + selection.  logits(T,E) f32 are accumulated per output in ascending k (the order of
  * gemm_cpu, xstar_cpp/include/ops/gemm.h:57-83; linear's x*W^T, xstar_cpp/src/ops/linear.cpp:20-31);
- * key = logit + bias; the k largest keys, ties to the lower id; slots in ascending expert id;
+ * key = logit + bias (a NaN key orders as -inf); the k largest keys, ties to the lower id; slots in ascending expert id;
  * weights = max-shifted softmax over the selected unbiased logits (xstar_cpp/src/ops/softmax.cpp:56-93).
  * logits_dev may be NULL when the caller does not want them (scratch is then taken from the workspace). */
 int xs_moe_route(const XsMoeConfig *cfg, const void *x_dev, const void *router_w_dev, const float *router_bias_dev,
                  float *logits_dev, int32_t *topk_ids_dev, float *topk_w_dev, void *workspace_dev,
                  size_t workspace_bytes, void *stream);
+
+/* The selection step of xs_moe_route by itself, on logits(T,E) f32 the caller already holds (same rule: key = logit +
+ * bias, a NaN key orders as -inf, ties to the lower id, ascending slots, softmax over the selected unbiased logits).
+ * Takes the role of softmax_launch over a row (xstar_cpp/include/ops/softmax.h:75-80) restricted to the k chosen. */
+int xs_moe_topk(const XsMoeConfig *cfg, const float *logits_dev, const float *router_bias_dev, int32_t *topk_ids_dev,
+                float *topk_w_dev, void *stream);
 
 /* Deterministic permutation: rows sorted by (expert asc, token asc).  counts(E), offsets(E+1),
  * perm(T*k): row -> t*k+slot, inv(T*k): t*k+slot -> row.  The index-array convention (raw integers next
@@ -168,7 +180,8 @@ int xs_moe_permute_noalloc(const XsMoeConfig *cfg, const int32_t *topk_ids_dev, 
  * (expert e owns rows [offsets[e], offsets[e+1]), e in [0, local_expert_count)); y_dev(M,H) f32 receives
  * down(silu(gate x) * up x) per row.  Takes the role of gemm_silu_and_mul_launch + the down linear
  * (xstar_cpp/include/ops/mlp.h:95-102, xstar_cpp/src/ops/mlp.cpp:64-70), once per expert segment.
- * max_rows is the capacity of rows_dev / y_dev (the true M is offsets[E_local], read on the device). */
+ * max_rows is the capacity of rows_dev / y_dev (the true M is offsets[E_local], read on the device); offsets that
+ * reach beyond it are clamped to it on the device and flagged (xs_moe_check_flags), never written through. */
 int xs_moe_grouped_mlp_workspace_bytes(const XsMoeConfig *cfg, int32_t max_rows, size_t *bytes);
 int xs_moe_grouped_mlp(const XsMoeConfig *cfg, const XsMoeWeights *w, const void *rows_dev,
                        const float *row_scales_dev, const int32_t *offsets_dev, int32_t max_rows, float *y_dev,
@@ -236,28 +249,13 @@ int xs_moe_ep_dispatch(const XsMoeConfig *cfg, int32_t ranks, const void *x_dev,
                        void *stream);
 
 /* Expert outputs (grouped rows, f32) back to row src_offsets[s][e] + j of their source rank's return buffer, as f32
- * or rounded to bf16 (wire_bf16 != 0).  The row count is read on the device from offsets_local. */
+ * or rounded to bf16 (wire_bf16 != 0).  The row count is read on the device from offsets_local and limited to
+ * y_capacity_rows, the rows y_grouped_dev holds; rows beyond it, and destination rows outside
+ * [0, back_capacity_rows), are skipped and flagged in the workspace status word. */
 int xs_moe_ep_return(const XsMoeConfig *cfg, int32_t ranks, int32_t rank, const float *y_grouped_dev,
                      const int32_t *all_counts_dev, const int32_t *offsets_local_dev, const int32_t *src_offsets_dev,
-                     void *const *peer_back_dev, int32_t back_capacity_rows, int32_t wire_bf16, void *workspace_dev,
-                     void *stream);
-
-/* Tensor-pipe rate probe (a tuning aid; no counterpart in the reference): every SM issues `iters` tcgen05.mma of
- * M = 128, N = n (16..256) on zeroed shared memory, round-robin over `chains` independent TMEM accumulators
- * (chains * n <= 480).  kind 0 = bf16 (K = 16), 1 = e4m3 (K = 32), 2 = block-scaled e4m3 x e2m1 (K = 32).
- * Returns cycles per MMA until completion, cycles per MMA spent issuing, and whole-chip TFLOP/s by CUDA events.
- * Needs a workspace of at least 256 bytes (status block).  Synchronises. */
-int xs_moe_probe_mma_rate(int32_t kind, int32_t n, int32_t iters, int32_t chains, void *workspace_dev,
-                          size_t workspace_bytes, double *cycles_per_mma, double *issue_cycles_per_mma, double *tflops,
-                          void *stream);
-
-/* Role profile of the warp-specialised GEMM kernels that ran on this workspace since the last call: eight
- * 64-bit cycle counters summed over CTAs (0 producer blocked on a free stage, 1 MMA issuer blocked on operands,
- * 2 on scales, 3 on a free accumulator, 4 scale writers blocked on a free slot, 5 epilogue blocked on an
- * accumulator, 6 CTA lifetime, 7 CTAs).  A wait that the first poll of its barrier already satisfies is not
- * counted, so the figures are lower bounds.  Reads and clears; synchronises.  A tuning aid with no counterpart in
- * the reference. */
-int xs_moe_debug_counters(void *workspace_dev, unsigned long long *out8, void *stream);
+                     int32_t y_capacity_rows, void *const *peer_back_dev, int32_t back_capacity_rows, int32_t wire_bf16,
+                     void *workspace_dev, void *stream);
 
 /* Reads and clears the device-side status word the kernels of the last calls on this workspace wrote
  * (bounded waits that gave up, index checks that failed).  Synchronises the stream. */

@@ -277,6 +277,8 @@ void xso_topk(const float *logits, const float *bias, int32_t *topk_ids, float *
                 if (sel[e])
                     continue;
                 float key = bias ? l[e] + bias[e] : l[e];
+                if (key != key)
+                    key = -INFINITY; /* a NaN key orders as -inf: the selection stays a total order */
                 if (best < 0 || key > bk) { /* strict >: ties keep the lower id */
                     best = e;
                     bk = key;

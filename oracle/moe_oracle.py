@@ -49,13 +49,18 @@ class _Args(C.Structure):
     ]
 
 
+def reference_root():
+    """The reference checkout: $XSTAR_REFERENCE_ROOT, else a directory named `reference` beside this repository."""
+    return os.environ.get("XSTAR_REFERENCE_ROOT") or os.path.join(os.path.dirname(os.path.dirname(_HERE)), "reference")
+
+
 def build(force=False):
     """Compile the oracle (and the reference composition when the reference tree is present)."""
     so = os.path.join(_HERE, "libxs_moe_oracle.so")
     if force or not os.path.exists(so) or os.path.getmtime(so) < os.path.getmtime(os.path.join(_HERE, "moe_oracle.c")):
         subprocess.run(["make", "-C", _HERE, "libxs_moe_oracle.so"], check=True, capture_output=True)
     ref = os.path.join(_HERE, "_ref", "libxsref.so")
-    if os.path.isdir("/root/reference/xstar_cpp/src") and (force or not os.path.exists(ref)):
+    if os.path.isdir(os.path.join(reference_root(), "xstar_cpp", "src")) and (force or not os.path.exists(ref)):
         subprocess.run(["make", "-C", _HERE, "ref"], check=True, capture_output=True)
 
 

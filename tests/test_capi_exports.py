@@ -10,9 +10,13 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
 def _declared():
-    text = open(os.path.join(ROOT, "include", "xs_moe.h")).read()
-    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
-    return sorted(set(re.findall(r"\b(xs_moe_[a-z0-9_]+)\s*\(", text)))
+    names = set()
+    inc = os.path.join(ROOT, "include")
+    for f in sorted(os.listdir(inc)):
+        if f.endswith(".h"):
+            text = re.sub(r"/\*.*?\*/", "", open(os.path.join(inc, f)).read(), flags=re.S)
+            names |= set(re.findall(r"\b(xs_moe_[a-z0-9_]+)\s*\(", text))
+    return sorted(names)
 
 
 def test_library_exports_every_declared_symbol():
@@ -20,7 +24,7 @@ def test_library_exports_every_declared_symbol():
     names = _declared()
     assert len(names) >= 15
     for n in names:
-        assert hasattr(L, n), f"{n} is declared in include/xs_moe.h but not exported"
+        assert hasattr(L, n), f"{n} is declared under include/ but not exported"
     assert sorted(capi.EXPORTS) == names, "the ctypes binding and the header list different entry points"
 
 

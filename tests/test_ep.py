@@ -339,7 +339,17 @@ def test_peer_exchange_flags_a_buffer_that_is_too_small(oracle):
     dims = dict(T=32, H=256, E=8, K=2, I=128, S=1, fmt="bf16", bias=None)
     d, ranks = _virtual_ranks(dims, R, seed=5, capacity=8)  # far fewer rows than the routing sends
     try:
-        _run_virtual(ranks)
+        # plan and dispatch only: rows that do not fit are skipped and flagged; an overflowed plan is never handed on
+        # to the expert GEMMs or the return trip
+        for k in ranks:
+            k["ids"], k["w"] = k["ops"].route(k["x"], k["ops"].keep[0]["router_w"], k["bias"])
+            k["counts"], k["offsets"], k["perm"], k["inv"] = k["ops"].permute(k["ids"])
+        all_counts = torch.cat([k["counts"] for k in ranks])
+        for k in ranks:
+            k["px"].plan(all_counts)
+            k["px"].dispatch(k["x"], k["ids"], k["inv"], k["offsets"], k["ops"].ws)
+        torch.cuda.synchronize()
+        assert int(ranks[0]["px"].offsets_local[-1]) > 8
         with pytest.raises(RuntimeError, match="out-of-range index"):
             for k in ranks:
                 k["ops"].check()

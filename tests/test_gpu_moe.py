@@ -118,6 +118,73 @@ def test_grouped_mlp_tcgen05_vs_simt_vs_oracle(oracle, counts):
     assert np.all(np.isfinite(y_tc))
 
 
+@pytest.mark.parametrize("fmt", ["bf16", "fp8", "fp4"])
+def test_grouped_mlp_clamps_offsets_beyond_the_row_capacity(fmt):
+    """Caller offsets that reach past max_rows must be flagged and never written through: y and the rows buffer are
+    followed by guard rows that have to survive the call."""
+    dims = _dims(E=4, H=256, I=256, fmt=fmt)
+    d = synth.make_inputs(dict(dims, T=1), seed=33, device="cuda")
+    cap, guard = 24, 40
+    g = torch.Generator(device="cuda").manual_seed(34)
+    x = torch.randn((cap + guard, dims["H"]), generator=g, device="cuda").to(torch.bfloat16)
+    L = capi.lib()
+    scales = None
+    rows = x
+    if fmt != "bf16":
+        rows = torch.empty(x.shape, dtype=torch.uint8, device="cuda")
+        if fmt == "fp8":
+            scales = torch.empty((x.shape[0], dims["H"] // 128), dtype=torch.float32, device="cuda")
+            capi.check(L.xs_moe_quantize_rows_fp8(capi.ptr(x), x.shape[0], dims["H"], capi.ptr(rows), capi.ptr(scales), gu.stream_ptr()))
+        else:
+            scales = torch.empty((x.shape[0], dims["H"] // 32), dtype=torch.uint8, device="cuda")
+            capi.check(L.xs_moe_quantize_rows_mxfp8(capi.ptr(x), x.shape[0], dims["H"], capi.ptr(rows), capi.ptr(scales), gu.stream_ptr()))
+    offsets = torch.tensor([0, 10, 20, 45, 60], dtype=torch.int32, device="cuda")  # 60 rows claimed, 24 held
+    cfg = gu.cfg_of(dims, T=1)
+    n = C.c_size_t(0)
+    capi.check(L.xs_moe_grouped_mlp_workspace_bytes(C.byref(cfg), cap, C.byref(n)))
+    ws = torch.zeros(n.value, dtype=torch.uint8, device="cuda")
+    y = torch.full((cap + guard, dims["H"]), 7.5, dtype=torch.float32, device="cuda")
+    w = capi.make_weights(d)
+    capi.check(L.xs_moe_grouped_mlp(C.byref(cfg), C.byref(w), capi.ptr(rows), capi.ptr(scales), capi.ptr(offsets), cap, capi.ptr(y),
+                                    capi.ptr(ws), ws.numel(), gu.stream_ptr()))
+    torch.cuda.synchronize()
+    assert torch.all(y[cap:] == 7.5), "rows beyond max_rows were written"
+    assert torch.all(y[:cap] != 7.5), "rows below max_rows were not all computed"
+    rc = L.xs_moe_check_flags(capi.ptr(ws), gu.stream_ptr())
+    assert rc == -1 and b"out-of-range index" in L.xs_moe_last_error()
+    # the rows that fit equal a clean call on those rows
+    ok_off = torch.tensor([0, 10, 20, 24, 24], dtype=torch.int32, device="cuda")
+    y2 = gu.grouped_mlp(dims, d, rows[:cap].contiguous(), ok_off, row_scales=None if scales is None else scales[:cap].contiguous())
+    assert torch.equal(y[:cap], y2)
+
+
+def test_route_nan_and_inf_keys_keep_k_distinct_experts(oracle):
+    """NaN keys order as -inf (ties to the lower id), +-inf order as numbers: every token still gets exactly K distinct
+    expert ids inside [0, E), in ascending order, equal to the oracle's."""
+    dims = _dims(T=6, E=40, K=4, H=128)
+    g = torch.Generator(device="cuda").manual_seed(23)
+    logits = torch.randn((6, 40), generator=g, device="cuda")
+    logits[0, 3] = float("nan")
+    logits[1, :] = float("nan")               # nothing but NaN: the K lowest ids win
+    logits[2, 5] = float("inf")
+    logits[2, 6] = float("-inf")
+    logits[3, 10:30] = float("nan")
+    logits[4, 0] = float("nan")
+    logits[4, 39] = float("inf")
+    logits[5, :38] = float("-inf")             # only two finite keys: -inf ties fill the rest, lower ids first
+    ids = torch.full((6, 4), -1, dtype=torch.int32, device="cuda")
+    w = torch.zeros((6, 4), dtype=torch.float32, device="cuda")
+    cfg = gu.cfg_of(dims)
+    L = capi.lib()
+    capi.check(L.xs_moe_topk(C.byref(cfg), capi.ptr(logits), None, capi.ptr(ids), capi.ptr(w), gu.stream_ptr()))
+    torch.cuda.synchronize()
+    got = ids.cpu().numpy()
+    ref_ids, _ = oracle.topk(logits.cpu().numpy(), None, 4)
+    assert np.array_equal(got, ref_ids)
+    assert np.all((got >= 0) & (got < 40)) and np.all(np.diff(got, axis=1) > 0)
+    assert list(got[1]) == [0, 1, 2, 3]
+
+
 # ---- whole layer ---------------------------------------------------------------------------------------------
 @pytest.mark.parametrize("impl", [0, 1])
 def test_forward_small_config(oracle, impl):
@@ -314,6 +381,74 @@ def test_forward_fp4_many_tokens_per_expert(oracle, T, S, E, K, H, I):
     assert torch.equal(out, gu.forward(dims, d))
 
 
+# ---- FP4 experts at the full layer shape (H=4096, I=2048: 32 / 16 k-blocks, so the scale ring of the GEMMs wraps) -----
+def test_forward_fp4_decode_shape_subset(oracle):
+    """'decode_fp4' (T=128, H=4096, E=256, k=6, FP8 always-on expert, I=2048) at full size: expert ids of all tokens
+    bit-exact, outputs on a seeded subset of tokens."""
+    dims = synth.CONFIGS["decode_fp4"]
+    d = synth.make_inputs(dims, seed=0, device="cuda")
+    out = gu.forward(dims, d)
+    sub = np.sort(np.random.default_rng(3).choice(dims["T"], 8, replace=False)).astype(np.int32)
+    ref = gu.oracle_forward(oracle, dims, d, token_subset=sub, threads=os.cpu_count() or 8)
+    logits, ids, w = gu.route(dims, d)
+    assert np.array_equal(ids.cpu().numpy(), ref["topk_ids"])
+    rel = synth.rel_l2(gu.bf16_to_f32(out)[sub], synth.bf16_bits_to_f32(ref["out"])[sub])
+    print(f"decode_fp4: rel-L2 {rel:.3e}")
+    assert rel <= FP8_TOL, rel
+    assert torch.equal(out, gu.forward(dims, d)), "FP4 forward is not deterministic"
+
+
+def test_forward_prefill_fp4_full_size_subset(oracle):
+    """'prefill_fp4' (T=8192, H=4096, E=256, k=6, FP8 always-on expert, I=2048, Zipf router bias) at full size: expert ids of
+    all tokens bit-exact, outputs on a seeded subset of tokens (the tokens-as-M kernels with hardware block scaling)."""
+    dims = synth.CONFIGS["prefill_fp4"]
+    d = synth.make_inputs(dims, seed=0, device="cuda")
+    out = gu.forward(dims, d)
+    sub = np.sort(np.random.default_rng(4).choice(dims["T"], 6, replace=False)).astype(np.int32)
+    ref = gu.oracle_forward(oracle, dims, d, token_subset=sub, threads=os.cpu_count() or 8)
+    logits, ids, w = gu.route(dims, d)
+    assert np.array_equal(ids.cpu().numpy(), ref["topk_ids"])
+    rel = synth.rel_l2(gu.bf16_to_f32(out)[sub], synth.bf16_bits_to_f32(ref["out"])[sub])
+    print(f"prefill_fp4: rel-L2 {rel:.3e}")
+    assert rel <= FP8_TOL, rel
+
+
+def test_grouped_mlp_fp4_rank_share_of_the_expert_parallel_config(oracle):
+    """What one of eight ranks computes in the expert-parallel FP4 layer: 32 local experts, 12 288 rows (2048 tokens x
+    top-6, grouped by expert), H=4096, I=2048, through xs_moe_grouped_mlp on MX-FP8 rows; per-row outputs against the
+    oracle on the rows of a seeded subset of tokens."""
+    dims = dict(T=2048, H=4096, E=32, K=6, I=2048, S=0, fmt="fp4", bias=None)
+    d = synth.make_inputs(dims, seed=5, device="cuda")
+    T, H, E, K = dims["T"], dims["H"], dims["E"], dims["K"]
+    L = capi.lib()
+    logits, ids, w = gu.route(dims, d)
+    counts, offsets, perm, inv = gu.permute(dims, ids)
+    q = torch.empty((T, H), dtype=torch.uint8, device="cuda")
+    sc = torch.empty((T, H // 32), dtype=torch.uint8, device="cuda")
+    capi.check(L.xs_moe_quantize_rows_mxfp8(capi.ptr(d["x"]), T, H, capi.ptr(q), capi.ptr(sc), gu.stream_ptr()))
+    tok = torch.div(perm, K, rounding_mode="floor").to(torch.int32)
+    rows = torch.empty((T * K, H), dtype=torch.uint8, device="cuda")
+    rsc = torch.empty((T * K, H // 32), dtype=torch.uint8, device="cuda")
+    capi.check(L.xs_moe_gather_rows(capi.ptr(q), capi.ptr(tok), capi.ptr(rows), T * K, H, gu.stream_ptr()))
+    capi.check(L.xs_moe_gather_rows(capi.ptr(sc), capi.ptr(tok), capi.ptr(rsc), T * K, H // 32, gu.stream_ptr()))
+    cfg = capi.make_config(T, H, E, K, dims["I"], 0, capi.FP4_MX32, capi.FP8_BLOCK128)
+    n = C.c_size_t(0)
+    capi.check(L.xs_moe_grouped_mlp_workspace_bytes(C.byref(cfg), T * K, C.byref(n)))
+    ws = torch.zeros(n.value, dtype=torch.uint8, device="cuda")
+    y = torch.empty((T * K, H), dtype=torch.float32, device="cuda")
+    wts = capi.make_weights(d)
+    capi.check(L.xs_moe_grouped_mlp(C.byref(cfg), C.byref(wts), capi.ptr(rows), capi.ptr(rsc), capi.ptr(offsets), T * K, capi.ptr(y),
+                                    capi.ptr(ws), ws.numel(), gu.stream_ptr()))
+    capi.check(L.xs_moe_check_flags(capi.ptr(ws), gu.stream_ptr()))
+    sub = np.sort(np.random.default_rng(6).choice(T, 24, replace=False)).astype(np.int32)
+    ref = gu.oracle_forward(oracle, dims, d, token_subset=sub, threads=os.cpu_count() or 8, want_y=True)
+    assert np.array_equal(ids.cpu().numpy(), ref["topk_ids"]) and np.array_equal(inv.cpu().numpy(), ref["inv"])
+    r = ref["inv"].reshape(T, K)[sub].reshape(-1)
+    rel = synth.rel_l2(y.cpu().numpy()[r], ref["y_rows"][r])
+    print(f"fp4 grouped MLP, 32 experts x {T * K} rows: rel-L2 {rel:.3e} on {len(r)} rows; loads {int(counts.min())}..{int(counts.max())}")
+    assert rel <= FP8_TOL, rel
+
+
 # ---- small stage entry points ----------------------------------------------------------------------------------
 def test_gather_rows_and_bf16_return_rows():
     g = torch.Generator(device="cuda").manual_seed(61)
@@ -353,9 +488,18 @@ def test_combine_with_bf16_rows_matches_f32_combine_on_rounded_rows():
     assert synth.rel_l2(b.float().cpu().numpy(), ref.cpu().numpy()) < 5e-3
 
 
-def test_mma_rate_probe_runs_and_reports():
+def test_rate_probes_run_and_report():
     ws = torch.zeros(4096, dtype=torch.uint8, device="cuda")
     cyc, iss, tf = C.c_double(), C.c_double(), C.c_double()
-    capi.check(capi.lib().xs_moe_probe_mma_rate(1, 64, 200, 2, capi.ptr(ws), ws.numel(), C.byref(cyc), C.byref(iss), C.byref(tf), None))
-    assert 10 < cyc.value < 5000 and tf.value > 1.0
-    assert capi.lib().xs_moe_probe_mma_rate(1, 24, 200, 1, capi.ptr(ws), ws.numel(), C.byref(cyc), C.byref(iss), C.byref(tf), None) == -1
+    L = capi.lib()
+    capi.check(L.xs_moe_probe_mma_rate(1, 64, 200, 2, capi.ptr(ws), ws.numel(), C.byref(cyc), C.byref(iss), C.byref(tf), None))
+    assert 1 < cyc.value < 5000 and tf.value > 1.0
+    assert L.xs_moe_probe_mma_rate(1, 24, 200, 1, capi.ptr(ws), ws.numel(), C.byref(cyc), C.byref(iss), C.byref(tf), None) == -1
+    bpc, mcyc = C.c_double(), C.c_double()
+    for shape in range(4):
+        capi.check(L.xs_moe_probe_tmem_ld_rate(shape, 8, 100, shape & 1, capi.ptr(ws), ws.numel(), C.byref(bpc), C.byref(mcyc), None))
+        assert 1.0 < bpc.value < 4096.0
+    assert L.xs_moe_probe_tmem_ld_rate(0, 6, 100, 0, capi.ptr(ws), ws.numel(), C.byref(bpc), C.byref(mcyc), None) == -1
+    before = capi.launch_count()
+    capi.check(L.xs_moe_probe_mma_rate(0, 64, 200, 1, capi.ptr(ws), ws.numel(), C.byref(cyc), C.byref(iss), C.byref(tf), None))
+    assert capi.launch_count() == before + 1

@@ -114,3 +114,29 @@ def test_moe_op_fp8_experts_through_the_binding(oracle):
     assert synth.rel_l2(got, synth.bf16_bits_to_f32(ref["out"])) <= 1e-2
     with pytest.raises(RuntimeError, match="missing scale"):
         xstar_cpp.moe(dev["x"], dev["router_w"], dev["gate_up_w"], dev["down_w"], dims["K"])
+
+
+@pytest.mark.gpu
+def test_moe_op_fp4_experts_through_the_binding(oracle):
+    """FP4 e2m1 experts enter as packed byte tensors tagged Float4E2M1x2 (last dim counts bytes: K/2) with UE8M0 scale
+    tensors (one byte per 32 elements of K); the always-on expert beside them is FP8 with Float32 block scales."""
+    dims = dict(T=40, H=512, E=8, K=2, I=256, S=1, fmt="fp4", bias=None)
+    d = synth.make_inputs(dims, seed=6)
+    D = xstar_cpp.DType
+    tag = {"gate_up_w": D.Float4E2M1x2, "down_w": D.Float4E2M1x2, "gate_up_scale": D.UE8M0, "down_scale": D.UE8M0,
+           "shared_gate_up_w": D.Float8E4M3, "shared_down_w": D.Float8E4M3}
+    dev = {k: xstar_cpp.to_cuda(torch_to_cpp(v, tag.get(k))) for k, v in d.items() if v is not None}
+    assert dev["gate_up_w"].shape() == [8, 512, 256] and dev["gate_up_w"].nbytes() == 8 * 512 * 256
+    assert dev["gate_up_scale"].shape() == [8, 512, 16] and dev["down_scale"].dtype() == D.UE8M0
+    out = xstar_cpp.moe(dev["x"], dev["router_w"], dev["gate_up_w"], dev["down_w"], dims["K"], gate_up_scale=dev["gate_up_scale"],
+                        down_scale=dev["down_scale"], shared_gate_up_weight=dev["shared_gate_up_w"], shared_down_weight=dev["shared_down_w"],
+                        shared_gate_up_scale=dev["shared_gate_up_scale"], shared_down_scale=dev["shared_down_scale"])
+    got = cpp_to_torch(xstar_cpp.to_cpu(out), (40, 512)).float().numpy()
+    n = synth.to_numpy_storage(d)
+    ref = oracle.moe_forward(oracle.FP4, n["x"], n["router_w"], n["gate_up_w"], n["down_w"], dims["K"], gate_up_scale=n["gate_up_scale"],
+                             down_scale=n["down_scale"], shared_gate_up_w=n["shared_gate_up_w"], shared_down_w=n["shared_down_w"],
+                             shared_gate_up_scale=n["shared_gate_up_scale"], shared_down_scale=n["shared_down_scale"], threads=4)
+    assert synth.rel_l2(got, synth.bf16_bits_to_f32(ref["out"])) <= 1e-2
+    with pytest.raises(RuntimeError, match="dtype mismatch"):  # f32 scales next to FP4 experts
+        xstar_cpp.moe(dev["x"], dev["router_w"], dev["gate_up_w"], dev["down_w"], dims["K"], gate_up_scale=dev["shared_gate_up_scale"],
+                      down_scale=dev["shared_down_scale"])

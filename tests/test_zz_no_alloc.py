@@ -1,7 +1,7 @@
 """xs_moe_permute_noalloc: the permutation for callers that cannot allocate device memory (an engine whose KV
 page pool already owns all free HBM; a serving thread that must not hit cudaMalloc's device-wide
 synchronisation).  Its scratch is a fixed array inside the library, so this test checks, through the C ABI,
-that it returns exactly what xs_moe_permute returns, on two calls in a row (the second smaller than the first,
+that it returns exactly what xs_moe_permute returns -- and what the CPU oracle's permutation gives -- on two calls in a row (the second smaller than the first,
 so anything the first call left in the shared array would show), that device memory does not move, and that
 oversized calls are refused with a clear message.  Collected last on purpose."""
 import ctypes as C
@@ -31,7 +31,7 @@ def _noalloc(T, E, K, ids_dev):
     return [o.cpu().numpy() for o in outs]
 
 
-def test_noalloc_permute_equals_workspace_permute_twice_in_a_row():
+def test_noalloc_permute_equals_workspace_permute_twice_in_a_row(oracle):
     if not torch.cuda.is_available():
         pytest.fail("needs a CUDA device")
     cases = [(3000, 256, 6, 1), (77, 64, 4, 2)]  # 12 chunks then 1 chunk: the second call reuses a dirtier array
@@ -41,8 +41,9 @@ def test_noalloc_permute_equals_workspace_permute_twice_in_a_row():
         got = _noalloc(T, E, K, ids_dev)
         dims = dict(T=T, H=256, E=E, K=K, I=128, S=0, fmt="bf16", bias=None)
         ref = [t.cpu().numpy() for t in gu.permute(dims, ids_dev)]
-        for name, a, b in zip(("counts", "offsets", "perm", "inv"), got, ref):
+        for name, a, b, c in zip(("counts", "offsets", "perm", "inv"), got, ref, oracle.permute(ids, E)):
             assert np.array_equal(a, b), name  # integer outputs: bit-exact
+            assert np.array_equal(a, c), name + " (against the CPU oracle)"
     # same inputs again after the small call: still identical
     T, E, K, seed = cases[0]
     ids_dev = torch.from_numpy(_ids(T, E, K, seed)).cuda()

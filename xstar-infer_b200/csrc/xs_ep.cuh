@@ -156,10 +156,15 @@ template <bool WIRE_BF16>
 __global__ void __launch_bounds__(256)
 ep_return_kernel(const float *__restrict__ y, const int32_t *__restrict__ all_counts, const int32_t *__restrict__ offsets_local,
                  const int32_t *__restrict__ src_offsets, uint8_t *const *__restrict__ peer_back, int H, int E, int R, int me,
-                 int back_capacity, int32_t *status)
+                 int y_capacity, int back_capacity, int32_t *status)
 {
     const int El = E / R;
-    const int total = offsets_local[El];
+    int total = offsets_local[El];
+    if (total > y_capacity) { // never read past the rows y holds; the shortfall is reported
+        total = y_capacity;
+        if (blockIdx.x == 0 && threadIdx.x == 0)
+            atomicOr(status, 2);
+    }
     __shared__ int s_dst_rank, s_dst_row;
     for (int g = blockIdx.x; g < total; g += gridDim.x) {
         if (threadIdx.x == 0) {

@@ -281,7 +281,7 @@ __global__ void grouped_gemm_bf16_simt_kernel(const __nv_bfloat16 *__restrict__ 
 {
     const int row = offsets[0] + blockIdx.x; // offsets may point into a longer table: segment 0 starts at offsets[0]
     const int total_rows = offsets[num_experts];
-    if (row >= total_rows)
+    if (row >= total_rows || row >= static_cast<int>(gridDim.x)) // gridDim.x = capacity of the row buffers
         return;
     // expert of this row: offsets is non-decreasing; linear scan by one thread then broadcast
     __shared__ int s_e;
@@ -391,7 +391,7 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     unsigned long long *prof = reinterpret_cast<unsigned long long *>(status + 16); // role profile, see xs_moe_debug_counters
-    const long long t_start = clock64();
+    const long long t_start = prof_clock();
     long long w0 = 0, w1 = 0;
 
     if (threadIdx.x == 0) {
@@ -460,9 +460,9 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
                 *abort_flag = 1;
                 atomicOr(status, kStatusWaitTimeout);
             }
-            atomicAdd(&prof[0], static_cast<unsigned long long>(w0));
-            atomicAdd(&prof[6], static_cast<unsigned long long>(clock64() - t_start));
-            atomicAdd(&prof[7], 1ull);
+            prof_add(prof, 0, w0);
+            prof_add(prof, 6, prof_clock() - t_start);
+            prof_add(prof, 7, 1);
         }
     } else if (warp == 1) {
         if (lane == 0) {
@@ -502,8 +502,8 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
                 *abort_flag = 1;
                 atomicOr(status, kStatusWaitTimeout);
             }
-            atomicAdd(&prof[1], static_cast<unsigned long long>(w0));
-            atomicAdd(&prof[3], static_cast<unsigned long long>(w1));
+            prof_add(prof, 1, w0);
+            prof_add(prof, 3, w1);
         }
     } else {
         const int q = warp & 3;
@@ -641,7 +641,7 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
             atomicOr(status, kStatusWaitTimeout);
         }
         if (warp == 2 && lane == 0)
-            atomicAdd(&prof[5], static_cast<unsigned long long>(w0));
+            prof_add(prof, 5, w0);
     }
 
     __syncwarp();

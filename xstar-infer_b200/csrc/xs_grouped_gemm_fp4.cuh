@@ -77,7 +77,7 @@ grouped_gemm_fp4_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
     const int lane = threadIdx.x & 31;
     // role profile: cycles each role spent blocked, summed over CTAs into eight 64-bit counters behind the status word
     unsigned long long *prof = reinterpret_cast<unsigned long long *>(status + 16);
-    const long long t_start = clock64();
+    const long long t_start = prof_clock();
     long long w0 = 0, w1 = 0, w2 = 0;
 
     if (threadIdx.x == 0) {
@@ -145,9 +145,9 @@ grouped_gemm_fp4_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
                 *abort_flag = 1;
                 atomicOr(status, kStatusWaitTimeout);
             }
-            atomicAdd(&prof[0], static_cast<unsigned long long>(w0));
-            atomicAdd(&prof[6], static_cast<unsigned long long>(clock64() - t_start));
-            atomicAdd(&prof[7], 1ull);
+            prof_add(prof, 0, w0);
+            prof_add(prof, 6, prof_clock() - t_start);
+            prof_add(prof, 7, 1);
         }
     } else if (warp == 1) {
         if (lane == 0) {
@@ -202,9 +202,9 @@ grouped_gemm_fp4_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
                 *abort_flag = 1;
                 atomicOr(status, kStatusWaitTimeout);
             }
-            atomicAdd(&prof[1], static_cast<unsigned long long>(w0));
-            atomicAdd(&prof[2], static_cast<unsigned long long>(w1));
-            atomicAdd(&prof[3], static_cast<unsigned long long>(w2));
+            prof_add(prof, 1, w0);
+            prof_add(prof, 2, w1);
+            prof_add(prof, 3, w2);
         }
     } else if (warp == 6) {
         // Scale loader.  The global loads run kSfAhead k-blocks ahead of the shared-memory stores (a register ring),
@@ -293,7 +293,7 @@ grouped_gemm_fp4_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
             atomicOr(status, kStatusWaitTimeout);
         }
         if (warp == 6 && lane == 0)
-            atomicAdd(&prof[4], static_cast<unsigned long long>(w0));
+            prof_add(prof, 4, w0);
     } else {
         const int q = warp & 3;
         bool ok = true;
@@ -360,7 +360,7 @@ grouped_gemm_fp4_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
             atomicOr(status, kStatusWaitTimeout);
         }
         if (warp == 2 && lane == 0)
-            atomicAdd(&prof[5], static_cast<unsigned long long>(w0));
+            prof_add(prof, 5, w0);
     }
 
     __syncwarp();

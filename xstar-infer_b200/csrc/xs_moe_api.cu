@@ -2,6 +2,7 @@
 // tensor-map construction and kernel launches.  No exception leaves this file; every failure becomes a
 // negative status plus a thread-local message.
 #include "xs_moe.h"
+#include "xs_moe_tuning.h"
 
 #include <cuda.h>
 #include <cuda_runtime.h>
@@ -10,6 +11,7 @@
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+#include <atomic>
 #include <mutex>
 #include <string>
 
@@ -25,6 +27,13 @@
 namespace {
 
 thread_local std::string g_last_error;
+
+// kernels this library has enqueued since the process started (captured launches count once, at capture)
+std::atomic<unsigned long long> g_launches{0};
+inline void note_launch()
+{
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+}
 
 int fail(int status, const char *fmt, ...)
 {
@@ -183,7 +192,7 @@ int pick_n_tile(long rows, int groups, int fmt, int hidden)
 // always-on expert is merged into the same launches, one more segment for its rows).
 struct GroupedPlan {
     int n_tile = 0, max_tiles = 0;
-    size_t off_tile_expert = 0, off_tile_row0 = 0, off_num_tiles = 0, off_act = 0, off_act_scale = 0, bytes = 0;
+    size_t off_tile_expert = 0, off_tile_row0 = 0, off_num_tiles = 0, off_offsets = 0, off_act = 0, off_act_scale = 0, bytes = 0;
 };
 
 GroupedPlan plan_grouped(int max_rows, int routed_rows, int routed_groups, int segments, int I, int fmt, int H)
@@ -195,6 +204,7 @@ GroupedPlan plan_grouped(int max_rows, int routed_rows, int routed_groups, int s
     p.off_tile_expert = o; o = align_up(o + sizeof(int32_t) * p.max_tiles, 256);
     p.off_tile_row0 = o;   o = align_up(o + sizeof(int32_t) * p.max_tiles, 256);
     p.off_num_tiles = o;   o = align_up(o + sizeof(int32_t), 256);
+    p.off_offsets = o;     o = align_up(o + sizeof(int32_t) * (segments + 1), 256); // segment offsets clamped to max_rows
     p.off_act = o;         o = align_up(o + static_cast<size_t>(max_rows) * I * (fmt == XS_MOE_BF16 ? 2 : 1), 256);
     p.off_act_scale = o;   o = align_up(o + (fmt == XS_MOE_BF16 ? 0 : static_cast<size_t>(max_rows) * (I / 128) * 4), 256); // FP4: I/32 bytes
     p.bytes = o;
@@ -286,6 +296,7 @@ int launch_logits(const XsMoeConfig *c, const void *x, const void *rw, float *lo
                 configured_rs[dev_rs] = true;
         }
         xs::router_logits_small_kernel<1><<<dim3((E + 31) / 32, T), 32, xs::rs_smem_bytes<1>(), st>>>(xb, rwb, logits, T, H, E);
+        note_launch();
     } else if (T <= 1024) {
         // decode-sized batch: one output per thread, 8 experts x 32 tokens per block, cp.async pipeline
         dim3 grid((E + xs::kRdExperts - 1) / xs::kRdExperts, (T + xs::kRdTokens - 1) / xs::kRdTokens);
@@ -298,6 +309,7 @@ int launch_logits(const XsMoeConfig *c, const void *x, const void *rw, float *lo
                 configured_rd[dev_rd] = true;
         }
         xs::router_logits_decode_kernel<<<grid, xs::kRdThreads, xs::kRdSmemBytes, st>>>(xb, rwb, logits, T, H, E);
+        note_launch();
     } else {
         static bool configured[64] = {};
         int dev = 0;
@@ -309,10 +321,13 @@ int launch_logits(const XsMoeConfig *c, const void *x, const void *rw, float *lo
                 configured[dev] = true;
         }
         const int eg = (E + xs::kRbExperts - 1) / xs::kRbExperts;
-        if (static_cast<long>(eg) * ((T + 63) / 64) >= 256)
+        if (static_cast<long>(eg) * ((T + 63) / 64) >= 256) {
             xs::router_logits_big_kernel<4><<<dim3(eg, (T + 63) / 64), xs::kRbThreads, xs::rb_smem_bytes<4>(), st>>>(xb, rwb, logits, T, H, E);
-        else // 32-token tiles keep more SMs busy on medium batches
+            note_launch();
+        } else { // 32-token tiles keep more SMs busy on medium batches
             xs::router_logits_mid_kernel<2><<<dim3(eg, (T + 31) / 32), xs::kRbThreads, xs::rm_smem_bytes<2>(), st>>>(xb, rwb, logits, T, H, E);
+            note_launch();
+        }
     }
     XS_CUDA(cudaGetLastError());
     return 0;
@@ -324,12 +339,16 @@ int launch_topk(const XsMoeConfig *c, const float *logits, const float *bias, in
     if (T == 0)
         return 0;
     const int blocks = (T + 3) / 4;
-    if (E <= 32)
+    if (E <= 32) {
         xs::topk_kernel<1><<<blocks, 128, 0, st>>>(logits, bias, ids, w, T, E, K);
-    else if (E <= 256)
+        note_launch();
+    } else if (E <= 256) {
         xs::topk_kernel<8><<<blocks, 128, 0, st>>>(logits, bias, ids, w, T, E, K);
-    else
+        note_launch();
+    } else {
         xs::topk_kernel<32><<<blocks, 128, 0, st>>>(logits, bias, ids, w, T, E, K);
+        note_launch();
+    }
     XS_CUDA(cudaGetLastError());
     return 0;
 }
@@ -349,11 +368,14 @@ int launch_permute(const XsMoeConfig *c, const int32_t *ids, int32_t *counts, in
     const int T = c->num_tokens, E = c->num_experts, K = c->top_k;
     const size_t smem = static_cast<size_t>(E) * xs::kChunkWords * 4;
     xs::permute_count_kernel<<<chunks, xs::kChunkTokens, smem, st>>>(ids, chunk_counts, T, E, K, status);
+    note_launch();
     XS_CUDA(cudaGetLastError());
     const int threads = (E + 31) / 32 * 32;
     xs::permute_scan_kernel<<<1, threads, 0, st>>>(chunk_counts, counts, offsets, chunk_base, chunks, E, extra_rows);
+    note_launch();
     XS_CUDA(cudaGetLastError());
     xs::permute_fill_kernel<<<chunks, xs::kChunkTokens, smem, st>>>(ids, chunk_base, perm, inv, T, E, K, status);
+    note_launch();
     XS_CUDA(cudaGetLastError());
     return 0;
 }
@@ -376,6 +398,7 @@ int launch_permute_small(const XsMoeConfig *c, const int32_t *ids, int32_t *coun
     const size_t smem = static_cast<size_t>(E) * xs::kChunkWords * 4 + static_cast<size_t>(E) * 4;
     xs::permute_small_kernel<<<1, xs::kChunkTokens, smem, st>>>(ids, counts, offsets, perm, inv, T, E, K, extra_rows, gp.n_tile,
                                                                 gp.max_tiles, tb.tile_expert, tb.tile_row0, tb.num_tiles, status);
+    note_launch();
     XS_CUDA(cudaGetLastError());
     return 0;
 }
@@ -407,6 +430,7 @@ int launch_gemm_t(const CUtensorMap &tw, const CUtensorMap &tw2, const CUtensorM
     if (grid < 1)
         grid = 1;
     kern<<<grid, xs::kGemmThreads, smem, st>>>(tw, tw2, tx, offsets, tt, groups, w_rows, n_out, K, out, status, stages);
+    note_launch();
     XS_CUDA(cudaGetLastError());
     return 0;
 }
@@ -454,6 +478,7 @@ int launch_gemm_fp8_t(const CUtensorMap &tw, const CUtensorMap &tw2, const CUten
     if (grid < 1)
         grid = 1;
     kern<<<grid, xs::kGemmThreads, smem, st>>>(tw, tw2, tx, offsets, tt, sc, groups, w_rows, n_out, K, out, status, stages);
+    note_launch();
     XS_CUDA(cudaGetLastError());
     return 0;
 }
@@ -498,6 +523,7 @@ int launch_prefill_fp8(const CUtensorMap &tw, const CUtensorMap &tw2, const CUte
     if (grid < 1)
         grid = 1;
     kern<<<grid, xs::kPfThreads, smem, st>>>(tw, tw2, tx, offsets, tt, sc, groups, w_rows, n_out, K, out, status, stages);
+    note_launch();
     XS_CUDA(cudaGetLastError());
     return 0;
 }
@@ -531,6 +557,7 @@ int launch_gemm_fp4_t(const CUtensorMap &tw, const CUtensorMap &tx, const int32_
     if (grid < 1)
         grid = 1;
     kern<<<grid, xs::kFp4Threads, smem, st>>>(tw, tx, offsets, tt, sc, w_rows, n_out, K, out, status, stages);
+    note_launch();
     XS_CUDA(cudaGetLastError());
     return 0;
 }
@@ -573,6 +600,7 @@ int launch_prefill_fp4(const CUtensorMap &tw, const CUtensorMap &tx, const int32
     if (grid < 1)
         grid = 1;
     kern<<<grid, xs::kPf4Threads, smem, st>>>(tw, tx, offsets, tt, sc, w_rows, n_out, K, out, status, stages);
+    note_launch();
     XS_CUDA(cudaGetLastError());
     return 0;
 }
@@ -637,30 +665,42 @@ int run_grouped(const GroupedArgs &a, cudaStream_t st, cudaEvent_t mid = nullptr
         const __nv_bfloat16 *rows = static_cast<const __nv_bfloat16 *>(a.rows);
         xs::grouped_gemm_bf16_simt_kernel<true><<<grid, 256, 0, st>>>(static_cast<const __nv_bfloat16 *>(a.gu), rows, a.offsets, groups,
                                                                       2 * I, I, H, act);
-        if (a.gu2)
+        note_launch();
+        if (a.gu2) {
             xs::grouped_gemm_bf16_simt_kernel<true><<<grid, 256, 0, st>>>(static_cast<const __nv_bfloat16 *>(a.gu2), rows,
                                                                           a.offsets + groups, 1, 2 * I, I, H, act);
+            note_launch();
+        }
         XS_CUDA(cudaGetLastError());
         if (mid)
             XS_CUDA(cudaEventRecord(mid, st));
         const __nv_bfloat16 *actb = static_cast<const __nv_bfloat16 *>(act);
         xs::grouped_gemm_bf16_simt_kernel<false><<<grid, 256, 0, st>>>(static_cast<const __nv_bfloat16 *>(a.dw), actb, a.offsets, groups,
                                                                        H, H, I, a.y);
-        if (a.gu2)
+        note_launch();
+        if (a.gu2) {
             xs::grouped_gemm_bf16_simt_kernel<false><<<grid, 256, 0, st>>>(static_cast<const __nv_bfloat16 *>(a.dw2), actb,
                                                                            a.offsets + groups, 1, H, H, I, a.y);
+            note_launch();
+        }
         XS_CUDA(cudaGetLastError());
         return 0;
     }
     TileBuffers tb = tile_buffers(a.scratch, a.gp);
     xs::TileTable tt{tb.tile_expert, tb.tile_row0, tb.num_tiles};
+    // The GEMM kernels read segment bounds from `offs`: the caller's offsets clamped to the capacity of the row buffers
+    // (a fused routing kernel that already built the tile table produced consistent offsets itself).
+    const int32_t *offs = a.offsets;
     if (!a.tiles_ready) {
         const int threads = (segments + 31) / 32 * 32;
         if (threads > 1024)
             return fail(XS_MOE_ERR_UNSUPPORTED, "expert count mismatch: at most 1023 local experts next to an always-on expert");
-        xs::tile_table_kernel<<<1, threads, 0, st>>>(a.offsets, segments, a.gp.n_tile, a.gp.max_tiles, tb.tile_expert, tb.tile_row0,
-                                                     tb.num_tiles, a.status);
+        int32_t *clamped = reinterpret_cast<int32_t *>(a.scratch + a.gp.off_offsets);
+        xs::tile_table_kernel<<<1, threads, 0, st>>>(a.offsets, segments, a.gp.n_tile, a.gp.max_tiles, a.max_rows, clamped, tb.tile_expert,
+                                                     tb.tile_row0, tb.num_tiles, a.status);
+        note_launch();
         XS_CUDA(cudaGetLastError());
+        offs = clamped;
     }
     if (fp4) {
         CUtensorMap t_wgu, t_wd, t_x, t_act;
@@ -676,21 +716,21 @@ int run_grouped(const GroupedArgs &a, cudaStream_t st, cudaEvent_t mid = nullptr
         if (a.gp.n_tile == 128) {
             // many tokens per expert: tokens as the M of N = 256 block-scaled MMAs
             xs::MxScales p1{static_cast<const uint8_t *>(a.gu_scale), reinterpret_cast<const uint8_t *>(a.row_scale), act_scale, a.max_rows};
-            if (int rc = launch_prefill_fp4<true>(t_wgu, t_x, a.offsets, tt, p1, 2 * I, I, H, act, a.status, a.gp.max_tiles * (I / 128), st))
+            if (int rc = launch_prefill_fp4<true>(t_wgu, t_x, offs, tt, p1, 2 * I, I, H, act, a.status, a.gp.max_tiles * (I / 128), st))
                 return rc;
             if (mid)
                 XS_CUDA(cudaEventRecord(mid, st));
             xs::MxScales p2{static_cast<const uint8_t *>(a.dw_scale), act_scale, nullptr, a.max_rows};
-            return launch_prefill_fp4<false>(t_wd, t_act, a.offsets, tt, p2, H, H, I, a.y, a.status, a.gp.max_tiles * (H / 256), st);
+            return launch_prefill_fp4<false>(t_wd, t_act, offs, tt, p2, H, H, I, a.y, a.status, a.gp.max_tiles * (H / 256), st);
         }
         xs::MxScales s1{static_cast<const uint8_t *>(a.gu_scale), reinterpret_cast<const uint8_t *>(a.row_scale), act_scale, a.max_rows};
-        if (int rc = launch_gemm_fp4<true>(a.gp.n_tile, t_wgu, t_x, a.offsets, tt, s1, 2 * I, I, H, act, a.status,
+        if (int rc = launch_gemm_fp4<true>(a.gp.n_tile, t_wgu, t_x, offs, tt, s1, 2 * I, I, H, act, a.status,
                                            a.gp.max_tiles * (I / xs::kTileM), st))
             return rc;
         if (mid)
             XS_CUDA(cudaEventRecord(mid, st));
         xs::MxScales s2{static_cast<const uint8_t *>(a.dw_scale), act_scale, nullptr, a.max_rows};
-        return launch_gemm_fp4<false>(a.gp.n_tile, t_wd, t_act, a.offsets, tt, s2, H, H, I, a.y, a.status,
+        return launch_gemm_fp4<false>(a.gp.n_tile, t_wd, t_act, offs, tt, s2, H, H, I, a.y, a.status,
                                       a.gp.max_tiles * (H / xs::kTileM), st);
     }
     const CUtensorMapDataType dt = fp8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
@@ -716,32 +756,32 @@ int run_grouped(const GroupedArgs &a, cudaStream_t st, cudaEvent_t mid = nullptr
         return rc;
     const int work_gu = a.gp.max_tiles * (I / xs::kTileM), work_d = a.gp.max_tiles * (H / xs::kTileM);
     if (!fp8) {
-        if (int rc = launch_gemm<true>(a.gp.n_tile, t_wgu, t_wgu2, t_x, a.offsets, tt, groups, 2 * I, I, H, act, a.status, work_gu, st))
+        if (int rc = launch_gemm<true>(a.gp.n_tile, t_wgu, t_wgu2, t_x, offs, tt, groups, 2 * I, I, H, act, a.status, work_gu, st))
             return rc;
         if (mid)
             XS_CUDA(cudaEventRecord(mid, st));
-        return launch_gemm<false>(a.gp.n_tile, t_wd, t_wd2, t_act, a.offsets, tt, groups, H, H, I, a.y, a.status, work_d, st);
+        return launch_gemm<false>(a.gp.n_tile, t_wd, t_wd2, t_act, offs, tt, groups, H, H, I, a.y, a.status, work_d, st);
     }
     float *act_scale = reinterpret_cast<float *>(a.scratch + a.gp.off_act_scale);
     if (a.gp.n_tile == 128) {
         // many tokens per expert: tokens as the M of N = 256 MMAs (prefill kernel); the maps above already use 128-row boxes
         xs::Fp8Scales p1{static_cast<const float *>(a.gu_scale), static_cast<const float *>(a.gu2_scale), a.row_scale, act_scale};
-        if (int rc = launch_prefill_fp8<true>(t_wgu, t_wgu2, t_x, a.offsets, tt, p1, groups, 2 * I, I, H, act, a.status,
+        if (int rc = launch_prefill_fp8<true>(t_wgu, t_wgu2, t_x, offs, tt, p1, groups, 2 * I, I, H, act, a.status,
                                               a.gp.max_tiles * (I / 128), st))
             return rc;
         if (mid)
             XS_CUDA(cudaEventRecord(mid, st));
         xs::Fp8Scales p2{static_cast<const float *>(a.dw_scale), static_cast<const float *>(a.dw2_scale), act_scale, nullptr};
-        return launch_prefill_fp8<false>(t_wd, t_wd2, t_act, a.offsets, tt, p2, groups, H, H, I, a.y, a.status,
+        return launch_prefill_fp8<false>(t_wd, t_wd2, t_act, offs, tt, p2, groups, H, H, I, a.y, a.status,
                                          a.gp.max_tiles * (H / 256), st);
     }
     xs::Fp8Scales s1{static_cast<const float *>(a.gu_scale), static_cast<const float *>(a.gu2_scale), a.row_scale, act_scale};
-    if (int rc = launch_gemm_fp8<true>(a.gp.n_tile, t_wgu, t_wgu2, t_x, a.offsets, tt, s1, groups, 2 * I, I, H, act, a.status, work_gu, st))
+    if (int rc = launch_gemm_fp8<true>(a.gp.n_tile, t_wgu, t_wgu2, t_x, offs, tt, s1, groups, 2 * I, I, H, act, a.status, work_gu, st))
         return rc;
     if (mid)
         XS_CUDA(cudaEventRecord(mid, st));
     xs::Fp8Scales s2{static_cast<const float *>(a.dw_scale), static_cast<const float *>(a.dw2_scale), act_scale, nullptr};
-    return launch_gemm_fp8<false>(a.gp.n_tile, t_wd, t_wd2, t_act, a.offsets, tt, s2, groups, H, H, I, a.y, a.status, work_d, st);
+    return launch_gemm_fp8<false>(a.gp.n_tile, t_wd, t_wd2, t_act, offs, tt, s2, groups, H, H, I, a.y, a.status, work_d, st);
 }
 
 __global__ void set_two_ints_kernel(int32_t *p, int a, int b)
@@ -755,6 +795,7 @@ int launch_quantize_rows_mx(const void *x, const int32_t *dst, int nd, uint8_t *
     if (rows == 0)
         return 0;
     xs::quantize_rows_mxfp8_kernel<<<rows, 256, 0, st>>>(static_cast<const __nv_bfloat16 *>(x), dst, nd, q, scale, rows, cols);
+    note_launch();
     XS_CUDA(cudaGetLastError());
     return 0;
 }
@@ -766,6 +807,7 @@ int launch_quantize_rows(const void *x, uint8_t *q, float *scale, int rows, int 
     const long warps = static_cast<long>(rows) * (cols / 128);
     const int blocks = static_cast<int>((warps + 7) / 8);
     xs::quantize_rows_fp8_kernel<<<blocks, 256, 0, st>>>(static_cast<const __nv_bfloat16 *>(x), q, scale, rows, cols);
+    note_launch();
     XS_CUDA(cudaGetLastError());
     return 0;
 }
@@ -798,6 +840,30 @@ int xs_moe_device_check(void)
 {
     DeviceInfo di;
     return device_info(&di);
+}
+
+int xs_moe_device_count(int32_t *count)
+{
+    if (!count)
+        return fail(XS_MOE_ERR_INVALID_ARG, "null out-pointer");
+    int n = 0;
+    XS_CUDA(cudaGetDeviceCount(&n));
+    *count = n;
+    return 0;
+}
+int xs_moe_set_device(int32_t device)
+{
+    XS_CUDA(cudaSetDevice(device));
+    return 0;
+}
+int xs_moe_current_device(int32_t *device)
+{
+    if (!device)
+        return fail(XS_MOE_ERR_INVALID_ARG, "null out-pointer");
+    int d = 0;
+    XS_CUDA(cudaGetDevice(&d));
+    *device = d;
+    return 0;
 }
 
 int xs_moe_device_alloc(void **ptr, size_t bytes)
@@ -866,6 +932,15 @@ int xs_moe_route(const XsMoeConfig *cfg, const void *x, const void *rw, const fl
         logits = reinterpret_cast<float *>(static_cast<uint8_t *>(ws) + p.off_logits);
     }
     return launch_route(cfg, x, rw, bias, logits, ids, w, static_cast<cudaStream_t>(stream));
+}
+
+int xs_moe_topk(const XsMoeConfig *cfg, const float *logits, const float *bias, int32_t *ids, float *w, void *stream)
+{
+    if (int rc = check_cfg(cfg))
+        return rc;
+    if (!logits || !ids || !w)
+        return fail(XS_MOE_ERR_INVALID_ARG, "null tensor pointer");
+    return launch_topk(cfg, logits, bias, ids, w, static_cast<cudaStream_t>(stream));
 }
 
 int xs_moe_permute(const XsMoeConfig *cfg, const int32_t *ids, int32_t *counts, int32_t *offsets, int32_t *perm, int32_t *inv,
@@ -970,12 +1045,15 @@ int xs_moe_gather_rows(const void *src, const int32_t *index, void *dst, int32_t
     if (n_rows == 0)
         return 0;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    if (row_bytes % 16 == 0 && reinterpret_cast<uintptr_t>(src) % 16 == 0 && reinterpret_cast<uintptr_t>(dst) % 16 == 0)
+    if (row_bytes % 16 == 0 && reinterpret_cast<uintptr_t>(src) % 16 == 0 && reinterpret_cast<uintptr_t>(dst) % 16 == 0) {
         xs::gather_rows_kernel<<<n_rows, 256, 0, st>>>(static_cast<const uint8_t *>(src), index, static_cast<uint8_t *>(dst), n_rows,
                                                        n_rows, 1, row_bytes);
-    else
+        note_launch();
+    } else {
         xs::gather_rows4_kernel<<<n_rows, 64, 0, st>>>(static_cast<const uint32_t *>(src), index, static_cast<uint32_t *>(dst), n_rows,
                                                        n_rows, 1, row_bytes / 4);
+        note_launch();
+    }
     XS_CUDA(cudaGetLastError());
     return 0;
 }
@@ -993,6 +1071,7 @@ int xs_moe_combine(const XsMoeConfig *cfg, const float *y, const int32_t *inv, c
     int gy = (H + 1023) / 1024;
     xs::combine_kernel<float><<<dim3(T, gy), 128, 0, static_cast<cudaStream_t>(stream)>>>(y, inv, topk_w, shared,
                                                                                          static_cast<__nv_bfloat16 *>(out), T, H, K);
+    note_launch();
     XS_CUDA(cudaGetLastError());
     return 0;
 }
@@ -1010,6 +1089,7 @@ int xs_moe_combine_bf16_rows(const XsMoeConfig *cfg, const void *y_bf16, const i
     int gy = (H + 1023) / 1024;
     xs::combine_kernel<__nv_bfloat16><<<dim3(T, gy), 128, 0, static_cast<cudaStream_t>(stream)>>>(
         static_cast<const __nv_bfloat16 *>(y_bf16), inv, topk_w, shared, static_cast<__nv_bfloat16 *>(out), T, H, K);
+    note_launch();
     XS_CUDA(cudaGetLastError());
     return 0;
 }
@@ -1024,6 +1104,7 @@ int xs_moe_gather_rows_f32_to_bf16(const float *src, const int32_t *index, void 
         return 0;
     xs::gather_rows_f32_to_bf16_kernel<<<n_rows, 256, 0, static_cast<cudaStream_t>(stream)>>>(src, index, static_cast<__nv_bfloat16 *>(dst_bf16),
                                                                                              n_rows, cols);
+    note_launch();
     XS_CUDA(cudaGetLastError());
     return 0;
 }
@@ -1100,10 +1181,13 @@ static int forward_impl(const XsMoeConfig *cfg, const XsMoeWeights *w, const voi
     if (fp4) {
         if (int rc = launch_quantize_rows_mx(x, inv, K, rows, reinterpret_cast<uint8_t *>(rows_scale), T, H, st))
             return rc;
-    } else if (fp8)
+    } else if (fp8) {
         xs::scatter_rows_kernel<true><<<T, 256, 0, st>>>(static_cast<const __nv_bfloat16 *>(x), inv, rows, rows_scale, T, H, K, n_routed, S);
-    else
+        note_launch();
+    } else {
         xs::scatter_rows_kernel<false><<<T, 256, 0, st>>>(static_cast<const __nv_bfloat16 *>(x), inv, rows, nullptr, T, H, K, n_routed, S);
+        note_launch();
+    }
     XS_CUDA(cudaGetLastError());
     XS_MARK(3);
     GroupedArgs a;
@@ -1141,6 +1225,7 @@ static int forward_impl(const XsMoeConfig *cfg, const XsMoeWeights *w, const voi
         if (int rc = launch_quantize_rows(x, xq, xs_, T, H, st))
             return rc;
         set_two_ints_kernel<<<1, 1, 0, st>>>(sh_off, 0, T);
+        note_launch();
         XS_CUDA(cudaGetLastError());
         GroupedArgs sa;
         sa.fmt = XS_MOE_FP8_BLOCK128;
@@ -1223,7 +1308,8 @@ int xs_moe_probe_mma_rate(int32_t kind, int32_t n, int32_t iters, int32_t chains
 {
     if (int rc = xs_moe_device_check())
         return rc;
-    if (kind < 0 || kind > 2 || n < 16 || n > 256 || n % 16 != 0 || iters < 1 || chains < 1 || chains * n > 480)
+    if (kind < 0 || kind > 2 || n < 16 || n > 256 || n % 16 != 0 || iters < 4 || iters % 4 != 0 ||
+        (chains != 1 && chains != 2 && chains != 4) || chains * n > (kind == 2 ? 496 : 512))
         return fail(XS_MOE_ERR_INVALID_ARG, "bad probe arguments");
     if (int rc = check_workspace(ws, ws_bytes, kStatusBytes))
         return rc;
@@ -1248,6 +1334,7 @@ int xs_moe_probe_mma_rate(int32_t kind, int32_t n, int32_t iters, int32_t chains
     XS_CUDA(cudaEventCreate(&e1));
     XS_CUDA(cudaEventRecord(e0, st));
     xs::mma_rate_kernel<<<di.sms, 64, smem, st>>>(kind, n, iters, chains, ctr, reinterpret_cast<int32_t *>(b));
+    note_launch();
     XS_CUDA(cudaGetLastError());
     XS_CUDA(cudaEventRecord(e1, st));
     XS_CUDA(cudaEventSynchronize(e1));
@@ -1268,6 +1355,59 @@ int xs_moe_probe_mma_rate(int32_t kind, int32_t n, int32_t iters, int32_t chains
         *tflops = 2.0 * 128.0 * n * k * iters * di.sms / (ms * 1e-3) / 1e12;
     }
     return xs_moe_check_flags(ws, stream);
+}
+
+int xs_moe_probe_tmem_ld_rate(int32_t shape, int32_t warps, int32_t iters, int32_t with_mma, void *ws, size_t ws_bytes,
+                              double *bytes_per_cycle_per_sm, double *mma_cycles_per_mma, void *stream)
+{
+    if (int rc = xs_moe_device_check())
+        return rc;
+    if (shape < 0 || shape > 3 || warps < 4 || warps > 16 || warps % 4 != 0 || iters < 1 || iters > (1 << 20))
+        return fail(XS_MOE_ERR_INVALID_ARG, "bad probe arguments");
+    if (int rc = check_workspace(ws, ws_bytes, kStatusBytes))
+        return rc;
+    DeviceInfo di;
+    if (int rc = device_info(&di))
+        return rc;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    uint8_t *b = static_cast<uint8_t *>(ws);
+    unsigned long long *ctr = reinterpret_cast<unsigned long long *>(b + 64);
+    XS_CUDA(cudaMemsetAsync(ctr, 0, 64, st));
+    const int smem = (128 + 256) * 128 + 1024;
+    static bool configured[64] = {};
+    int dev = 0;
+    XS_CUDA(cudaGetDevice(&dev));
+    if (dev >= 64 || !configured[dev]) {
+        XS_CUDA(cudaFuncSetAttribute(xs::tmem_ld_rate_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        if (dev < 64)
+            configured[dev] = true;
+    }
+    // the MMA stream is sized to outlast the readers at the slowest rate seen so far (64 bytes per cycle) and is bounded
+    long mma_iters = with_mma ? (static_cast<long>(warps) * iters * 8192 / 64 / 128 + 64) / 4 * 4 : 0;
+    if (mma_iters > (1 << 22))
+        mma_iters = 1 << 22;
+    xs::tmem_ld_rate_kernel<<<di.sms, (warps + 1) * 32, smem, st>>>(shape, warps, iters, with_mma, static_cast<int>(mma_iters), ctr,
+                                                                    reinterpret_cast<int32_t *>(b));
+    note_launch();
+    XS_CUDA(cudaGetLastError());
+    unsigned long long h[3];
+    XS_CUDA(cudaMemcpyAsync(h, ctr, sizeof(h), cudaMemcpyDeviceToHost, st));
+    XS_CUDA(cudaStreamSynchronize(st));
+    XS_CUDA(cudaMemsetAsync(ctr, 0, 64, st));
+    const double ctas = h[2] ? static_cast<double>(h[2]) : 1.0;
+    if (bytes_per_cycle_per_sm)
+        *bytes_per_cycle_per_sm = h[0] ? static_cast<double>(warps) * iters * 8192.0 / (static_cast<double>(h[0]) / ctas) : 0.0;
+    if (mma_cycles_per_mma)
+        *mma_cycles_per_mma = mma_iters ? static_cast<double>(h[1]) / ctas / static_cast<double>(mma_iters) : 0.0;
+    return xs_moe_check_flags(ws, stream);
+}
+
+int xs_moe_launch_count(unsigned long long *count)
+{
+    if (!count)
+        return fail(XS_MOE_ERR_INVALID_ARG, "null out-pointer");
+    *count = g_launches.load(std::memory_order_relaxed);
+    return 0;
 }
 
 int xs_moe_debug_counters(void *ws, unsigned long long *out8, void *stream)
@@ -1427,6 +1567,7 @@ int xs_moe_ep_plan(const int32_t *all_counts, int32_t ranks, int32_t experts, in
     int threads = ((experts > ranks ? experts : ranks) + 31) / 32 * 32;
     xs::ep_plan_kernel<<<1, threads, 0, static_cast<cudaStream_t>(stream)>>>(all_counts, ranks, experts, rank, dest_base, offsets_local,
                                                                             src_offsets);
+    note_launch();
     XS_CUDA(cudaGetLastError());
     return 0;
 }
@@ -1451,22 +1592,26 @@ int xs_moe_ep_dispatch(const XsMoeConfig *cfg, int32_t ranks, const void *x, con
     auto xb = static_cast<const __nv_bfloat16 *>(x);
     int32_t *status = static_cast<int32_t *>(ws);
     const int T = cfg->num_tokens, H = cfg->hidden, K = cfg->top_k, E = cfg->num_experts;
-    if (cfg->routed_format == XS_MOE_BF16)
+    if (cfg->routed_format == XS_MOE_BF16) {
         xs::ep_dispatch_kernel<0><<<T, 256, 0, st>>>(xb, ids, inv, my_offsets, dest_base, rows, scales, T, H, K, E, ranks, capacity_rows,
                                                      status);
-    else if (cfg->routed_format == XS_MOE_FP8_BLOCK128)
+        note_launch();
+    } else if (cfg->routed_format == XS_MOE_FP8_BLOCK128) {
         xs::ep_dispatch_kernel<1><<<T, 256, 0, st>>>(xb, ids, inv, my_offsets, dest_base, rows, scales, T, H, K, E, ranks, capacity_rows,
                                                      status);
-    else
+        note_launch();
+    } else {
         xs::ep_dispatch_kernel<2><<<T, 256, 0, st>>>(xb, ids, inv, my_offsets, dest_base, rows, scales, T, H, K, E, ranks, capacity_rows,
                                                      status);
+        note_launch();
+    }
     XS_CUDA(cudaGetLastError());
     return 0;
 }
 
 int xs_moe_ep_return(const XsMoeConfig *cfg, int32_t ranks, int32_t rank, const float *y_grouped, const int32_t *all_counts,
-                     const int32_t *offsets_local, const int32_t *src_offsets, void *const *peer_back, int32_t back_capacity_rows,
-                     int32_t wire_bf16, void *ws, void *stream)
+                     const int32_t *offsets_local, const int32_t *src_offsets, int32_t y_capacity_rows, void *const *peer_back,
+                     int32_t back_capacity_rows, int32_t wire_bf16, void *ws, void *stream)
 {
     if (int rc = check_cfg(cfg))
         return rc;
@@ -1474,7 +1619,7 @@ int xs_moe_ep_return(const XsMoeConfig *cfg, int32_t ranks, int32_t rank, const 
         return rc;
     if (!y_grouped || !all_counts || !offsets_local || !src_offsets || !peer_back || !ws)
         return fail(XS_MOE_ERR_INVALID_ARG, "null tensor pointer");
-    if (back_capacity_rows < 0 || cfg->hidden % 8 != 0)
+    if (back_capacity_rows < 0 || y_capacity_rows < 0 || cfg->hidden % 8 != 0)
         return fail(XS_MOE_ERR_INVALID_ARG, "shape mismatch");
     DeviceInfo di;
     if (int rc = device_info(&di))
@@ -1483,12 +1628,15 @@ int xs_moe_ep_return(const XsMoeConfig *cfg, int32_t ranks, int32_t rank, const 
     auto back = reinterpret_cast<uint8_t *const *>(peer_back);
     int32_t *status = static_cast<int32_t *>(ws);
     const int grid = di.sms * 8;
-    if (wire_bf16)
+    if (wire_bf16) {
         xs::ep_return_kernel<true><<<grid, 256, 0, st>>>(y_grouped, all_counts, offsets_local, src_offsets, back, cfg->hidden,
-                                                         cfg->num_experts, ranks, rank, back_capacity_rows, status);
-    else
+                                                         cfg->num_experts, ranks, rank, y_capacity_rows, back_capacity_rows, status);
+        note_launch();
+    } else {
         xs::ep_return_kernel<false><<<grid, 256, 0, st>>>(y_grouped, all_counts, offsets_local, src_offsets, back, cfg->hidden,
-                                                          cfg->num_experts, ranks, rank, back_capacity_rows, status);
+                                                          cfg->num_experts, ranks, rank, y_capacity_rows, back_capacity_rows, status);
+        note_launch();
+    }
     XS_CUDA(cudaGetLastError());
     return 0;
 }

@@ -117,21 +117,29 @@ permute_scan_kernel(const int32_t *__restrict__ chunk_counts, int32_t *__restric
 }
 
 // one block, blockDim.x >= E.  Token tiles of n_tile rows per expert segment, in expert order.
+// `offsets` may come from a caller: every entry is clamped into [0, max_rows] (and made non-decreasing) before use, and
+// the clamped copy, E + 1 entries, is what the GEMM kernels read, so that no tile and no epilogue store can reach a row
+// at or beyond the capacity of the row buffers.  A clamp that changed anything raises the bad-index status bit.
 __global__ void __launch_bounds__(1024)
-tile_table_kernel(const int32_t *__restrict__ offsets, int E, int n_tile, int max_tiles, int32_t *__restrict__ tile_expert,
-                  int32_t *__restrict__ tile_row0, int32_t *__restrict__ num_tiles, int32_t *status)
+tile_table_kernel(const int32_t *__restrict__ offsets, int E, int n_tile, int max_tiles, int max_rows, int32_t *__restrict__ offsets_clamped,
+                  int32_t *__restrict__ tile_expert, int32_t *__restrict__ tile_row0, int32_t *__restrict__ num_tiles, int32_t *status)
 {
     __shared__ int warp_sums[32];
     __shared__ int total;
     const int e = threadIdx.x;
     int rows = 0, start = 0;
     if (e < E) {
-        start = offsets[e];
-        rows = offsets[e + 1] - start;
-        if (rows < 0) {
-            rows = 0;
+        const int a = offsets[e], b = offsets[e + 1];
+        start = a < 0 ? 0 : (a > max_rows ? max_rows : a);
+        int end = b < 0 ? 0 : (b > max_rows ? max_rows : b);
+        if (end < start)
+            end = start;
+        if (start != a || end != b)
             atomicOr(status, 2);
-        }
+        rows = end - start;
+        offsets_clamped[e] = start;
+        if (e == E - 1)
+            offsets_clamped[E] = end;
     }
     const int nt = (rows + n_tile - 1) / n_tile;
     const int first = block_exclusive_scan(nt, warp_sums, &total);

@@ -83,7 +83,7 @@
             atomicOr(status, kStatusWaitTimeout);
         }
         if (lane == 0 && loader == 0)
-            atomicAdd(&prof[4], static_cast<unsigned long long>(w0));
+            prof_add(prof, 4, w0);
     } else {
     constexpr int kSfAhead = 3;
     struct Cursor {
@@ -176,6 +176,6 @@
         atomicOr(status, kStatusWaitTimeout);
     }
     if (lane == 0 && loader == 0)
-        atomicAdd(&prof[4], static_cast<unsigned long long>(w0));
+        prof_add(prof, 4, w0);
     }
 }

@@ -57,7 +57,7 @@ prefill_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
     const int lane = threadIdx.x & 31;
     // role profile (see xs_moe_debug_counters): cycles each role spent blocked, summed over CTAs
     unsigned long long *prof = reinterpret_cast<unsigned long long *>(status + 16);
-    const long long t_start = clock64();
+    const long long t_start = prof_clock();
     long long w0 = 0, w1 = 0;
 
     if (threadIdx.x == 0) {
@@ -125,9 +125,9 @@ prefill_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
                 *abort_flag = 1;
                 atomicOr(status, kStatusWaitTimeout);
             }
-            atomicAdd(&prof[0], static_cast<unsigned long long>(w0));
-            atomicAdd(&prof[6], static_cast<unsigned long long>(clock64() - t_start));
-            atomicAdd(&prof[7], 1ull);
+            prof_add(prof, 0, w0);
+            prof_add(prof, 6, prof_clock() - t_start);
+            prof_add(prof, 7, 1);
         }
     } else if (warp == 1) {
         if (lane == 0) {
@@ -163,8 +163,8 @@ prefill_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
                 *abort_flag = 1;
                 atomicOr(status, kStatusWaitTimeout);
             }
-            atomicAdd(&prof[1], static_cast<unsigned long long>(w0));
-            atomicAdd(&prof[3], static_cast<unsigned long long>(w1));
+            prof_add(prof, 1, w0);
+            prof_add(prof, 3, w1);
         }
     } else {
 #include "xs_prefill_fp8_epilogue.inl"

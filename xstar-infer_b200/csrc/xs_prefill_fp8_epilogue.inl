@@ -111,5 +111,5 @@
         atomicOr(status, kStatusWaitTimeout);
     }
     if (warp == 2 && lane == 0)
-        atomicAdd(&prof[5], static_cast<unsigned long long>(w0));
+        prof_add(prof, 5, w0);
 }

@@ -64,15 +64,44 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volati
     return false;
 }
 
-// Same wait, adding the cycles spent to `acc` (role profiling: who waits for whom inside a warp-specialised kernel).
+// Role profiling (who waits for whom inside a warp-specialised kernel) is a tuning aid compiled in only with
+// -DXS_ROLE_PROFILE=1: cycle counters summed into the eight 64-bit words behind the workspace status word.  In the
+// default build the helpers below reduce to the plain bounded wait and to nothing.
+#ifndef XS_ROLE_PROFILE
+#define XS_ROLE_PROFILE 0
+#endif
+__device__ __forceinline__ long long prof_clock()
+{
+#if XS_ROLE_PROFILE
+    return clock64();
+#else
+    return 0;
+#endif
+}
+__device__ __forceinline__ void prof_add(unsigned long long *prof, int slot, long long v)
+{
+#if XS_ROLE_PROFILE
+    atomicAdd(&prof[slot], static_cast<unsigned long long>(v));
+#else
+    (void)prof;
+    (void)slot;
+    (void)v;
+#endif
+}
+// The bounded wait, adding the cycles spent blocked to `acc` when role profiling is compiled in.
 __device__ __forceinline__ bool mbar_wait_t(uint64_t *bar, uint32_t parity, volatile uint32_t *abort_flag, long long &acc)
 {
+#if XS_ROLE_PROFILE
     if (mbar_try_wait(bar, parity))
         return true;
     const long long t0 = clock64();
     const bool ok = mbar_wait(bar, parity, abort_flag);
     acc += clock64() - t0;
     return ok;
+#else
+    (void)acc;
+    return mbar_wait(bar, parity, abort_flag);
+#endif
 }
 
 // ---- TMA ----------------------------------------------------------------------------------------------

@@ -431,7 +431,7 @@ router_logits_small_kernel(const __nv_bfloat16 *__restrict__ x, const __nv_bfloa
 }
 
 // One warp per token.  Lane l holds experts l, l+32, l+64, ...  (NPL per lane).
-// Selection: K rounds of "largest key, ties to the lower expert id" by butterfly shuffles.
+// Selection: K rounds of "largest key, ties to the lower expert id" by butterfly shuffles; a NaN key counts as -inf.
 // Output slots are in ascending expert id.  Weights: softmax over the selected unbiased logits,
 // max-shifted, summed in slot order.
 template <int NPL>
@@ -446,7 +446,8 @@ __device__ __forceinline__ void topk_warp(const float *__restrict__ logits, cons
         const int e = lane + 32 * i;
         if (e < E) {
             lg[i] = l[e];
-            key[i] = bias ? __fadd_rn(lg[i], bias[e]) : lg[i];
+            const float kv = bias ? __fadd_rn(lg[i], bias[e]) : lg[i];
+            key[i] = (kv != kv) ? -INFINITY : kv; // a NaN key orders as -inf, so every lane sees one total order
         } else {
             lg[i] = 0.0f;
             key[i] = 0.0f;
@@ -488,8 +489,8 @@ __device__ __forceinline__ void topk_warp(const float *__restrict__ logits, cons
     for (int i = 0; i < NPL; i++) {
         const bool c = (chosen >> i) & 1u;
         const uint32_t mask = __ballot_sync(0xffffffffu, c);
-        if (c) {
-            const int slot = base + __popc(mask & ((1u << lane) - 1u));
+        const int slot = base + __popc(mask & ((1u << lane) - 1u));
+        if (c && slot < K) {
             topk_ids[static_cast<size_t>(warp) * K + slot] = lane + 32 * i;
             topk_w[static_cast<size_t>(warp) * K + slot] = lg[i]; // raw logit for now
             m = fmaxf(m, lg[i]);

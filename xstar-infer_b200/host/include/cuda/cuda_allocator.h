@@ -14,17 +14,21 @@ void cuda_memcpy_h2d(void *dst, const void *src, std::size_t bytes);
 void cuda_memcpy_d2h(void *dst, const void *src, std::size_t bytes);
 void cuda_memcpy_d2d(void *dst, const void *src, std::size_t bytes);
 std::size_t cuda_free_bytes();
+int cuda_current_device();
+void cuda_set_device(int device);
 
 // Grow-only arena for per-call scratch.  The reference allocates every temporary with cudaMalloc and frees
 // it when the Tensor dies (xstar_cpp/src/tensor.cpp:34-37); an MoE call needs a dozen temporaries, so the
 // op leases ONE buffer from this pool and carves it up.  A lease is exclusive; returning it keeps the
-// memory for the next call.  trim() gives everything back to the driver.
+// memory for the next call on the same device (blocks are keyed by the device that was current when they were
+// allocated).  trim() gives everything back to the driver.
 class WorkspacePool
 {
 public:
     struct Lease {
         void *ptr = nullptr;
         std::size_t bytes = 0;
+        int device = 0; // the device the block lives on: a lease is only ever handed to a call on that device
     };
     static WorkspacePool &instance();
     Lease acquire(std::size_t bytes);

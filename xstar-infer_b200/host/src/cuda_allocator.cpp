@@ -34,6 +34,14 @@ std::size_t cuda_free_bytes()
     return b;
 }
 
+int cuda_current_device()
+{
+    int32_t d = 0;
+    raise_if(xs_moe_current_device(&d));
+    return d;
+}
+void cuda_set_device(int device) { raise_if(xs_moe_set_device(device)); }
+
 WorkspacePool &WorkspacePool::instance()
 {
     static WorkspacePool pool;
@@ -42,24 +50,31 @@ WorkspacePool &WorkspacePool::instance()
 
 WorkspacePool::Lease WorkspacePool::acquire(std::size_t bytes)
 {
+    const int dev = cuda_current_device();
     {
         std::lock_guard<std::mutex> g(mu_);
-        // smallest cached block that fits
+        // smallest cached block of THIS device that fits
         int best = -1;
         for (int i = 0; i < static_cast<int>(free_.size()); i++)
-            if (free_[i].bytes >= bytes && (best < 0 || free_[i].bytes < free_[best].bytes))
+            if (free_[i].device == dev && free_[i].bytes >= bytes && (best < 0 || free_[i].bytes < free_[best].bytes))
                 best = i;
         if (best >= 0) {
             Lease l = free_[best];
             free_.erase(free_.begin() + best);
             return l;
         }
-        // nothing fits: drop the cached blocks so the pool does not hold stale smaller buffers
-        for (auto &l : free_)
-            cuda_free(l.ptr);
-        free_.clear();
+        // nothing fits: drop this device's cached blocks so the pool does not hold stale smaller buffers
+        for (std::size_t i = 0; i < free_.size();) {
+            if (free_[i].device == dev) {
+                cuda_free(free_[i].ptr);
+                free_.erase(free_.begin() + static_cast<std::ptrdiff_t>(i));
+            } else {
+                i++;
+            }
+        }
     }
     Lease l;
+    l.device = dev;
     l.bytes = (bytes + 255) / 256 * 256;
     l.ptr = cuda_alloc(l.bytes);
     raise_if(xs_moe_workspace_init(l.ptr, l.bytes, nullptr));

@@ -30,7 +30,7 @@ def _sources(d, exts):
 
 
 def build_cuda(force=False, verbose=False):
-    srcs = _sources(CSRC, (".cu", ".cuh")) + [os.path.join(ROOT, "include", "xs_moe.h")]
+    srcs = _sources(CSRC, (".cu", ".cuh", ".inl", ".h")) + _sources(os.path.join(ROOT, "include"), (".h",))
     if not (force or _newer(LIB, srcs)):
         return LIB
     cmd = ["nvcc", *NVCC_FLAGS, "-shared", "-Xcompiler", "-fPIC", "-I" + os.path.join(ROOT, "include"), "-o", LIB,
@@ -50,7 +50,7 @@ def build_host(force=False):
     ext = sysconfig.get_config_var("EXT_SUFFIX")
     os.makedirs(PYMOD_DIR, exist_ok=True)
     target = os.path.join(PYMOD_DIR, "xstar_cpp" + ext)
-    srcs = _sources(HOST, (".cpp", ".h")) + [os.path.join(ROOT, "include", "xs_moe.h")]
+    srcs = _sources(HOST, (".cpp", ".h")) + _sources(os.path.join(ROOT, "include"), (".h",))
     if not (force or _newer(target, srcs) or _newer(target, [LIB])):
         return target
     cpps = [s for s in srcs if s.endswith(".cpp")]

@@ -1,4 +1,4 @@
-"""ctypes binding of the C ABI in include/xs_moe.h.
+"""ctypes binding of the C ABI in include/xs_moe.h and include/xs_moe_tuning.h.
 
 This is plumbing for the tests and the benchmark: it passes raw device pointers (from torch tensors or
 from the library's own allocator) straight to the `extern "C"` entry points.  There is no fallback: if the
@@ -39,11 +39,11 @@ class XsMoeWeights(C.Structure):
 IPC_HANDLE_BYTES = 64
 
 EXPORTS = [
-    "xs_moe_status_string", "xs_moe_last_error", "xs_moe_device_check", "xs_moe_device_alloc", "xs_moe_device_free",
+    "xs_moe_status_string", "xs_moe_last_error", "xs_moe_device_check", "xs_moe_device_count", "xs_moe_set_device", "xs_moe_current_device", "xs_moe_device_alloc", "xs_moe_device_free",
     "xs_moe_memcpy_h2d", "xs_moe_memcpy_d2h", "xs_moe_memcpy_d2d", "xs_moe_device_free_bytes",
     "xs_moe_stream_synchronize", "xs_moe_workspace_bytes", "xs_moe_workspace_init", "xs_moe_forward",
-    "xs_moe_forward_host", "xs_moe_forward_profile", "xs_moe_route", "xs_moe_permute", "xs_moe_permute_noalloc", "xs_moe_grouped_mlp_workspace_bytes",
-    "xs_moe_grouped_mlp", "xs_moe_quantize_rows_fp8", "xs_moe_quantize_rows_mxfp8", "xs_moe_gather_rows", "xs_moe_combine", "xs_moe_combine_bf16_rows", "xs_moe_gather_rows_f32_to_bf16", "xs_moe_check_flags", "xs_moe_debug_counters", "xs_moe_probe_mma_rate",
+    "xs_moe_forward_host", "xs_moe_forward_profile", "xs_moe_route", "xs_moe_topk", "xs_moe_permute", "xs_moe_permute_noalloc", "xs_moe_grouped_mlp_workspace_bytes",
+    "xs_moe_grouped_mlp", "xs_moe_quantize_rows_fp8", "xs_moe_quantize_rows_mxfp8", "xs_moe_gather_rows", "xs_moe_combine", "xs_moe_combine_bf16_rows", "xs_moe_gather_rows_f32_to_bf16", "xs_moe_check_flags", "xs_moe_debug_counters", "xs_moe_probe_mma_rate", "xs_moe_probe_tmem_ld_rate", "xs_moe_launch_count",
     "xs_moe_ipc_export", "xs_moe_ipc_import", "xs_moe_ipc_close", "xs_moe_ep_plan", "xs_moe_ep_dispatch", "xs_moe_ep_return",
 ]
 
@@ -63,6 +63,9 @@ def lib():
         cfgp, wp = C.POINTER(XsMoeConfig), C.POINTER(XsMoeWeights)
         sig = {
             "xs_moe_device_check": [],
+            "xs_moe_device_count": [C.POINTER(i32)],
+            "xs_moe_set_device": [i32],
+            "xs_moe_current_device": [C.POINTER(i32)],
             "xs_moe_device_alloc": [C.POINTER(vp), sz],
             "xs_moe_device_free": [vp],
             "xs_moe_memcpy_h2d": [vp, vp, sz],
@@ -76,6 +79,7 @@ def lib():
             "xs_moe_forward_host": [cfgp, wp, vp, vp, vp, vp, vp, sz, vp],
             "xs_moe_forward_profile": [cfgp, wp, vp, vp, vp, sz, vp, C.POINTER(C.c_float)],
             "xs_moe_route": [cfgp, vp, vp, vp, vp, vp, vp, vp, sz, vp],
+            "xs_moe_topk": [cfgp, vp, vp, vp, vp, vp],
             "xs_moe_permute": [cfgp, vp, vp, vp, vp, vp, vp, sz, vp],
             "xs_moe_permute_noalloc": [cfgp, vp, vp, vp, vp, vp, vp],
             "xs_moe_grouped_mlp_workspace_bytes": [cfgp, i32, C.POINTER(sz)],
@@ -88,13 +92,15 @@ def lib():
             "xs_moe_gather_rows_f32_to_bf16": [vp, vp, vp, i32, i32, vp],
             "xs_moe_check_flags": [vp, vp],
             "xs_moe_probe_mma_rate": [i32, i32, i32, i32, vp, sz, C.POINTER(C.c_double), C.POINTER(C.c_double), C.POINTER(C.c_double), vp],
+            "xs_moe_probe_tmem_ld_rate": [i32, i32, i32, i32, vp, sz, C.POINTER(C.c_double), C.POINTER(C.c_double), vp],
             "xs_moe_debug_counters": [vp, C.POINTER(C.c_ulonglong), vp],
+            "xs_moe_launch_count": [C.POINTER(C.c_ulonglong)],
             "xs_moe_ipc_export": [vp, vp],
             "xs_moe_ipc_import": [vp, C.POINTER(vp)],
             "xs_moe_ipc_close": [vp],
             "xs_moe_ep_plan": [vp, i32, i32, i32, vp, vp, vp, vp],
             "xs_moe_ep_dispatch": [cfgp, i32, vp, vp, vp, vp, vp, vp, vp, i32, vp, vp],
-            "xs_moe_ep_return": [cfgp, i32, i32, vp, vp, vp, vp, vp, i32, i32, vp, vp],
+            "xs_moe_ep_return": [cfgp, i32, i32, vp, vp, vp, vp, i32, vp, i32, i32, vp, vp],
         }
         for name, args in sig.items():
             fn = getattr(L, name)
@@ -145,3 +151,10 @@ def workspace_bytes(cfg):
     n = C.c_size_t(0)
     check(lib().xs_moe_workspace_bytes(C.byref(cfg), C.byref(n)))
     return n.value
+
+
+def launch_count():
+    """Kernels the library has enqueued in this process so far."""
+    n = C.c_ulonglong(0)
+    check(lib().xs_moe_launch_count(C.byref(n)))
+    return int(n.value)

@@ -289,8 +289,8 @@ class PeerExchange:
 
     def give_back(self, y_grouped, all_counts, ws):
         capi.check(self.L.xs_moe_ep_return(C.byref(self.cfg), self.R, self.rank, capi.ptr(y_grouped), capi.ptr(all_counts),
-                                           capi.ptr(self.offsets_local), capi.ptr(self.src_offsets), capi.ptr(self.tables[2]),
-                                           self.back_rows, int(self.wire_bf16), capi.ptr(ws), self._st()))
+                                           capi.ptr(self.offsets_local), capi.ptr(self.src_offsets), int(y_grouped.shape[0]),
+                                           capi.ptr(self.tables[2]), self.back_rows, int(self.wire_bf16), capi.ptr(ws), self._st()))
 
     def close(self):
         """Unmap the peers' buffers and free this rank's (call on every rank, after a barrier)."""
