@@ -16,7 +16,10 @@ extern "C" {
 /* Tensor-pipe rate probe: every SM issues `iters` (a multiple of 4) tcgen05.mma of M = 128, N = n (16..256) on zeroed
  * shared memory from one thread, round-robin over `chains` (1, 2 or 4) independent TMEM accumulators (chains * n <= 512;
  * <= 496 for the block-scaled kind, whose scales take the last columns).  kind 0 = bf16 (K = 16), 1 = e4m3 (K = 32),
- * 2 = block-scaled e4m3 x e2m1 (K = 32).  Returns cycles per MMA until completion, cycles per MMA spent issuing, and
+ * 2 = block-scaled e4m3 x e2m1 (K = 32), 3 = the same with three tcgen05.cp scale copies (3 x 512 bytes, shared memory
+ * to TMEM) issued by the same thread before every four MMAs, as a block-scaled GEMM's k-block needs; 4 and 5 = e4m3 issued
+ * as a loop with per-k-block accumulators issues it (every four MMAs start afresh in the other of two accumulators and are
+ * followed by two, resp. one, tcgen05.commit; `chains` is ignored).  Returns cycles per MMA until completion, cycles per MMA spent issuing, and
  * whole-chip TFLOP/s by CUDA events.  Needs a workspace of at least 256 bytes (status block).  Synchronises. */
 int xs_moe_probe_mma_rate(int32_t kind, int32_t n, int32_t iters, int32_t chains, void *workspace_dev,
                           size_t workspace_bytes, double *cycles_per_mma, double *issue_cycles_per_mma, double *tflops,
@@ -31,13 +34,18 @@ int xs_moe_probe_tmem_ld_rate(int32_t shape, int32_t warps, int32_t iters, int32
                               size_t workspace_bytes, double *bytes_per_cycle_per_sm, double *mma_cycles_per_mma,
                               void *stream);
 
-/* Role profile of the warp-specialised GEMM kernels that ran on this workspace since the last call: eight 64-bit
+/* Role profile of the warp-specialised GEMM kernels that ran on this workspace since the last call: sixteen 64-bit
  * cycle counters summed over CTAs (0 producer blocked on a free stage, 1 MMA issuer blocked on operands, 2 on scales,
  * 3 on a free accumulator, 4 scale writers blocked on a free slot, 5 epilogue blocked on an accumulator, 6 CTA lifetime,
- * 7 CTAs).  A wait that the first poll of its barrier already satisfies is not counted, so the figures are lower
- * bounds.  The counters are compiled into the kernels only when the library is built with -DXS_ROLE_PROFILE=1; the
+ * 7 CTAs; the FP8 prefill kernel uses 2 and 4 for the cycles of its promotion bodies and of its per-tile tails, 8 for the
+ * amax exchange waits and 9 for the MMA thread's issue time; 10..15 are spare).  The counters are compiled into the kernels only when the library is built with -DXS_ROLE_PROFILE=1; the
  * default build returns zeros.  Reads and clears; synchronises. */
-int xs_moe_debug_counters(void *workspace_dev, unsigned long long *out8, void *stream);
+int xs_moe_debug_counters(void *workspace_dev, unsigned long long *out16, void *stream);
+
+/* Which GEMM kernels xs_moe_forward will launch for `cfg`: the token tile (16, 32 or 64: tokens as the N of 128-weight-row
+ * MMAs, the decode shape; 128: tokens as the M of N = 256 MMAs, the prefill kernels of the FP8 / FP4 formats, or the
+ * 128-token decode-shape tile of bf16) and whether the prefill kernels run. */
+int xs_moe_plan_info(const XsMoeConfig *cfg, int32_t *token_tile, int32_t *prefill_kernels);
 
 /* Kernels this library has enqueued in this process so far (a launch captured into a CUDA graph counts once, at capture;
  * its replays are the caller's to multiply).  For benchmarks that report how many of the library's kernels a timed region

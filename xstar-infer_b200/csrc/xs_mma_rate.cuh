@@ -7,13 +7,18 @@
 
 namespace xs {
 
-// kind: 0 = f16 (bf16 operands, K = 16), 1 = f8f6f4 (e4m3, K = 32), 2 = mxf8f6f4.block_scale (e4m3 x e2m1, K = 32)
+// kind: 0 = f16 (bf16 operands, K = 16), 1 = f8f6f4 (e4m3, K = 32), 2 = mxf8f6f4.block_scale (e4m3 x e2m1, K = 32),
+//       3 = kind 2 with three tcgen05.cp.32x128b.warpx4 scale copies before every four MMAs (one 128-deep k-block of a
+//           block-scaled GEMM whose issuing thread also moves the scales from shared memory to TMEM),
+//       4 / 5 = kind 1 issued the way a k-block loop with per-k-block accumulators issues it: every four MMAs start a
+//           fresh accumulation in the other of two accumulators and are followed by two (4) or one (5) tcgen05.commit
 __global__ void __launch_bounds__(64, 1)
 mma_rate_kernel(int kind, int n, int iters, int chains, unsigned long long *cycles, int32_t *status)
 {
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     __shared__ uint64_t bar;
+    __shared__ uint64_t side_bar[2]; // targets of the per-group commits of kinds 4 and 5; nobody waits on them
     __shared__ uint32_t tmem_slot;
     __shared__ uint32_t abort_flag;
     // A: 128 rows x 128 B, B: 256 rows x 128 B, scale block 1.5 KB
@@ -21,6 +26,8 @@ mma_rate_kernel(int kind, int n, int iters, int chains, unsigned long long *cycl
         reinterpret_cast<uint4 *>(smem)[i] = make_uint4(0, 0, 0, 0);
     if (threadIdx.x == 0) {
         mbar_init(&bar, 1);
+        mbar_init(&side_bar[0], 1);
+        mbar_init(&side_bar[1], 1);
         abort_flag = 0;
         fence_mbar_init();
     }
@@ -38,7 +45,7 @@ mma_rate_kernel(int kind, int n, int iters, int chains, unsigned long long *cycl
         const uint64_t da = make_desc_sw128(sa), db = make_desc_sw128(sa + 128 * 128);
         const uint32_t sfs = sa + (128 + 256) * 128;
         const uint32_t sf_t = tmem_base + 2 * 256 - 16; // last 16 columns hold scales (block-scaled kind: chains * n <= 496)
-        if (kind == 2) {
+        if (kind == 2 || kind == 3) {
             tmem_cp_32x128b_x4(sf_t, make_desc_rows16(sfs));
             tmem_cp_32x128b_x4(sf_t + 4, make_desc_rows16(sfs + 512));
             tmem_cp_32x128b_x4(sf_t + 8, make_desc_rows16(sfs + 1024));
@@ -47,10 +54,25 @@ mma_rate_kernel(int kind, int n, int iters, int chains, unsigned long long *cycl
         uint32_t idesc[4], dcol[4];
         for (int j = 0; j < 4; j++) {
             dcol[j] = tmem_base + static_cast<uint32_t>((j % chains) * n); // `chains` (1, 2 or 4) independent accumulators
-            idesc[j] = kind == 0 ? make_idesc(1, 1, 128, n) : (kind == 1 ? make_idesc(0, 0, 128, n) : make_idesc_mx(0, 5, 128, n, j));
+            idesc[j] = kind == 0 ? make_idesc(1, 1, 128, n) : ((kind == 1 || kind >= 4) ? make_idesc(0, 0, 128, n) : make_idesc_mx(0, 5, 128, n, j));
         }
         const long long t0 = clock64();
         for (int i = 0; i < iters; i += 4) {
+            if (kind == 3) {
+                tmem_cp_32x128b_x4(sf_t, make_desc_rows16(sfs));
+                tmem_cp_32x128b_x4(sf_t + 4, make_desc_rows16(sfs + 512));
+                tmem_cp_32x128b_x4(sf_t + 8, make_desc_rows16(sfs + 1024));
+            }
+            if (kind >= 4) {
+                const uint32_t d = tmem_base + static_cast<uint32_t>(((i >> 2) & 1) * n);
+#pragma unroll
+                for (int j = 0; j < 4; j++)
+                    mma_f8(d, da + 2 * j, db + 2 * j, idesc[j], j ? 1u : 0u);
+                tc_commit(&side_bar[0]);
+                if (kind == 4)
+                    tc_commit(&side_bar[1]);
+                continue;
+            }
 #pragma unroll
             for (int j = 0; j < 4; j++) {
                 const uint32_t acc = (i + j) >= chains ? 1u : 0u;

@@ -1308,8 +1308,8 @@ int xs_moe_probe_mma_rate(int32_t kind, int32_t n, int32_t iters, int32_t chains
 {
     if (int rc = xs_moe_device_check())
         return rc;
-    if (kind < 0 || kind > 2 || n < 16 || n > 256 || n % 16 != 0 || iters < 4 || iters % 4 != 0 ||
-        (chains != 1 && chains != 2 && chains != 4) || chains * n > (kind == 2 ? 496 : 512))
+    if (kind < 0 || kind > 5 || n < 16 || n > 256 || n % 16 != 0 || iters < 4 || iters % 4 != 0 ||
+        (chains != 1 && chains != 2 && chains != 4) || chains * n > ((kind == 2 || kind == 3) ? 496 : 512) || (kind >= 4 && 2 * n > 512))
         return fail(XS_MOE_ERR_INVALID_ARG, "bad probe arguments");
     if (int rc = check_workspace(ws, ws_bytes, kStatusBytes))
         return rc;
@@ -1402,6 +1402,18 @@ int xs_moe_probe_tmem_ld_rate(int32_t shape, int32_t warps, int32_t iters, int32
     return xs_moe_check_flags(ws, stream);
 }
 
+int xs_moe_plan_info(const XsMoeConfig *cfg, int32_t *token_tile, int32_t *prefill_kernels)
+{
+    if (int rc = check_cfg(cfg))
+        return rc;
+    const ForwardPlan p = plan_forward(cfg);
+    if (token_tile)
+        *token_tile = p.grouped.n_tile;
+    if (prefill_kernels)
+        *prefill_kernels = (p.grouped.n_tile == 128 && cfg->routed_format != XS_MOE_BF16) ? 1 : 0;
+    return 0;
+}
+
 int xs_moe_launch_count(unsigned long long *count)
 {
     if (!count)
@@ -1410,14 +1422,14 @@ int xs_moe_launch_count(unsigned long long *count)
     return 0;
 }
 
-int xs_moe_debug_counters(void *ws, unsigned long long *out8, void *stream)
+int xs_moe_debug_counters(void *ws, unsigned long long *out16, void *stream)
 {
-    if (!ws || !out8)
+    if (!ws || !out16)
         return fail(XS_MOE_ERR_INVALID_ARG, "null pointer");
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     uint8_t *p = static_cast<uint8_t *>(ws) + 64;
-    XS_CUDA(cudaMemcpyAsync(out8, p, 64, cudaMemcpyDeviceToHost, st));
-    XS_CUDA(cudaMemsetAsync(p, 0, 64, st));
+    XS_CUDA(cudaMemcpyAsync(out16, p, 128, cudaMemcpyDeviceToHost, st));
+    XS_CUDA(cudaMemsetAsync(p, 0, 128, st));
     XS_CUDA(cudaStreamSynchronize(st));
     return 0;
 }

@@ -18,7 +18,32 @@
 #pragma once
 #include "xs_grouped_gemm.cuh"
 
+#ifndef XS_PF8_SPIN
+#define XS_PF8_SPIN 0
+#endif
+#ifndef XS_PF8_FMA2
+#define XS_PF8_FMA2 0
+#endif
+#ifndef XS_PF8_DEBUG
+#define XS_PF8_DEBUG 0
+#endif
+
 namespace xs {
+
+// d0 += a0 * s, d1 += a1 * s as one packed instruction (two independent IEEE fused multiply-adds)
+__device__ __forceinline__ void ffma2(float &d0, float &d1, float a0, float a1, float s)
+{
+    asm("{\n\t"
+        ".reg .b64 ra, rb, rc;\n\t"
+        "mov.b64 ra, {%2, %3};\n\t"
+        "mov.b64 rb, {%4, %4};\n\t"
+        "mov.b64 rc, {%0, %1};\n\t"
+        "fma.rn.f32x2 rc, ra, rb, rc;\n\t"
+        "mov.b64 {%0, %1}, rc;\n\t"
+        "}\n"
+        : "+f"(d0), "+f"(d1)
+        : "f"(a0), "f"(a1), "f"(s));
+}
 
 constexpr int kPfGroups = 4;                     // epilogue warpgroups sharing the 256 columns
 constexpr int kPfThreads = 64 + kPfGroups * 128;
@@ -111,10 +136,19 @@ prefill_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
                         break;
                     }
                     uint8_t *st = smem + static_cast<size_t>(stage) * kPfStageBytes;
+#if XS_PF8_DEBUG == 6
+                    (void)st; (void)tw; (void)wbase; (void)wrow2; (void)row0; (void)pol_x; (void)pol_w;
+                    mbar_arrive(&full[stage]);
+#elif XS_PF8_DEBUG == 7
+                    (void)tw; (void)wbase; (void)wrow2; (void)pol_w;
+                    mbar_arrive_expect_tx(&full[stage], X_BYTES);
+                    tma_load_2d(st, &tmap_x, &full[stage], kb * kBlockK8, row0, pol_x);
+#else
                     mbar_arrive_expect_tx(&full[stage], kPfStageBytes);
                     tma_load_2d(st, &tmap_x, &full[stage], kb * kBlockK8, row0, pol_x);
                     tma_load_2d(st + X_BYTES, tw, &full[stage], kb * kBlockK8, wbase, pol_w);
                     tma_load_2d(st + X_BYTES + W_HALF, tw, &full[stage], kb * kBlockK8, wrow2, pol_w);
+#endif
                     if (++stage == stages) {
                         stage = 0;
                         phase ^= 1;
@@ -135,15 +169,22 @@ prefill_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
             uint32_t phase = 0;
             bool ok = true;
             uint32_t g_kb = 0;
+            long long w_issue = 0; // role profile: cycles spent issuing (descriptors, four MMAs, two commits)
             for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x) {
                 for (int kb = 0; kb < num_kb; kb++, g_kb++) {
                     const int buf = g_kb & 1;
+#if XS_PF8_SPIN
+                    if (!mbar_wait_t(&full[stage], phase, abort_flag, w0) ||
+                        !mbar_spin_wait_t(&tmem_empty[buf], ((g_kb >> 1) & 1) ^ 1, abort_flag, w1)) {
+#else
                     if (!mbar_wait_t(&full[stage], phase, abort_flag, w0) ||
                         !mbar_wait_t(&tmem_empty[buf], ((g_kb >> 1) & 1) ^ 1, abort_flag, w1)) {
+#endif
                         ok = false;
                         break;
                     }
                     tc_fence_after();
+                    const long long t_issue = prof_clock();
                     const uint32_t d0 = tmem_base + static_cast<uint32_t>(buf * kPfCols);
                     const uint32_t sa = smem_u32(smem + static_cast<size_t>(stage) * kPfStageBytes);
                     const uint64_t dx = make_desc_sw128(sa);
@@ -153,6 +194,7 @@ prefill_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
                         mma_f8(d0, dx + 2 * kk, dw + 2 * kk, IDESC, kk ? 1u : 0u);
                     tc_commit(&empty[stage]);
                     tc_commit(&tmem_full[buf]);
+                    w_issue += prof_clock() - t_issue;
                     if (++stage == stages) {
                         stage = 0;
                         phase ^= 1;
@@ -165,6 +207,7 @@ prefill_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
             }
             prof_add(prof, 1, w0);
             prof_add(prof, 3, w1);
+            prof_add(prof, 9, w_issue);
         }
     } else {
 #include "xs_prefill_fp8_epilogue.inl"

@@ -9,19 +9,50 @@
     const int kbs = K / kBlockK8;
     bool ok = true;
     uint32_t g_kb = 0, it = 0;
+    long long w_body = 0, w_tail = 0, w_x = 0; // role profile: cycles in the promotion bodies / per-tile tails / amax exchange waits
+    // scale rows of a work item: gate/up -> gate block nt and up block nt; down -> the 128-column block this group's columns
+    // fall into (twice)
+    auto weight_scale_rows = [&](int e_, int nt_, const float *&a, const float *&b) {
+        const float *wbase = e_ < groups ? sc.w_scale + static_cast<size_t>(e_) * (w_rows_per_expert / 128) * kbs : sc.w_scale2;
+        a = wbase + static_cast<size_t>(GATE_UP ? nt_ : nt_ * 2 + (g * CPT) / 128) * kbs;
+        b = GATE_UP ? wbase + static_cast<size_t>(n_out / 128 + nt_) * kbs : a;
+    };
+    // Token scales four k-blocks per 16-byte load and weight scales one k-block per lane (see below) need scale rows that
+    // are 16-byte multiples and at most 32 k-blocks; other shapes take one k-block at a time.
+    const bool wide = (kbs & 3) == 0 && num_kb <= 32 && (reinterpret_cast<uintptr_t>(sc.x_scale) & 15) == 0;
+    // The tile-table entry of the NEXT work item and its weight scales are fetched while the current one is processed, so
+    // that a work item starts with one memory latency in front of it instead of three dependent ones.
+    int e_cur = 0, row0_cur = 0;
+    float wa_cur = 0.0f, wb_cur = 0.0f;
+    if (static_cast<int>(blockIdx.x) < total_work) {
+        const int tile0 = blockIdx.x / n_n_tiles;
+        e_cur = tt.tile_expert[tile0];
+        row0_cur = tt.tile_row0[tile0];
+        if (wide && lane < num_kb) {
+            const float *a, *b;
+            weight_scale_rows(e_cur, blockIdx.x - tile0 * n_n_tiles, a, b);
+            wa_cur = __ldg(a + lane);
+            wb_cur = __ldg(b + lane);
+        }
+    }
     for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x, it++) {
         const int tile = w / n_n_tiles;
         const int nt = w - tile * n_n_tiles;
-        const int e = tt.tile_expert[tile];
-        const int row0 = tt.tile_row0[tile];
+        const int e = e_cur;
+        const int row0 = row0_cur;
+        const int w_next = w + gridDim.x;
+        const int tile_next = w_next / n_n_tiles;
+        int e_next = 0, row0_next = 0;
+        if (w_next < total_work) {
+            e_next = __ldg(tt.tile_expert + tile_next);
+            row0_next = __ldg(tt.tile_row0 + tile_next);
+        }
         int nvalid = offsets[e + 1] - row0;
         nvalid = nvalid < kPfTokens ? nvalid : kPfTokens;
         const bool valid = r < nvalid;
         const float *xs_row = sc.x_scale + static_cast<size_t>(row0 + (valid ? r : 0)) * kbs;
-        const float *wbase = e < groups ? sc.w_scale + static_cast<size_t>(e) * (w_rows_per_expert / 128) * kbs : sc.w_scale2;
-        // gate/up: gate block nt and up block nt; down: the 128-column block this group's columns fall into
-        const float *ws_a = wbase + static_cast<size_t>(GATE_UP ? nt : nt * 2 + (g * CPT) / 128) * kbs;
-        const float *ws_b = GATE_UP ? wbase + static_cast<size_t>(n_out / 128 + nt) * kbs : ws_a;
+        const float *ws_a, *ws_b;
+        weight_scale_rows(e, nt, ws_a, ws_b);
         // columns of this thread: gate/up -> gate [32g, 32g+32) and up [128+32g, 128+32g+32); down -> [64g, 64g+64)
         const uint32_t col_a = GATE_UP ? static_cast<uint32_t>(HALF * g) : static_cast<uint32_t>(CPT * g);
         const uint32_t col_b = GATE_UP ? 128u + static_cast<uint32_t>(HALF * g) : static_cast<uint32_t>(CPT * g + HALF);
@@ -29,37 +60,101 @@
 #pragma unroll
         for (int c = 0; c < CPT; c++)
             acc[c] = 0.0f;
-        for (int kb = 0; kb < num_kb; kb++, g_kb++) {
+        // One k-block: wait for its partial product in TMEM, promote it into the register accumulators with the block's
+        // combined scales, hand the TMEM buffer back.
+        auto promote = [&](float sa, float sb) -> bool {
             const int buf = g_kb & 1;
-            const float sx = __ldg(xs_row + kb);
-            const float sa = __fmul_rn(sx, __ldg(ws_a + kb));
-            const float sb = __fmul_rn(sx, __ldg(ws_b + kb));
-            if (!mbar_wait_t(&tmem_full[buf], (g_kb >> 1) & 1, abort_flag, w0)) {
-                ok = false;
-                break;
-            }
+#if XS_PF8_SPIN
+            if (!mbar_spin_wait_t(&tmem_full[buf], (g_kb >> 1) & 1, abort_flag, w0))
+                return false;
+#else
+            if (!mbar_wait_t(&tmem_full[buf], (g_kb >> 1) & 1, abort_flag, w0))
+                return false;
+#endif
             tc_fence_after();
+            const long long t_body = prof_clock();
             const uint32_t t0 = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(buf * kPfCols);
+#if XS_PF8_DEBUG >= 4
+            acc[0] += sa + sb + __uint_as_float(t0);
+#else
 #pragma unroll
             for (int i = 0; i < HALF / 16; i++) {
                 uint32_t pa[16], pb[16];
                 tmem_ld16(t0 + col_a + i * 16, pa);
                 tmem_ld16(t0 + col_b + i * 16, pb);
                 tmem_ld_wait_for(pa, pb);
+#if XS_PF8_FMA2
+#pragma unroll
+                for (int c = 0; c < 16; c += 2) {
+                    ffma2(acc[i * 16 + c], acc[i * 16 + c + 1], __uint_as_float(pa[c]), __uint_as_float(pa[c + 1]), sa);
+                    ffma2(acc[HALF + i * 16 + c], acc[HALF + i * 16 + c + 1], __uint_as_float(pb[c]), __uint_as_float(pb[c + 1]), sb);
+                }
+#else
 #pragma unroll
                 for (int c = 0; c < 16; c++) {
                     acc[i * 16 + c] = __fmaf_rn(__uint_as_float(pa[c]), sa, acc[i * 16 + c]);
                     acc[HALF + i * 16 + c] = __fmaf_rn(__uint_as_float(pb[c]), sb, acc[HALF + i * 16 + c]);
                 }
+#endif
             }
+#endif
             tc_fence_before();
             __syncwarp();
             if (lane == 0)
                 mbar_arrive(&tmem_empty[buf]);
+            w_body += prof_clock() - t_body;
+            g_kb++;
+            return true;
+        };
+        // The scales of a k-block (one per token row, one per 128-column weight block) come from global memory.  Fetched
+        // where they are used, their latency -- the same for all sixteen warps, which leave the accumulator barrier together
+        // -- is paid once per k-block and the tensor pipe waits for it.  So:
+        //   * token scales: the four scales of a row for four consecutive k-blocks are 16 contiguous bytes; they are
+        //     fetched one such group ahead, so a group's registers are first read four k-blocks after its loads;
+        //   * weight scales (the same for every thread of a warp): lane l holds the scales of k-block l -- one coalesced
+        //     load per scale row and work item, issued during the previous work item -- and every k-block takes its pair
+        //     by a warp shuffle.
+        float wa_next = 0.0f, wb_next = 0.0f;
+        if (wide) {
+            float4 cx = __ldg(reinterpret_cast<const float4 *>(xs_row));
+            for (int kb = 0; kb < num_kb && ok; kb += 4) {
+                float4 nx = cx;
+                if (kb + 4 < num_kb)
+                    nx = __ldg(reinterpret_cast<const float4 *>(xs_row + kb + 4));
+                const float sx[4] = {cx.x, cx.y, cx.z, cx.w};
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    const float a = __shfl_sync(0xffffffffu, wa_cur, kb + j), b = __shfl_sync(0xffffffffu, wb_cur, kb + j);
+                    ok = ok && promote(__fmul_rn(sx[j], a), __fmul_rn(sx[j], b));
+                }
+                cx = nx;
+                if (kb == 0 && w_next < total_work && lane < num_kb) { // the next work item's table entry has arrived by now
+                    const float *a, *b;
+                    weight_scale_rows(e_next, w_next - tile_next * n_n_tiles, a, b);
+                    wa_next = __ldg(a + lane);
+                    wb_next = __ldg(b + lane);
+                }
+            }
+        } else {
+            for (int kb = 0; kb < num_kb && ok; kb++) {
+                const float sx = __ldg(xs_row + kb);
+                ok = promote(__fmul_rn(sx, __ldg(ws_a + kb)), __fmul_rn(sx, __ldg(ws_b + kb)));
+            }
         }
+        e_cur = e_next;
+        row0_cur = row0_next;
+        wa_cur = wa_next;
+        wb_cur = wb_next;
         if (!ok)
             break;
+        const long long t_tail = prof_clock();
+#if XS_PF8_DEBUG == 3 || XS_PF8_DEBUG >= 5
+        if (valid && acc[3] == 1.2345f)
+            static_cast<float *>(out)[0] = acc[5] + acc[40];
+        if constexpr (false) {
+#else
         if constexpr (GATE_UP) {
+#endif
             // act = silu(gate) * up for this thread's 32 features; the 1x128 group spans the four warpgroups
             float m = 0.0f;
 #pragma unroll
@@ -72,14 +167,18 @@
             __syncwarp();
             if (lane == 0)
                 mbar_arrive(xbar);
-            if (!mbar_wait(xbar, it & 1, abort_flag)) {
+            if (!mbar_wait_t(xbar, it & 1, abort_flag, w_x)) {
                 ok = false;
                 break;
             }
 #pragma unroll
             for (int j = 0; j < kPfGroups; j++)
                 m = fmaxf(m, ax[j * 128 + r]);
-            const float s = __fdiv_rn(fmaxf(m, 1e-10f), 448.0f);
+            // s = max(amax, 1e-10) / 448 is what the down GEMM multiplies back; the codes are acc * (1 / s) with the
+            // reciprocal taken once per row (against a division per element: at most one f32 ulp before the e4m3 rounding)
+            const float mm = fmaxf(m, 1e-10f);
+            const float s = __fdiv_rn(mm, 448.0f);
+            const float rs = __fdiv_rn(448.0f, mm);
             if (valid) {
                 uint8_t *dst = static_cast<uint8_t *>(out) + static_cast<size_t>(row0 + r) * n_out + nt * 128 + HALF * g;
 #pragma unroll
@@ -87,17 +186,17 @@
                     uint32_t pk[4];
 #pragma unroll
                     for (int j = 0; j < 4; j++) {
-                        pk[j] = 0;
-#pragma unroll
-                        for (int b = 0; b < 4; b++)
-                            pk[j] |= static_cast<uint32_t>(f32_to_e4m3(__fdiv_rn(acc[v * 16 + j * 4 + b], s))) << (8 * b);
+                        const int c = v * 16 + j * 4;
+                        const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(__fmul_rn(acc[c], rs), __fmul_rn(acc[c + 1], rs)), __NV_SATFINITE, __NV_E4M3);
+                        const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(__fmul_rn(acc[c + 2], rs), __fmul_rn(acc[c + 3], rs)), __NV_SATFINITE, __NV_E4M3);
+                        pk[j] = lo | (hi << 16);
                     }
                     *reinterpret_cast<uint4 *>(dst + v * 16) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
                 }
                 if (g == 0)
                     sc.act_scale[static_cast<size_t>(row0 + r) * (n_out / 128) + nt] = s;
             }
-        } else {
+        } else if (XS_PF8_DEBUG != 3 && XS_PF8_DEBUG < 5) {
             if (valid) {
                 float *dst = static_cast<float *>(out) + static_cast<size_t>(row0 + r) * n_out + nt * 256 + CPT * g;
 #pragma unroll
@@ -105,11 +204,16 @@
                     *reinterpret_cast<float4 *>(dst + v * 4) = make_float4(acc[v * 4], acc[v * 4 + 1], acc[v * 4 + 2], acc[v * 4 + 3]);
             }
         }
+        w_tail += prof_clock() - t_tail;
     }
     if (!ok && lane == 0) {
         *abort_flag = 1;
         atomicOr(status, kStatusWaitTimeout);
     }
-    if (warp == 2 && lane == 0)
+    if (warp == 2 && lane == 0) {
         prof_add(prof, 5, w0);
+        prof_add(prof, 2, w_body);
+        prof_add(prof, 4, w_tail - w_x); // the tail's own work
+        prof_add(prof, 8, w_x);
+    }
 }

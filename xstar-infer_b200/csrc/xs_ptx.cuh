@@ -64,6 +64,34 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volati
     return false;
 }
 
+// Non-suspending variant for waits on the critical path of a two-stage hand-over (accumulator buffers): polls with
+// mbarrier.test_wait, which never parks the thread, so the waiter resumes within a poll of the phase completing.  Bounded
+// like mbar_wait (about a quarter of a second of polling).
+__device__ __forceinline__ bool mbar_test_wait(uint64_t *bar, uint32_t parity)
+{
+    uint32_t ok;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred P;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 P, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, P;\n\t"
+        "}\n"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ bool mbar_spin_wait(uint64_t *bar, uint32_t parity, volatile uint32_t *abort_flag)
+{
+    for (uint32_t i = 0; i < (1u << 24); i++) {
+        if (mbar_test_wait(bar, parity))
+            return true;
+        if ((i & 1023u) == 1023u && *abort_flag)
+            return false;
+    }
+    return false;
+}
+
 // Role profiling (who waits for whom inside a warp-specialised kernel) is a tuning aid compiled in only with
 // -DXS_ROLE_PROFILE=1: cycle counters summed into the eight 64-bit words behind the workspace status word.  In the
 // default build the helpers below reduce to the plain bounded wait and to nothing.
@@ -92,8 +120,8 @@ __device__ __forceinline__ void prof_add(unsigned long long *prof, int slot, lon
 __device__ __forceinline__ bool mbar_wait_t(uint64_t *bar, uint32_t parity, volatile uint32_t *abort_flag, long long &acc)
 {
 #if XS_ROLE_PROFILE
-    if (mbar_try_wait(bar, parity))
-        return true;
+    // the whole wait is timed, first poll included: mbarrier.try_wait may itself suspend the thread until the phase
+    // completes, so a wait that its first poll satisfies can still have been a long one
     const long long t0 = clock64();
     const bool ok = mbar_wait(bar, parity, abort_flag);
     acc += clock64() - t0;
@@ -101,6 +129,18 @@ __device__ __forceinline__ bool mbar_wait_t(uint64_t *bar, uint32_t parity, vola
 #else
     (void)acc;
     return mbar_wait(bar, parity, abort_flag);
+#endif
+}
+__device__ __forceinline__ bool mbar_spin_wait_t(uint64_t *bar, uint32_t parity, volatile uint32_t *abort_flag, long long &acc)
+{
+#if XS_ROLE_PROFILE
+    const long long t0 = clock64();
+    const bool ok = mbar_spin_wait(bar, parity, abort_flag);
+    acc += clock64() - t0;
+    return ok;
+#else
+    (void)acc;
+    return mbar_spin_wait(bar, parity, abort_flag);
 #endif
 }
 
