@@ -755,7 +755,8 @@ def run_mma_rate():
     rows = []
     for kind, name in ((0, "bf16 K=16"), (1, "e4m3 K=32"), (2, "e4m3 x e2m1 block-scaled K=32"),
                        (3, "block-scaled K=32 + 3 tcgen05.cp per 4 MMAs"), (4, "e4m3 K=32, fresh accumulator + 2 commits per 4 MMAs"),
-                       (5, "e4m3 K=32, fresh accumulator + 1 commit per 4 MMAs")):
+                       (5, "e4m3 K=32, fresh accumulator + 1 commit per 4 MMAs"),
+                       (6, "e4m3 K=32, 4 MMAs + commit + wait for it (latency)")):
         for n in (16, 64, 128, 256):
             for chains in (1, 2, 4):
                 if chains * n > (496 if kind in (2, 3) else 512) or (kind >= 4 and chains > 1):

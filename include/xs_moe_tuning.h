@@ -19,7 +19,8 @@ extern "C" {
  * 2 = block-scaled e4m3 x e2m1 (K = 32), 3 = the same with three tcgen05.cp scale copies (3 x 512 bytes, shared memory
  * to TMEM) issued by the same thread before every four MMAs, as a block-scaled GEMM's k-block needs; 4 and 5 = e4m3 issued
  * as a loop with per-k-block accumulators issues it (every four MMAs start afresh in the other of two accumulators and are
- * followed by two, resp. one, tcgen05.commit; `chains` is ignored).  Returns cycles per MMA until completion, cycles per MMA spent issuing, and
+ * followed by two, resp. one, tcgen05.commit; `chains` is ignored), 6 = 5 with the issuing thread waiting for every
+ * group's commit before the next group (four times its cycles per MMA = latency from issue to observed completion).  Returns cycles per MMA until completion, cycles per MMA spent issuing, and
  * whole-chip TFLOP/s by CUDA events.  Needs a workspace of at least 256 bytes (status block).  Synchronises. */
 int xs_moe_probe_mma_rate(int32_t kind, int32_t n, int32_t iters, int32_t chains, void *workspace_dev,
                           size_t workspace_bytes, double *cycles_per_mma, double *issue_cycles_per_mma, double *tflops,
@@ -33,6 +34,14 @@ int xs_moe_probe_mma_rate(int32_t kind, int32_t n, int32_t iters, int32_t chains
 int xs_moe_probe_tmem_ld_rate(int32_t shape, int32_t warps, int32_t iters, int32_t with_mma, void *workspace_dev,
                               size_t workspace_bytes, double *bytes_per_cycle_per_sm, double *mma_cycles_per_mma,
                               void *stream);
+
+/* Accumulator hand-over probe: on every SM one thread issues `iters` k-blocks of four N = 256 e4m3 MMAs alternately into
+ * two TMEM buffers and commits each to a barrier; `responders` warps (1..16) wait for it, read ld_cols (0, 32 or 64) columns
+ * of the buffer and arrive on the barrier the issuer waits for before it reuses the buffer.  mode bit 0: responders poll
+ * with mbarrier.test_wait, bit 1: the issuer too, bit 2: no tcgen05 fences around the waits, bit 3: two issuer warps take
+ * k-blocks alternately.  Returns cycles per k-block.  Needs a workspace of at least 256 bytes.  Synchronises. */
+int xs_moe_probe_handoff(int32_t responders, int32_t iters, int32_t mode, int32_t ld_cols, void *workspace_dev,
+                         size_t workspace_bytes, double *cycles_per_kblock, void *stream);
 
 /* Role profile of the warp-specialised GEMM kernels that ran on this workspace since the last call: sixteen 64-bit
  * cycle counters summed over CTAs (0 producer blocked on a free stage, 1 MMA issuer blocked on operands, 2 on scales,

@@ -356,6 +356,7 @@ struct Fp8Scales {
     const float *w_scale2;  // same for the always-on expert (segments >= groups): (w_rows_per_expert / 128, K / 128)
     const float *x_scale;   // (rows, K / 128)
     float *act_scale;       // GATE_UP only: (rows, n_out / 128) written by the epilogue
+    int max_rows;           // rows of x_scale (reads past the last segment are clamped to it)
 };
 
 template <int N_TILE, bool GATE_UP>

@@ -11,7 +11,9 @@ namespace xs {
 //       3 = kind 2 with three tcgen05.cp.32x128b.warpx4 scale copies before every four MMAs (one 128-deep k-block of a
 //           block-scaled GEMM whose issuing thread also moves the scales from shared memory to TMEM),
 //       4 / 5 = kind 1 issued the way a k-block loop with per-k-block accumulators issues it: every four MMAs start a
-//           fresh accumulation in the other of two accumulators and are followed by two (4) or one (5) tcgen05.commit
+//           fresh accumulation in the other of two accumulators and are followed by two (4) or one (5) tcgen05.commit,
+//       6 = kind 5 with the issuing thread WAITING for each group's commit before it issues the next group: cycles per
+//           MMA x 4 is then the latency from issuing a k-block to seeing its completion on an mbarrier
 __global__ void __launch_bounds__(64, 1)
 mma_rate_kernel(int kind, int n, int iters, int chains, unsigned long long *cycles, int32_t *status)
 {
@@ -71,6 +73,10 @@ mma_rate_kernel(int kind, int n, int iters, int chains, unsigned long long *cycl
                 tc_commit(&side_bar[0]);
                 if (kind == 4)
                     tc_commit(&side_bar[1]);
+                if (kind == 6 && !mbar_wait(&side_bar[0], (i >> 2) & 1, &abort_flag)) {
+                    atomicOr(status, 1);
+                    break;
+                }
                 continue;
             }
 #pragma unroll
@@ -233,6 +239,108 @@ tmem_ld_rate_kernel(int shape, int warps, int iters, int with_mma, int mma_iters
         atomicAdd(&cycles[0], s_max);
         atomicAdd(&cycles[2], 1ull);
     }
+    if (warp == 0) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, 512);
+    }
+}
+
+// Accumulator hand-over round trip: one thread issues k-blocks of four N = 256 e4m3 MMAs alternately into two TMEM
+// buffers, committing each to a "full" barrier; `resp` responder warps wait for it, (optionally) read `ld_cols` columns
+// of the buffer, and arrive on the buffer's "empty" barrier, which the issuer waits for before it reuses the buffer --
+// the protocol of a GEMM whose accumulator changes hands every k-block, with nothing else in the way.
+// mode bit 0: responders poll with mbarrier.test_wait instead of try_wait; bit 1: the issuer does too;
+// bit 2: no tcgen05 fences around the waits; bit 3: a second issuer warp takes the odd k-blocks.
+__global__ void __launch_bounds__(640, 1)
+handoff_rate_kernel(int resp, int iters, int mode, int ld_cols, unsigned long long *cycles, int32_t *status)
+{
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    __shared__ uint64_t full[2], empty[2];
+    __shared__ uint32_t tmem_slot;
+    __shared__ uint32_t abort_flag;
+    for (int i = threadIdx.x; i < (128 + 256) * 128 / 16; i += blockDim.x)
+        reinterpret_cast<uint4 *>(smem)[i] = make_uint4(0, 0, 0, 0);
+    if (threadIdx.x == 0) {
+        for (int b = 0; b < 2; b++) {
+            mbar_init(&full[b], 1);
+            mbar_init(&empty[b], resp);
+        }
+        abort_flag = 0;
+        fence_mbar_init();
+    }
+    fence_proxy_async_smem();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (warp == 0) {
+        tmem_alloc(&tmem_slot, 512);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = tmem_slot;
+    const bool two_issuers = (mode & 8) != 0;
+    auto wait = [&](uint64_t *bar, uint32_t parity, bool spin) { return spin ? mbar_spin_wait(bar, parity, &abort_flag) : mbar_wait(bar, parity, &abort_flag); };
+    if (warp == 0 || (two_issuers && warp == 1)) {
+        if (lane == 0) {
+            const uint32_t sa = smem_u32(smem);
+            const uint64_t da = make_desc_sw128(sa), db = make_desc_sw128(sa + 128 * 128);
+            const uint32_t idesc = make_idesc(0, 0, 128, 256);
+            const int first = two_issuers ? warp : 0, step = two_issuers ? 2 : 1;
+            bool ok = true;
+            const long long t0 = clock64();
+            for (int i = first; i < iters && ok; i += step) {
+                const int b = i & 1;
+                ok = wait(&empty[b], ((i >> 1) & 1) ^ 1, (mode & 2) != 0);
+                if (!(mode & 4))
+                    tc_fence_after();
+#pragma unroll
+                for (int j = 0; j < 4; j++)
+                    mma_f8(tmem_base + b * 256, da + 2 * j, db + 2 * j, idesc, j ? 1u : 0u);
+                tc_commit(&full[b]);
+            }
+            const long long t1 = clock64();
+            if (!ok) {
+                abort_flag = 1;
+                atomicOr(status, 1);
+            }
+            if (warp == 0) {
+                atomicAdd(&cycles[0], static_cast<unsigned long long>(t1 - t0));
+                atomicAdd(&cycles[2], 1ull);
+            }
+        }
+    } else if (warp >= 4 && warp < 4 + resp) {
+        bool ok = true;
+        uint32_t sink = 0;
+        for (int i = 0; i < iters && ok; i++) {
+            const int b = i & 1;
+            ok = wait(&full[b], (i >> 1) & 1, (mode & 1) != 0);
+            if (!(mode & 4))
+                tc_fence_after();
+            for (int c = 0; c < ld_cols; c += 32) {
+                uint32_t x[16], y[16];
+                const uint32_t t = tmem_base + (static_cast<uint32_t>((warp & 3) * 32) << 16) + b * 256 + ((warp - 4) >> 2) * 64 + c;
+                tmem_ld16(t, x);
+                tmem_ld16(t + 16, y);
+                tmem_ld_wait_for(x, y);
+                sink ^= x[0] ^ y[15];
+            }
+            if (!(mode & 4))
+                tc_fence_before();
+            __syncwarp();
+            if (lane == 0)
+                mbar_arrive(&empty[b]);
+        }
+        if (sink == 0x9e3779b9u && lane == 0)
+            atomicOr(status, 0);
+        if (!ok && lane == 0) {
+            abort_flag = 1;
+            atomicOr(status, 1);
+        }
+    }
+    __syncwarp();
+    tc_fence_before();
+    __syncthreads();
     if (warp == 0) {
         tc_fence_after();
         tmem_dealloc(tmem_base, 512);

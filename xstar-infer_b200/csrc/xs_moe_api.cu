@@ -765,22 +765,22 @@ int run_grouped(const GroupedArgs &a, cudaStream_t st, cudaEvent_t mid = nullptr
     float *act_scale = reinterpret_cast<float *>(a.scratch + a.gp.off_act_scale);
     if (a.gp.n_tile == 128) {
         // many tokens per expert: tokens as the M of N = 256 MMAs (prefill kernel); the maps above already use 128-row boxes
-        xs::Fp8Scales p1{static_cast<const float *>(a.gu_scale), static_cast<const float *>(a.gu2_scale), a.row_scale, act_scale};
+        xs::Fp8Scales p1{static_cast<const float *>(a.gu_scale), static_cast<const float *>(a.gu2_scale), a.row_scale, act_scale, a.max_rows};
         if (int rc = launch_prefill_fp8<true>(t_wgu, t_wgu2, t_x, offs, tt, p1, groups, 2 * I, I, H, act, a.status,
                                               a.gp.max_tiles * (I / 128), st))
             return rc;
         if (mid)
             XS_CUDA(cudaEventRecord(mid, st));
-        xs::Fp8Scales p2{static_cast<const float *>(a.dw_scale), static_cast<const float *>(a.dw2_scale), act_scale, nullptr};
+        xs::Fp8Scales p2{static_cast<const float *>(a.dw_scale), static_cast<const float *>(a.dw2_scale), act_scale, nullptr, a.max_rows};
         return launch_prefill_fp8<false>(t_wd, t_wd2, t_act, offs, tt, p2, groups, H, H, I, a.y, a.status,
                                          a.gp.max_tiles * (H / 256), st);
     }
-    xs::Fp8Scales s1{static_cast<const float *>(a.gu_scale), static_cast<const float *>(a.gu2_scale), a.row_scale, act_scale};
+    xs::Fp8Scales s1{static_cast<const float *>(a.gu_scale), static_cast<const float *>(a.gu2_scale), a.row_scale, act_scale, a.max_rows};
     if (int rc = launch_gemm_fp8<true>(a.gp.n_tile, t_wgu, t_wgu2, t_x, offs, tt, s1, groups, 2 * I, I, H, act, a.status, work_gu, st))
         return rc;
     if (mid)
         XS_CUDA(cudaEventRecord(mid, st));
-    xs::Fp8Scales s2{static_cast<const float *>(a.dw_scale), static_cast<const float *>(a.dw2_scale), act_scale, nullptr};
+    xs::Fp8Scales s2{static_cast<const float *>(a.dw_scale), static_cast<const float *>(a.dw2_scale), act_scale, nullptr, a.max_rows};
     return launch_gemm_fp8<false>(a.gp.n_tile, t_wd, t_wd2, t_act, offs, tt, s2, groups, H, H, I, a.y, a.status, work_d, st);
 }
 
@@ -1308,7 +1308,7 @@ int xs_moe_probe_mma_rate(int32_t kind, int32_t n, int32_t iters, int32_t chains
 {
     if (int rc = xs_moe_device_check())
         return rc;
-    if (kind < 0 || kind > 5 || n < 16 || n > 256 || n % 16 != 0 || iters < 4 || iters % 4 != 0 ||
+    if (kind < 0 || kind > 6 || n < 16 || n > 256 || n % 16 != 0 || iters < 4 || iters % 4 != 0 ||
         (chains != 1 && chains != 2 && chains != 4) || chains * n > ((kind == 2 || kind == 3) ? 496 : 512) || (kind >= 4 && 2 * n > 512))
         return fail(XS_MOE_ERR_INVALID_ARG, "bad probe arguments");
     if (int rc = check_workspace(ws, ws_bytes, kStatusBytes))
@@ -1399,6 +1399,45 @@ int xs_moe_probe_tmem_ld_rate(int32_t shape, int32_t warps, int32_t iters, int32
         *bytes_per_cycle_per_sm = h[0] ? static_cast<double>(warps) * iters * 8192.0 / (static_cast<double>(h[0]) / ctas) : 0.0;
     if (mma_cycles_per_mma)
         *mma_cycles_per_mma = mma_iters ? static_cast<double>(h[1]) / ctas / static_cast<double>(mma_iters) : 0.0;
+    return xs_moe_check_flags(ws, stream);
+}
+
+int xs_moe_probe_handoff(int32_t responders, int32_t iters, int32_t mode, int32_t ld_cols, void *ws, size_t ws_bytes,
+                         double *cycles_per_kblock, void *stream)
+{
+    if (int rc = xs_moe_device_check())
+        return rc;
+    if (responders < 1 || responders > 16 || iters < 2 || iters > (1 << 22) || mode < 0 || mode > 15 || ld_cols < 0 || ld_cols > 64 ||
+        ld_cols % 32 != 0)
+        return fail(XS_MOE_ERR_INVALID_ARG, "bad probe arguments");
+    if (int rc = check_workspace(ws, ws_bytes, kStatusBytes))
+        return rc;
+    DeviceInfo di;
+    if (int rc = device_info(&di))
+        return rc;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    uint8_t *b = static_cast<uint8_t *>(ws);
+    unsigned long long *ctr = reinterpret_cast<unsigned long long *>(b + 64);
+    XS_CUDA(cudaMemsetAsync(ctr, 0, 64, st));
+    const int smem = (128 + 256) * 128 + 1024;
+    static bool configured[64] = {};
+    int dev = 0;
+    XS_CUDA(cudaGetDevice(&dev));
+    if (dev >= 64 || !configured[dev]) {
+        XS_CUDA(cudaFuncSetAttribute(xs::handoff_rate_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        if (dev < 64)
+            configured[dev] = true;
+    }
+    xs::handoff_rate_kernel<<<di.sms, 640, smem, st>>>(responders, iters, mode, ld_cols, ctr, reinterpret_cast<int32_t *>(b));
+    note_launch();
+    XS_CUDA(cudaGetLastError());
+    unsigned long long h[3];
+    XS_CUDA(cudaMemcpyAsync(h, ctr, sizeof(h), cudaMemcpyDeviceToHost, st));
+    XS_CUDA(cudaStreamSynchronize(st));
+    XS_CUDA(cudaMemsetAsync(ctr, 0, 64, st));
+    const double ctas = h[2] ? static_cast<double>(h[2]) : 1.0;
+    if (cycles_per_kblock)
+        *cycles_per_kblock = static_cast<double>(h[0]) / ctas / ((mode & 8) ? (iters + 1) / 2 : iters) / ((mode & 8) ? 0.5 : 1.0);
     return xs_moe_check_flags(ws, stream);
 }
 

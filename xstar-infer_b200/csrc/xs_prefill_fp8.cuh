@@ -9,44 +9,31 @@
 //
 // Block scales: each 128-deep k-block is accumulated on its own and promoted by the epilogue warps,
 //     acc += partial * (s_token[kb] * s_weight_block[kb]),
-// with one scalar token scale per TMEM lane and one scalar weight scale per 128 columns.  The promotion is bound by the
-// latency of the TMEM reads, so FOUR epilogue warpgroups (16 warps, 4 per scheduler) share the 256 columns, 64
-// accumulator registers per thread: for gate/up each takes 32 gate + the matching 32 up columns so that SwiGLU needs no
-// exchange; only the 1x128 amax of the re-quantised activations crosses the warpgroups.
+// with one scalar token scale per TMEM lane and one scalar weight scale per 128 columns.  FOUR epilogue warpgroups (16
+// warps, 4 per scheduler) share the 256 columns, 64 accumulator registers per thread: for gate/up each takes 32 gate +
+// the matching 32 up columns so that SwiGLU needs no exchange; only the 1x128 amax of the re-quantised activations
+// crosses the warpgroups.
 //
-// Warps: 0 TMA producer | 1 MMA issuer, TMEM owner | 2..17 epilogue (group = (warp - 2) / 4, lane quarter = warp % 4).
+// Because the accumulator changes hands once per k-block (four MMAs), what the issuing thread does BETWEEN k-blocks is on
+// the tensor pipe's critical path: a thread that issues tcgen05.mma is held until the pipe takes the instruction, so it
+// cannot run ahead, and its two commits, two barrier waits and descriptor set-up for the next k-block (a few hundred cycles
+// of dependent latency) leave the pipe idle every time -- measured, a loop of nothing but these steps ran at 1150 cycles
+// per k-block against 630 for its four MMAs.  So TWO warps issue, taking k-blocks alternately (each owns one of the two
+// accumulator buffers): while one is held by its MMAs the other gets through its waits and queues the next k-block.
+//
+// Warps: 0 TMA producer | 1, 2 MMA issuers (1 owns TMEM) | 3 idle | 4..19 epilogue (group = (warp - 4) / 4, lane quarter =
+// warp % 4).  Warps 0..3 hand most of their registers to the epilogue warpgroups (setmaxnreg), whose 64 accumulators + TMEM
+// staging registers per thread do not fit the even share of 20 warps.
 #pragma once
 #include "xs_grouped_gemm.cuh"
 
-#ifndef XS_PF8_SPIN
-#define XS_PF8_SPIN 0
-#endif
-#ifndef XS_PF8_FMA2
-#define XS_PF8_FMA2 0
-#endif
-#ifndef XS_PF8_DEBUG
-#define XS_PF8_DEBUG 0
-#endif
 
 namespace xs {
 
-// d0 += a0 * s, d1 += a1 * s as one packed instruction (two independent IEEE fused multiply-adds)
-__device__ __forceinline__ void ffma2(float &d0, float &d1, float a0, float a1, float s)
-{
-    asm("{\n\t"
-        ".reg .b64 ra, rb, rc;\n\t"
-        "mov.b64 ra, {%2, %3};\n\t"
-        "mov.b64 rb, {%4, %4};\n\t"
-        "mov.b64 rc, {%0, %1};\n\t"
-        "fma.rn.f32x2 rc, ra, rb, rc;\n\t"
-        "mov.b64 {%0, %1}, rc;\n\t"
-        "}\n"
-        : "+f"(d0), "+f"(d1)
-        : "f"(a0), "f"(a1), "f"(s));
-}
-
 constexpr int kPfGroups = 4;                     // epilogue warpgroups sharing the 256 columns
-constexpr int kPfThreads = 64 + kPfGroups * 128;
+constexpr int kPfIssuers = 2;                     // MMA issuer warps, k-blocks taken round-robin (== accumulator buffers)
+constexpr int kPfEpiWarp0 = 4;                   // first epilogue warp: warps 0..3 form the light warpgroup (3 idles)
+constexpr int kPfThreads = 32 * kPfEpiWarp0 + kPfGroups * 128;
 constexpr int kPfTokens = 128;  // MMA M
 constexpr int kPfCols = 256;    // MMA N
 constexpr int kPfStageBytes = (kPfTokens + kPfCols) * kBlockK8; // 48 KB
@@ -61,7 +48,7 @@ prefill_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
 {
     constexpr int X_BYTES = kPfTokens * kBlockK8;
     constexpr int W_HALF = 128 * kBlockK8;
-    constexpr int NBUF = 2;
+    constexpr int NBUF = kPfIssuers; // issuer m fills buffer m
     constexpr int TMEM_COLS = 512;
     constexpr uint32_t IDESC = make_idesc(0, 0, kPfTokens, kPfCols);
     constexpr int N_PER_TILE = GATE_UP ? 128 : 256; // output features covered by one work item
@@ -115,6 +102,10 @@ prefill_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
     const int total_work = num_tiles * n_n_tiles;
     const int num_kb = K / kBlockK8;
 
+    if (warp < kPfEpiWarp0)
+        reg_dealloc<40>();
+    else
+        reg_alloc<104>();
     if (warp == 0) {
         if (lane == 0) {
             const uint64_t pol_w = policy_evict_last(); // weights are re-read by the other token tiles of the expert
@@ -136,19 +127,10 @@ prefill_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
                         break;
                     }
                     uint8_t *st = smem + static_cast<size_t>(stage) * kPfStageBytes;
-#if XS_PF8_DEBUG == 6
-                    (void)st; (void)tw; (void)wbase; (void)wrow2; (void)row0; (void)pol_x; (void)pol_w;
-                    mbar_arrive(&full[stage]);
-#elif XS_PF8_DEBUG == 7
-                    (void)tw; (void)wbase; (void)wrow2; (void)pol_w;
-                    mbar_arrive_expect_tx(&full[stage], X_BYTES);
-                    tma_load_2d(st, &tmap_x, &full[stage], kb * kBlockK8, row0, pol_x);
-#else
                     mbar_arrive_expect_tx(&full[stage], kPfStageBytes);
                     tma_load_2d(st, &tmap_x, &full[stage], kb * kBlockK8, row0, pol_x);
                     tma_load_2d(st + X_BYTES, tw, &full[stage], kb * kBlockK8, wbase, pol_w);
                     tma_load_2d(st + X_BYTES + W_HALF, tw, &full[stage], kb * kBlockK8, wrow2, pol_w);
-#endif
                     if (++stage == stages) {
                         stage = 0;
                         phase ^= 1;
@@ -163,53 +145,48 @@ prefill_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
             prof_add(prof, 6, prof_clock() - t_start);
             prof_add(prof, 7, 1);
         }
-    } else if (warp == 1) {
+    } else if (warp <= kPfIssuers) {
         if (lane == 0) {
-            int stage = 0;
-            uint32_t phase = 0;
+            const uint32_t me = static_cast<uint32_t>(warp - 1); // this issuer's k-blocks: g_kb % kPfIssuers == me
+            // k-blocks of this CTA, over all its work items
+            const uint32_t n_items = static_cast<int>(blockIdx.x) < total_work
+                                         ? static_cast<uint32_t>((total_work - 1 - static_cast<int>(blockIdx.x)) / static_cast<int>(gridDim.x) + 1)
+                                         : 0u;
+            const uint32_t n_kb = n_items * static_cast<uint32_t>(num_kb);
             bool ok = true;
-            uint32_t g_kb = 0;
             long long w_issue = 0; // role profile: cycles spent issuing (descriptors, four MMAs, two commits)
-            for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x) {
-                for (int kb = 0; kb < num_kb; kb++, g_kb++) {
-                    const int buf = g_kb & 1;
-#if XS_PF8_SPIN
-                    if (!mbar_wait_t(&full[stage], phase, abort_flag, w0) ||
-                        !mbar_spin_wait_t(&tmem_empty[buf], ((g_kb >> 1) & 1) ^ 1, abort_flag, w1)) {
-#else
-                    if (!mbar_wait_t(&full[stage], phase, abort_flag, w0) ||
-                        !mbar_wait_t(&tmem_empty[buf], ((g_kb >> 1) & 1) ^ 1, abort_flag, w1)) {
-#endif
-                        ok = false;
-                        break;
-                    }
-                    tc_fence_after();
-                    const long long t_issue = prof_clock();
-                    const uint32_t d0 = tmem_base + static_cast<uint32_t>(buf * kPfCols);
-                    const uint32_t sa = smem_u32(smem + static_cast<size_t>(stage) * kPfStageBytes);
-                    const uint64_t dx = make_desc_sw128(sa);
-                    const uint64_t dw = make_desc_sw128(sa + X_BYTES); // 256 rows: the two 128-row boxes are contiguous
-#pragma unroll
-                    for (int kk = 0; kk < kBlockK8 / kUmmaK8; kk++)
-                        mma_f8(d0, dx + 2 * kk, dw + 2 * kk, IDESC, kk ? 1u : 0u);
-                    tc_commit(&empty[stage]);
-                    tc_commit(&tmem_full[buf]);
-                    w_issue += prof_clock() - t_issue;
-                    if (++stage == stages) {
-                        stage = 0;
-                        phase ^= 1;
-                    }
+            for (uint32_t g_kb = me; g_kb < n_kb; g_kb += kPfIssuers) {
+                const uint32_t stage = g_kb % static_cast<uint32_t>(stages);
+                const uint32_t phase = (g_kb / static_cast<uint32_t>(stages)) & 1u;
+                const uint32_t use = g_kb / kPfIssuers; // how often this issuer's buffer has been filled before
+                if (!mbar_wait_t(&full[stage], phase, abort_flag, w0) || !mbar_wait_t(&tmem_empty[me], (use & 1u) ^ 1u, abort_flag, w1)) {
+                    ok = false;
+                    break;
                 }
+                tc_fence_after();
+                const long long t_issue = prof_clock();
+                const uint32_t d0 = tmem_base + me * kPfCols;
+                const uint32_t sa = smem_u32(smem + static_cast<size_t>(stage) * kPfStageBytes);
+                const uint64_t dx = make_desc_sw128(sa);
+                const uint64_t dw = make_desc_sw128(sa + X_BYTES); // 256 rows: the two 128-row boxes are contiguous
+#pragma unroll
+                for (int kk = 0; kk < kBlockK8 / kUmmaK8; kk++)
+                    mma_f8(d0, dx + 2 * kk, dw + 2 * kk, IDESC, kk ? 1u : 0u);
+                tc_commit(&empty[stage]);
+                tc_commit(&tmem_full[me]);
+                w_issue += prof_clock() - t_issue;
             }
             if (!ok) {
                 *abort_flag = 1;
                 atomicOr(status, kStatusWaitTimeout);
             }
-            prof_add(prof, 1, w0);
-            prof_add(prof, 3, w1);
-            prof_add(prof, 9, w_issue);
+            if (me == 0) {
+                prof_add(prof, 1, w0);
+                prof_add(prof, 3, w1);
+                prof_add(prof, 9, w_issue);
+            }
         }
-    } else {
+    } else if (warp >= kPfEpiWarp0) {
 #include "xs_prefill_fp8_epilogue.inl"
     }
 

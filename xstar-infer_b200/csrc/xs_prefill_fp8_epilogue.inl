@@ -1,14 +1,16 @@
-// Epilogue of prefill_gemm_fp8_kernel (included inside the kernel body; warps 2..17).
+// Epilogue of prefill_gemm_fp8_kernel (included inside the kernel body; warps kPfEpiWarp0 .. kPfEpiWarp0 + 15).
 // Group g = 0..3, TMEM lane quarter q: this thread owns token row r = q*32 + lane of the tile and 64 of its 256 columns.
 {
     constexpr int CPT = 256 / kPfGroups; // columns per thread (64)
     constexpr int HALF = CPT / 2;        // gate/up: 32 gate + 32 up columns
-    const int g = (warp - 2) >> 2;
+    const int g = (warp - kPfEpiWarp0) >> 2;
     const int q = warp & 3;
     const int r = q * 32 + lane;
     const int kbs = K / kBlockK8;
     bool ok = true;
     uint32_t g_kb = 0, it = 0;
+    long long w_fence = 0, w_gap = 0, t_exit = prof_clock();
+    long long w_ga = 0, w_gb = 0, w_gc = 0, w_gd = 0;
     long long w_body = 0, w_tail = 0, w_x = 0; // role profile: cycles in the promotion bodies / per-tile tails / amax exchange waits
     // scale rows of a work item: gate/up -> gate block nt and up block nt; down -> the 128-column block this group's columns
     // fall into (twice)
@@ -22,8 +24,13 @@
     const bool wide = (kbs & 3) == 0 && num_kb <= 32 && (reinterpret_cast<uintptr_t>(sc.x_scale) & 15) == 0;
     // The tile-table entry of the NEXT work item and its weight scales are fetched while the current one is processed, so
     // that a work item starts with one memory latency in front of it instead of three dependent ones.
+    auto scale_row = [&](int row0_) {
+        const int row = row0_ + r;
+        return sc.x_scale + static_cast<size_t>(row < sc.max_rows ? row : sc.max_rows - 1) * kbs;
+    };
     int e_cur = 0, row0_cur = 0;
     float wa_cur = 0.0f, wb_cur = 0.0f;
+    float4 cx = make_float4(0.0f, 0.0f, 0.0f, 0.0f); // token scales of the coming four k-blocks (wide path)
     if (static_cast<int>(blockIdx.x) < total_work) {
         const int tile0 = blockIdx.x / n_n_tiles;
         e_cur = tt.tile_expert[tile0];
@@ -34,6 +41,8 @@
             wa_cur = __ldg(a + lane);
             wb_cur = __ldg(b + lane);
         }
+        if (wide)
+            cx = ldg_f4_pinned(scale_row(row0_cur));
     }
     for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x, it++) {
         const int tile = w / n_n_tiles;
@@ -50,7 +59,9 @@
         int nvalid = offsets[e + 1] - row0;
         nvalid = nvalid < kPfTokens ? nvalid : kPfTokens;
         const bool valid = r < nvalid;
-        const float *xs_row = sc.x_scale + static_cast<size_t>(row0 + (valid ? r : 0)) * kbs;
+        // rows past the segment's end read some other row's scales (their results are never stored); the clamp keeps the
+        // read inside the array, and the address does not wait for the segment's length
+        const float *xs_row = scale_row(row0);
         const float *ws_a, *ws_b;
         weight_scale_rows(e, nt, ws_a, ws_b);
         // columns of this thread: gate/up -> gate [32g, 32g+32) and up [128+32g, 128+32g+32); down -> [64g, 64g+64)
@@ -63,46 +74,34 @@
         // One k-block: wait for its partial product in TMEM, promote it into the register accumulators with the block's
         // combined scales, hand the TMEM buffer back.
         auto promote = [&](float sa, float sb) -> bool {
-            const int buf = g_kb & 1;
-#if XS_PF8_SPIN
-            if (!mbar_spin_wait_t(&tmem_full[buf], (g_kb >> 1) & 1, abort_flag, w0))
+            const uint32_t buf = g_kb % kPfIssuers;
+            const long long t_in = prof_clock();
+            w_gap += t_in - t_exit;
+            if (!mbar_wait_t(&tmem_full[buf], (g_kb / kPfIssuers) & 1u, abort_flag, w0))
                 return false;
-#else
-            if (!mbar_wait_t(&tmem_full[buf], (g_kb >> 1) & 1, abort_flag, w0))
-                return false;
-#endif
+            const long long t_f = prof_clock();
             tc_fence_after();
             const long long t_body = prof_clock();
-            const uint32_t t0 = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(buf * kPfCols);
-#if XS_PF8_DEBUG >= 4
-            acc[0] += sa + sb + __uint_as_float(t0);
-#else
+            w_fence += t_body - t_f;
+            const uint32_t t0 = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * kPfCols;
+            // sixteen columns at a time: the register budget leaves room for one staging block beside the 64 accumulators
 #pragma unroll
-            for (int i = 0; i < HALF / 16; i++) {
-                uint32_t pa[16], pb[16];
-                tmem_ld16(t0 + col_a + i * 16, pa);
-                tmem_ld16(t0 + col_b + i * 16, pb);
-                tmem_ld_wait_for(pa, pb);
-#if XS_PF8_FMA2
+            for (int i = 0; i < CPT / 16; i++) {
+                uint32_t p[16];
+                const bool second = i >= HALF / 16; // gate/up: the up columns; down: the upper half of the 64 columns
+                tmem_ld16(t0 + (second ? col_b + (i - HALF / 16) * 16 : col_a + i * 16), p);
+                tmem_ld_wait_16(p);
+                const float sc_ = second ? sb : sa;
 #pragma unroll
-                for (int c = 0; c < 16; c += 2) {
-                    ffma2(acc[i * 16 + c], acc[i * 16 + c + 1], __uint_as_float(pa[c]), __uint_as_float(pa[c + 1]), sa);
-                    ffma2(acc[HALF + i * 16 + c], acc[HALF + i * 16 + c + 1], __uint_as_float(pb[c]), __uint_as_float(pb[c + 1]), sb);
-                }
-#else
-#pragma unroll
-                for (int c = 0; c < 16; c++) {
-                    acc[i * 16 + c] = __fmaf_rn(__uint_as_float(pa[c]), sa, acc[i * 16 + c]);
-                    acc[HALF + i * 16 + c] = __fmaf_rn(__uint_as_float(pb[c]), sb, acc[HALF + i * 16 + c]);
-                }
-#endif
+                for (int c = 0; c < 16; c++)
+                    acc[i * 16 + c] = __fmaf_rn(__uint_as_float(p[c]), sc_, acc[i * 16 + c]);
             }
-#endif
             tc_fence_before();
             __syncwarp();
             if (lane == 0)
                 mbar_arrive(&tmem_empty[buf]);
-            w_body += prof_clock() - t_body;
+            t_exit = prof_clock();
+            w_body += t_exit - t_body;
             g_kb++;
             return true;
         };
@@ -116,17 +115,28 @@
         //     by a warp shuffle.
         float wa_next = 0.0f, wb_next = 0.0f;
         if (wide) {
-            float4 cx = __ldg(reinterpret_cast<const float4 *>(xs_row));
             for (int kb = 0; kb < num_kb && ok; kb += 4) {
+                const long long t_g0 = prof_clock();
+                // pinned: the compiler would otherwise sink this load to its first use (it costs four live registers),
+                // and the use would then wait out the whole memory latency once per group.  The last group of a work item
+                // fetches the first group of the next one.
                 float4 nx = cx;
                 if (kb + 4 < num_kb)
-                    nx = __ldg(reinterpret_cast<const float4 *>(xs_row + kb + 4));
+                    nx = ldg_f4_pinned(xs_row + kb + 4);
+                else if (w_next < total_work)
+                    nx = ldg_f4_pinned(scale_row(row0_next));
+                const long long t_g1 = prof_clock();
+                w_gb += t_g1 - t_g0;
                 const float sx[4] = {cx.x, cx.y, cx.z, cx.w};
 #pragma unroll
                 for (int j = 0; j < 4; j++) {
+                    const long long t_s0 = prof_clock();
                     const float a = __shfl_sync(0xffffffffu, wa_cur, kb + j), b = __shfl_sync(0xffffffffu, wb_cur, kb + j);
-                    ok = ok && promote(__fmul_rn(sx[j], a), __fmul_rn(sx[j], b));
+                    const float pa_ = __fmul_rn(sx[j], a), pb_ = __fmul_rn(sx[j], b);
+                    w_gc += prof_clock() - t_s0;
+                    ok = ok && promote(pa_, pb_);
                 }
+                const long long t_e0 = prof_clock();
                 cx = nx;
                 if (kb == 0 && w_next < total_work && lane < num_kb) { // the next work item's table entry has arrived by now
                     const float *a, *b;
@@ -134,6 +144,7 @@
                     wa_next = __ldg(a + lane);
                     wb_next = __ldg(b + lane);
                 }
+                w_gd += prof_clock() - t_e0;
             }
         } else {
             for (int kb = 0; kb < num_kb && ok; kb++) {
@@ -148,13 +159,8 @@
         if (!ok)
             break;
         const long long t_tail = prof_clock();
-#if XS_PF8_DEBUG == 3 || XS_PF8_DEBUG >= 5
-        if (valid && acc[3] == 1.2345f)
-            static_cast<float *>(out)[0] = acc[5] + acc[40];
-        if constexpr (false) {
-#else
+        w_gap += t_tail - t_exit;
         if constexpr (GATE_UP) {
-#endif
             // act = silu(gate) * up for this thread's 32 features; the 1x128 group spans the four warpgroups
             float m = 0.0f;
 #pragma unroll
@@ -196,7 +202,7 @@
                 if (g == 0)
                     sc.act_scale[static_cast<size_t>(row0 + r) * (n_out / 128) + nt] = s;
             }
-        } else if (XS_PF8_DEBUG != 3 && XS_PF8_DEBUG < 5) {
+        } else {
             if (valid) {
                 float *dst = static_cast<float *>(out) + static_cast<size_t>(row0 + r) * n_out + nt * 256 + CPT * g;
 #pragma unroll
@@ -204,16 +210,22 @@
                     *reinterpret_cast<float4 *>(dst + v * 4) = make_float4(acc[v * 4], acc[v * 4 + 1], acc[v * 4 + 2], acc[v * 4 + 3]);
             }
         }
-        w_tail += prof_clock() - t_tail;
+        t_exit = prof_clock();
+        w_tail += t_exit - t_tail;
     }
     if (!ok && lane == 0) {
         *abort_flag = 1;
         atomicOr(status, kStatusWaitTimeout);
     }
-    if (warp == 2 && lane == 0) {
+    if (warp == kPfEpiWarp0 && lane == 0) {
         prof_add(prof, 5, w0);
         prof_add(prof, 2, w_body);
         prof_add(prof, 4, w_tail - w_x); // the tail's own work
         prof_add(prof, 8, w_x);
+        prof_add(prof, 10, w_fence);
+        prof_add(prof, 11, w_gap);
+        prof_add(prof, 12, w_gb);
+        prof_add(prof, 13, w_gc);
+        prof_add(prof, 14, w_gd);
     }
 }

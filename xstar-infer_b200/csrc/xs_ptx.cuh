@@ -144,6 +144,19 @@ __device__ __forceinline__ bool mbar_spin_wait_t(uint64_t *bar, uint32_t parity,
 #endif
 }
 
+// Register budget of the calling warpgroup (four consecutive warps, all of which must execute the same instruction):
+// the light roles of a warp-specialised kernel give registers back so that the register-hungry ones can take them.
+template <int N>
+__device__ __forceinline__ void reg_dealloc()
+{
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
+}
+template <int N>
+__device__ __forceinline__ void reg_alloc()
+{
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N));
+}
+
 // ---- TMA ----------------------------------------------------------------------------------------------
 __device__ __forceinline__ void prefetch_tmap(const CUtensorMap *m)
 {
@@ -172,6 +185,27 @@ __device__ __forceinline__ void tma_load_2d(void *smem_dst, const CUtensorMap *m
         :
         : "r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(m)), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "l"(policy)
         : "memory");
+}
+
+// 16-byte read-only global load that stays where it is written: a volatile asm is not moved across the other volatile
+// asms of a loop body (barrier waits, TMEM loads), so a load placed one iteration ahead of its use is ISSUED there.
+__device__ __forceinline__ float4 ldg_f4_pinned(const float *p)
+{
+    float4 v;
+    asm volatile("ld.global.nc.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p));
+    return v;
+}
+__device__ __forceinline__ float ldg_f32_pinned(const float *p)
+{
+    float v;
+    asm volatile("ld.global.nc.f32 %0, [%1];" : "=f"(v) : "l"(p));
+    return v;
+}
+__device__ __forceinline__ int ldg_s32_pinned(const int32_t *p)
+{
+    int v;
+    asm volatile("ld.global.nc.s32 %0, [%1];" : "=r"(v) : "l"(p));
+    return v;
 }
 
 // ---- tcgen05 ------------------------------------------------------------------------------------------
@@ -267,6 +301,14 @@ __device__ __forceinline__ void tmem_ld_wait_for(uint32_t (&a)[16], uint32_t (&b
                    "+r"(a[10]), "+r"(a[11]), "+r"(a[12]), "+r"(a[13]), "+r"(a[14]), "+r"(a[15]), "+r"(b[0]), "+r"(b[1]), "+r"(b[2]),
                    "+r"(b[3]), "+r"(b[4]), "+r"(b[5]), "+r"(b[6]), "+r"(b[7]), "+r"(b[8]), "+r"(b[9]), "+r"(b[10]), "+r"(b[11]),
                    "+r"(b[12]), "+r"(b[13]), "+r"(b[14]), "+r"(b[15])
+                 :
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait_16(uint32_t (&a)[16])
+{
+    asm volatile("tcgen05.wait::ld.sync.aligned;"
+                 : "+r"(a[0]), "+r"(a[1]), "+r"(a[2]), "+r"(a[3]), "+r"(a[4]), "+r"(a[5]), "+r"(a[6]), "+r"(a[7]), "+r"(a[8]), "+r"(a[9]),
+                   "+r"(a[10]), "+r"(a[11]), "+r"(a[12]), "+r"(a[13]), "+r"(a[14]), "+r"(a[15])
                  :
                  : "memory");
 }

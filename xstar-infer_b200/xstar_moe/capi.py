@@ -44,7 +44,7 @@ EXPORTS = [
     "xs_moe_memcpy_h2d", "xs_moe_memcpy_d2h", "xs_moe_memcpy_d2d", "xs_moe_device_free_bytes",
     "xs_moe_stream_synchronize", "xs_moe_workspace_bytes", "xs_moe_workspace_init", "xs_moe_forward",
     "xs_moe_forward_host", "xs_moe_forward_profile", "xs_moe_route", "xs_moe_topk", "xs_moe_permute", "xs_moe_permute_noalloc", "xs_moe_grouped_mlp_workspace_bytes",
-    "xs_moe_grouped_mlp", "xs_moe_quantize_rows_fp8", "xs_moe_quantize_rows_mxfp8", "xs_moe_gather_rows", "xs_moe_combine", "xs_moe_combine_bf16_rows", "xs_moe_gather_rows_f32_to_bf16", "xs_moe_check_flags", "xs_moe_debug_counters", "xs_moe_probe_mma_rate", "xs_moe_probe_tmem_ld_rate", "xs_moe_launch_count", "xs_moe_plan_info",
+    "xs_moe_grouped_mlp", "xs_moe_quantize_rows_fp8", "xs_moe_quantize_rows_mxfp8", "xs_moe_gather_rows", "xs_moe_combine", "xs_moe_combine_bf16_rows", "xs_moe_gather_rows_f32_to_bf16", "xs_moe_check_flags", "xs_moe_debug_counters", "xs_moe_probe_mma_rate", "xs_moe_probe_tmem_ld_rate", "xs_moe_probe_handoff", "xs_moe_launch_count", "xs_moe_plan_info",
     "xs_moe_ipc_export", "xs_moe_ipc_import", "xs_moe_ipc_close", "xs_moe_ep_plan", "xs_moe_ep_dispatch", "xs_moe_ep_return",
 ]
 
@@ -94,6 +94,7 @@ def lib():
             "xs_moe_check_flags": [vp, vp],
             "xs_moe_probe_mma_rate": [i32, i32, i32, i32, vp, sz, C.POINTER(C.c_double), C.POINTER(C.c_double), C.POINTER(C.c_double), vp],
             "xs_moe_probe_tmem_ld_rate": [i32, i32, i32, i32, vp, sz, C.POINTER(C.c_double), C.POINTER(C.c_double), vp],
+            "xs_moe_probe_handoff": [i32, i32, i32, i32, vp, sz, C.POINTER(C.c_double), vp],
             "xs_moe_debug_counters": [vp, C.POINTER(C.c_ulonglong), vp],
             "xs_moe_launch_count": [C.POINTER(C.c_ulonglong)],
             "xs_moe_plan_info": [cfgp, C.POINTER(i32), C.POINTER(i32)],
