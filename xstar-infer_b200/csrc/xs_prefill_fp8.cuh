@@ -16,10 +16,16 @@
 //
 // Because the accumulator changes hands once per k-block (four MMAs), what the issuing thread does BETWEEN k-blocks is on
 // the tensor pipe's critical path: a thread that issues tcgen05.mma is held until the pipe takes the instruction, so it
-// cannot run ahead, and its two commits, two barrier waits and descriptor set-up for the next k-block (a few hundred cycles
-// of dependent latency) leave the pipe idle every time -- measured, a loop of nothing but these steps ran at 1150 cycles
-// per k-block against 630 for its four MMAs.  So TWO warps issue, taking k-blocks alternately (each owns one of the two
-// accumulator buffers): while one is held by its MMAs the other gets through its waits and queues the next k-block.
+// cannot run ahead, and its commits, barrier waits and descriptor set-up for the next k-block leave the pipe idle every
+// time.  Measured with the hand-over probe (xs_moe_probe_handoff: this protocol and nothing else): one issuing thread
+// 810-880 cycles per k-block, TWO warps issuing alternate k-blocks (each owns one of the two accumulator buffers) 510-580,
+// the rate of the four MMAs themselves.  So two warps issue.
+//
+// What bounds the kernel after that (gate/up launch of the 8192-token layer, 2048 k-blocks per CTA; each line removes one
+// thing from the kernel and times it): protocol + MMAs alone 0.77 ms; + the promotion FMAs 0.94; + the operand loads
+// 1.18 without / 1.31 with the FMAs (48 KB per k-block per SM: 12 TB/s out of L2, the floor of this tile shape); + the
+// per-tile tail (SwiGLU, re-quantisation, stores; the accumulator registers are busy, so the next tile's k-loop stops
+// after two k-blocks) 1.78 ms.
 //
 // Warps: 0 TMA producer | 1, 2 MMA issuers (1 owns TMEM) | 3 idle | 4..19 epilogue (group = (warp - 4) / 4, lane quarter =
 // warp % 4).  Warps 0..3 hand most of their registers to the epilogue warpgroups (setmaxnreg), whose 64 accumulators + TMEM

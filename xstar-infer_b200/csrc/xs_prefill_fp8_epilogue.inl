@@ -9,8 +9,6 @@
     const int kbs = K / kBlockK8;
     bool ok = true;
     uint32_t g_kb = 0, it = 0;
-    long long w_fence = 0, w_gap = 0, t_exit = prof_clock();
-    long long w_ga = 0, w_gb = 0, w_gc = 0, w_gd = 0;
     long long w_body = 0, w_tail = 0, w_x = 0; // role profile: cycles in the promotion bodies / per-tile tails / amax exchange waits
     // scale rows of a work item: gate/up -> gate block nt and up block nt; down -> the 128-column block this group's columns
     // fall into (twice)
@@ -75,14 +73,10 @@
         // combined scales, hand the TMEM buffer back.
         auto promote = [&](float sa, float sb) -> bool {
             const uint32_t buf = g_kb % kPfIssuers;
-            const long long t_in = prof_clock();
-            w_gap += t_in - t_exit;
             if (!mbar_wait_t(&tmem_full[buf], (g_kb / kPfIssuers) & 1u, abort_flag, w0))
                 return false;
-            const long long t_f = prof_clock();
             tc_fence_after();
             const long long t_body = prof_clock();
-            w_fence += t_body - t_f;
             const uint32_t t0 = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * kPfCols;
             // sixteen columns at a time: the register budget leaves room for one staging block beside the 64 accumulators
 #pragma unroll
@@ -100,8 +94,7 @@
             __syncwarp();
             if (lane == 0)
                 mbar_arrive(&tmem_empty[buf]);
-            t_exit = prof_clock();
-            w_body += t_exit - t_body;
+            w_body += prof_clock() - t_body;
             g_kb++;
             return true;
         };
@@ -116,7 +109,6 @@
         float wa_next = 0.0f, wb_next = 0.0f;
         if (wide) {
             for (int kb = 0; kb < num_kb && ok; kb += 4) {
-                const long long t_g0 = prof_clock();
                 // pinned: the compiler would otherwise sink this load to its first use (it costs four live registers),
                 // and the use would then wait out the whole memory latency once per group.  The last group of a work item
                 // fetches the first group of the next one.
@@ -125,18 +117,12 @@
                     nx = ldg_f4_pinned(xs_row + kb + 4);
                 else if (w_next < total_work)
                     nx = ldg_f4_pinned(scale_row(row0_next));
-                const long long t_g1 = prof_clock();
-                w_gb += t_g1 - t_g0;
                 const float sx[4] = {cx.x, cx.y, cx.z, cx.w};
 #pragma unroll
                 for (int j = 0; j < 4; j++) {
-                    const long long t_s0 = prof_clock();
                     const float a = __shfl_sync(0xffffffffu, wa_cur, kb + j), b = __shfl_sync(0xffffffffu, wb_cur, kb + j);
-                    const float pa_ = __fmul_rn(sx[j], a), pb_ = __fmul_rn(sx[j], b);
-                    w_gc += prof_clock() - t_s0;
-                    ok = ok && promote(pa_, pb_);
+                    ok = ok && promote(__fmul_rn(sx[j], a), __fmul_rn(sx[j], b));
                 }
-                const long long t_e0 = prof_clock();
                 cx = nx;
                 if (kb == 0 && w_next < total_work && lane < num_kb) { // the next work item's table entry has arrived by now
                     const float *a, *b;
@@ -144,7 +130,6 @@
                     wa_next = __ldg(a + lane);
                     wb_next = __ldg(b + lane);
                 }
-                w_gd += prof_clock() - t_e0;
             }
         } else {
             for (int kb = 0; kb < num_kb && ok; kb++) {
@@ -159,13 +144,12 @@
         if (!ok)
             break;
         const long long t_tail = prof_clock();
-        w_gap += t_tail - t_exit;
         if constexpr (GATE_UP) {
             // act = silu(gate) * up for this thread's 32 features; the 1x128 group spans the four warpgroups
             float m = 0.0f;
 #pragma unroll
             for (int c = 0; c < HALF; c++) {
-                acc[c] = silu_fast(acc[c]) * acc[HALF + c];
+                acc[c] = __fdividef(acc[c], 1.0f + __expf(-acc[c])) * acc[HALF + c]; // SiLU with the approximate reciprocal
                 m = fmaxf(m, fabsf(acc[c]));
             }
             float *ax = amax_x + (it & 1) * (kPfGroups * 128);
@@ -203,15 +187,61 @@
                     sc.act_scale[static_cast<size_t>(row0 + r) * (n_out / 128) + nt] = s;
             }
         } else {
-            if (valid) {
-                float *dst = static_cast<float *>(out) + static_cast<size_t>(row0 + r) * n_out + nt * 256 + CPT * g;
+            // This thread holds 64 consecutive f32 columns of ONE row, so a plain 16-byte store per lane would touch 32
+            // rows per instruction (32 separate lines for the store path to walk).  The four lanes of a quad first
+            // transpose 4 x 4 blocks of 16-byte chunks among themselves: afterwards lane q of quad a holds chunks q, q + 4,
+            // q + 8, q + 12 of each of the quad's four rows, and one store instruction writes 64 contiguous bytes per quad,
+            // 8 rows instead of 32.
+            const int qd = lane & 3;
+            float4 ch[16];
 #pragma unroll
-                for (int v = 0; v < CPT / 4; v++)
-                    *reinterpret_cast<float4 *>(dst + v * 4) = make_float4(acc[v * 4], acc[v * 4 + 1], acc[v * 4 + 2], acc[v * 4 + 3]);
+            for (int v = 0; v < 16; v++)
+                ch[v] = make_float4(acc[v * 4], acc[v * 4 + 1], acc[v * 4 + 2], acc[v * 4 + 3]);
+            auto shfl4 = [](const float4 &v, int m) {
+                return make_float4(__shfl_xor_sync(0xffffffffu, v.x, m), __shfl_xor_sync(0xffffffffu, v.y, m),
+                                   __shfl_xor_sync(0xffffffffu, v.z, m), __shfl_xor_sync(0xffffffffu, v.w, m));
+            };
+#pragma unroll
+            for (int m = 0; m < 4; m++) {
+                float4 *b = ch + 4 * m; // b[j] = chunk 4m + j of my row; transpose b across the quad
+                // round 1: lanes l and l ^ 1 swap the off-diagonal elements of each 2 x 2 block
+                {
+                    const bool odd = qd & 1;
+                    const float4 s0 = shfl4(odd ? b[0] : b[1], 1), s1 = shfl4(odd ? b[2] : b[3], 1);
+                    if (odd) {
+                        b[0] = s0;
+                        b[2] = s1;
+                    } else {
+                        b[1] = s0;
+                        b[3] = s1;
+                    }
+                }
+                // round 2: lanes l and l ^ 2 swap the off-diagonal 2 x 2 blocks
+                {
+                    const bool hi = qd & 2;
+                    const float4 s0 = shfl4(hi ? b[0] : b[2], 2), s1 = shfl4(hi ? b[1] : b[3], 2);
+                    if (hi) {
+                        b[0] = s0;
+                        b[1] = s1;
+                    } else {
+                        b[2] = s0;
+                        b[3] = s1;
+                    }
+                }
+                // now b[i] = chunk 4m + qd of row (lane & ~3) + i of this warp's 32 rows
+            }
+            const int rq = q * 32 + (lane & ~3); // first row of the quad within the tile
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                if (rq + i < nvalid) {
+                    float *dst = static_cast<float *>(out) + static_cast<size_t>(row0 + rq + i) * n_out + nt * 256 + CPT * g;
+#pragma unroll
+                    for (int m = 0; m < 4; m++)
+                        *reinterpret_cast<float4 *>(dst + (4 * m + qd) * 4) = ch[4 * m + i];
+                }
             }
         }
-        t_exit = prof_clock();
-        w_tail += t_exit - t_tail;
+        w_tail += prof_clock() - t_tail;
     }
     if (!ok && lane == 0) {
         *abort_flag = 1;
@@ -222,10 +252,5 @@
         prof_add(prof, 2, w_body);
         prof_add(prof, 4, w_tail - w_x); // the tail's own work
         prof_add(prof, 8, w_x);
-        prof_add(prof, 10, w_fence);
-        prof_add(prof, 11, w_gap);
-        prof_add(prof, 12, w_gb);
-        prof_add(prof, 13, w_gc);
-        prof_add(prof, 14, w_gd);
     }
 }

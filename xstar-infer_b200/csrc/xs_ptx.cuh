@@ -131,18 +131,6 @@ __device__ __forceinline__ bool mbar_wait_t(uint64_t *bar, uint32_t parity, vola
     return mbar_wait(bar, parity, abort_flag);
 #endif
 }
-__device__ __forceinline__ bool mbar_spin_wait_t(uint64_t *bar, uint32_t parity, volatile uint32_t *abort_flag, long long &acc)
-{
-#if XS_ROLE_PROFILE
-    const long long t0 = clock64();
-    const bool ok = mbar_spin_wait(bar, parity, abort_flag);
-    acc += clock64() - t0;
-    return ok;
-#else
-    (void)acc;
-    return mbar_spin_wait(bar, parity, abort_flag);
-#endif
-}
 
 // Register budget of the calling warpgroup (four consecutive warps, all of which must execute the same instruction):
 // the light roles of a warp-specialised kernel give registers back so that the register-hungry ones can take them.
