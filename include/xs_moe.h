@@ -136,7 +136,10 @@ int xs_moe_forward_host(const XsMoeConfig *cfg, const XsMoeWeights *w, const voi
  * gemm_cpu, xstar_cpp/include/ops/gemm.h:57-83; linear's x*W^T, xstar_cpp/src/ops/linear.cpp:20-31);
  * key = logit + bias (a NaN key orders as -inf); the k largest keys, ties to the lower id; slots in ascending expert id;
  * weights = max-shifted softmax over the selected unbiased logits (xstar_cpp/src/ops/softmax.cpp:56-93).
- * logits_dev may be NULL when the caller does not want them (scratch is then taken from the workspace). */
+ * logits_dev may be NULL when the caller does not want them (scratch is then taken from the workspace); batches of more
+ * than 256 tokens then take a two-step router -- approximate logits on the tensor core, exact ascending-k recomputation of
+ * every logit the selection can depend on (the chosen experts and all within a proven error bound of the k / k+1 boundary)
+ * -- whose ids and weights are the same as those of the all-exact path. */
 int xs_moe_route(const XsMoeConfig *cfg, const void *x_dev, const void *router_w_dev, const float *router_bias_dev,
                  float *logits_dev, int32_t *topk_ids_dev, float *topk_w_dev, void *workspace_dev,
                  size_t workspace_bytes, void *stream);

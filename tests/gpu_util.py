@@ -49,6 +49,22 @@ def route(dims, d):
     return logits, ids, w
 
 
+def route_selected(dims, d):
+    """xs_moe_route without asking for the logits: large batches take the tensor-core filter + exact refine router.
+    Returns ids, w and the refine counters (tokens recomputed in full, exact logits computed)."""
+    cfg = cfg_of(dims, T=d["x"].shape[0])
+    T, K = cfg.num_tokens, cfg.top_k
+    ws = new_workspace(cfg)
+    ids = torch.empty((T, K), dtype=torch.int32, device="cuda")
+    w = torch.empty((T, K), dtype=torch.float32, device="cuda")
+    L = capi.lib()
+    capi.check(L.xs_moe_route(C.byref(cfg), capi.ptr(d["x"]), capi.ptr(d["router_w"]), capi.ptr(d.get("router_bias")), None,
+                              capi.ptr(ids), capi.ptr(w), capi.ptr(ws), ws.numel(), stream_ptr()))
+    capi.check(L.xs_moe_check_flags(capi.ptr(ws), stream_ptr()))
+    counters = ws[200:216].view(torch.int64).cpu().tolist()
+    return ids, w, counters
+
+
 def permute(dims, ids):
     T, K = ids.shape
     cfg = cfg_of(dims, T=T)

@@ -71,6 +71,62 @@ def test_route_ties_and_bias(oracle):
     assert np.allclose(w.cpu().numpy(), ref_w, atol=1e-6, rtol=0)
 
 
+# ---- large batches: tensor-core filter + exact refine must give the all-exact router's ids and weights ----------------
+def _oracle_route(oracle, x, rw, bias, K):
+    xf, rwf = x.float().cpu().numpy(), rw.float().cpu().numpy()
+    ref_logits = np.zeros((x.shape[0], rw.shape[0]), np.float32)
+    oracle.lib().xso_router_logits(C.c_void_p(xf.ctypes.data), C.c_void_p(rwf.ctypes.data), C.c_void_p(ref_logits.ctypes.data),
+                                   x.shape[0], x.shape[1], rw.shape[0])
+    return oracle.topk(ref_logits, None if bias is None else bias.cpu().numpy(), K)
+
+
+@pytest.mark.parametrize("T,H,E,K,bias", [(8192, 4096, 256, 6, "zipf"), (2048, 4096, 256, 6, None), (300, 512, 40, 4, None),
+                                          (700, 256, 512, 8, "zipf"), (257, 1024, 16, 2, None)])
+def test_route_filtered_equals_exact(oracle, T, H, E, K, bias):
+    dims = _dims(T=T, H=H, E=E, K=K)
+    g = torch.Generator(device="cuda").manual_seed(T + E)
+    x = torch.randn((T, H), generator=g, device="cuda").to(torch.bfloat16)
+    rw = (torch.randn((E, H), generator=g, device="cuda") * 0.02).to(torch.bfloat16)
+    b = synth.zipf_bias(E, 5).cuda() if bias == "zipf" else None
+    ids, w, counters = gu.route_selected(dims, dict(x=x, router_w=rw, router_bias=b))
+    ref_ids, ref_w = _oracle_route(oracle, x, rw, b, K)
+    assert np.array_equal(ids.cpu().numpy(), ref_ids), "filtered router chose other experts than the exact one"
+    assert np.allclose(w.cpu().numpy(), ref_w, atol=1e-6, rtol=0)
+    print(f"T={T} E={E}: tokens recomputed in full {counters[0]}, exact logits per token {counters[1] / T:.1f}")
+    assert counters[1] >= T * K and counters[0] < T // 10 + 1
+
+
+@pytest.mark.parametrize("cluster", [12, 40])
+def test_route_filtered_near_ties_at_the_boundary(oracle, cluster):
+    """Dozens of experts whose keys sit within 1e-4 .. 0 of one another, exact ties included, pushed to the top by a bias
+    so that the k / k+1 boundary falls inside the cluster: the choice hangs on the last bits of the exact ascending-k sums
+    (a cluster of 40 exceeds the 32 candidates of the per-lane recomputation and takes the full exact path)."""
+    T, H, E, K = 320, 1024, 64, 6
+    dims = _dims(T=T, H=H, E=E, K=K)
+    g = torch.Generator(device="cuda").manual_seed(91 + cluster)
+    x = torch.randn((T, H), generator=g, device="cuda").to(torch.bfloat16)
+    rw = (torch.randn((E, H), generator=g, device="cuda") * 0.02).to(torch.bfloat16)
+    base = rw[3].clone()
+    members = list(range(5, 5 + cluster))
+    for j, e in enumerate(members):
+        row = base.clone()
+        if j % 3:  # every third member is an exact copy (exact ties); the others differ by one bf16 ulp in one element
+            v = row[j].view(torch.int16)
+            row[j] = (v + 1).view(torch.bfloat16)
+        rw[e] = row
+    bias = torch.zeros(E, device="cuda")
+    bias[members] = 9.0
+    ids, w, counters = gu.route_selected(dims, dict(x=x, router_w=rw, router_bias=bias))
+    ref_ids, ref_w = _oracle_route(oracle, x, rw, bias, K)
+    assert np.array_equal(ids.cpu().numpy(), ref_ids)
+    assert np.allclose(w.cpu().numpy(), ref_w, atol=1e-6, rtol=0)
+    assert set(ref_ids.flatten().tolist()) <= set(members)
+    if cluster > 32:
+        assert counters[0] == T, "every token should have taken the full exact path"
+    else:
+        assert counters[0] == 0 and counters[1] >= T * cluster
+
+
 # ---- permutation: bit-exact -----------------------------------------------------------------------------------
 @pytest.mark.parametrize("T,E,K", [(1, 8, 2), (64, 16, 2), (300, 256, 6), (1000, 64, 8), (4096, 256, 6)])
 def test_permute_bit_exact(oracle, T, E, K):

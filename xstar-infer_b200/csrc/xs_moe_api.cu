@@ -22,6 +22,7 @@
 #include "xs_mma_rate.cuh"
 #include "xs_permute.cuh"
 #include "xs_route.cuh"
+#include "xs_route_tc.cuh"
 #include "xs_ep.cuh"
 
 namespace {
@@ -212,10 +213,11 @@ GroupedPlan plan_grouped(int max_rows, int routed_rows, int routed_groups, int s
 }
 
 constexpr size_t kStatusBytes = 256;
+constexpr int kRouterFilterTokens = 256; // larger batches may take the tensor-core filter + exact refine router
 
 struct ForwardPlan {
     int chunks = 0;
-    size_t off_logits = 0, off_ids = 0, off_w = 0, off_counts = 0, off_offsets = 0, off_perm = 0, off_inv = 0;
+    size_t off_logits = 0, off_cand = 0, off_cand_meta = 0, off_ids = 0, off_w = 0, off_counts = 0, off_offsets = 0, off_perm = 0, off_inv = 0;
     size_t off_chunk_counts = 0, off_chunk_base = 0, off_rows = 0, off_rows_scale = 0, off_y = 0, off_grouped = 0;
     size_t off_sh_rows = 0, off_sh_scale = 0, off_sh_offsets = 0, off_sh_grouped = 0; // FP4: the FP8 always-on expert runs on its own
     GroupedPlan grouped, sh_grouped;
@@ -238,6 +240,8 @@ ForwardPlan plan_forward(const XsMoeConfig *c)
     const bool fp8 = c->routed_format == XS_MOE_FP8_BLOCK128, fp4 = c->routed_format == XS_MOE_FP4_MX32;
     const size_t Sm = fp4 ? 0 : S; // rows of the always-on expert merged behind the routed rows
     p.off_logits = take(T * E * 4);
+    p.off_cand = take(T > kRouterFilterTokens ? T * 32 * 4 : 0);      // filter + refine router: experts to recompute exactly
+    p.off_cand_meta = take(T > kRouterFilterTokens ? T * 2 * 4 : 0);  // ... their count and the token's error bound
     p.off_ids = take(T * K * 4);
     p.off_w = take(T * K * 4);
     p.off_counts = take(E * 4);
@@ -278,11 +282,82 @@ int check_workspace(const void *ws, size_t have, size_t need)
 // ---- launches --------------------------------------------------------------------------------------------
 constexpr int kRouterSmallTokens = 64;
 
-int launch_logits(const XsMoeConfig *c, const void *x, const void *rw, float *logits, cudaStream_t st)
+constexpr size_t kOffWnorm = 192;        // status block: f32 max router-row norm
+constexpr size_t kOffRefineCounters = 200; // status block: two u64 (tokens recomputed in full, exact logits computed)
+
+// Filter + refine (xs_route_tc.cuh): approximate logits on the tensor core, exact recomputation of everything the
+// selection can depend on.  `status_block` is the head of the caller's workspace.
+int launch_logits_filtered(const XsMoeConfig *c, const void *x, const void *rw, const float *bias, float *logits, uint8_t *status_block,
+                           int32_t *cand, int32_t *cand_meta, cudaStream_t st)
+{
+    const int T = c->num_tokens, H = c->hidden, E = c->num_experts, K = c->top_k;
+    DeviceInfo di;
+    if (int rc = device_info(&di))
+        return rc;
+    const int n = E >= xs::kRtMaxN ? xs::kRtMaxN : (E + 15) / 16 * 16;
+    const int stage_bytes = xs::rt_stage_bytes(n);
+    int stages = (di.max_smem - 1024 - 256) / stage_bytes;
+    if (stages > 6)
+        stages = 6;
+    if (stages < 2)
+        return fail(XS_MOE_ERR_DEVICE, "not enough shared memory for the router pipeline");
+    const int smem = stages * stage_bytes + 1024 + 256;
+    static bool configured[64] = {};
+    int dev = 0;
+    XS_CUDA(cudaGetDevice(&dev));
+    if (dev >= 64 || !configured[dev]) {
+        XS_CUDA(cudaFuncSetAttribute(xs::router_logits_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, di.max_smem));
+        XS_CUDA(cudaFuncSetAttribute(xs::router_exact_slices_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, xs::kRxSmemBytes));
+        if (dev < 64)
+            configured[dev] = true;
+    }
+    CUtensorMap t_x, t_w;
+    if (int rc = make_tmap_2d(&t_x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, x, T, H, xs::kRtTokens, xs::kBlockK))
+        return rc;
+    if (int rc = make_tmap_2d(&t_w, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, rw, E, H, n, xs::kBlockK))
+        return rc;
+    int32_t *status = reinterpret_cast<int32_t *>(status_block);
+    float *wnorm = reinterpret_cast<float *>(status_block + kOffWnorm);
+    unsigned long long *counters = reinterpret_cast<unsigned long long *>(status_block + kOffRefineCounters);
+    const __nv_bfloat16 *xb = static_cast<const __nv_bfloat16 *>(x), *rwb = static_cast<const __nv_bfloat16 *>(rw);
+    XS_CUDA(cudaMemsetAsync(wnorm, 0, sizeof(float), st));
+    xs::router_wnorm_kernel<<<(E + 7) / 8, 256, 0, st>>>(rwb, E, H, wnorm);
+    note_launch();
+    dim3 grid((T + xs::kRtTokens - 1) / xs::kRtTokens, (E + xs::kRtMaxN - 1) / xs::kRtMaxN);
+    xs::router_logits_tc_kernel<<<grid, xs::kRtThreads, smem, st>>>(t_x, t_w, logits, T, H, E, n, status, stages);
+    note_launch();
+    const int blocks = (T + xs::kRcWarps - 1) / xs::kRcWarps;
+    const float coeff = xs::router_delta_coeff(H);
+    if (E <= 32)
+        xs::router_candidates_kernel<1><<<blocks, xs::kRcWarps * 32, 0, st>>>(xb, bias, logits, wnorm, cand, cand_meta, T, H, E, K, coeff);
+    else if (E <= 256)
+        xs::router_candidates_kernel<8><<<blocks, xs::kRcWarps * 32, 0, st>>>(xb, bias, logits, wnorm, cand, cand_meta, T, H, E, K, coeff);
+    else
+        xs::router_candidates_kernel<32><<<blocks, xs::kRcWarps * 32, 0, st>>>(xb, bias, logits, wnorm, cand, cand_meta, T, H, E, K, coeff);
+    note_launch();
+    if (E <= xs::kRxMaxExperts)
+        xs::router_exact_slices_kernel<<<(T + xs::kRxTokens - 1) / xs::kRxTokens, xs::kRxThreads, xs::kRxSmemBytes, st>>>(
+            xb, rwb, logits, cand, cand_meta, T, H, E, counters);
+    else
+        xs::router_exact_rows_kernel<<<T, 32, xs::kReSmemBytes, st>>>(xb, rwb, logits, cand, cand_meta, T, H, E, counters, status);
+    note_launch();
+    XS_CUDA(cudaGetLastError());
+    return 0;
+}
+
+// filter_ws: head of a workspace (status block) if the caller only needs what the SELECTION reads to be exact -- large
+// batches then take the tensor-core filter + exact refine path; null: every logit exact (the CUDA-core kernels).
+int launch_logits(const XsMoeConfig *c, const void *x, const void *rw, float *logits, cudaStream_t st, const float *bias = nullptr,
+                  uint8_t *filter_ws = nullptr)
 {
     const int T = c->num_tokens, H = c->hidden, E = c->num_experts;
     if (T == 0)
         return 0;
+    if (filter_ws && T > kRouterFilterTokens && (reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(rw)) % 16 == 0) {
+        const ForwardPlan p = plan_forward(c);
+        return launch_logits_filtered(c, x, rw, bias, logits, filter_ws, reinterpret_cast<int32_t *>(filter_ws + p.off_cand),
+                                      reinterpret_cast<int32_t *>(filter_ws + p.off_cand_meta), st);
+    }
     const __nv_bfloat16 *xb = static_cast<const __nv_bfloat16 *>(x), *rwb = static_cast<const __nv_bfloat16 *>(rw);
     if (T <= kRouterSmallTokens) {
         // a few tokens per SM at most: one warp per block, lane = expert, one token per block (measured faster than the
@@ -354,9 +429,9 @@ int launch_topk(const XsMoeConfig *c, const float *logits, const float *bias, in
 }
 
 int launch_route(const XsMoeConfig *c, const void *x, const void *rw, const float *bias, float *logits, int32_t *ids, float *w,
-                 cudaStream_t st)
+                 cudaStream_t st, uint8_t *filter_ws = nullptr)
 {
-    if (int rc = launch_logits(c, x, rw, logits, st))
+    if (int rc = launch_logits(c, x, rw, logits, st, bias, filter_ws))
         return rc;
     return launch_topk(c, logits, bias, ids, w, st);
 }
@@ -925,13 +1000,15 @@ int xs_moe_route(const XsMoeConfig *cfg, const void *x, const void *rw, const fl
         return rc;
     if (!x || !rw || !ids || !w)
         return fail(XS_MOE_ERR_INVALID_ARG, "null tensor pointer");
+    uint8_t *filter_ws = nullptr;
     if (!logits) {
         ForwardPlan p = plan_forward(cfg);
-        if (int rc = check_workspace(ws, ws_bytes, p.off_logits + static_cast<size_t>(cfg->num_tokens) * cfg->num_experts * 4))
+        if (int rc = check_workspace(ws, ws_bytes, p.off_ids))
             return rc;
         logits = reinterpret_cast<float *>(static_cast<uint8_t *>(ws) + p.off_logits);
+        filter_ws = static_cast<uint8_t *>(ws); // nobody reads the logits: only what the selection depends on has to be exact
     }
-    return launch_route(cfg, x, rw, bias, logits, ids, w, static_cast<cudaStream_t>(stream));
+    return launch_route(cfg, x, rw, bias, logits, ids, w, static_cast<cudaStream_t>(stream), filter_ws);
 }
 
 int xs_moe_topk(const XsMoeConfig *cfg, const float *logits, const float *bias, int32_t *ids, float *w, void *stream)
@@ -1157,7 +1234,7 @@ static int forward_impl(const XsMoeConfig *cfg, const XsMoeWeights *w, const voi
     uint8_t *gscratch = b + p.off_grouped;
 
     XS_MARK(0);
-    if (int rc = launch_logits(cfg, x, w->router_w_dev, logits, st))
+    if (int rc = launch_logits(cfg, x, w->router_w_dev, logits, st, w->router_bias_dev, b))
         return rc;
     XS_MARK(1);
     bool tiles_ready = false;
