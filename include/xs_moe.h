@@ -116,6 +116,16 @@ int xs_moe_workspace_init(void *workspace_dev, size_t workspace_bytes, void *str
 int xs_moe_forward(const XsMoeConfig *cfg, const XsMoeWeights *w, const void *x_dev, void *out_dev,
                    void *workspace_dev, size_t workspace_bytes, void *stream);
 
+/* The block's feed-forward half, out = x + MoE(rmsnorm(x, norm_weight, eps)): the expression the reference's block ends with
+ * (xstar_cpp/src/ops/transformer_block.cpp:353, `add(attention_x, mlp(rmsnorm(attention_x, ln2_w, eps), ...))`) with the MoE
+ * layer in mlp's place.  x (T,H) bf16 is the block's residual stream; norm_weight (H) bf16.  The normalised rows are written
+ * once (the router's tensor-core pass and the row scatter both read them) with the arithmetic of the reference's rmsnorm
+ * (xstar_cpp/src/ops/rmsnorm.cpp:52-72, sum of squares in ascending order: bit-identical); the residual add is fused into the
+ * combine kernel with add's two roundings (xstar_cpp/src/ops/add.cpp:27-49).  Workspace: xs_moe_block_workspace_bytes. */
+int xs_moe_block_workspace_bytes(const XsMoeConfig *cfg, size_t *bytes);
+int xs_moe_block_forward(const XsMoeConfig *cfg, const XsMoeWeights *w, const void *x_dev, const void *norm_weight_dev, float eps,
+                         void *out_dev, void *workspace_dev, size_t workspace_bytes, void *stream);
+
 /* xs_moe_forward with CUDA events recorded between its stages on `stream`; synchronises and returns SIX stage
  * times in milliseconds: router logits, selection + permutation + tile table, row scatter (+ activation
  * quantisation for FP8), gate/up GEMM, down GEMM, combine.  The always-on expert runs inside the two GEMM
@@ -189,6 +199,11 @@ int xs_moe_grouped_mlp_workspace_bytes(const XsMoeConfig *cfg, int32_t max_rows,
 int xs_moe_grouped_mlp(const XsMoeConfig *cfg, const XsMoeWeights *w, const void *rows_dev,
                        const float *row_scales_dev, const int32_t *offsets_dev, int32_t max_rows, float *y_dev,
                        void *workspace_dev, size_t workspace_bytes, void *stream);
+
+/* out(rows, hidden) bf16 = rmsnorm(x, weight, eps) with the reference's arithmetic (rmsnorm_launch,
+ * xstar_cpp/include/ops/rmsnorm.h:46-52; CPU loop xstar_cpp/src/ops/rmsnorm.cpp:52-72): f32 sum of squares in ascending column
+ * order, inv = 1 / sqrt(sum / hidden + eps), out[j] = bf16(bf16(x[j] * inv) * weight[j]).  Bit-identical to the CPU op. */
+int xs_moe_rmsnorm(const void *x_dev, const void *weight_dev, void *out_dev, int32_t rows, int32_t hidden, float eps, void *stream);
 
 /* Activation quantisation for FP8 experts: x (rows, cols) bf16 -> e4m3 codes (rows, cols) and one f32 scale
  * per (row, 128 columns): s = max(amax, 1e-10) / 448, code = e4m3_rne_saturating(x / s).  No counterpart in

@@ -481,6 +481,31 @@ int xso_expert_mlp(int mode, const void *x, const void *gate_up_w, const void *d
     return 0;
 }
 
+/* xstar_cpp/src/ops/rmsnorm.cpp:52-72 */
+void xso_rmsnorm_bf16(const uint16_t *x, const uint16_t *w, uint16_t *out, int rows, int H, float eps)
+{
+    for (int r = 0; r < rows; r++) {
+        const uint16_t *xr = x + (size_t)r * H;
+        float rms = 0;
+        for (int j = 0; j < H; j++) {
+            float v = xso_bf16_to_f32(xr[j]);
+            rms += v * v;
+        }
+        float inv_rms = 1.0f / sqrtf(rms / (float)H + eps);
+        for (int j = 0; j < H; j++) {
+            float n = xso_bf16_to_f32(xso_f32_to_bf16(xso_bf16_to_f32(xr[j]) * inv_rms));
+            out[(size_t)r * H + j] = xso_f32_to_bf16(n * xso_bf16_to_f32(w[j]));
+        }
+    }
+}
+
+/* xstar_cpp/src/ops/add.cpp:40-49 */
+void xso_add_bf16(const uint16_t *a, const uint16_t *b, uint16_t *out, size_t n)
+{
+    for (size_t i = 0; i < n; i++)
+        out[i] = xso_f32_to_bf16(xso_bf16_to_f32(a[i]) + xso_bf16_to_f32(b[i]));
+}
+
 /* ------------------------------------------------------------------------------------------------ */
 /* whole layer                                                                                       */
 /* ------------------------------------------------------------------------------------------------ */

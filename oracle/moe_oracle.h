@@ -127,6 +127,13 @@ int xso_moe_forward(const XsOracleArgs *a);
 int xso_expert_mlp(int mode, const void *x, const void *gate_up_w, const void *down_w, float *y,
                    int rows, int H, int I);
 
+/* The two ops around the layer in the engine's block, `add(x, mlp(rmsnorm(x, w, eps), ...))`
+ * (xstar_cpp/src/ops/transformer_block.cpp:353), on bf16 storage (uint16 bits):
+ * rmsnorm as xstar_cpp/src/ops/rmsnorm.cpp:52-72 (f32 sum of squares in ascending order, 1 / sqrt(sum / H + eps),
+ * out = bf16(bf16(x * inv) * w)); add as xstar_cpp/src/ops/add.cpp:40-49 (f32 add, one rounding). */
+void xso_rmsnorm_bf16(const uint16_t *x, const uint16_t *w, uint16_t *out, int rows, int H, float eps);
+void xso_add_bf16(const uint16_t *a, const uint16_t *b, uint16_t *out, size_t n);
+
 #ifdef __cplusplus
 }
 #endif

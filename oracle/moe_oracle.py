@@ -225,6 +225,56 @@ def expert_mlp(mode, x, gate_up_w, down_w):
     return y
 
 
+def rmsnorm_bf16(x_bits, w_bits, eps):
+    """bf16 storage (uint16) in and out; the oracle's restatement of the reference's rmsnorm."""
+    x_bits, w_bits = _c(x_bits, np.uint16), _c(w_bits, np.uint16)
+    rows, H = x_bits.shape
+    out = np.zeros((rows, H), np.uint16)
+    L = lib()
+    L.xso_rmsnorm_bf16.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_float]
+    L.xso_rmsnorm_bf16.restype = None
+    L.xso_rmsnorm_bf16(_p(x_bits), _p(w_bits), _p(out), rows, H, C.c_float(eps))
+    return out
+
+
+def add_bf16(a_bits, b_bits):
+    a_bits, b_bits = _c(a_bits, np.uint16), _c(b_bits, np.uint16)
+    out = np.zeros(a_bits.shape, np.uint16)
+    L = lib()
+    L.xso_add_bf16.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t]
+    L.xso_add_bf16.restype = None
+    L.xso_add_bf16(_p(a_bits), _p(b_bits), _p(out), a_bits.size)
+    return out
+
+
+def ref_rmsnorm_bf16(x_bits, w_bits, eps):
+    """The reference's own rmsnorm (compiled in place); None if the reference library is absent."""
+    r = ref_lib()
+    if r is None or not hasattr(r, "xsref_rmsnorm_bf16"):
+        return None
+    x_bits, w_bits = _c(x_bits, np.uint16), _c(w_bits, np.uint16)
+    rows, H = x_bits.shape
+    out = np.zeros((rows, H), np.uint16)
+    r.xsref_rmsnorm_bf16.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_float]
+    r.xsref_rmsnorm_bf16.restype = C.c_int
+    if r.xsref_rmsnorm_bf16(_p(x_bits), _p(w_bits), _p(out), rows, H, C.c_float(eps)) != 0:
+        raise RuntimeError("reference rmsnorm failed")
+    return out
+
+
+def ref_add_bf16(a_bits, b_bits):
+    r = ref_lib()
+    if r is None or not hasattr(r, "xsref_add_bf16"):
+        return None
+    a_bits, b_bits = _c(a_bits, np.uint16), _c(b_bits, np.uint16)
+    out = np.zeros(a_bits.shape, np.uint16)
+    r.xsref_add_bf16.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_longlong]
+    r.xsref_add_bf16.restype = C.c_int
+    if r.xsref_add_bf16(_p(a_bits), _p(b_bits), _p(out), a_bits.size) != 0:
+        raise RuntimeError("reference add failed")
+    return out
+
+
 def ref_router_logits(x_f32, router_w_f32):
     r = ref_lib()
     T, H = x_f32.shape

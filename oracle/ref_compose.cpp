@@ -10,6 +10,7 @@
  *
  * The reference sources are compiled where they lie (see the Makefile); nothing is copied.
  * Used (a) to pin moe_oracle.c bit-for-bit and (b) as the timed "reference" CPU baseline.
+ * Also exposes the two ops around the layer in the block, rmsnorm and add (xstar_cpp/src/ops/transformer_block.cpp:353).
  */
 #include <atomic>
 #include <cstdint>
@@ -20,7 +21,9 @@
 #include "bfloat16.h"
 #include "ops/embedding.h"
 #include "ops/linear.h"
+#include "ops/add.h"
 #include "ops/mlp.h"
+#include "ops/rmsnorm.h"
 #include "tensor.h"
 
 namespace {
@@ -149,6 +152,34 @@ int xsref_moe_experts_combine(int bf16, int T, int H, int E, int K, int I, int S
                     static_cast<float *>(out)[(std::size_t)t * H + h] = acc;
             }
         }
+        return 0;
+    } catch (...) {
+        return -1;
+    }
+}
+
+/* rmsnorm(x (rows,H) bf16, w (H) bf16, eps) -> out bf16, by the reference's own op (xstar_cpp/src/ops/rmsnorm.cpp) */
+int xsref_rmsnorm_bf16(const void *x, const void *w, void *out, int rows, int H, float eps)
+{
+    try {
+        Tensor xt = view(x, {rows, H}, DType::BFloat16);
+        Tensor wt = view(w, {H}, DType::BFloat16);
+        Tensor r = rmsnorm(xt, wt, eps);
+        std::memcpy(out, r.data(), sizeof(std::uint16_t) * (std::size_t)rows * H);
+        return 0;
+    } catch (...) {
+        return -1;
+    }
+}
+
+/* add(a, b) on bf16 tensors of n elements, by the reference's own op (xstar_cpp/src/ops/add.cpp) */
+int xsref_add_bf16(const void *a, const void *b, void *out, long long n)
+{
+    try {
+        Tensor at = view(a, {n}, DType::BFloat16);
+        Tensor bt = view(b, {n}, DType::BFloat16);
+        Tensor r = add(at, bt);
+        std::memcpy(out, r.data(), sizeof(std::uint16_t) * (std::size_t)n);
         return 0;
     } catch (...) {
         return -1;

@@ -13,6 +13,7 @@
 #include "ops/embedding.h"
 #include "ops/gemm.h"
 #include "ops/mlp.h"
+#include "ops/rmsnorm.h"
 #include "ops/softmax.h"
 
 [[noreturn]] static void no_cuda()
@@ -40,3 +41,4 @@ void gemm_silu_and_mul_launch(void *, const void *, const void *, std::int64_t, 
 void embedding_launch(void *, const void *, const std::int64_t *, std::int64_t, std::int64_t, DType) { no_cuda(); }
 void add_launch(void *, const void *, const void *, std::int64_t, DType) { no_cuda(); }
 void softmax_launch(void *, const void *, std::int64_t, std::int64_t, std::int64_t, DType) { no_cuda(); }
+void rmsnorm_launch(void *, const void *, const void *, std::int64_t, std::int64_t, float, DType) { no_cuda(); }

@@ -8,6 +8,9 @@ Each fixture stores the inputs (storage form) and, from the reference ops: route
 per-assignment expert outputs (embedding gather + mlp) and the combined layer output.  Selection and
 permutation inputs of the composition come from the oracle (the reference has no such op); they are stored
 too so that a change of those rules is caught as well.
+
+block_norm_add.npz holds the two ops either side of the layer in the reference's transformer block: the
+reference's bf16 `rmsnorm` (rows with large, tiny and zero entries, two eps values) and bf16 `add`.
 """
 import os
 import sys
@@ -52,5 +55,30 @@ def main():
         print(name, "written")
 
 
+def block_fixture(here):
+    rng = np.random.default_rng(21)
+    R, H = 7, 384
+    x = rng.standard_normal((R, H)).astype(np.float32)
+    x[1] *= 1e3
+    x[2] *= 1e-4
+    x[3] = 0.0
+    x[4, ::2] = 0.0
+    w = (1.0 + 0.25 * rng.standard_normal(H)).astype(np.float32)
+    other = rng.standard_normal((R, H)).astype(np.float32) * 3.0
+    import torch
+
+    def bits(a):
+        return torch.from_numpy(a).to(torch.bfloat16).view(torch.uint16).numpy()
+
+    xb, wb, ob = bits(x), bits(w), bits(other)
+    np.savez_compressed(
+        os.path.join(here, "block_norm_add.npz"), x=xb, weight=wb, other=ob, eps=np.array([1e-6, 1e-5], np.float32),
+        ref_norm_eps0=mo.ref_rmsnorm_bf16(xb, wb, 1e-6), ref_norm_eps1=mo.ref_rmsnorm_bf16(xb, wb, 1e-5), ref_add=mo.ref_add_bf16(xb, ob))
+    print("block_norm_add written")
+
+
 if __name__ == "__main__":
+    if mo.ref_lib() is None:
+        raise SystemExit("oracle/_ref is not built: the fixtures come from the reference's compiled ops")
+    block_fixture(os.path.dirname(os.path.abspath(__file__)))
     main()

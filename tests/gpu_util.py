@@ -37,6 +37,40 @@ def forward(dims, d, gemm_impl=0, ws=None):
     return out
 
 
+def rmsnorm(x, weight, eps):
+    out = torch.empty_like(x)
+    capi.check(capi.lib().xs_moe_rmsnorm(capi.ptr(x), capi.ptr(weight), capi.ptr(out), x.shape[0], x.shape[1], C.c_float(eps), stream_ptr()))
+    torch.cuda.synchronize()
+    return out
+
+
+def block_forward(dims, d, norm_weight, eps):
+    """x + moe(rmsnorm(x, norm_weight, eps)) through the C ABI; returns (T,H) bf16."""
+    cfg = cfg_of(dims, T=d["x"].shape[0])
+    L = capi.lib()
+    need = C.c_size_t(0)
+    capi.check(L.xs_moe_block_workspace_bytes(C.byref(cfg), C.byref(need)))
+    ws = torch.empty(need.value, dtype=torch.uint8, device="cuda")
+    capi.check(L.xs_moe_workspace_init(capi.ptr(ws), ws.numel(), stream_ptr()))
+    w = capi.make_weights(d)
+    out = torch.empty_like(d["x"])
+    capi.check(L.xs_moe_block_forward(C.byref(cfg), C.byref(w), capi.ptr(d["x"]), capi.ptr(norm_weight), C.c_float(eps), capi.ptr(out),
+                                      capi.ptr(ws), ws.numel(), stream_ptr()))
+    capi.check(L.xs_moe_check_flags(capi.ptr(ws), stream_ptr()))
+    return out
+
+
+def oracle_block(oracle, dims, d, norm_weight, eps, threads=8):
+    """The reference composition add(x, moe(rmsnorm(x, w, eps))) on the CPU; returns (out bits, routing of the normalised x)."""
+    xb = d["x"].detach().cpu().contiguous().view(torch.uint16).numpy()
+    wb = norm_weight.detach().cpu().contiguous().view(torch.uint16).numpy()
+    xn = oracle.rmsnorm_bf16(xb, wb, eps)
+    dn = dict(d)
+    dn["x"] = torch.from_numpy(xn).view(torch.bfloat16)
+    r = oracle_forward(oracle, dims, dn, threads=threads)
+    return oracle.add_bf16(xb, r["out"]), r, xn
+
+
 def route(dims, d):
     cfg = cfg_of(dims, T=d["x"].shape[0])
     T, E, K = cfg.num_tokens, cfg.num_experts, cfg.top_k

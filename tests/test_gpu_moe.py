@@ -559,3 +559,57 @@ def test_rate_probes_run_and_report():
     before = capi.launch_count()
     capi.check(L.xs_moe_probe_mma_rate(0, 64, 200, 1, capi.ptr(ws), ws.numel(), C.byref(cyc), C.byref(iss), C.byref(tf), None))
     assert capi.launch_count() == before + 1
+
+
+# ---- the layer in its transformer-block slot: x + moe(rmsnorm(x)) -----------------------------------------------------
+@pytest.mark.parametrize("rows,H", [(1, 128), (5, 1000), (33, 4096), (300, 7168), (64, 8)])
+def test_rmsnorm_is_bit_exact(oracle, rows, H):
+    g = torch.Generator().manual_seed(rows * 7 + H)
+    x = (torch.randn((rows, H), generator=g) * 3).to(torch.bfloat16)
+    x[0, : H // 2] = 0
+    if rows > 2:
+        x[1] = 0
+        x[2] *= 1e3
+    w = (1 + 0.2 * torch.randn(H, generator=g)).to(torch.bfloat16)
+    for eps in (1e-6, 1e-5):
+        got = gu.rmsnorm(x.cuda(), w.cuda(), eps).cpu().view(torch.uint16).numpy()
+        ref = oracle.rmsnorm_bf16(x.view(torch.uint16).numpy(), w.view(torch.uint16).numpy(), eps)
+        assert np.array_equal(got, ref), (rows, H, eps, int((got != ref).sum()))
+
+
+def test_rmsnorm_reproduces_reference_golden():
+    g = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "block_norm_add.npz"))
+    x = torch.from_numpy(g["x"]).view(torch.bfloat16).cuda()
+    w = torch.from_numpy(g["weight"]).view(torch.bfloat16).cuda()
+    for i in range(2):
+        got = gu.rmsnorm(x, w, float(g["eps"][i])).cpu().view(torch.uint16).numpy()
+        assert np.array_equal(got, g["ref_norm_eps%d" % i])
+
+
+@pytest.mark.parametrize("fmt,T,tol", [("bf16", 70, BF16_TOL), ("fp8", 40, FP8_TOL), ("bf16", 600, BF16_TOL)])
+def test_block_forward_matches_the_reference_composition(oracle, fmt, T, tol):
+    """xs_moe_block_forward against add(x, moe(rmsnorm(x))) composed from the oracle's restatements of the reference's
+    rmsnorm and add around the layer oracle: the normalised rows and the expert choices bit-exact, the block output
+    within the layer's tolerance measured on the layer's share of it."""
+    dims = _dims(T=T, H=512, E=16, K=4, I=256, S=1, fmt=fmt)
+    d = synth.make_inputs(dims, seed=9, device="cuda")
+    d["x"] = (d["x"].float() * 4 + 0.5).to(torch.bfloat16)  # un-normalised activations, as a residual stream has
+    g = torch.Generator().manual_seed(5)
+    nw = (1 + 0.2 * torch.randn(dims["H"], generator=g)).to(torch.bfloat16).cuda()
+    out = gu.block_forward(dims, d, nw, 1e-6)
+    ref_bits, r, xn = gu.oracle_block(oracle, dims, {k: (v.cpu() if v is not None else None) for k, v in d.items()}, nw, 1e-6)
+    assert np.array_equal(gu.rmsnorm(d["x"], nw, 1e-6).cpu().view(torch.uint16).numpy(), xn)
+    dn = dict(d)
+    dn["x"] = torch.from_numpy(xn).view(torch.bfloat16).cuda()
+    _, ids, _ = gu.route(dims, dn)
+    assert np.array_equal(ids.cpu().numpy(), r["topk_ids"])
+    x32 = gu.bf16_to_f32(d["x"])
+    got_layer = gu.bf16_to_f32(out) - x32
+    ref_layer = synth.bf16_bits_to_f32(ref_bits) - x32
+    rel = synth.rel_l2(got_layer, ref_layer)
+    # the residual add rounds the sum to bf16: the layer's share carries that rounding of the larger x as well
+    assert rel <= tol + 2.0 ** -8 * np.linalg.norm(x32) / np.linalg.norm(ref_layer), rel
+    # and given the same layer output the fused residual equals the reference's add bit for bit
+    layer = gu.forward(dims, dn)
+    fused = oracle.add_bf16(d["x"].cpu().view(torch.uint16).numpy(), layer.cpu().view(torch.uint16).numpy())
+    assert np.array_equal(out.cpu().view(torch.uint16).numpy(), fused)

@@ -140,3 +140,36 @@ def test_moe_op_fp4_experts_through_the_binding(oracle):
     with pytest.raises(RuntimeError, match="dtype mismatch"):  # f32 scales next to FP4 experts
         xstar_cpp.moe(dev["x"], dev["router_w"], dev["gate_up_w"], dev["down_w"], dims["K"], gate_up_scale=dev["shared_gate_up_scale"],
                       down_scale=dev["shared_down_scale"])
+
+
+@pytest.mark.gpu
+def test_moe_block_op_matches_the_reference_composition(oracle):
+    """xstar_cpp.moe_block(x, ln_w, eps, ...) = x + moe(rmsnorm(x)), the call that replaces
+    add(attention_x, mlp(rmsnorm(attention_x, ln2_w, eps), ...)) in the reference's transformer block."""
+    dims = dict(T=50, H=512, E=8, K=2, I=256, S=0, fmt="bf16", bias=None)
+    d = synth.make_inputs(dims, seed=4)
+    d["x"] = (d["x"].float() * 3).to(torch.bfloat16)
+    nw = (1 + 0.1 * torch.randn(512, generator=torch.Generator().manual_seed(1))).to(torch.bfloat16)
+    dev = {k: xstar_cpp.to_cuda(torch_to_cpp(v)) for k, v in d.items() if v is not None}
+    NW = xstar_cpp.to_cuda(torch_to_cpp(nw))
+    out = xstar_cpp.moe_block(dev["x"], NW, 1e-6, dev["router_w"], dev["gate_up_w"], dev["down_w"], dims["K"])
+    assert out.shape() == [50, 512] and out.dtype() == xstar_cpp.DType.BFloat16
+    got = cpp_to_torch(xstar_cpp.to_cpu(out), (50, 512))
+    xb = d["x"].view(torch.uint16).numpy()
+    xn = oracle.rmsnorm_bf16(xb, nw.view(torch.uint16).numpy(), 1e-6)
+    n = synth.to_numpy_storage(d)
+    ref = oracle.moe_forward(oracle.BF16, xn, n["router_w"], n["gate_up_w"], n["down_w"], dims["K"], threads=4)
+    want = synth.bf16_bits_to_f32(oracle.add_bf16(xb, ref["out"]))
+    x32 = d["x"].float().numpy()
+    rel = synth.rel_l2(got.float().numpy() - x32, want - x32)
+    assert rel <= 2e-3 + 2.0 ** -8 * np.linalg.norm(x32) / np.linalg.norm(want - x32), rel
+    # the same call in two steps through the layer op gives the same bits
+    xn_dev = xstar_cpp.to_cuda(torch_to_cpp(torch.from_numpy(xn).view(torch.bfloat16)))
+    layer = cpp_to_torch(xstar_cpp.to_cpu(xstar_cpp.moe(xn_dev, dev["router_w"], dev["gate_up_w"], dev["down_w"], dims["K"])), (50, 512))
+    assert np.array_equal(oracle.add_bf16(xb, layer.view(torch.uint16).numpy()), got.view(torch.uint16).numpy())
+    with pytest.raises(RuntimeError, match="shape mismatch"):
+        xstar_cpp.moe_block(dev["x"], xstar_cpp.to_cuda(torch_to_cpp(nw[:256].contiguous())), 1e-6, dev["router_w"], dev["gate_up_w"],
+                            dev["down_w"], dims["K"])
+    with pytest.raises(RuntimeError, match="dtype mismatch"):
+        xstar_cpp.moe_block(dev["x"], xstar_cpp.to_cuda(torch_to_cpp(nw.float())), 1e-6, dev["router_w"], dev["gate_up_w"], dev["down_w"],
+                            dims["K"])

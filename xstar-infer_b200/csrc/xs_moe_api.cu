@@ -1135,8 +1135,8 @@ int xs_moe_gather_rows(const void *src, const int32_t *index, void *dst, int32_t
     return 0;
 }
 
-int xs_moe_combine(const XsMoeConfig *cfg, const float *y, const int32_t *inv, const float *topk_w, const float *shared, void *out,
-                   void *stream)
+static int combine_impl(const XsMoeConfig *cfg, const float *y, const int32_t *inv, const float *topk_w, const float *shared, void *out,
+                        const void *residual, void *stream)
 {
     if (int rc = check_cfg(cfg))
         return rc;
@@ -1146,8 +1146,31 @@ int xs_moe_combine(const XsMoeConfig *cfg, const float *y, const int32_t *inv, c
     if (T == 0)
         return 0;
     int gy = (H + 1023) / 1024;
-    xs::combine_kernel<float><<<dim3(T, gy), 128, 0, static_cast<cudaStream_t>(stream)>>>(y, inv, topk_w, shared,
-                                                                                         static_cast<__nv_bfloat16 *>(out), T, H, K);
+    xs::combine_kernel<float><<<dim3(T, gy), 128, 0, static_cast<cudaStream_t>(stream)>>>(
+        y, inv, topk_w, shared, static_cast<__nv_bfloat16 *>(out), T, H, K, static_cast<const __nv_bfloat16 *>(residual));
+    note_launch();
+    XS_CUDA(cudaGetLastError());
+    return 0;
+}
+
+int xs_moe_combine(const XsMoeConfig *cfg, const float *y, const int32_t *inv, const float *topk_w, const float *shared, void *out,
+                   void *stream)
+{
+    return combine_impl(cfg, y, inv, topk_w, shared, out, nullptr, stream);
+}
+
+int xs_moe_rmsnorm(const void *x, const void *weight, void *out, int32_t rows, int32_t hidden, float eps, void *stream)
+{
+    if (!x || !weight || !out)
+        return fail(XS_MOE_ERR_INVALID_ARG, "null tensor pointer");
+    if (rows < 0 || hidden <= 0 || hidden % 8 != 0)
+        return fail(XS_MOE_ERR_INVALID_ARG, "shape mismatch: hidden must be a positive multiple of 8");
+    if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(weight) | reinterpret_cast<uintptr_t>(out)) % 16 != 0)
+        return fail(XS_MOE_ERR_INVALID_ARG, "tensors must be 16-byte aligned");
+    if (rows == 0)
+        return 0;
+    xs::rmsnorm_rows_kernel<<<(rows + xs::kRnRows - 1) / xs::kRnRows, xs::kRnThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const __nv_bfloat16 *>(x), static_cast<const __nv_bfloat16 *>(weight), static_cast<__nv_bfloat16 *>(out), rows, hidden, eps);
     note_launch();
     XS_CUDA(cudaGetLastError());
     return 0;
@@ -1189,7 +1212,7 @@ int xs_moe_gather_rows_f32_to_bf16(const float *src, const int32_t *index, void 
 // Stage marks of xs_moe_forward_profile: logits | select + permute + tile table | scatter (+ quantise) |
 // gate/up GEMM | down GEMM | combine
 static int forward_impl(const XsMoeConfig *cfg, const XsMoeWeights *w, const void *x, void *out, void *ws, size_t ws_bytes,
-                        void *stream, cudaEvent_t *ev)
+                        void *stream, cudaEvent_t *ev, const void *residual = nullptr)
 {
 #define XS_MARK(i)                                                       \
     do {                                                                 \
@@ -1325,7 +1348,7 @@ static int forward_impl(const XsMoeConfig *cfg, const XsMoeWeights *w, const voi
             return rc;
     }
     XS_MARK(5);
-    if (int rc = xs_moe_combine(cfg, y, inv, tw, S ? y + static_cast<size_t>(n_routed) * H : nullptr, out, stream))
+    if (int rc = combine_impl(cfg, y, inv, tw, S ? y + static_cast<size_t>(n_routed) * H : nullptr, out, residual, stream))
         return rc;
     XS_MARK(6);
     return 0;
@@ -1335,6 +1358,33 @@ static int forward_impl(const XsMoeConfig *cfg, const XsMoeWeights *w, const voi
 int xs_moe_forward(const XsMoeConfig *cfg, const XsMoeWeights *w, const void *x, void *out, void *ws, size_t ws_bytes, void *stream)
 {
     return forward_impl(cfg, w, x, out, ws, ws_bytes, stream, nullptr);
+}
+
+int xs_moe_block_workspace_bytes(const XsMoeConfig *cfg, size_t *bytes)
+{
+    if (int rc = check_cfg(cfg))
+        return rc;
+    if (!bytes)
+        return fail(XS_MOE_ERR_INVALID_ARG, "null out-pointer");
+    *bytes = plan_forward(cfg).bytes + align_up(static_cast<size_t>(cfg->num_tokens) * cfg->hidden * 2, 256);
+    return 0;
+}
+
+int xs_moe_block_forward(const XsMoeConfig *cfg, const XsMoeWeights *w, const void *x, const void *norm_weight, float eps, void *out,
+                         void *ws, size_t ws_bytes, void *stream)
+{
+    if (int rc = check_cfg(cfg))
+        return rc;
+    if (!x || !norm_weight || !out)
+        return fail(XS_MOE_ERR_INVALID_ARG, "null tensor pointer");
+    const size_t fwd = plan_forward(cfg).bytes;
+    const size_t xn_bytes = align_up(static_cast<size_t>(cfg->num_tokens) * cfg->hidden * 2, 256);
+    if (int rc = check_workspace(ws, ws_bytes, fwd + xn_bytes))
+        return rc;
+    void *xn = static_cast<uint8_t *>(ws) + fwd;
+    if (int rc = xs_moe_rmsnorm(x, norm_weight, xn, cfg->num_tokens, cfg->hidden, eps, stream))
+        return rc;
+    return forward_impl(cfg, w, xn, out, ws, fwd, stream, nullptr, x);
 }
 
 int xs_moe_forward_profile(const XsMoeConfig *cfg, const XsMoeWeights *w, const void *x, void *out, void *ws, size_t ws_bytes,

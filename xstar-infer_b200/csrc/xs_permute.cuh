@@ -369,10 +369,14 @@ __device__ __forceinline__ void load8(const __nv_bfloat16 *p, float (&v)[8])
     v[6] = __uint_as_float(r.w << 16); v[7] = __uint_as_float(r.w & 0xffff0000u);
 }
 
+// residual (T, H) bf16 or null: the block's skip connection, added the way the engine's `add` op adds two bf16 tensors
+// (xstar_cpp/src/ops/add.cpp:27-49 in the reference): the layer's result is rounded to bf16 first, then
+// out = bf16(float(residual) + float(result)).
 template <typename YT>
 __global__ void __launch_bounds__(128)
 combine_kernel(const YT *__restrict__ y, const int32_t *__restrict__ inv, const float *__restrict__ topk_w,
-               const float *__restrict__ shared, __nv_bfloat16 *__restrict__ out, int T, int H, int K)
+               const float *__restrict__ shared, __nv_bfloat16 *__restrict__ out, int T, int H, int K,
+               const __nv_bfloat16 *__restrict__ residual = nullptr)
 {
     const int t = blockIdx.x;
     if (t >= T)
@@ -408,7 +412,76 @@ combine_kernel(const YT *__restrict__ y, const int32_t *__restrict__ inv, const 
 #pragma unroll
         for (int i = 0; i < 4; i++)
             o[i] = __floats2bfloat162_rn(acc[2 * i], acc[2 * i + 1]);
+        if (residual) {
+            const uint4 rr = *reinterpret_cast<const uint4 *>(residual + static_cast<size_t>(t) * H + h0);
+            const uint32_t rw4[4] = {rr.x, rr.y, rr.z, rr.w};
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const float2 m = __bfloat1622float2(o[i]);
+                o[i] = __floats2bfloat162_rn(__fadd_rn(__uint_as_float(rw4[i] << 16), m.x),
+                                             __fadd_rn(__uint_as_float(rw4[i] & 0xffff0000u), m.y));
+            }
+        }
         *reinterpret_cast<uint4 *>(out + static_cast<size_t>(t) * H + h0) = *reinterpret_cast<uint4 *>(o);
+    }
+}
+
+// RMS norm of bf16 rows with the reference's arithmetic (xstar_cpp/src/ops/rmsnorm.cpp:52-72): the sum of squares is
+// accumulated in f32 in ASCENDING column order (so the result equals the CPU op bit for bit, and the router that reads it
+// makes the same expert choices), inv = 1 / sqrt(sum / H + eps) with IEEE square root and division, and
+// out[j] = bf16(bf16(x[j] * inv) * w[j]).
+// One block per 32 rows: 256-column chunks are staged in shared memory by all threads (coalesced), then ONE thread per row
+// walks its row's chunk in order; the write pass is done by all threads again.
+constexpr int kRnRows = 32, kRnChunk = 256, kRnThreads = 256, kRnStride = kRnChunk + 8;
+__global__ void __launch_bounds__(kRnThreads)
+rmsnorm_rows_kernel(const __nv_bfloat16 *__restrict__ x, const __nv_bfloat16 *__restrict__ w, __nv_bfloat16 *__restrict__ out, int rows,
+                    int H, float eps)
+{
+    __shared__ __align__(16) __nv_bfloat16 tile[kRnRows][kRnStride];
+    __shared__ float s_inv[kRnRows];
+    const int r0 = blockIdx.x * kRnRows;
+    const int nr = rows - r0 < kRnRows ? rows - r0 : kRnRows;
+    float sum = 0.0f;
+    for (int c0 = 0; c0 < H; c0 += kRnChunk) {
+        const int cw = H - c0 < kRnChunk ? H - c0 : kRnChunk; // a multiple of 8
+        __syncthreads();
+        for (int p = threadIdx.x; p < nr * (cw / 8); p += kRnThreads) {
+            const int r = p / (cw / 8), c = (p - r * (cw / 8)) * 8;
+            *reinterpret_cast<uint4 *>(&tile[r][c]) = __ldg(reinterpret_cast<const uint4 *>(x + static_cast<size_t>(r0 + r) * H + c0 + c));
+        }
+        __syncthreads();
+        if (threadIdx.x < nr) {
+            const uint4 *p = reinterpret_cast<const uint4 *>(&tile[threadIdx.x][0]);
+            for (int i = 0; i < cw / 8; i++) {
+                const uint4 v = p[i];
+                const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    const float a = __uint_as_float(u[j] << 16), b = __uint_as_float(u[j] & 0xffff0000u);
+                    sum = __fadd_rn(sum, __fmul_rn(a, a));
+                    sum = __fadd_rn(sum, __fmul_rn(b, b));
+                }
+            }
+        }
+    }
+    if (threadIdx.x < nr)
+        s_inv[threadIdx.x] = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(sum, static_cast<float>(H)), eps)));
+    __syncthreads();
+    for (int p = threadIdx.x; p < nr * (H / 8); p += kRnThreads) {
+        const int r = p / (H / 8), c = (p - r * (H / 8)) * 8;
+        const float inv = s_inv[r];
+        const uint4 xv = __ldg(reinterpret_cast<const uint4 *>(x + static_cast<size_t>(r0 + r) * H + c));
+        const uint4 wv = __ldg(reinterpret_cast<const uint4 *>(w + c));
+        const uint32_t xu[4] = {xv.x, xv.y, xv.z, xv.w}, wu[4] = {wv.x, wv.y, wv.z, wv.w};
+        __nv_bfloat162 o[4];
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const __nv_bfloat162 n = __floats2bfloat162_rn(__fmul_rn(__uint_as_float(xu[j] << 16), inv),
+                                                           __fmul_rn(__uint_as_float(xu[j] & 0xffff0000u), inv));
+            const float2 nf = __bfloat1622float2(n);
+            o[j] = __floats2bfloat162_rn(__fmul_rn(nf.x, __uint_as_float(wu[j] << 16)), __fmul_rn(nf.y, __uint_as_float(wu[j] & 0xffff0000u)));
+        }
+        *reinterpret_cast<uint4 *>(out + static_cast<size_t>(r0 + r) * H + c) = *reinterpret_cast<uint4 *>(o);
     }
 }
 

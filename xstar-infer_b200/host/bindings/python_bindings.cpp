@@ -46,9 +46,9 @@ const Tensor *opt(py::object o)
     return o.is_none() ? nullptr : &o.cast<const Tensor &>();
 }
 
-Tensor moe_py(const Tensor &x, const Tensor &router_weight, const Tensor &gate_up_weight, const Tensor &down_weight, std::int64_t top_k,
-              py::object router_bias, py::object gate_up_scale, py::object down_scale, py::object shared_gate_up_weight,
-              py::object shared_down_weight, py::object shared_gate_up_scale, py::object shared_down_scale)
+MoEWeights weights_of(const Tensor &router_weight, const Tensor &gate_up_weight, const Tensor &down_weight, py::object router_bias,
+                      py::object gate_up_scale, py::object down_scale, py::object shared_gate_up_weight, py::object shared_down_weight,
+                      py::object shared_gate_up_scale, py::object shared_down_scale)
 {
     MoEWeights w;
     w.router_weight = &router_weight;
@@ -61,10 +61,32 @@ Tensor moe_py(const Tensor &x, const Tensor &router_weight, const Tensor &gate_u
     w.shared_down_weight = opt(shared_down_weight);
     w.shared_gate_up_scale = opt(shared_gate_up_scale);
     w.shared_down_scale = opt(shared_down_scale);
+    return w;
+}
+
+Tensor moe_py(const Tensor &x, const Tensor &router_weight, const Tensor &gate_up_weight, const Tensor &down_weight, std::int64_t top_k,
+              py::object router_bias, py::object gate_up_scale, py::object down_scale, py::object shared_gate_up_weight,
+              py::object shared_down_weight, py::object shared_gate_up_scale, py::object shared_down_scale)
+{
+    MoEWeights w = weights_of(router_weight, gate_up_weight, down_weight, router_bias, gate_up_scale, down_scale, shared_gate_up_weight,
+                              shared_down_weight, shared_gate_up_scale, shared_down_scale);
     MoEConfig cfg;
     cfg.top_k = top_k;
     py::gil_scoped_release nogil; // the device work does not touch Python state
     return moe(x, w, cfg);
+}
+
+Tensor moe_block_py(const Tensor &x, const Tensor &norm_weight, float eps, const Tensor &router_weight, const Tensor &gate_up_weight,
+                    const Tensor &down_weight, std::int64_t top_k, py::object router_bias, py::object gate_up_scale, py::object down_scale,
+                    py::object shared_gate_up_weight, py::object shared_down_weight, py::object shared_gate_up_scale,
+                    py::object shared_down_scale)
+{
+    MoEWeights w = weights_of(router_weight, gate_up_weight, down_weight, router_bias, gate_up_scale, down_scale, shared_gate_up_weight,
+                              shared_down_weight, shared_gate_up_scale, shared_down_scale);
+    MoEConfig cfg;
+    cfg.top_k = top_k;
+    py::gil_scoped_release nogil;
+    return moe_block(x, norm_weight, eps, w, cfg);
 }
 
 py::dict moe_route_py(const Tensor &x, const Tensor &router_weight, std::int64_t top_k, py::object router_bias)
@@ -126,5 +148,10 @@ PYBIND11_MODULE(xstar_cpp, m)
           py::arg("router_bias") = py::none(), py::arg("gate_up_scale") = py::none(), py::arg("down_scale") = py::none(),
           py::arg("shared_gate_up_weight") = py::none(), py::arg("shared_down_weight") = py::none(),
           py::arg("shared_gate_up_scale") = py::none(), py::arg("shared_down_scale") = py::none());
+    m.def("moe_block", &moe_block_py, py::arg("x"), py::arg("norm_weight"), py::arg("eps"), py::arg("router_weight"),
+          py::arg("gate_up_weight"), py::arg("down_weight"), py::arg("top_k"), py::arg("router_bias") = py::none(),
+          py::arg("gate_up_scale") = py::none(), py::arg("down_scale") = py::none(), py::arg("shared_gate_up_weight") = py::none(),
+          py::arg("shared_down_weight") = py::none(), py::arg("shared_gate_up_scale") = py::none(),
+          py::arg("shared_down_scale") = py::none());
     m.def("moe_route", &moe_route_py, py::arg("x"), py::arg("router_weight"), py::arg("top_k"), py::arg("router_bias") = py::none());
 }

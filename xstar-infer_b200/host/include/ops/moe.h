@@ -46,6 +46,17 @@ struct MoEWeights {
 
 Tensor moe(const Tensor &x, const MoEWeights &weights, const MoEConfig &config);
 
+// The feed-forward half of a transformer block with the MoE layer in the MLP slot:
+//     x + moe(rmsnorm(x, norm_weight, eps))
+// which is what `add(attention_x, mlp(rmsnorm(attention_x, ln2_w, eps), gate_up_w, down_w))` computes in the
+// engine's block (reference xstar_cpp/src/ops/transformer_block.cpp:353) with `mlp` replaced by `moe`.
+// norm_weight (H) bf16.  Numerics follow the engine's ops one for one: rmsnorm sums the squares in f32 in
+// ascending order, rounds x*inv to bf16 and then the product with the weight to bf16 (reference
+// xstar_cpp/src/ops/rmsnorm.cpp:41-60); the layer output is rounded to bf16 before the residual is added in
+// f32 and rounded once more (reference xstar_cpp/src/ops/add.cpp).  One normalisation kernel, and the
+// residual add rides in the combine kernel: no extra pass over the activations.
+Tensor moe_block(const Tensor &x, const Tensor &norm_weight, float eps, const MoEWeights &weights, const MoEConfig &config);
+
 // Routing decisions for inspection and tests: ids (T, k) ascending per row, weights (T, k),
 // counts (E), offsets (E+1), perm (T*k), inv (T*k).  Host vectors; x and router tensors on the device.
 struct MoERouting {

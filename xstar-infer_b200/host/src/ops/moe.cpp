@@ -151,6 +151,28 @@ Tensor moe(const Tensor &x, const MoEWeights &weights, const MoEConfig &config)
     return out;
 }
 
+Tensor moe_block(const Tensor &x, const Tensor &norm_weight, float eps, const MoEWeights &weights, const MoEConfig &config)
+{
+    if (norm_weight.dtype() != DType::BFloat16)
+        throw std::runtime_error("dtype mismatch");
+    if (norm_weight.rank() != 1)
+        throw std::runtime_error("rank mismatch");
+    Checked c = validate(x, weights, config, true);
+    if (norm_weight.dim(0) != x.dim(-1))
+        throw std::runtime_error("shape mismatch");
+    if (norm_weight.device() != x.device())
+        throw std::runtime_error("device mismatch");
+    if (x.device() != Device::CUDA)
+        throw std::runtime_error("unsupported device");
+    std::size_t need = 0;
+    raise_if(xs_moe_block_workspace_bytes(&c.cfg, &need));
+    Tensor out(x.shape(), DType::BFloat16, Device::CUDA);
+    Workspace ws(need);
+    raise_if(xs_moe_block_forward(&c.cfg, &c.w, x.data(), norm_weight.data(), eps, out.data(), ws.data(), ws.bytes(), nullptr));
+    raise_if(xs_moe_check_flags(ws.data(), nullptr));
+    return out;
+}
+
 MoERouting moe_route(const Tensor &x, const Tensor &router_weight, const Tensor *router_bias, const MoEConfig &config)
 {
     MoEWeights m;

@@ -43,7 +43,7 @@ EXPORTS = [
     "xs_moe_status_string", "xs_moe_last_error", "xs_moe_device_check", "xs_moe_device_count", "xs_moe_set_device", "xs_moe_current_device", "xs_moe_device_alloc", "xs_moe_device_free",
     "xs_moe_memcpy_h2d", "xs_moe_memcpy_d2h", "xs_moe_memcpy_d2d", "xs_moe_device_free_bytes",
     "xs_moe_stream_synchronize", "xs_moe_workspace_bytes", "xs_moe_workspace_init", "xs_moe_forward",
-    "xs_moe_forward_host", "xs_moe_forward_profile", "xs_moe_route", "xs_moe_topk", "xs_moe_permute", "xs_moe_permute_noalloc", "xs_moe_grouped_mlp_workspace_bytes",
+    "xs_moe_forward_host", "xs_moe_forward_profile", "xs_moe_block_workspace_bytes", "xs_moe_block_forward", "xs_moe_rmsnorm", "xs_moe_route", "xs_moe_topk", "xs_moe_permute", "xs_moe_permute_noalloc", "xs_moe_grouped_mlp_workspace_bytes",
     "xs_moe_grouped_mlp", "xs_moe_quantize_rows_fp8", "xs_moe_quantize_rows_mxfp8", "xs_moe_gather_rows", "xs_moe_combine", "xs_moe_combine_bf16_rows", "xs_moe_gather_rows_f32_to_bf16", "xs_moe_check_flags", "xs_moe_debug_counters", "xs_moe_probe_mma_rate", "xs_moe_probe_tmem_ld_rate", "xs_moe_probe_handoff", "xs_moe_launch_count", "xs_moe_plan_info",
     "xs_moe_ipc_export", "xs_moe_ipc_import", "xs_moe_ipc_close", "xs_moe_ep_plan", "xs_moe_ep_dispatch", "xs_moe_ep_return",
 ]
@@ -79,6 +79,9 @@ def lib():
             "xs_moe_forward": [cfgp, wp, vp, vp, vp, sz, vp],
             "xs_moe_forward_host": [cfgp, wp, vp, vp, vp, vp, vp, sz, vp],
             "xs_moe_forward_profile": [cfgp, wp, vp, vp, vp, sz, vp, C.POINTER(C.c_float)],
+            "xs_moe_block_workspace_bytes": [cfgp, C.POINTER(sz)],
+            "xs_moe_block_forward": [cfgp, wp, vp, vp, C.c_float, vp, vp, sz, vp],
+            "xs_moe_rmsnorm": [vp, vp, vp, i32, i32, C.c_float, vp],
             "xs_moe_route": [cfgp, vp, vp, vp, vp, vp, vp, vp, sz, vp],
             "xs_moe_topk": [cfgp, vp, vp, vp, vp, vp],
             "xs_moe_permute": [cfgp, vp, vp, vp, vp, vp, vp, sz, vp],
