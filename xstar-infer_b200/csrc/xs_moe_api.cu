@@ -102,6 +102,27 @@ int make_tmap_2d(CUtensorMap *m, CUtensorMapDataType dt, int elem_bytes, const v
     return 0;
 }
 
+// 2-D row-major byte matrix (rows, row_bytes) read in boxes of (box_bytes, box_rows) WITHOUT swizzle: rows of the box land
+// back to back in shared memory.
+int make_tmap_bytes(CUtensorMap *m, const void *base, uint64_t rows, uint64_t row_bytes, uint32_t box_rows, uint32_t box_bytes)
+{
+    EncodeTiledFn fn = get_encode_fn();
+    if (!fn)
+        return fail(XS_MOE_ERR_CUDA, "CUDA error: cuTensorMapEncodeTiled entry point not available");
+    if (reinterpret_cast<uintptr_t>(base) % 16 != 0 || row_bytes % 16 != 0 || box_bytes % 16 != 0)
+        return fail(XS_MOE_ERR_INVALID_ARG, "tensor map operand must be 16-byte aligned with a 16-byte multiple row pitch");
+    cuuint64_t dims[2] = {row_bytes, rows};
+    cuuint64_t strides[1] = {row_bytes};
+    cuuint32_t box[2] = {box_bytes, box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS)
+        return fail(XS_MOE_ERR_CUDA, "CUDA error: cuTensorMapEncodeTiled failed with code %d (rows=%llu row bytes=%llu)", (int)r,
+                    (unsigned long long)rows, (unsigned long long)row_bytes);
+    return 0;
+}
+
 struct DeviceInfo {
     int ok = 0;
     int sms = 0;
@@ -172,9 +193,20 @@ int check_cfg(const XsMoeConfig *c)
 // Rows per token tile.  bf16: 16..128 tokens as the N of a 128-weight-row MMA.  FP8/FP4: up to 64 in that shape (the
 // FP8 epilogue keeps one f32 accumulator per token column in registers); FP8 batches with many tokens per expert use
 // the prefill kernel instead, whose tiles are 128 tokens as the M of an N = 256 MMA (needs hidden % 256 == 0).
+#ifdef XS_FP4_SWAPAB_DECODE
+#define XS_FP4_TOKENS_AS_M 0
+#else
+#define XS_FP4_TOKENS_AS_M 1
+#endif
 int pick_n_tile(long rows, int groups, int fmt, int hidden)
 {
     const long avg = groups > 0 ? (rows + groups - 1) / groups : rows;
+#ifndef XS_FP4_SWAPAB_DECODE
+    // FP4: the tokens-as-M kernel at every batch size (an N = 256 block-scaled MMA consumes twice the packed weight bytes of
+    // a weights-as-M one); 32-row token boxes while experts see a handful of tokens, 128-row ones beyond
+    if (fmt == XS_MOE_FP4_MX32 && hidden % 256 == 0)
+        return avg <= 20 ? 32 : 128;
+#endif
     if (avg <= 8)
         return 16;
     if (avg <= 20)
@@ -649,13 +681,27 @@ int launch_gemm_fp4(int n_tile, const CUtensorMap &tw, const CUtensorMap &tx, co
     return fail(XS_MOE_ERR_INVALID_ARG, "internal: bad token tile %d for FP4", n_tile);
 }
 
+// w_scale_rows: rows of the weight-scale matrix (all local experts).  tile_rows: 32 or 128, the token rows of a tile (and of
+// the token box of tx).
 template <bool GATE_UP>
 int launch_prefill_fp4(const CUtensorMap &tw, const CUtensorMap &tx, const int32_t *offsets, xs::TileTable tt, xs::MxScales sc, int w_rows,
-                       int n_out, int K, void *out, int32_t *status, int max_work, cudaStream_t st)
+                       uint64_t w_scale_rows, int n_out, int K, void *out, int32_t *status, int max_work, int tile_rows, cudaStream_t st)
 {
     DeviceInfo di;
     if (int rc = device_info(&di))
         return rc;
+    // scales through the TMA unit where the shapes allow: 16 bytes (four k-blocks) per row and request
+    const int kbs = K / 32;
+    CUtensorMap t_ws{}, t_xs{};
+    int sf_tma = 0;
+    if (kbs % 16 == 0 && (K / xs::kBlockK8) % 4 == 0 && reinterpret_cast<uintptr_t>(sc.w_scale) % 16 == 0 &&
+        reinterpret_cast<uintptr_t>(sc.x_scale) % 16 == 0) {
+        if (int rc = make_tmap_bytes(&t_ws, sc.w_scale, w_scale_rows, kbs, 128, 16))
+            return rc;
+        if (int rc = make_tmap_bytes(&t_xs, sc.x_scale, sc.max_rows, kbs, 128, 16))
+            return rc;
+        sf_tma = 1;
+    }
     int stages = (di.max_smem - 1024 - xs::kPf4TailBytes) / xs::kPfStageBytes;
     if (stages > 6)
         stages = 6;
@@ -674,7 +720,7 @@ int launch_prefill_fp4(const CUtensorMap &tw, const CUtensorMap &tx, const int32
     int grid = di.sms < max_work ? di.sms : max_work;
     if (grid < 1)
         grid = 1;
-    kern<<<grid, xs::kPf4Threads, smem, st>>>(tw, tx, offsets, tt, sc, w_rows, n_out, K, out, status, stages);
+    kern<<<grid, xs::kPf4Threads, smem, st>>>(tw, tx, t_ws, t_xs, offsets, tt, sc, w_rows, n_out, K, out, status, stages, tile_rows, sf_tma);
     note_launch();
     XS_CUDA(cudaGetLastError());
     return 0;
@@ -788,15 +834,17 @@ int run_grouped(const GroupedArgs &a, cudaStream_t st, cudaEvent_t mid = nullptr
         if (int rc = make_tmap_2d(&t_act, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, act, a.max_rows, I, a.gp.n_tile, xs::kBlockK8))
             return rc;
         uint8_t *act_scale = a.scratch + a.gp.off_act_scale;
-        if (a.gp.n_tile == 128) {
-            // many tokens per expert: tokens as the M of N = 256 block-scaled MMAs
+        if (a.gp.n_tile == 128 || (a.gp.n_tile == 32 && H % 256 == 0 && XS_FP4_TOKENS_AS_M)) {
+            // tokens as the M of N = 256 block-scaled MMAs (token box of 32 or 128 rows)
             xs::MxScales p1{static_cast<const uint8_t *>(a.gu_scale), reinterpret_cast<const uint8_t *>(a.row_scale), act_scale, a.max_rows};
-            if (int rc = launch_prefill_fp4<true>(t_wgu, t_x, offs, tt, p1, 2 * I, I, H, act, a.status, a.gp.max_tiles * (I / 128), st))
+            if (int rc = launch_prefill_fp4<true>(t_wgu, t_x, offs, tt, p1, 2 * I, static_cast<uint64_t>(groups) * 2 * I, I, H, act, a.status,
+                                                  a.gp.max_tiles * (I / 128), a.gp.n_tile, st))
                 return rc;
             if (mid)
                 XS_CUDA(cudaEventRecord(mid, st));
             xs::MxScales p2{static_cast<const uint8_t *>(a.dw_scale), act_scale, nullptr, a.max_rows};
-            return launch_prefill_fp4<false>(t_wd, t_act, offs, tt, p2, H, H, I, a.y, a.status, a.gp.max_tiles * (H / 256), st);
+            return launch_prefill_fp4<false>(t_wd, t_act, offs, tt, p2, H, static_cast<uint64_t>(groups) * H, H, I, a.y, a.status,
+                                             a.gp.max_tiles * (H / 256), a.gp.n_tile, st);
         }
         xs::MxScales s1{static_cast<const uint8_t *>(a.gu_scale), reinterpret_cast<const uint8_t *>(a.row_scale), act_scale, a.max_rows};
         if (int rc = launch_gemm_fp4<true>(a.gp.n_tile, t_wgu, t_x, offs, tt, s1, 2 * I, I, H, act, a.status,

@@ -12,7 +12,7 @@
         const int e = tt.tile_expert[tile];
         const int row0 = tt.tile_row0[tile];
         int nvalid = offsets[e + 1] - row0;
-        nvalid = nvalid < kPfTokens ? nvalid : kPfTokens;
+        nvalid = nvalid < tile_rows ? nvalid : tile_rows;
         const bool valid = r < nvalid;
         if (!mbar_wait_t(tmem_full, it & 1, abort_flag, w0)) {
             ok = false;
