@@ -13,6 +13,7 @@
 #include <cstring>
 #include <atomic>
 #include <mutex>
+#include <vector>
 #include <string>
 
 #include "xs_grouped_gemm.cuh"
@@ -1257,6 +1258,51 @@ int xs_moe_gather_rows_f32_to_bf16(const float *src, const int32_t *index, void 
     return 0;
 }
 
+// A second stream per (device, caller stream) for work of a layer call that does not depend on the routing (the always-on
+// expert of an FP4 layer, which runs in its own launches): forked from the caller's stream by an event at the start of the
+// call and joined before the combine, so the pair behaves like one stream to the caller -- also under stream capture, where
+// the fork and join become graph edges.  Created on first use (outside of a capture: creating streams is not a stream
+// operation and may be refused while a global-mode capture is active).
+struct SideStream {
+    cudaStream_t side = nullptr;
+    cudaEvent_t fork = nullptr, join = nullptr;
+};
+static int side_stream_for(cudaStream_t user, SideStream *out)
+{
+    struct Entry {
+        int dev;
+        cudaStream_t user;
+        SideStream s;
+    };
+    static std::mutex mu;
+    static std::vector<Entry> table;
+    int dev = 0;
+    XS_CUDA(cudaGetDevice(&dev));
+    std::lock_guard<std::mutex> lock(mu);
+    for (const Entry &e : table)
+        if (e.dev == dev && e.user == user) {
+            *out = e.s;
+            return 0;
+        }
+    if (table.size() >= 256) { // more caller streams than anyone keeps alive: run on the caller's stream
+        *out = SideStream{};
+        return 0;
+    }
+    cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(user, &cs) != cudaSuccess || cs != cudaStreamCaptureStatusNone) {
+        (void)cudaGetLastError();
+        *out = SideStream{}; // first use inside a capture: no fork this time
+        return 0;
+    }
+    SideStream s;
+    XS_CUDA(cudaStreamCreateWithFlags(&s.side, cudaStreamNonBlocking));
+    XS_CUDA(cudaEventCreateWithFlags(&s.fork, cudaEventDisableTiming));
+    XS_CUDA(cudaEventCreateWithFlags(&s.join, cudaEventDisableTiming));
+    table.push_back(Entry{dev, user, s});
+    *out = s;
+    return 0;
+}
+
 // Stage marks of xs_moe_forward_profile: logits | select + permute + tile table | scatter (+ quantise) |
 // gate/up GEMM | down GEMM | combine
 static int forward_impl(const XsMoeConfig *cfg, const XsMoeWeights *w, const void *x, void *out, void *ws, size_t ws_bytes,
@@ -1303,6 +1349,53 @@ static int forward_impl(const XsMoeConfig *cfg, const XsMoeWeights *w, const voi
     const int extra_rows = (S && !fp4) ? T : -1; // FP4 experts: the FP8 always-on expert runs in its own launches
     const bool tensor_path = cfg->gemm_impl == 0;
     uint8_t *gscratch = b + p.off_grouped;
+
+    // FP4 experts: the always-on expert is FP8 (128x128 scales) and runs in launches of its own -- quantise x per 1x128, then
+    // a one-segment grouped MLP.  None of it depends on the routing, so it goes to the side stream and overlaps the router,
+    // the permutation and the scatter.
+    SideStream side;
+    bool joined = false;
+    if (fp4 && S) {
+        if (int rc = side_stream_for(st, &side))
+            return rc;
+        cudaStream_t ss = st;
+        if (side.side) {
+            XS_CUDA(cudaEventRecord(side.fork, st));
+            XS_CUDA(cudaStreamWaitEvent(side.side, side.fork, 0));
+            ss = side.side;
+            joined = true;
+        }
+        uint8_t *xq = b + p.off_sh_rows;
+        float *xs_ = reinterpret_cast<float *>(b + p.off_sh_scale);
+        int32_t *sh_off = reinterpret_cast<int32_t *>(b + p.off_sh_offsets);
+        if (int rc = launch_quantize_rows(x, xq, xs_, T, H, ss))
+            return rc;
+        set_two_ints_kernel<<<1, 1, 0, ss>>>(sh_off, 0, T);
+        note_launch();
+        XS_CUDA(cudaGetLastError());
+        GroupedArgs sa;
+        sa.fmt = XS_MOE_FP8_BLOCK128;
+        sa.H = H;
+        sa.I = I;
+        sa.groups = 1;
+        sa.gu = w->shared_gate_up_w_dev;
+        sa.gu_scale = w->shared_gate_up_scale_dev;
+        sa.dw = w->shared_down_w_dev;
+        sa.dw_scale = w->shared_down_scale_dev;
+        sa.rows = xq;
+        sa.row_scale = xs_;
+        sa.offsets = sh_off;
+        sa.max_rows = T;
+        sa.y = y + static_cast<size_t>(n_routed) * H;
+        sa.scratch = b + p.off_sh_grouped;
+        sa.gp = p.sh_grouped;
+        sa.status = status;
+        const int rc_sh = run_grouped(sa, ss);
+        if (joined) // join even when a launch failed: a capture in progress must not be left forked
+            XS_CUDA(cudaEventRecord(side.join, side.side));
+        if (rc_sh)
+            return rc_sh;
+    }
 
     XS_MARK(0);
     if (int rc = launch_logits(cfg, x, w->router_w_dev, logits, st, w->router_bias_dev, b))
@@ -1365,36 +1458,8 @@ static int forward_impl(const XsMoeConfig *cfg, const XsMoeWeights *w, const voi
     a.tiles_ready = tiles_ready;
     if (int rc = run_grouped(a, st, ev ? ev[4] : nullptr))
         return rc;
-    if (fp4 && S) {
-        // always-on expert in FP8 (128x128 scales): quantise x per 1x128 and run it as a one-segment grouped MLP
-        uint8_t *xq = b + p.off_sh_rows;
-        float *xs_ = reinterpret_cast<float *>(b + p.off_sh_scale);
-        int32_t *sh_off = reinterpret_cast<int32_t *>(b + p.off_sh_offsets);
-        if (int rc = launch_quantize_rows(x, xq, xs_, T, H, st))
-            return rc;
-        set_two_ints_kernel<<<1, 1, 0, st>>>(sh_off, 0, T);
-        note_launch();
-        XS_CUDA(cudaGetLastError());
-        GroupedArgs sa;
-        sa.fmt = XS_MOE_FP8_BLOCK128;
-        sa.H = H;
-        sa.I = I;
-        sa.groups = 1;
-        sa.gu = w->shared_gate_up_w_dev;
-        sa.gu_scale = w->shared_gate_up_scale_dev;
-        sa.dw = w->shared_down_w_dev;
-        sa.dw_scale = w->shared_down_scale_dev;
-        sa.rows = xq;
-        sa.row_scale = xs_;
-        sa.offsets = sh_off;
-        sa.max_rows = T;
-        sa.y = y + static_cast<size_t>(n_routed) * H;
-        sa.scratch = b + p.off_sh_grouped;
-        sa.gp = p.sh_grouped;
-        sa.status = status;
-        if (int rc = run_grouped(sa, st))
-            return rc;
-    }
+    if (joined)
+        XS_CUDA(cudaStreamWaitEvent(st, side.join, 0));
     XS_MARK(5);
     if (int rc = combine_impl(cfg, y, inv, tw, S ? y + static_cast<size_t>(n_routed) * H : nullptr, out, residual, stream))
         return rc;

@@ -97,13 +97,23 @@
             __syncwarp();
             if (lane == 0)
                 mbar_arrive(tmem_empty);
-            if (valid) {
-                float *yrow = static_cast<float *>(out) + static_cast<size_t>(row0 + r) * n_out + nt * 256 + 128 * half;
+            // (all lanes of an active warp take part in the quad transposes; rows past the segment are not stored)
+            if (active) {
+                const int qd = lane & 3;
+                const int rq = q * 32 + (lane & ~3); // first row of the quad within the tile
+                float *ybase = static_cast<float *>(out) + static_cast<size_t>(row0 + rq) * n_out + nt * 256 + 128 * half;
 #pragma unroll
-                for (int i = 0; i < 8; i++)
+                for (int i = 0; i < 8; i++) {
+                    uint4 b[4];
 #pragma unroll
                     for (int v = 0; v < 4; v++)
-                        *reinterpret_cast<uint4 *>(yrow + i * 16 + v * 4) = make_uint4(y[i][v * 4], y[i][v * 4 + 1], y[i][v * 4 + 2], y[i][v * 4 + 3]);
+                        b[v] = make_uint4(y[i][v * 4], y[i][v * 4 + 1], y[i][v * 4 + 2], y[i][v * 4 + 3]);
+                    quad_transpose_chunks(b, qd); // b[r] = chunk qd of columns [16 i, 16 i + 16) of row rq + r
+#pragma unroll
+                    for (int r = 0; r < 4; r++)
+                        if (rq + r < nvalid)
+                            *reinterpret_cast<uint4 *>(ybase + static_cast<size_t>(r) * n_out + i * 16 + qd * 4) = b[r];
+                }
             }
         }
     }

@@ -354,4 +354,40 @@ __device__ __forceinline__ void fence_proxy_async_smem()
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
 
+// 4 x 4 transpose of 16-byte chunks among the four lanes of a quad (lanes 4a..4a+3): on entry b[j] is chunk j of this
+// lane's row, on exit b[i] is chunk (lane & 3) of the row of lane 4a + i.  A thread that holds consecutive columns of ONE
+// row would store 16 bytes per lane to 32 different rows per instruction; after the transpose a quad writes 64 contiguous
+// bytes of one row, 8 rows per instruction.
+__device__ __forceinline__ void quad_transpose_chunks(uint4 (&b)[4], int qd)
+{
+    auto shfl4 = [](const uint4 &v, int m) {
+        return make_uint4(__shfl_xor_sync(0xffffffffu, v.x, m), __shfl_xor_sync(0xffffffffu, v.y, m),
+                          __shfl_xor_sync(0xffffffffu, v.z, m), __shfl_xor_sync(0xffffffffu, v.w, m));
+    };
+    {
+        // lanes l and l ^ 1 swap the off-diagonal elements of each 2 x 2 block
+        const bool odd = qd & 1;
+        const uint4 s0 = shfl4(odd ? b[0] : b[1], 1), s1 = shfl4(odd ? b[2] : b[3], 1);
+        if (odd) {
+            b[0] = s0;
+            b[2] = s1;
+        } else {
+            b[1] = s0;
+            b[3] = s1;
+        }
+    }
+    {
+        // lanes l and l ^ 2 swap the off-diagonal 2 x 2 blocks
+        const bool hi = qd & 2;
+        const uint4 s0 = shfl4(hi ? b[0] : b[2], 2), s1 = shfl4(hi ? b[1] : b[3], 2);
+        if (hi) {
+            b[0] = s0;
+            b[1] = s1;
+        } else {
+            b[2] = s0;
+            b[3] = s1;
+        }
+    }
+}
+
 } // namespace xs
