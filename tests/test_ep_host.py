@@ -1,0 +1,222 @@
+"""The C++ host of the expert-parallel layer (xstar_cpp.EpGroup / EpContext: NCCL + peer stores, one thread per GPU).
+CPU tests cover the host-side failure detection -- a rank that never posts, a rank that leaves, ranks that disagree --
+none of which touches a GPU; GPU tests run the layer through EpContext against the CPU oracle on the global problem."""
+import threading
+import time
+
+import numpy as np
+import pytest
+import torch
+
+from xstar_moe import capi, synth
+
+from bridge import cpp_to_torch, torch_to_cpp, xstar_cpp
+
+
+def _run_threads(fns):
+    out = [None] * len(fns)
+
+    def wrap(i):
+        try:
+            out[i] = ("ok", fns[i]())
+        except Exception as e:  # noqa: BLE001 - the test inspects what each rank raised
+            out[i] = ("err", e)
+
+    ts = [threading.Thread(target=wrap, args=(i,)) for i in range(len(fns))]
+    for t in ts:
+        t.start()
+    for t in ts:
+        t.join(60)
+        assert not t.is_alive(), "a rank thread did not come back"
+    return out
+
+
+def test_group_releases_all_ranks_step_after_step():
+    g = xstar_cpp.EpGroup(3, 5000)
+
+    def rank(r):
+        def run():
+            for step in range(20):
+                g.arrive(r, 1000 + step)
+            return True
+        return run
+
+    assert [o[0] for o in _run_threads([rank(r) for r in range(3)])] == ["ok"] * 3
+    assert not g.broken()
+
+
+def test_group_times_out_when_a_rank_never_posts():
+    g = xstar_cpp.EpGroup(3, 300)
+    t0 = time.monotonic()
+    res = _run_threads([lambda: g.arrive(0, 7), lambda: g.arrive(2, 7)])  # rank 1 never shows up
+    dt = time.monotonic() - t0
+    assert all(k == "err" for k, _ in res)
+    assert all("peer timeout: rank 1 did not arrive" in str(e) for _, e in res), res
+    assert 0.25 <= dt < 5.0
+    assert g.broken()
+    with pytest.raises(RuntimeError, match="group is broken: peer timeout"):
+        g.arrive(1, 7)  # the late rank learns of it as soon as it does arrive
+
+
+def test_group_reports_a_rank_that_left():
+    g = xstar_cpp.EpGroup(2, 10000)
+    res = {}
+
+    def waiter():
+        try:
+            g.arrive(0, 1)
+            res["r"] = "ok"
+        except RuntimeError as e:
+            res["r"] = str(e)
+
+    t = threading.Thread(target=waiter)
+    t.start()
+    time.sleep(0.2)
+    g.leave(1)  # rank 1 unwinds instead of joining the step
+    t.join(10)
+    assert not t.is_alive() and "peer left: rank 1" in res["r"]
+    # a rank that left before anyone waited is noticed at the next check-in
+    g2 = xstar_cpp.EpGroup(2, 10000)
+    g2.leave(0)
+    with pytest.raises(RuntimeError, match="peer left: rank 0"):
+        g2.arrive(1, 1)
+
+
+def test_group_rejects_ranks_that_disagree_on_the_step():
+    g = xstar_cpp.EpGroup(2, 5000)
+    res = _run_threads([lambda: g.arrive(0, 11), lambda: g.arrive(1, 12)])
+    assert all(k == "err" and "step mismatch" in str(e) for k, e in res), res
+    g = xstar_cpp.EpGroup(2, 300)
+    g_res = _run_threads([lambda: (g.arrive(0, 1), g.arrive(0, 1))])  # the same rank twice in one step
+    assert g_res[0][0] == "err" and ("peer timeout" in str(g_res[0][1]) or "arrived twice" in str(g_res[0][1]))
+    with pytest.raises(RuntimeError, match="bad rank"):
+        xstar_cpp.EpGroup(2, 100).arrive(5, 0)
+
+
+def test_capacity_rule():
+    assert xstar_cpp.ep_capacity_rows(2048, 6, 8, 0.0) == 8 * 2048 * 6  # worst case: every row of every rank
+    assert xstar_cpp.ep_capacity_rows(2048, 6, 8, 2.0) == 2 * 2048 * 6
+    assert xstar_cpp.ep_capacity_rows(2048, 6, 8, 100.0) == 8 * 2048 * 6  # never more than the worst case
+    assert xstar_cpp.ep_capacity_rows(5, 3, 2, 1.5) == 128  # rounded up to whole 128-row tiles
+    with pytest.raises(RuntimeError, match="bad capacity"):
+        xstar_cpp.ep_capacity_rows(8, 2, 2, -1.0)
+
+
+def test_comm_layer_loads_nccl_by_name():
+    assert capi.lib().xs_moe_comm_available() == 0, capi.lib().xs_moe_last_error()
+
+
+# ---- on GPUs ---------------------------------------------------------------------------------------------------------
+_DT = {"bf16": "BFloat16", "fp8": "Float8E4M3", "fp4": "Float4E2M1x2"}
+
+
+def _cpp(t, kind=None):
+    return torch_to_cpp(t, getattr(xstar_cpp.DType, kind)) if kind else torch_to_cpp(t)
+
+
+def _rank_tensors(d, dims, rank, world):
+    """This rank's tensors on ITS device (the calling thread's current device): router and always-on expert replicated,
+    experts [rank * E / world, ...) and the rank's slice of the tokens."""
+    fmt, T, El = dims["fmt"], dims["T"], dims["E"] // world
+    wk = {"bf16": None, "fp8": "Float8E4M3", "fp4": "Float4E2M1x2"}[fmt]
+    sk = {"bf16": None, "fp8": None, "fp4": "UE8M0"}[fmt]
+    up = lambda t, k=None: xstar_cpp.to_cuda(_cpp(t.contiguous(), k))  # noqa: E731
+    sl = slice(rank * El, (rank + 1) * El)
+    kw = {}
+    if fmt != "bf16":
+        kw["gate_up_scale"] = up(d["gate_up_scale"][sl], sk)
+        kw["down_scale"] = up(d["down_scale"][sl], sk)
+    if dims["S"]:
+        shk = None if fmt == "bf16" else "Float8E4M3"
+        kw["shared_gate_up_weight"] = up(d["shared_gate_up_w"], shk)
+        kw["shared_down_weight"] = up(d["shared_down_w"], shk)
+        if fmt != "bf16":
+            kw["shared_gate_up_scale"] = up(d["shared_gate_up_scale"])
+            kw["shared_down_scale"] = up(d["shared_down_scale"])
+    if d.get("router_bias") is not None:
+        kw["router_bias"] = up(d["router_bias"])
+    return (up(d["x"][rank * T:(rank + 1) * T]), up(d["router_w"]), up(d["gate_up_w"][sl], wk), up(d["down_w"][sl], wk)), kw
+
+
+def _oracle(oracle, dims, d):
+    n = synth.to_numpy_storage(d)
+    mode = {"bf16": oracle.BF16, "fp8": oracle.FP8, "fp4": oracle.FP4}[dims["fmt"]]
+    return oracle.moe_forward(mode, n["x"], n["router_w"], n["gate_up_w"], n["down_w"], dims["K"], router_bias=n.get("router_bias"),
+                              gate_up_scale=n.get("gate_up_scale"), down_scale=n.get("down_scale"),
+                              shared_gate_up_w=n.get("shared_gate_up_w"), shared_down_w=n.get("shared_down_w"),
+                              shared_gate_up_scale=n.get("shared_gate_up_scale"), shared_down_scale=n.get("shared_down_scale"), threads=8)
+
+
+def _run_world(dims, world, seed, capacity_factor=0.0, steps=2, timeout_ms=60000):
+    d = synth.make_inputs(dict(dims, T=dims["T"] * world), seed=seed)
+    group = xstar_cpp.EpGroup(world, timeout_ms)
+    uid = xstar_cpp.ep_unique_id()
+
+    def rank(r):
+        def run():
+            xstar_cpp.set_device(r)
+            (x, rw, gu, dw), kw = _rank_tensors(d, dims, r, world)
+            ctx = xstar_cpp.EpContext(group, uid, r, world, r, dims["T"], dims["H"], dims["E"], dims["K"], dims["I"],
+                                      getattr(xstar_cpp.DType, _DT[dims["fmt"]]), bool(dims["S"]), capacity_factor)
+            outs = [cpp_to_torch(xstar_cpp.to_cpu(ctx.moe(x, rw, gu, dw, dims["K"], **kw)), (dims["T"], dims["H"])) for _ in range(steps)]
+            for o in outs[1:]:
+                assert torch.equal(o, outs[0])
+            return outs[0]
+        return run
+
+    return d, _run_threads([rank(r) for r in range(world)])
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("fmt,tol", [("bf16", 2e-3), ("fp8", 1e-2), ("fp4", 1e-2)])
+def test_cpp_ep_single_rank_matches_oracle(oracle, fmt, tol):
+    """world = 1: the whole expert-parallel step (NCCL communicator of one rank, dispatch and return kernels storing into this
+    rank's own buffers) on one GPU."""
+    dims = dict(T=96, H=512, E=16, K=4, I=256, S=1, fmt=fmt, bias=None)
+    d, res = _run_world(dims, 1, seed=31)
+    assert res[0][0] == "ok", res[0][1]
+    ref = _oracle(oracle, dims, d)
+    rel = synth.rel_l2(res[0][1].float().numpy(), synth.bf16_bits_to_f32(ref["out"]))
+    assert rel <= tol, rel
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("fmt,tol", [("bf16", 2e-3), ("fp8", 1e-2), ("fp4", 1e-2)])
+def test_cpp_ep_two_rank_threads_match_oracle(oracle, fmt, tol):
+    """Two host threads, one GPU each, rows crossing NVLink both ways: outputs of both ranks against the oracle on the global
+    batch; bf16 experts also bit-identical to the single-GPU layer's contract (same roundings)."""
+    world = 2
+    if torch.cuda.device_count() < world:
+        pytest.skip("needs two GPUs on one box")
+    dims = dict(T=96, H=512, E=16, K=4, I=256, S=1, fmt=fmt, bias=None)
+    d, res = _run_world(dims, world, seed=23)
+    for k, v in res:
+        assert k == "ok", v
+    got = torch.cat([v for _, v in res]).float().numpy()
+    ref = _oracle(oracle, dims, d)
+    rel = synth.rel_l2(got, synth.bf16_bits_to_f32(ref["out"]))
+    assert rel <= tol, rel
+
+
+@pytest.mark.gpu
+def test_cpp_ep_flags_a_receive_buffer_that_is_too_small():
+    """capacity_factor far below the rows that arrive: the dispatch kernel skips the rows that do not fit and flags it, the
+    grouped MLP clamps its segments to the capacity, and check() raises on the host -- nothing is written out of bounds."""
+    dims = dict(T=256, H=256, E=8, K=4, I=128, S=0, fmt="bf16", bias=None)
+    d, res = _run_world(dims, 1, seed=3, capacity_factor=0.25, steps=1)
+    assert res[0][0] == "err" and "out-of-range index" in str(res[0][1]), res[0]
+
+
+@pytest.mark.gpu
+def test_cpp_ep_rejects_calls_that_do_not_fit_the_context():
+    dims = dict(T=32, H=256, E=8, K=2, I=128, S=0, fmt="bf16", bias=None)
+    d = synth.make_inputs(dims, seed=1)
+    xstar_cpp.set_device(0)
+    (x, rw, gu, dw), kw = _rank_tensors(d, dims, 0, 1)
+    ctx = xstar_cpp.EpContext(None, xstar_cpp.ep_unique_id(), 0, 1, 0, 32, 256, 8, 2, 128, xstar_cpp.DType.BFloat16, False)
+    with pytest.raises(RuntimeError, match="shape mismatch"):
+        ctx.moe(x, rw, gu, dw, 3)  # another top_k than the context was sized for
+    with pytest.raises(RuntimeError, match="expert count mismatch"):
+        xstar_cpp.EpContext(None, xstar_cpp.ep_unique_id(), 0, 3, 0, 32, 256, 8, 2, 128, xstar_cpp.DType.BFloat16, False)
+    out = cpp_to_torch(xstar_cpp.to_cpu(ctx.moe(x, rw, gu, dw, 2)), (32, 256))
+    assert torch.isfinite(out.float()).all()

@@ -13,6 +13,7 @@
 #include <cstring>
 #include <atomic>
 #include <mutex>
+#include <type_traits>
 #include <vector>
 #include <string>
 
@@ -1933,3 +1934,5 @@ int xs_moe_ep_return(const XsMoeConfig *cfg, int32_t ranks, int32_t rank, const 
 }
 
 } // extern "C"
+
+#include "xs_comm.inl"

@@ -10,6 +10,8 @@
 
 #include "cuda/cuda_allocator.h"
 #include "ops/moe.h"
+#include "ops/moe_ep.h"
+#include "parallel/ep_group.h"
 #include "tensor.h"
 
 namespace py = pybind11;
@@ -89,6 +91,20 @@ Tensor moe_block_py(const Tensor &x, const Tensor &norm_weight, float eps, const
     return moe_block(x, norm_weight, eps, w, cfg);
 }
 
+EpShape ep_shape(std::int64_t max_tokens, std::int64_t hidden, std::int64_t experts, std::int64_t top_k, std::int64_t intermediate,
+                 DType expert_dtype, bool shared)
+{
+    EpShape s;
+    s.max_tokens = max_tokens;
+    s.hidden = hidden;
+    s.experts = experts;
+    s.top_k = top_k;
+    s.intermediate = intermediate;
+    s.expert_dtype = expert_dtype;
+    s.shared = shared;
+    return s;
+}
+
 py::dict moe_route_py(const Tensor &x, const Tensor &router_weight, std::int64_t top_k, py::object router_bias)
 {
     MoEConfig cfg;
@@ -153,5 +169,76 @@ PYBIND11_MODULE(xstar_cpp, m)
           py::arg("gate_up_scale") = py::none(), py::arg("down_scale") = py::none(), py::arg("shared_gate_up_weight") = py::none(),
           py::arg("shared_down_weight") = py::none(), py::arg("shared_gate_up_scale") = py::none(),
           py::arg("shared_down_scale") = py::none());
+    m.def("set_device", &cuda_set_device, py::arg("device"));
+    m.def("current_device", &cuda_current_device);
+    m.def("ep_unique_id", [] {
+        const EpUniqueId id = ep_unique_id();
+        return py::bytes(reinterpret_cast<const char *>(id.data()), id.size());
+    });
+    m.def("ep_capacity_rows", &ep_capacity_rows, py::arg("max_tokens"), py::arg("top_k"), py::arg("world"), py::arg("capacity_factor"));
+    py::register_exception<EpError>(m, "EpError", PyExc_RuntimeError);
+    py::class_<EpGroup, std::shared_ptr<EpGroup>>(m, "EpGroup")
+        .def(py::init([](int world, int timeout_ms) { return std::make_shared<EpGroup>(world, std::chrono::milliseconds(timeout_ms)); }),
+             py::arg("world"), py::arg("timeout_ms") = 30000)
+        .def("arrive", &EpGroup::arrive, py::arg("rank"), py::arg("signature"), py::call_guard<py::gil_scoped_release>())
+        .def("leave", &EpGroup::leave, py::arg("rank"))
+        .def("broken", &EpGroup::broken)
+        .def("world", &EpGroup::world);
+    py::class_<EpContext>(m, "EpContext")
+        .def(py::init([](std::shared_ptr<EpGroup> group, py::bytes id, int rank, int world, int device, std::int64_t max_tokens,
+                         std::int64_t hidden, std::int64_t experts, std::int64_t top_k, std::int64_t intermediate, DType expert_dtype,
+                         bool shared, double capacity_factor) {
+                 const std::string raw = id;
+                 if (raw.size() != 128)
+                     throw std::runtime_error("unique id must be 128 bytes");
+                 EpUniqueId u;
+                 std::memcpy(u.data(), raw.data(), 128);
+                 EpOptions o;
+                 o.capacity_factor = capacity_factor;
+                 const EpShape s = ep_shape(max_tokens, hidden, experts, top_k, intermediate, expert_dtype, shared);
+                 py::gil_scoped_release nogil; // collective: the other ranks' threads must be able to run
+                 return std::make_unique<EpContext>(std::move(group), u, rank, world, device, s, o);
+             }),
+             py::arg("group"), py::arg("unique_id"), py::arg("rank"), py::arg("world"), py::arg("device"), py::arg("max_tokens"),
+             py::arg("hidden"), py::arg("experts"), py::arg("top_k"), py::arg("intermediate"), py::arg("expert_dtype"), py::arg("shared"),
+             py::arg("capacity_factor") = 0.0)
+        .def("rank", &EpContext::rank)
+        .def("world", &EpContext::world)
+        .def("capacity_rows", &EpContext::capacity_rows)
+        .def("abandon", &EpContext::abandon)
+        .def("check", [](EpContext &c, std::uintptr_t stream) { c.check(reinterpret_cast<void *>(stream)); }, py::arg("stream") = 0,
+             py::call_guard<py::gil_scoped_release>())
+        .def(
+            "moe",
+            [](EpContext &c, const Tensor &x, const Tensor &router_weight, const Tensor &gate_up_weight, const Tensor &down_weight,
+               std::int64_t top_k, py::object router_bias, py::object gate_up_scale, py::object down_scale, py::object shared_gate_up_weight,
+               py::object shared_down_weight, py::object shared_gate_up_scale, py::object shared_down_scale) {
+                MoEWeights w = weights_of(router_weight, gate_up_weight, down_weight, router_bias, gate_up_scale, down_scale,
+                                          shared_gate_up_weight, shared_down_weight, shared_gate_up_scale, shared_down_scale);
+                MoEConfig cfg;
+                cfg.top_k = top_k;
+                py::gil_scoped_release nogil;
+                return moe(x, w, cfg, &c);
+            },
+            py::arg("x"), py::arg("router_weight"), py::arg("gate_up_weight"), py::arg("down_weight"), py::arg("top_k"),
+            py::arg("router_bias") = py::none(), py::arg("gate_up_scale") = py::none(), py::arg("down_scale") = py::none(),
+            py::arg("shared_gate_up_weight") = py::none(), py::arg("shared_down_weight") = py::none(),
+            py::arg("shared_gate_up_scale") = py::none(), py::arg("shared_down_scale") = py::none())
+        .def(
+            "moe_into",
+            [](EpContext &c, const Tensor &x, Tensor &out, std::uintptr_t stream, const Tensor &router_weight, const Tensor &gate_up_weight,
+               const Tensor &down_weight, std::int64_t top_k, py::object router_bias, py::object gate_up_scale, py::object down_scale,
+               py::object shared_gate_up_weight, py::object shared_down_weight, py::object shared_gate_up_scale, py::object shared_down_scale) {
+                MoEWeights w = weights_of(router_weight, gate_up_weight, down_weight, router_bias, gate_up_scale, down_scale,
+                                          shared_gate_up_weight, shared_down_weight, shared_gate_up_scale, shared_down_scale);
+                MoEConfig cfg;
+                cfg.top_k = top_k;
+                py::gil_scoped_release nogil;
+                c.forward_into(x, w, cfg, out, reinterpret_cast<void *>(stream));
+            },
+            py::arg("x"), py::arg("out"), py::arg("stream"), py::arg("router_weight"), py::arg("gate_up_weight"), py::arg("down_weight"),
+            py::arg("top_k"), py::arg("router_bias") = py::none(), py::arg("gate_up_scale") = py::none(), py::arg("down_scale") = py::none(),
+            py::arg("shared_gate_up_weight") = py::none(), py::arg("shared_down_weight") = py::none(),
+            py::arg("shared_gate_up_scale") = py::none(), py::arg("shared_down_scale") = py::none());
     m.def("moe_route", &moe_route_py, py::arg("x"), py::arg("router_weight"), py::arg("top_k"), py::arg("router_bias") = py::none());
 }

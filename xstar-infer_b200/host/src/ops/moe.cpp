@@ -4,9 +4,10 @@
 #include <string>
 
 #include "cuda/cuda_allocator.h"
+#include "ops/moe_checked.h"
 #include "xs_moe.h"
 
-namespace {
+namespace moe_detail {
 
 void raise_if(int rc)
 {
@@ -24,13 +25,8 @@ int format_of(const Tensor &w)
     }
 }
 
-struct Checked {
-    XsMoeConfig cfg{};
-    XsMoeWeights w{};
-};
-
 // validation in the order the reference's ops use: dtype, rank, shape, device
-Checked validate(const Tensor &x, const MoEWeights &m, const MoEConfig &config, bool need_experts)
+Checked validate(const Tensor &x, const MoEWeights &m, const MoEConfig &config, bool need_experts, std::int64_t local_experts)
 {
     if (!m.router_weight || (need_experts && (!m.gate_up_weight || !m.down_weight)))
         throw std::runtime_error("missing weight");
@@ -67,7 +63,8 @@ Checked validate(const Tensor &x, const MoEWeights &m, const MoEConfig &config, 
     const int fmt = format_of(gu);
     if (gu.rank() != 3 || dw.rank() != 3)
         throw std::runtime_error("rank mismatch");
-    if (gu.dim(0) != E || dw.dim(0) != E)
+    const std::int64_t held = local_experts >= 0 ? local_experts : E; // expert-parallel ranks hold a slice of the experts
+    if (gu.dim(0) != held || dw.dim(0) != held)
         throw std::runtime_error("expert count mismatch");
     if (gu.dim(1) % 2 != 0)
         throw std::runtime_error("gate_up out must be even");
@@ -85,12 +82,12 @@ Checked validate(const Tensor &x, const MoEWeights &m, const MoEConfig &config, 
         if (fmt == XS_MOE_FP8_BLOCK128) {
             if (m.gate_up_scale->dtype() != DType::Float32 || m.down_scale->dtype() != DType::Float32)
                 throw std::runtime_error("dtype mismatch");
-            if (m.gate_up_scale->numel() != E * (2 * I / 128) * (H / 128) || m.down_scale->numel() != E * (H / 128) * (I / 128))
+            if (m.gate_up_scale->numel() != held * (2 * I / 128) * (H / 128) || m.down_scale->numel() != held * (H / 128) * (I / 128))
                 throw std::runtime_error("shape mismatch");
         } else {
             if (m.gate_up_scale->dtype() != DType::UE8M0 || m.down_scale->dtype() != DType::UE8M0)
                 throw std::runtime_error("dtype mismatch");
-            if (m.gate_up_scale->numel() != E * 2 * I * (H / 32) || m.down_scale->numel() != E * H * (I / 32))
+            if (m.gate_up_scale->numel() != held * 2 * I * (H / 32) || m.down_scale->numel() != held * H * (I / 32))
                 throw std::runtime_error("shape mismatch");
         }
     }
@@ -133,11 +130,14 @@ Checked validate(const Tensor &x, const MoEWeights &m, const MoEConfig &config, 
     return c;
 }
 
-} // namespace
+} // namespace moe_detail
+
+using moe_detail::Checked;
+using moe_detail::raise_if;
 
 Tensor moe(const Tensor &x, const MoEWeights &weights, const MoEConfig &config)
 {
-    Checked c = validate(x, weights, config, true);
+    Checked c = moe_detail::validate(x, weights, config, true);
     if (x.device() != Device::CUDA)
         throw std::runtime_error("unsupported device");
     std::size_t need = 0;
@@ -157,7 +157,7 @@ Tensor moe_block(const Tensor &x, const Tensor &norm_weight, float eps, const Mo
         throw std::runtime_error("dtype mismatch");
     if (norm_weight.rank() != 1)
         throw std::runtime_error("rank mismatch");
-    Checked c = validate(x, weights, config, true);
+    Checked c = moe_detail::validate(x, weights, config, true);
     if (norm_weight.dim(0) != x.dim(-1))
         throw std::runtime_error("shape mismatch");
     if (norm_weight.device() != x.device())
@@ -178,7 +178,7 @@ MoERouting moe_route(const Tensor &x, const Tensor &router_weight, const Tensor 
     MoEWeights m;
     m.router_weight = &router_weight;
     m.router_bias = router_bias;
-    Checked c = validate(x, m, config, false);
+    Checked c = moe_detail::validate(x, m, config, false);
     if (x.device() != Device::CUDA)
         throw std::runtime_error("unsupported device");
     const std::size_t T = c.cfg.num_tokens, E = c.cfg.num_experts, K = c.cfg.top_k;

@@ -34,7 +34,7 @@ def build_cuda(force=False, verbose=False):
     if not (force or _newer(LIB, srcs)):
         return LIB
     cmd = ["nvcc", *NVCC_FLAGS, "-shared", "-Xcompiler", "-fPIC", "-I" + os.path.join(ROOT, "include"), "-o", LIB,
-           os.path.join(CSRC, "xs_moe_api.cu")]
+           os.path.join(CSRC, "xs_moe_api.cu"), "-ldl"]
     if verbose:
         cmd.insert(1, "-Xptxas=-v")
     subprocess.run(cmd, check=True)

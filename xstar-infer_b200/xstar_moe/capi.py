@@ -46,6 +46,10 @@ EXPORTS = [
     "xs_moe_forward_host", "xs_moe_forward_profile", "xs_moe_block_workspace_bytes", "xs_moe_block_forward", "xs_moe_rmsnorm", "xs_moe_route", "xs_moe_topk", "xs_moe_permute", "xs_moe_permute_noalloc", "xs_moe_grouped_mlp_workspace_bytes",
     "xs_moe_grouped_mlp", "xs_moe_quantize_rows_fp8", "xs_moe_quantize_rows_mxfp8", "xs_moe_gather_rows", "xs_moe_combine", "xs_moe_combine_bf16_rows", "xs_moe_gather_rows_f32_to_bf16", "xs_moe_check_flags", "xs_moe_debug_counters", "xs_moe_probe_mma_rate", "xs_moe_probe_tmem_ld_rate", "xs_moe_probe_handoff", "xs_moe_launch_count", "xs_moe_plan_info",
     "xs_moe_ipc_export", "xs_moe_ipc_import", "xs_moe_ipc_close", "xs_moe_ep_plan", "xs_moe_ep_dispatch", "xs_moe_ep_return",
+    "xs_moe_comm_available", "xs_moe_comm_unique_id", "xs_moe_comm_create", "xs_moe_comm_destroy", "xs_moe_comm_abort",
+    "xs_moe_comm_async_error", "xs_moe_comm_all_gather", "xs_moe_comm_barrier", "xs_moe_comm_all_to_all_v", "xs_moe_stream_create",
+    "xs_moe_stream_destroy", "xs_moe_event_create", "xs_moe_event_destroy", "xs_moe_event_record", "xs_moe_stream_wait_event",
+    "xs_moe_memset_async", "xs_moe_enable_peer_access",
 ]
 
 _lib = None
@@ -74,6 +78,23 @@ def lib():
             "xs_moe_memcpy_d2d": [vp, vp, sz],
             "xs_moe_device_free_bytes": [C.POINTER(sz)],
             "xs_moe_stream_synchronize": [vp],
+            "xs_moe_comm_available": [],
+            "xs_moe_comm_unique_id": [vp],
+            "xs_moe_comm_create": [C.POINTER(vp), vp, i32, i32],
+            "xs_moe_comm_destroy": [vp],
+            "xs_moe_comm_abort": [vp],
+            "xs_moe_comm_async_error": [vp, C.POINTER(i32)],
+            "xs_moe_comm_all_gather": [vp, vp, vp, sz, vp],
+            "xs_moe_comm_barrier": [vp, vp, vp],
+            "xs_moe_comm_all_to_all_v": [vp, i32, vp, C.POINTER(sz), C.POINTER(sz), vp, C.POINTER(sz), C.POINTER(sz), vp],
+            "xs_moe_stream_create": [C.POINTER(vp)],
+            "xs_moe_stream_destroy": [vp],
+            "xs_moe_event_create": [C.POINTER(vp)],
+            "xs_moe_event_destroy": [vp],
+            "xs_moe_event_record": [vp, vp],
+            "xs_moe_stream_wait_event": [vp, vp],
+            "xs_moe_memset_async": [vp, i32, sz, vp],
+            "xs_moe_enable_peer_access": [i32],
             "xs_moe_workspace_bytes": [cfgp, C.POINTER(sz)],
             "xs_moe_workspace_init": [vp, sz, vp],
             "xs_moe_forward": [cfgp, wp, vp, vp, vp, sz, vp],
