@@ -496,6 +496,77 @@ def ep_parity(dims, rank, world, out_local, ids_local, oracle_threads):
             "ranks_checked": check_ranks, "against": "CPU oracle on the global problem (all ranks' experts), worst rank's rel-L2"}
 
 
+class CppEpStep:
+    """One rank's expert-parallel step through the C++ host: torch owns x / out / the weights, xstar_cpp.EpContext owns the
+    exchange buffers and drives the stage calls and NCCL.  The unique id travels through torch.distributed once."""
+
+    def __init__(self, dims, rank, local_rank, world, x, weights, shared, bias):
+        import torch
+        import torch.distributed as dist
+
+        sys.path.insert(0, os.path.join(ROOT, "xstar-infer_b200", "xstar_cpp_py"))
+        import xstar_cpp
+
+        self.m, self.torch = xstar_cpp, torch
+        T, H, E, K, I, S = (dims[k] for k in "THEKIS")
+        fmt = dims["fmt"]
+        box = [xstar_cpp.ep_unique_id() if rank == 0 else None]
+        dist.broadcast_object_list(box, src=0)
+        dt = {"bf16": xstar_cpp.DType.BFloat16, "fp8": xstar_cpp.DType.Float8E4M3, "fp4": xstar_cpp.DType.Float4E2M1x2}[fmt]
+        self.ctx = xstar_cpp.EpContext(None, box[0], rank, world, local_rank, T, H, E, K, I, dt, bool(S), 0.0)
+        self.shape = (T, H)
+        self.K = K
+        self.keep = (weights, shared, bias)
+        wk = dt
+        sk = {"bf16": None, "fp8": xstar_cpp.DType.Float32, "fp4": xstar_cpp.DType.UE8M0}[fmt]
+        shk = xstar_cpp.DType.BFloat16 if fmt == "bf16" else xstar_cpp.DType.Float8E4M3
+        self.w = [self.view(weights["router_w"], xstar_cpp.DType.BFloat16), self.view(weights["gate_up_w"], wk), self.view(weights["down_w"], wk)]
+        kw = {}
+        if fmt != "bf16":
+            kw["gate_up_scale"] = self.view(weights["gate_up_scale"], sk)
+            kw["down_scale"] = self.view(weights["down_scale"], sk)
+        if S:
+            kw["shared_gate_up_weight"] = self.view(shared["shared_gate_up_w"], shk)
+            kw["shared_down_weight"] = self.view(shared["shared_down_w"], shk)
+            if fmt != "bf16":
+                kw["shared_gate_up_scale"] = self.view(shared["shared_gate_up_scale"], xstar_cpp.DType.Float32)
+                kw["shared_down_scale"] = self.view(shared["shared_down_scale"], xstar_cpp.DType.Float32)
+        if bias is not None:
+            kw["router_bias"] = self.view(bias, xstar_cpp.DType.Float32)
+        self.kw = kw
+
+    def view(self, t, dtype):
+        assert t.is_contiguous() and t.is_cuda
+        return self.m.from_device_ptr(t.data_ptr(), list(t.shape), dtype)
+
+    def run(self, x, stream, out=None):
+        out = self.torch.empty(self.shape, dtype=self.torch.bfloat16, device="cuda") if out is None else out
+        self.ctx.moe_into(self.view(x, self.m.DType.BFloat16), self.view(out, self.m.DType.BFloat16), stream.cuda_stream, *self.w, self.K,
+                          **self.kw)
+        return out
+
+    def capture(self, x_static):
+        torch = self.torch
+        out_static = torch.empty(self.shape, dtype=torch.bfloat16, device="cuda")
+        warm = torch.cuda.Stream()
+        warm.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(warm):
+            for _ in range(2):
+                self.run(x_static, warm, out_static)
+        torch.cuda.current_stream().wait_stream(warm)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            self.run(x_static, torch.cuda.current_stream(), out_static)
+        return graph, out_static
+
+    def check(self, stream):
+        self.ctx.check(stream.cuda_stream)
+
+    def close(self):
+        self.ctx = None
+
+
 def measure_ep(name, dims, args, steps, repeats, rank, local_rank, world, want_e2e=True):
     """One expert-parallel workload on the initialised process group.  Returns the entry dict on rank 0 (None elsewhere)."""
     import torch
@@ -527,15 +598,34 @@ def measure_ep(name, dims, args, steps, repeats, rank, local_rank, world, want_e
     def forward(xd, marks=None):
         return layer.forward_peer(xd, px, marks) if peer else layer.forward(xd, marks)
 
+    # The timed step is driven by the C++ host (xstar_cpp.EpContext: NCCL + peer stores, no torch in the step); the Python
+    # composition above stays for the phase marks and as the fallback when the context cannot be made on some rank.
+    cpp = None
+    if peer and args.ep_host == "cpp":
+        try:
+            cpp = CppEpStep(dims, rank, local_rank, world, x, weights, shared, bias)
+        except Exception as e:  # noqa: BLE001 - any failure here means "use the Python host", on every rank
+            print(f"rank {rank}: C++ expert-parallel host unavailable ({type(e).__name__}: {e})", file=sys.stderr, flush=True)
+        agreed = torch.tensor([1 if cpp is not None else 0], dtype=torch.int32, device="cuda")
+        dist.all_reduce(agreed, op=dist.ReduceOp.MIN)
+        if int(agreed.item()) == 0:
+            cpp = None
+
     c0 = capi.launch_count()
-    forward(x)
+    if cpp is not None:
+        cpp.run(x, stream)
+    else:
+        forward(x)
     launches_per_step = capi.launch_count() - c0
     use_graph = peer and args.graph != "off"  # nothing in the peer step touches the host: replay it whole at any size
     graph = None
     if use_graph:
         x_static = x.clone()
         try:
-            graph, out_static = layer.capture_peer(x_static, px)
+            if cpp is not None:
+                graph, out_static = cpp.capture(x_static)
+            else:
+                graph, out_static = layer.capture_peer(x_static, px)
         except RuntimeError as e:
             print(f"rank {rank}: graph capture failed ({e}); launching the step eagerly", file=sys.stderr, flush=True)
         agreed = torch.tensor([1 if graph is not None else 0], dtype=torch.int32, device="cuda")
@@ -557,11 +647,11 @@ def measure_ep(name, dims, args, steps, repeats, rank, local_rank, world, want_e
             torch.cuda.synchronize()
     else:
         def step():
-            return forward(x)
+            return cpp.run(x, stream) if cpp is not None else forward(x)
 
         def step_host():
             xd = x_host.to("cuda", non_blocking=True)
-            out_host.copy_(forward(xd), non_blocking=True)
+            out_host.copy_(cpp.run(xd, stream) if cpp is not None else forward(xd), non_blocking=True)
             torch.cuda.synchronize()
 
     def barrier():
@@ -583,6 +673,8 @@ def measure_ep(name, dims, args, steps, repeats, rank, local_rank, world, want_e
     for _ in range(max(3, args.warmup)):
         step()
     ops.check()
+    if cpp is not None:
+        cpp.check(stream)
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
@@ -598,6 +690,8 @@ def measure_ep(name, dims, args, steps, repeats, rank, local_rank, world, want_e
     ids_dev = ops.route(x, weights["router_w"], bias)[0]
     torch.cuda.synchronize()
     ops.check()
+    if cpp is not None:
+        cpp.check(stream)
     parity = ep_parity(dims, rank, world, out_dev, ids_dev, host_cores())
     # the grouped expert MLPs of this rank, timed on their own with CUDA events
     counts_now = torch.empty(world * E, dtype=torch.int32, device="cuda")
@@ -665,6 +759,8 @@ def measure_ep(name, dims, args, steps, repeats, rank, local_rank, world, want_e
                     "parallelism": f"ep{world}: experts sharded, " + ("dispatch/return by peer-memory stores over NVLink, no host synchronisation"
                                                                      if peer else "NCCL all-to-all dispatch/combine"),
                     "cuda_graph": bool(use_graph), "exchange_fallback": fallback,
+                    "host": ("C++ (xstar_cpp.EpContext: NCCL all-gather / all-reduce + peer stores, one process per GPU)" if cpp is not None
+                             else "Python composition of the stage calls (torch.distributed for the collectives)"),
                     "l2": "inputs larger than L2: expert weights streamed per step exceed 126 MB"},
             "e2e": None if ms_e2e is None else {"value": T * world / (ms_e2e["median"] * 1e-3), "unit": UNIT, "h2d_bytes_per_step": T * H * 2,
                                                 "d2h_bytes_per_step": T * H * 2, "ms_per_step": ms_e2e["median"]},
@@ -690,6 +786,9 @@ def measure_ep(name, dims, args, steps, repeats, rank, local_rank, world, want_e
     dist.barrier()
     if px is not None:
         px.close()
+    if cpp is not None:
+        cpp.close()
+        dist.barrier()
     del ops, layer, x, weights, shared
     torch.cuda.empty_cache()
     return entry
@@ -799,6 +898,9 @@ def main():
     ap.add_argument("--graph", default="auto", choices=["auto", "on", "off"], help="replay the step as a CUDA graph (auto: T <= 1024)")
     ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
                     help="N > 1: rows travel by peer-memory stores from the dispatch/return kernels (default) or by NCCL all-to-all")
+    ap.add_argument("--ep-host", default="cpp", choices=["cpp", "py"],
+                    help="N > 1 with the peer exchange: the step is driven by the C++ host (xstar_cpp.EpContext, default) or by the "
+                         "Python composition of the stage calls")
     ap.add_argument("--mma-rate", action="store_true", help="print the tensor-pipe and TMEM read-rate probe tables and exit")
     args = ap.parse_args()
     if args.mma_rate:

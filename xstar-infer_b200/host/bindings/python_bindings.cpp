@@ -154,6 +154,13 @@ PYBIND11_MODULE(xstar_cpp, m)
 
     m.def("from_numpy_raw", &from_numpy_raw, py::arg("array"), py::arg("shape"), py::arg("dtype"));
     m.def("to_numpy_raw", &to_numpy_raw, py::arg("tensor"));
+    // borrowed view of device memory another owner keeps alive (a framework's tensor): no copy, no ownership
+    m.def(
+        "from_device_ptr",
+        [](std::uintptr_t ptr, std::vector<std::int64_t> shape, DType dtype) {
+            return Tensor(reinterpret_cast<const void *>(ptr), std::move(shape), dtype, Device::CUDA);
+        },
+        py::arg("ptr"), py::arg("shape"), py::arg("dtype"));
     m.def("to_cuda", &to_cuda, py::arg("tensor"));
     m.def("to_cpu", &to_cpu, py::arg("tensor"));
     m.def("cuda_free_bytes", &cuda_free_bytes);
