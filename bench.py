@@ -365,6 +365,71 @@ def l2_note(dims, active):
     return f"{b / 1e6:.0f} MB per step fit in the 126 MB L2"
 
 
+def measure_host_op(dims, d, steps):
+    """The layer through the reference-facing C++ op on device tensors: xstar_cpp.moe (synchronous: the call returns when the
+    result is finished and checked, as every reference op does) and xstar_cpp.moe_into (enqueue on a stream, caller's scratch and
+    output).  CUDA events on the stream the op uses; the synchronous form's time includes its host synchronisation."""
+    import torch
+
+    sys.path.insert(0, os.path.join(ROOT, "xstar-infer_b200", "xstar_cpp_py"))
+    import xstar_cpp as xc
+
+    fmt = dims["fmt"]
+    wk = {"bf16": xc.DType.BFloat16, "fp8": xc.DType.Float8E4M3, "fp4": xc.DType.Float4E2M1x2}[fmt]
+    sk = {"bf16": None, "fp8": xc.DType.Float32, "fp4": xc.DType.UE8M0}[fmt]
+    shk = xc.DType.BFloat16 if fmt == "bf16" else xc.DType.Float8E4M3
+
+    def view(t, dt):
+        return xc.from_device_ptr(t.data_ptr(), list(t.shape), dt)
+
+    a = [view(d["x"], xc.DType.BFloat16), view(d["router_w"], xc.DType.BFloat16), view(d["gate_up_w"], wk), view(d["down_w"], wk)]
+    kw = {}
+    if fmt != "bf16":
+        kw.update(gate_up_scale=view(d["gate_up_scale"], sk), down_scale=view(d["down_scale"], sk))
+    if dims["S"]:
+        kw.update(shared_gate_up_weight=view(d["shared_gate_up_w"], shk), shared_down_weight=view(d["shared_down_w"], shk))
+        if fmt != "bf16":
+            kw.update(shared_gate_up_scale=view(d["shared_gate_up_scale"], xc.DType.Float32),
+                      shared_down_scale=view(d["shared_down_scale"], xc.DType.Float32))
+    if d.get("router_bias") is not None:
+        kw["router_bias"] = view(d["router_bias"], xc.DType.Float32)
+    K = dims["K"]
+    stream = torch.cuda.current_stream()
+
+    def timed(fn, n):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record(stream)
+        for _ in range(n):
+            fn()
+        e1.record(stream)
+        torch.cuda.synchronize()
+        return float(e0.elapsed_time(e1)) / n
+
+    def sync_op():
+        xc.moe(*a, K, **kw)
+
+    out_t = torch.empty_like(d["x"])
+    out = view(out_t, xc.DType.BFloat16)
+    scratch = xc.MoEScratch()
+
+    def stream_op():
+        xc.moe_into(a[0], out, scratch, stream.cuda_stream, *a[1:], K, **kw)
+
+    for _ in range(3):
+        sync_op()
+        stream_op()
+    xc.moe_check(scratch, stream.cuda_stream)
+    ms_sync = timed(sync_op, steps)
+    ms_stream = timed(stream_op, steps)
+    xc.moe_check(scratch, stream.cuda_stream)
+    T = dims["T"]
+    return {"call": "xstar_cpp.moe(x, router_weight, gate_up_weight, down_weight, top_k, ...) on device tensors",
+            "ms_per_call": ms_sync, "value": T / (ms_sync * 1e-3), "unit": UNIT,
+            "stream_form": {"call": "xstar_cpp.moe_into(x, out, scratch, stream, ...): enqueue only, caller's output and scratch",
+                            "ms_per_call": ms_stream, "value": T / (ms_stream * 1e-3), "unit": UNIT}}
+
+
 def run_ours(args, dims):
     import torch
 
@@ -381,6 +446,10 @@ def run_ours(args, dims):
     res = measure_single(args.workload, dims, args, args.steps, args.repeats)
     clocks = sampler.stop()
     roofline = roofline_single(dims, res)
+    try:
+        host_op = measure_host_op(dims, res["inputs"], args.steps)
+    except Exception as e:  # noqa: BLE001 - the host module is optional for the headline
+        host_op = {"error": f"{type(e).__name__}: {e}"}
 
     # CPU baseline on a bounded sample of the same batch
     cpu = None
@@ -429,6 +498,7 @@ def run_ours(args, dims):
         "e2e": {"value": T / (res["ms_e2e"]["median"] * 1e-3), "unit": UNIT, "h2d_bytes_per_step": T * dims["H"] * 2,
                 "d2h_bytes_per_step": T * dims["H"] * 2 + 4, "ms_per_step": res["ms_e2e"]["median"],
                 "ms_per_step_min_max": [res["ms_e2e"]["min"], res["ms_e2e"]["max"]]},
+        "host_op": host_op,
         "gpu_launches": res["launches_per_step"] * args.steps,
         "gpu_launches_note": "kernels the library enqueued for one step (counted by the library) x steps of one timed repeat",
         "roofline": roofline, "cpu_baseline": cpu, "clocks": clocks, "workloads": workloads,

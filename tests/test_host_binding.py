@@ -173,3 +173,35 @@ def test_moe_block_op_matches_the_reference_composition(oracle):
     with pytest.raises(RuntimeError, match="dtype mismatch"):
         xstar_cpp.moe_block(dev["x"], xstar_cpp.to_cuda(torch_to_cpp(nw.float())), 1e-6, dev["router_w"], dev["gate_up_w"], dev["down_w"],
                             dims["K"])
+
+
+@pytest.mark.gpu
+def test_stream_form_and_recycled_results(oracle):
+    """moe_into on a caller's stream with a caller's scratch gives the bits of the synchronous op; results of the synchronous op
+    come from the result cache (no device allocation once the size has been seen)."""
+    dims = dict(T=40, H=512, E=8, K=2, I=256, S=1, fmt="bf16", bias=None)
+    d = synth.make_inputs(dims, seed=8)
+    dev = {k: xstar_cpp.to_cuda(torch_to_cpp(v)) for k, v in d.items() if v is not None}
+    kw = dict(shared_gate_up_weight=dev["shared_gate_up_w"], shared_down_weight=dev["shared_down_w"])
+    ref = cpp_to_torch(xstar_cpp.to_cpu(xstar_cpp.moe(dev["x"], dev["router_w"], dev["gate_up_w"], dev["down_w"], 2, **kw)), (40, 512))
+    stream = torch.cuda.Stream()
+    out_t = torch.zeros((40, 512), dtype=torch.bfloat16, device="cuda")
+    out = xstar_cpp.from_device_ptr(out_t.data_ptr(), [40, 512], xstar_cpp.DType.BFloat16)
+    scratch = xstar_cpp.MoEScratch()
+    for _ in range(3):
+        xstar_cpp.moe_into(dev["x"], out, scratch, stream.cuda_stream, dev["router_w"], dev["gate_up_w"], dev["down_w"], 2, **kw)
+    xstar_cpp.moe_check(scratch, stream.cuda_stream)
+    assert scratch.bytes() > 0 and torch.equal(out_t.cpu(), ref)
+    with pytest.raises(RuntimeError, match="shape mismatch"):
+        bad = xstar_cpp.from_device_ptr(out_t.data_ptr(), [20, 512], xstar_cpp.DType.BFloat16)
+        xstar_cpp.moe_into(dev["x"], bad, scratch, 0, dev["router_w"], dev["gate_up_w"], dev["down_w"], 2, **kw)
+    # the synchronous op: a dropped result goes to the cache and the next call takes it from there
+    xstar_cpp.workspace_trim()
+    assert xstar_cpp.result_cache_bytes() == 0
+    r1 = xstar_cpp.moe(dev["x"], dev["router_w"], dev["gate_up_w"], dev["down_w"], 2, **kw)
+    del r1
+    cached = xstar_cpp.result_cache_bytes()
+    assert cached >= 40 * 512 * 2
+    r2 = xstar_cpp.moe(dev["x"], dev["router_w"], dev["gate_up_w"], dev["down_w"], 2, **kw)
+    assert xstar_cpp.result_cache_bytes() == cached - max(4096, 1 << (40 * 512 * 2 - 1).bit_length())
+    assert torch.equal(cpp_to_torch(xstar_cpp.to_cpu(r2), (40, 512)), ref)

@@ -81,6 +81,57 @@ EncodeTiledFn get_encode_fn()
     return fn;
 }
 
+// Encoded maps are kept: a layer call describes the same weight matrices (and, with a reused workspace, the same
+// activation buffers) every time, and an encode costs about a microsecond of host time -- a tenth of a decode step's launch
+// budget when a call needs eight of them.  The key is everything the encoding depends on, so a cached map is exactly the map
+// a fresh encode would give.  Small, linear, thread-safe; the oldest entry is replaced when it is full.
+struct TmapKey {
+    uintptr_t base;
+    uint64_t d0, d1, s0;
+    uint32_t b0, b1;
+    int32_t dt, swizzle, l2;
+    bool operator==(const TmapKey &o) const
+    {
+        return base == o.base && d0 == o.d0 && d1 == o.d1 && s0 == o.s0 && b0 == o.b0 && b1 == o.b1 && dt == o.dt && swizzle == o.swizzle &&
+               l2 == o.l2;
+    }
+};
+CUresult encode_2d_cached(EncodeTiledFn fn, CUtensorMap *m, CUtensorMapDataType dt, const void *base, const cuuint64_t *dims,
+                          const cuuint64_t *strides, const cuuint32_t *box, CUtensorMapSwizzle swz, CUtensorMapL2promotion l2)
+{
+    constexpr int kEntries = 128;
+    struct Entry {
+        TmapKey key;
+        CUtensorMap map;
+    };
+    static std::mutex mu;
+    static std::vector<Entry> table;
+    static size_t next = 0;
+    const TmapKey key{reinterpret_cast<uintptr_t>(base), dims[0], dims[1], strides[0], box[0], box[1], static_cast<int32_t>(dt),
+                      static_cast<int32_t>(swz), static_cast<int32_t>(l2)};
+    {
+        std::lock_guard<std::mutex> lock(mu);
+        for (const Entry &e : table)
+            if (e.key == key) {
+                *m = e.map;
+                return CUDA_SUCCESS;
+            }
+    }
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(m, dt, 2, const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swz, l2,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r == CUDA_SUCCESS) {
+        std::lock_guard<std::mutex> lock(mu);
+        if (table.size() < kEntries) {
+            table.push_back(Entry{key, *m});
+        } else {
+            table[next] = Entry{key, *m};
+            next = (next + 1) % kEntries;
+        }
+    }
+    return r;
+}
+
 // 2-D row-major matrix (rows, cols) of `elem_bytes`-wide elements; box = (box_cols, box_rows); 128-byte swizzle.
 int make_tmap_2d(CUtensorMap *m, CUtensorMapDataType dt, int elem_bytes, const void *base, uint64_t rows, uint64_t cols,
                  uint32_t box_rows, uint32_t box_cols)
@@ -95,9 +146,7 @@ int make_tmap_2d(CUtensorMap *m, CUtensorMapDataType dt, int elem_bytes, const v
     cuuint64_t dims[2] = {cols, rows};
     cuuint64_t strides[1] = {cols * static_cast<uint64_t>(elem_bytes)};
     cuuint32_t box[2] = {box_cols, box_rows};
-    cuuint32_t estr[2] = {1, 1};
-    CUresult r = fn(m, dt, 2, const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    CUresult r = encode_2d_cached(fn, m, dt, base, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B);
     if (r != CUDA_SUCCESS)
         return fail(XS_MOE_ERR_CUDA, "CUDA error: cuTensorMapEncodeTiled failed with code %d (rows=%llu cols=%llu)", (int)r,
                     (unsigned long long)rows, (unsigned long long)cols);
@@ -116,9 +165,8 @@ int make_tmap_bytes(CUtensorMap *m, const void *base, uint64_t rows, uint64_t ro
     cuuint64_t dims[2] = {row_bytes, rows};
     cuuint64_t strides[1] = {row_bytes};
     cuuint32_t box[2] = {box_bytes, box_rows};
-    cuuint32_t estr[2] = {1, 1};
-    CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                    CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    CUresult r = encode_2d_cached(fn, m, CU_TENSOR_MAP_DATA_TYPE_UINT8, base, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE,
+                                  CU_TENSOR_MAP_L2_PROMOTION_NONE);
     if (r != CUDA_SUCCESS)
         return fail(XS_MOE_ERR_CUDA, "CUDA error: cuTensorMapEncodeTiled failed with code %d (rows=%llu row bytes=%llu)", (int)r,
                     (unsigned long long)rows, (unsigned long long)row_bytes);
@@ -740,10 +788,8 @@ int make_tmap_fp4(CUtensorMap *m, const void *base, uint64_t rows, uint64_t k_el
     cuuint64_t dims[2] = {k_elems, rows};
     cuuint64_t strides[1] = {k_elems / 2};
     cuuint32_t box[2] = {128, box_rows};
-    cuuint32_t estr[2] = {1, 1};
-    CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B, 2, const_cast<void *>(base), dims, strides, box, estr,
-                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    CUresult r = encode_2d_cached(fn, m, CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B, base, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B,
+                                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B);
     if (r != CUDA_SUCCESS)
         return fail(XS_MOE_ERR_CUDA, "CUDA error: cuTensorMapEncodeTiled (packed FP4) failed with code %d (rows=%llu k=%llu)", (int)r,
                     (unsigned long long)rows, (unsigned long long)k_elems);

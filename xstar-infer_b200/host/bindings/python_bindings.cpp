@@ -165,7 +165,30 @@ PYBIND11_MODULE(xstar_cpp, m)
     m.def("to_cpu", &to_cpu, py::arg("tensor"));
     m.def("cuda_free_bytes", &cuda_free_bytes);
     m.def("workspace_cached_bytes", [] { return WorkspacePool::instance().cached_bytes(); });
-    m.def("workspace_trim", [] { WorkspacePool::instance().trim(); });
+    m.def("workspace_trim", [] {
+        WorkspacePool::instance().trim();
+        cuda_trim_cached();
+    });
+    m.def("result_cache_bytes", &cuda_cached_result_bytes);
+    py::class_<MoEScratch>(m, "MoEScratch").def(py::init<>()).def("bytes", &MoEScratch::bytes);
+    m.def(
+        "moe_into",
+        [](const Tensor &x, Tensor &out, MoEScratch &scratch, std::uintptr_t stream, const Tensor &router_weight, const Tensor &gate_up_weight,
+           const Tensor &down_weight, std::int64_t top_k, py::object router_bias, py::object gate_up_scale, py::object down_scale,
+           py::object shared_gate_up_weight, py::object shared_down_weight, py::object shared_gate_up_scale, py::object shared_down_scale) {
+            MoEWeights w = weights_of(router_weight, gate_up_weight, down_weight, router_bias, gate_up_scale, down_scale, shared_gate_up_weight,
+                                      shared_down_weight, shared_gate_up_scale, shared_down_scale);
+            MoEConfig cfg;
+            cfg.top_k = top_k;
+            py::gil_scoped_release nogil;
+            moe_into(x, w, cfg, out, scratch, reinterpret_cast<void *>(stream));
+        },
+        py::arg("x"), py::arg("out"), py::arg("scratch"), py::arg("stream"), py::arg("router_weight"), py::arg("gate_up_weight"),
+        py::arg("down_weight"), py::arg("top_k"), py::arg("router_bias") = py::none(), py::arg("gate_up_scale") = py::none(),
+        py::arg("down_scale") = py::none(), py::arg("shared_gate_up_weight") = py::none(), py::arg("shared_down_weight") = py::none(),
+        py::arg("shared_gate_up_scale") = py::none(), py::arg("shared_down_scale") = py::none());
+    m.def("moe_check", [](MoEScratch &s, std::uintptr_t stream) { moe_check(s, reinterpret_cast<void *>(stream)); }, py::arg("scratch"),
+          py::arg("stream") = 0, py::call_guard<py::gil_scoped_release>());
 
     m.def("moe", &moe_py, py::arg("x"), py::arg("router_weight"), py::arg("gate_up_weight"), py::arg("down_weight"), py::arg("top_k"),
           py::arg("router_bias") = py::none(), py::arg("gate_up_scale") = py::none(), py::arg("down_scale") = py::none(),

@@ -41,6 +41,17 @@ private:
     std::vector<Lease> free_;
 };
 
+// Recycled device blocks for RESULT tensors.  The reference's ops return a fresh Tensor whose bytes come from cudaMalloc
+// and go back with cudaFree (xstar_cpp/src/tensor.cpp:34-37) -- two device-wide synchronisations per call.  The MoE ops
+// take their results from this cache instead: blocks are kept per device and size class (powers of two from 4 KB) and
+// handed out again once their Tensor died.  A block goes back as soon as its Tensor is destroyed; with the synchronous ops
+// ("returns => finished") that is always after the work that wrote it, and a caller of the stream forms must keep a result
+// alive until its stream has passed the call, as with any asynchronous API.
+void *cuda_alloc_cached(std::size_t bytes);
+void cuda_free_cached(void *ptr) noexcept;
+std::size_t cuda_cached_result_bytes();
+void cuda_trim_cached() noexcept;
+
 // RAII lease
 class Workspace
 {

@@ -57,6 +57,35 @@ Tensor moe(const Tensor &x, const MoEWeights &weights, const MoEConfig &config);
 // residual add rides in the combine kernel: no extra pass over the activations.
 Tensor moe_block(const Tensor &x, const Tensor &norm_weight, float eps, const MoEWeights &weights, const MoEConfig &config);
 
+// Stream forms for an engine that runs its layers on a stream of its own.  The reference's ops are synchronous on the
+// default stream (xstar_cpp/src/ops/mlp.cu:188-189); its roadmap row "explicit streams" (README.md:33) is what these are
+// for.  moe_into / moe_block_into enqueue the layer on `stream` (nullptr = the default stream) and return without waiting;
+// x, the weights, `out` (same shape as x, bf16, on the device) and `scratch` must stay alive until the stream has passed
+// the call.  MoEScratch is the layer's scratch between calls: it grows to what the largest call needed (leased from the
+// workspace pool, given back on destruction) and carries the device-side status word; moe_check waits for the stream and
+// raises what the kernels flagged.  One scratch serves calls that do not overlap on the device (one stream, or streams that
+// the caller orders).
+class MoEScratch
+{
+public:
+    MoEScratch() = default;
+    ~MoEScratch();
+    MoEScratch(const MoEScratch &) = delete;
+    MoEScratch &operator=(const MoEScratch &) = delete;
+    void *data() const { return ptr_; }
+    std::size_t bytes() const { return bytes_; }
+    void reserve(std::size_t bytes); // synchronises when it has to grow (the old block may still be in use)
+
+private:
+    void *ptr_ = nullptr;
+    std::size_t bytes_ = 0;
+    int device_ = 0;
+};
+void moe_into(const Tensor &x, const MoEWeights &weights, const MoEConfig &config, Tensor &out, MoEScratch &scratch, void *stream);
+void moe_block_into(const Tensor &x, const Tensor &norm_weight, float eps, const MoEWeights &weights, const MoEConfig &config, Tensor &out,
+                    MoEScratch &scratch, void *stream);
+void moe_check(MoEScratch &scratch, void *stream);
+
 // Routing decisions for inspection and tests: ids (T, k) ascending per row, weights (T, k),
 // counts (E), offsets (E+1), perm (T*k), inv (T*k).  Host vectors; x and router tensors on the device.
 struct MoERouting {

@@ -18,6 +18,9 @@ public:
     Tensor(Shape shape, DType dtype, Device device = Device::CPU);
     // borrowing view of memory that outlives this object
     Tensor(const void *ptr, Shape shape, DType dtype, Device device);
+    // owning device tensor whose bytes come from, and return to, the result cache (cuda/cuda_allocator.h): what the MoE ops
+    // return, so that a call costs no cudaMalloc / cudaFree once the sizes have been seen
+    static Tensor result(Shape shape, DType dtype);
     ~Tensor();
 
     Tensor(const Tensor &) = delete;
@@ -58,6 +61,7 @@ private:
     DType dtype_ = DType::Float32;
     Device device_ = Device::CPU;
     bool owner_ = false;
+    bool cached_ = false; // owner_ && bytes from the result cache
 };
 
 Tensor to_cuda(const Tensor &t); // throws unless t is on the CPU

@@ -1,7 +1,10 @@
 #include "cuda/cuda_allocator.h"
 
+#include <map>
 #include <stdexcept>
 #include <string>
+#include <unordered_map>
+#include <utility>
 
 #include "xs_moe.h"
 
@@ -41,6 +44,86 @@ int cuda_current_device()
     return d;
 }
 void cuda_set_device(int device) { raise_if(xs_moe_set_device(device)); }
+
+namespace {
+struct ResultCache {
+    std::mutex mu;
+    std::map<std::pair<int, std::size_t>, std::vector<void *>> free_blocks;       // (device, class bytes) -> blocks
+    std::unordered_map<void *, std::pair<int, std::size_t>> live;                 // block -> (device, class bytes)
+    std::size_t cached = 0;
+};
+ResultCache &result_cache()
+{
+    static ResultCache c;
+    return c;
+}
+std::size_t size_class(std::size_t bytes)
+{
+    std::size_t c = 4096;
+    while (c < bytes)
+        c <<= 1;
+    return c;
+}
+} // namespace
+
+void *cuda_alloc_cached(std::size_t bytes)
+{
+    const int dev = cuda_current_device();
+    const std::size_t cls = size_class(bytes);
+    ResultCache &c = result_cache();
+    {
+        std::lock_guard<std::mutex> g(c.mu);
+        auto it = c.free_blocks.find({dev, cls});
+        if (it != c.free_blocks.end() && !it->second.empty()) {
+            void *p = it->second.back();
+            it->second.pop_back();
+            c.cached -= cls;
+            c.live[p] = {dev, cls};
+            return p;
+        }
+    }
+    void *p = cuda_alloc(cls);
+    std::lock_guard<std::mutex> g(c.mu);
+    c.live[p] = {dev, cls};
+    return p;
+}
+
+void cuda_free_cached(void *ptr) noexcept
+{
+    if (!ptr)
+        return;
+    ResultCache &c = result_cache();
+    try {
+        std::lock_guard<std::mutex> g(c.mu);
+        auto it = c.live.find(ptr);
+        if (it == c.live.end()) {
+            cuda_free(ptr); // not one of ours
+            return;
+        }
+        c.free_blocks[it->second].push_back(ptr);
+        c.cached += it->second.second;
+        c.live.erase(it);
+    } catch (...) {
+    }
+}
+
+std::size_t cuda_cached_result_bytes()
+{
+    ResultCache &c = result_cache();
+    std::lock_guard<std::mutex> g(c.mu);
+    return c.cached;
+}
+
+void cuda_trim_cached() noexcept
+{
+    ResultCache &c = result_cache();
+    std::lock_guard<std::mutex> g(c.mu);
+    for (auto &kv : c.free_blocks)
+        for (void *p : kv.second)
+            cuda_free(p);
+    c.free_blocks.clear();
+    c.cached = 0;
+}
 
 WorkspacePool &WorkspacePool::instance()
 {

@@ -135,6 +135,86 @@ Checked validate(const Tensor &x, const MoEWeights &m, const MoEConfig &config, 
 using moe_detail::Checked;
 using moe_detail::raise_if;
 
+MoEScratch::~MoEScratch()
+{
+    if (ptr_) {
+        WorkspacePool::Lease l;
+        l.ptr = ptr_;
+        l.bytes = bytes_;
+        l.device = device_;
+        WorkspacePool::instance().release(l);
+    }
+}
+
+void MoEScratch::reserve(std::size_t bytes)
+{
+    if (bytes <= bytes_ && ptr_)
+        return;
+    if (ptr_) {
+        raise_if(xs_moe_stream_synchronize(nullptr)); // legacy default stream: waits for every blocking stream of the device
+        WorkspacePool::Lease old;
+        old.ptr = ptr_;
+        old.bytes = bytes_;
+        old.device = device_;
+        WorkspacePool::instance().release(old);
+        ptr_ = nullptr;
+        bytes_ = 0;
+    }
+    WorkspacePool::Lease l = WorkspacePool::instance().acquire(bytes);
+    ptr_ = l.ptr;
+    bytes_ = l.bytes;
+    device_ = l.device;
+}
+
+namespace {
+void check_out(const Tensor &x, const Tensor &out)
+{
+    if (out.dtype() != DType::BFloat16)
+        throw std::runtime_error("dtype mismatch");
+    if (out.numel() != x.numel())
+        throw std::runtime_error("shape mismatch");
+    if (out.device() != Device::CUDA || x.device() != Device::CUDA)
+        throw std::runtime_error("unsupported device");
+}
+} // namespace
+
+void moe_into(const Tensor &x, const MoEWeights &weights, const MoEConfig &config, Tensor &out, MoEScratch &scratch, void *stream)
+{
+    Checked c = moe_detail::validate(x, weights, config, true);
+    check_out(x, out);
+    std::size_t need = 0;
+    raise_if(xs_moe_workspace_bytes(&c.cfg, &need));
+    scratch.reserve(need);
+    raise_if(xs_moe_forward(&c.cfg, &c.w, x.data(), out.data(), scratch.data(), scratch.bytes(), stream));
+}
+
+void moe_block_into(const Tensor &x, const Tensor &norm_weight, float eps, const MoEWeights &weights, const MoEConfig &config, Tensor &out,
+                    MoEScratch &scratch, void *stream)
+{
+    if (norm_weight.dtype() != DType::BFloat16)
+        throw std::runtime_error("dtype mismatch");
+    if (norm_weight.rank() != 1)
+        throw std::runtime_error("rank mismatch");
+    Checked c = moe_detail::validate(x, weights, config, true);
+    if (norm_weight.dim(0) != x.dim(-1))
+        throw std::runtime_error("shape mismatch");
+    if (norm_weight.device() != x.device())
+        throw std::runtime_error("device mismatch");
+    check_out(x, out);
+    std::size_t need = 0;
+    raise_if(xs_moe_block_workspace_bytes(&c.cfg, &need));
+    scratch.reserve(need);
+    raise_if(xs_moe_block_forward(&c.cfg, &c.w, x.data(), norm_weight.data(), eps, out.data(), scratch.data(), scratch.bytes(), stream));
+}
+
+void moe_check(MoEScratch &scratch, void *stream)
+{
+    if (scratch.data())
+        raise_if(xs_moe_check_flags(scratch.data(), stream));
+    else
+        raise_if(xs_moe_stream_synchronize(stream));
+}
+
 Tensor moe(const Tensor &x, const MoEWeights &weights, const MoEConfig &config)
 {
     Checked c = moe_detail::validate(x, weights, config, true);
@@ -142,7 +222,7 @@ Tensor moe(const Tensor &x, const MoEWeights &weights, const MoEConfig &config)
         throw std::runtime_error("unsupported device");
     std::size_t need = 0;
     raise_if(xs_moe_workspace_bytes(&c.cfg, &need));
-    Tensor out(x.shape(), DType::BFloat16, Device::CUDA);
+    Tensor out = Tensor::result(x.shape(), DType::BFloat16);
     Workspace ws(need);
     // explicit stream semantics of the engine: default stream, and "returns => finished"
     // (reference xstar_cpp/src/ops/mlp.cu:188-189), with ONE synchronisation at op exit
@@ -166,7 +246,7 @@ Tensor moe_block(const Tensor &x, const Tensor &norm_weight, float eps, const Mo
         throw std::runtime_error("unsupported device");
     std::size_t need = 0;
     raise_if(xs_moe_block_workspace_bytes(&c.cfg, &need));
-    Tensor out(x.shape(), DType::BFloat16, Device::CUDA);
+    Tensor out = Tensor::result(x.shape(), DType::BFloat16);
     Workspace ws(need);
     raise_if(xs_moe_block_forward(&c.cfg, &c.w, x.data(), norm_weight.data(), eps, out.data(), ws.data(), ws.bytes(), nullptr));
     raise_if(xs_moe_check_flags(ws.data(), nullptr));

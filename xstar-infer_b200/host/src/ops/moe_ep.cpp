@@ -411,7 +411,7 @@ Tensor moe(const Tensor &x, const MoEWeights &weights, const MoEConfig &config, 
 {
     if (!ep)
         return moe(x, weights, config);
-    Tensor out(x.shape(), DType::BFloat16, Device::CUDA);
+    Tensor out = Tensor::result(x.shape(), DType::BFloat16);
     ep->forward_into(x, weights, config, out, nullptr);
     ep->check(nullptr);
     return out;

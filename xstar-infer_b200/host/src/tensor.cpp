@@ -48,11 +48,22 @@ Tensor::Tensor(const void *ptr, Shape shape, DType dtype, Device device)
     layout();
 }
 
+Tensor Tensor::result(Shape shape, DType dtype)
+{
+    Tensor t(nullptr, std::move(shape), dtype, Device::CUDA);
+    t.bytes_ = cuda_alloc_cached(padded(t.nbytes()));
+    t.owner_ = true;
+    t.cached_ = true;
+    return t;
+}
+
 void Tensor::drop() noexcept
 {
     if (owner_ && bytes_) {
         if (device_ == Device::CPU)
             std::free(bytes_);
+        else if (cached_)
+            cuda_free_cached(bytes_);
         else
             cuda_free(bytes_);
     }
@@ -66,7 +77,7 @@ Tensor::~Tensor()
 
 Tensor::Tensor(Tensor &&o) noexcept
     : bytes_(std::exchange(o.bytes_, nullptr)), shape_(std::move(o.shape_)), strides_(std::move(o.strides_)), numel_(o.numel_),
-      dtype_(o.dtype_), device_(o.device_), owner_(o.owner_)
+      dtype_(o.dtype_), device_(o.device_), owner_(o.owner_), cached_(o.cached_)
 {
 }
 
@@ -81,6 +92,7 @@ Tensor &Tensor::operator=(Tensor &&o) noexcept
         dtype_ = o.dtype_;
         device_ = o.device_;
         owner_ = o.owner_;
+        cached_ = o.cached_;
     }
     return *this;
 }
