@@ -275,6 +275,20 @@ int xs_moe_ep_return(const XsMoeConfig *cfg, int32_t ranks, int32_t rank, const 
                      int32_t y_capacity_rows, void *const *peer_back_dev, int32_t back_capacity_rows, int32_t wire_bf16,
                      void *workspace_dev, void *stream);
 
+/* xs_moe_grouped_mlp with the return trip folded into the down GEMM: instead of writing f32 rows to y for xs_moe_ep_return
+ * to carry, the epilogue rounds each output row to bf16 and stores it straight into its source rank's return buffer
+ * (row src_offsets[s][e] + j, as xs_moe_ep_return computes it), tile by tile, so the NVLink transfer overlaps the math and
+ * the f32 y buffer is neither written nor read.  `cfg` carries this rank's expert slice (local_expert_begin / _count).
+ * Implemented for FP4 experts with hidden % 256 == 0 (the tokens-as-M kernels); xs_moe_grouped_mlp_return_supported says
+ * whether a configuration takes it, other configurations get XS_MOE_ERR_UNSUPPORTED and use the two-step form.  Destination
+ * rows outside [0, back_capacity_rows) are skipped and flagged.  The caller's barrier after this call takes the place of
+ * the one after xs_moe_ep_return. */
+int xs_moe_grouped_mlp_return_supported(const XsMoeConfig *cfg, int32_t max_rows, int32_t *supported);
+int xs_moe_grouped_mlp_return(const XsMoeConfig *cfg, const XsMoeWeights *w, const void *rows_dev, const float *row_scales_dev,
+                              const int32_t *offsets_local_dev, int32_t max_rows, int32_t ranks, int32_t rank,
+                              const int32_t *all_counts_dev, const int32_t *src_offsets_dev, void *const *peer_back_dev,
+                              int32_t back_capacity_rows, void *workspace_dev, size_t workspace_bytes, void *stream);
+
 /* Reads and clears the device-side status word the kernels of the last calls on this workspace wrote
  * (bounded waits that gave up, index checks that failed).  Synchronises the stream. */
 int xs_moe_check_flags(void *workspace_dev, void *stream);

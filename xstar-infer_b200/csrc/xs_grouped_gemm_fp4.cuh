@@ -31,6 +31,17 @@ struct MxScales {
     int max_rows;           // rows of x_scale (for clamping reads past the last segment)
 };
 
+// Expert-parallel return trip folded into the down GEMM's epilogue: with peer_back set, output row g of local expert el
+// -- the j-th row that source rank s sent for that expert -- is rounded to bf16 and stored straight into row
+// src_offsets[s][e] + j of rank s's return buffer (plain peer stores over NVLink), instead of going to y as f32 for a
+// separate return kernel to pick up.  all_counts (ranks, experts), src_offsets (ranks, experts): the tables of ep_plan.
+struct EpReturnArgs {
+    uint8_t *const *peer_back = nullptr; // `ranks` pointers (this rank's own buffer included); null: store f32 rows to y
+    const int32_t *all_counts = nullptr;
+    const int32_t *src_offsets = nullptr;
+    int experts = 0, ranks = 1, me = 0, back_capacity = 0;
+};
+
 // smallest e8m0 exponent whose power of two is >= v (v > 0, normal)
 __device__ __forceinline__ uint32_t e8m0_ceil(float v)
 {

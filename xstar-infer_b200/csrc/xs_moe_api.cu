@@ -735,7 +735,8 @@ int launch_gemm_fp4(int n_tile, const CUtensorMap &tw, const CUtensorMap &tx, co
 // the token box of tx).
 template <bool GATE_UP>
 int launch_prefill_fp4(const CUtensorMap &tw, const CUtensorMap &tx, const int32_t *offsets, xs::TileTable tt, xs::MxScales sc, int w_rows,
-                       uint64_t w_scale_rows, int n_out, int K, void *out, int32_t *status, int max_work, int tile_rows, cudaStream_t st)
+                       uint64_t w_scale_rows, int n_out, int K, void *out, int32_t *status, int max_work, int tile_rows, cudaStream_t st,
+                       const xs::EpReturnArgs &ret = xs::EpReturnArgs{})
 {
     DeviceInfo di;
     if (int rc = device_info(&di))
@@ -770,7 +771,7 @@ int launch_prefill_fp4(const CUtensorMap &tw, const CUtensorMap &tx, const int32
     int grid = di.sms < max_work ? di.sms : max_work;
     if (grid < 1)
         grid = 1;
-    kern<<<grid, xs::kPf4Threads, smem, st>>>(tw, tx, t_ws, t_xs, offsets, tt, sc, w_rows, n_out, K, out, status, stages, tile_rows, sf_tma);
+    kern<<<grid, xs::kPf4Threads, smem, st>>>(tw, tx, t_ws, t_xs, offsets, tt, sc, w_rows, n_out, K, out, status, stages, tile_rows, sf_tma, ret);
     note_launch();
     XS_CUDA(cudaGetLastError());
     return 0;
@@ -812,7 +813,14 @@ struct GroupedArgs {
     GroupedPlan gp;
     int32_t *status = nullptr;
     bool tiles_ready = false; // the tile table was already built (fused routing kernel)
+    xs::EpReturnArgs ret;     // expert-parallel return folded into the down epilogue (kernels that support it)
 };
+
+// does run_grouped take the tokens-as-M FP4 kernels for this problem (the ones whose down epilogue can store to peers)?
+bool grouped_supports_fused_return(int fmt, int H, int I, const GroupedPlan &gp)
+{
+    return fmt == XS_MOE_FP4_MX32 && H % 256 == 0 && I % 128 == 0 && (gp.n_tile == 128 || (gp.n_tile == 32 && XS_FP4_TOKENS_AS_M));
+}
 
 int run_grouped(const GroupedArgs &a, cudaStream_t st, cudaEvent_t mid = nullptr)
 {
@@ -892,8 +900,10 @@ int run_grouped(const GroupedArgs &a, cudaStream_t st, cudaEvent_t mid = nullptr
                 XS_CUDA(cudaEventRecord(mid, st));
             xs::MxScales p2{static_cast<const uint8_t *>(a.dw_scale), act_scale, nullptr, a.max_rows};
             return launch_prefill_fp4<false>(t_wd, t_act, offs, tt, p2, H, static_cast<uint64_t>(groups) * H, H, I, a.y, a.status,
-                                             a.gp.max_tiles * (H / 256), a.gp.n_tile, st);
+                                             a.gp.max_tiles * (H / 256), a.gp.n_tile, st, a.ret);
         }
+        if (a.ret.peer_back)
+            return fail(XS_MOE_ERR_UNSUPPORTED, "the fused expert-parallel return needs the tokens-as-M FP4 kernels (hidden % 256 == 0)");
         xs::MxScales s1{static_cast<const uint8_t *>(a.gu_scale), reinterpret_cast<const uint8_t *>(a.row_scale), act_scale, a.max_rows};
         if (int rc = launch_gemm_fp4<true>(a.gp.n_tile, t_wgu, t_x, offs, tt, s1, 2 * I, I, H, act, a.status,
                                            a.gp.max_tiles * (I / xs::kTileM), st))
@@ -904,6 +914,8 @@ int run_grouped(const GroupedArgs &a, cudaStream_t st, cudaEvent_t mid = nullptr
         return launch_gemm_fp4<false>(a.gp.n_tile, t_wd, t_act, offs, tt, s2, H, H, I, a.y, a.status,
                                       a.gp.max_tiles * (H / xs::kTileM), st);
     }
+    if (a.ret.peer_back)
+        return fail(XS_MOE_ERR_UNSUPPORTED, "the fused expert-parallel return is implemented for FP4 experts");
     const CUtensorMapDataType dt = fp8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
     const int eb = fp8 ? 1 : 2;
     const uint32_t box_k = fp8 ? xs::kBlockK8 : xs::kBlockK;
@@ -1188,6 +1200,68 @@ int xs_moe_grouped_mlp(const XsMoeConfig *cfg, const XsMoeWeights *w, const void
     a.y = y;
     a.scratch = b + kStatusBytes;
     a.status = reinterpret_cast<int32_t *>(b);
+    return run_grouped(a, static_cast<cudaStream_t>(stream));
+}
+
+static int check_ep(int32_t ranks, int32_t rank, int32_t experts);
+
+int xs_moe_grouped_mlp_return_supported(const XsMoeConfig *cfg, int32_t max_rows, int32_t *supported)
+{
+    if (int rc = check_cfg(cfg))
+        return rc;
+    if (!supported || max_rows < 0)
+        return fail(XS_MOE_ERR_INVALID_ARG, "null out-pointer");
+    const GroupedPlan gp = plan_grouped_stage(cfg, max_rows);
+    *supported = (cfg->gemm_impl == 0 && grouped_supports_fused_return(cfg->routed_format, cfg->hidden, cfg->intermediate, gp)) ? 1 : 0;
+    return 0;
+}
+
+int xs_moe_grouped_mlp_return(const XsMoeConfig *cfg, const XsMoeWeights *w, const void *rows, const float *row_scales,
+                              const int32_t *offsets, int32_t max_rows, int32_t ranks, int32_t rank, const int32_t *all_counts,
+                              const int32_t *src_offsets, void *const *peer_back, int32_t back_capacity_rows, void *ws, size_t ws_bytes,
+                              void *stream)
+{
+    if (int rc = check_cfg(cfg))
+        return rc;
+    if (int rc = check_ep(ranks, rank, cfg->num_experts))
+        return rc;
+    if (!w || !rows || !offsets || !all_counts || !src_offsets || !peer_back || !w->gate_up_w_dev || !w->down_w_dev)
+        return fail(XS_MOE_ERR_INVALID_ARG, "null tensor pointer");
+    if (max_rows < 0 || back_capacity_rows < 0)
+        return fail(XS_MOE_ERR_INVALID_ARG, "shape mismatch: negative row capacity");
+    if (cfg->local_expert_count * ranks != cfg->num_experts || cfg->local_expert_begin != rank * cfg->local_expert_count)
+        return fail(XS_MOE_ERR_INVALID_ARG, "expert count mismatch: the config's expert slice is not this rank's");
+    if (int rc = xs_moe_device_check())
+        return rc;
+    GroupedArgs a;
+    a.gp = plan_grouped_stage(cfg, max_rows);
+    if (cfg->gemm_impl != 0 || !grouped_supports_fused_return(cfg->routed_format, cfg->hidden, cfg->intermediate, a.gp))
+        return fail(XS_MOE_ERR_UNSUPPORTED, "the fused expert-parallel return is implemented for FP4 experts with hidden % 256 == 0");
+    if (int rc = check_workspace(ws, ws_bytes, kStatusBytes + a.gp.bytes))
+        return rc;
+    uint8_t *b = static_cast<uint8_t *>(ws);
+    a.fmt = cfg->routed_format;
+    a.H = cfg->hidden;
+    a.I = cfg->intermediate;
+    a.groups = cfg->local_expert_count;
+    a.gu = w->gate_up_w_dev;
+    a.gu_scale = w->gate_up_scale_dev;
+    a.dw = w->down_w_dev;
+    a.dw_scale = w->down_scale_dev;
+    a.rows = rows;
+    a.row_scale = row_scales;
+    a.offsets = offsets;
+    a.max_rows = max_rows;
+    a.y = nullptr;
+    a.scratch = b + kStatusBytes;
+    a.status = reinterpret_cast<int32_t *>(b);
+    a.ret.peer_back = reinterpret_cast<uint8_t *const *>(peer_back);
+    a.ret.all_counts = all_counts;
+    a.ret.src_offsets = src_offsets;
+    a.ret.experts = cfg->num_experts;
+    a.ret.ranks = ranks;
+    a.ret.me = rank;
+    a.ret.back_capacity = back_capacity_rows;
     return run_grouped(a, static_cast<cudaStream_t>(stream));
 }
 

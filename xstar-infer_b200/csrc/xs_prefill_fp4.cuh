@@ -40,7 +40,7 @@ __global__ void __launch_bounds__(kPf4Threads, 1)
 prefill_gemm_fp4_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
                         const __grid_constant__ CUtensorMap tmap_ws, const __grid_constant__ CUtensorMap tmap_xs,
                         const int32_t *__restrict__ offsets, TileTable tt, MxScales sc, int w_rows_per_expert, int n_out, int K,
-                        void *__restrict__ out, int32_t *__restrict__ status, int stages, int tile_rows, int sf_tma)
+                        void *__restrict__ out, int32_t *__restrict__ status, int stages, int tile_rows, int sf_tma, EpReturnArgs ret)
 {
     constexpr int X_BYTES = kPfTokens * kBlockK8;
     constexpr int W_HALF = 128 * kBlockK8;               // shared-memory footprint (one code per byte)

@@ -98,7 +98,7 @@
             if (lane == 0)
                 mbar_arrive(tmem_empty);
             // (all lanes of an active warp take part in the quad transposes; rows past the segment are not stored)
-            if (active) {
+            if (active && ret.peer_back == nullptr) {
                 const int qd = lane & 3;
                 const int rq = q * 32 + (lane & ~3); // first row of the quad within the tile
                 float *ybase = static_cast<float *>(out) + static_cast<size_t>(row0 + rq) * n_out + nt * 256 + 128 * half;
@@ -113,6 +113,53 @@
                     for (int r = 0; r < 4; r++)
                         if (rq + r < nvalid)
                             *reinterpret_cast<uint4 *>(ybase + static_cast<size_t>(r) * n_out + i * 16 + qd * 4) = b[r];
+                }
+            } else if (active) {
+                // Expert-parallel return: this thread's row is the j-th row source rank s sent for this expert; it goes, as
+                // bf16, to row src_offsets[s][e] + j of that rank's return buffer.
+                uint8_t *dst = nullptr;
+                if (valid) {
+                    const int El = ret.experts / ret.ranks;
+                    const int eg = ret.me * El + e;
+                    int j = row0 + r - offsets[e];
+                    int s = 0;
+                    while (s < ret.ranks - 1 && j >= ret.all_counts[s * ret.experts + eg]) {
+                        j -= ret.all_counts[s * ret.experts + eg];
+                        s++;
+                    }
+                    const int drow = ret.src_offsets[s * ret.experts + eg] + j;
+                    if (drow >= 0 && drow < ret.back_capacity)
+                        dst = ret.peer_back[s] + (static_cast<size_t>(drow) * n_out + nt * 256 + 128 * half) * 2;
+                    else
+                        atomicOr(status, kStatusBadIndex);
+                }
+                const int qd = lane & 3;
+                const unsigned long long mine = reinterpret_cast<unsigned long long>(dst);
+                unsigned long long qdst[4]; // destinations of the four rows of this lane's quad
+#pragma unroll
+                for (int rr = 0; rr < 4; rr++)
+                    qdst[rr] = __shfl_sync(0xffffffffu, mine, (lane & ~3) + rr);
+                // 128 f32 columns -> 64 bf16 pairs = 16 chunks of 16 bytes (8 columns each); quads transpose four chunks at a
+                // time, so each store instruction writes 64 contiguous bytes per row
+#pragma unroll
+                for (int m = 0; m < 4; m++) {
+                    uint4 b[4];
+#pragma unroll
+                    for (int v = 0; v < 4; v++) {
+                        const uint32_t *src = &y[(4 * m + v) >> 1][((4 * m + v) & 1) * 8];
+                        uint32_t pk[4];
+#pragma unroll
+                        for (int u = 0; u < 4; u++) {
+                            const __nv_bfloat162 h2 = __floats2bfloat162_rn(__uint_as_float(src[2 * u]), __uint_as_float(src[2 * u + 1]));
+                            pk[u] = *reinterpret_cast<const uint32_t *>(&h2);
+                        }
+                        b[v] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+                    }
+                    quad_transpose_chunks(b, qd); // b[rr] = chunk 4 m + qd (8 columns) of row rq + rr
+#pragma unroll
+                    for (int rr = 0; rr < 4; rr++)
+                        if (qdst[rr])
+                            *reinterpret_cast<uint4 *>(reinterpret_cast<uint8_t *>(qdst[rr]) + (4 * m + qd) * 16) = b[rr];
                 }
             }
         }

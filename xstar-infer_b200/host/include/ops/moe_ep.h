@@ -44,6 +44,9 @@ struct EpOptions {
     // Otherwise capacity_factor * T * k rows (T * k is a rank's share under balanced routing; 2 is generous); rows
     // that would not fit are dropped and flagged -- check() then throws "out-of-range index".
     double capacity_factor = 0.0;
+    // Let the down GEMM's epilogue store the result rows into their source ranks (where the kernels support it: FP4 experts
+    // with hidden % 256 == 0) instead of a separate return kernel after the GEMM.  Same bits either way.
+    bool fused_return = true;
 };
 
 // rows a receive buffer holds for these sizes (the rule of EpOptions::capacity_factor), a multiple of 128
@@ -62,6 +65,7 @@ public:
     int rank() const;
     int world() const;
     std::int64_t capacity_rows() const;
+    bool fused_return() const; // whether steps of this context take the fused return path
 
     // One step, enqueued on `stream` (nullptr = the default stream), no host synchronisation after the check-in with
     // the group: x (T, H) bf16 and out (T, H) bf16 on this rank's device, T <= max_tokens.  `weights` holds the router

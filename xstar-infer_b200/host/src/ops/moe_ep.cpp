@@ -99,6 +99,7 @@ struct EpContext::Impl {
     int fmt = XS_MOE_BF16, fmt_shared = XS_MOE_BF16;
     std::int64_t El = 0, capacity = 0, back_rows = 0;
     bool wire_bf16 = false;
+    bool fused_return = false; // the down GEMM's epilogue stores the result rows into their source ranks itself
     void *comm = nullptr;
     void *side = nullptr, *ev_fork = nullptr, *ev_join = nullptr;
     std::uint64_t steps = 0;
@@ -202,7 +203,6 @@ EpContext::EpContext(std::shared_ptr<EpGroup> group, const EpUniqueId &id, int r
     m.scales = DevBuf(m.capacity * scale_bytes);
     m.back = DevBuf(m.back_rows * H * (m.wire_bf16 ? 2 : 4));
     m.tables = DevBuf(3 * R * sizeof(void *));
-    m.y_grouped = DevBuf(static_cast<std::size_t>(m.capacity) * H * 4);
     m.topk_w = DevBuf(T * K * 4);
 
     // small int arrays carved from one allocation (each 256-byte aligned)
@@ -237,6 +237,11 @@ EpContext::EpContext(std::shared_ptr<EpGroup> group, const EpUniqueId &id, int r
     raise_if(xs_moe_grouped_mlp_workspace_bytes(&c_local, static_cast<int32_t>(m.capacity), &m.ws_grouped_bytes));
     m.ws_grouped = DevBuf(m.ws_grouped_bytes);
     raise_if(xs_moe_workspace_init(m.ws_grouped.p, m.ws_grouped_bytes, nullptr));
+    std::int32_t fused = 0;
+    raise_if(xs_moe_grouped_mlp_return_supported(&c_local, static_cast<int32_t>(m.capacity), &fused));
+    m.fused_return = fused != 0 && m.wire_bf16 && options.fused_return;
+    if (!m.fused_return)
+        m.y_grouped = DevBuf(static_cast<std::size_t>(m.capacity) * H * 4);
     if (shape.shared) {
         const XsMoeConfig c_sh = m.cfg(T, m.fmt_shared, 0, 1);
         raise_if(xs_moe_grouped_mlp_workspace_bytes(&c_sh, static_cast<int32_t>(T), &m.ws_shared_bytes));
@@ -303,6 +308,10 @@ int EpContext::world() const
 std::int64_t EpContext::capacity_rows() const
 {
     return impl_->capacity;
+}
+bool EpContext::fused_return() const
+{
+    return impl_->fused_return;
 }
 
 void EpContext::abandon() noexcept
@@ -376,11 +385,18 @@ void EpContext::forward_into(const Tensor &x, const MoEWeights &weights, const M
                                 static_cast<int32_t>(m.capacity), m.ws_route.p, stream));
     raise_if(xs_moe_comm_barrier(m.comm, m.token, stream)); // every rank's rows have landed
     XsMoeWeights w_local = c.w;
-    raise_if(xs_moe_grouped_mlp(&c_local, &w_local, m.rows.p, m.fmt == XS_MOE_BF16 ? nullptr : m.scales.as<float>(), m.offsets_local,
-                                static_cast<int32_t>(m.capacity), m.y_grouped.as<float>(), m.ws_grouped.p, m.ws_grouped_bytes, stream));
-    raise_if(xs_moe_ep_return(&c_route, R, m.rank, m.y_grouped.as<float>(), m.all_counts, m.offsets_local, m.src_offsets,
-                              static_cast<int32_t>(m.capacity), t_back, static_cast<int32_t>(m.back_rows), m.wire_bf16 ? 1 : 0,
-                              m.ws_route.p, stream));
+    if (m.fused_return) {
+        // the down GEMM stores each finished tile's rows into their source ranks: the return trip overlaps the math
+        raise_if(xs_moe_grouped_mlp_return(&c_local, &w_local, m.rows.p, m.scales.as<float>(), m.offsets_local, static_cast<int32_t>(m.capacity), R,
+                                           m.rank, m.all_counts, m.src_offsets, t_back, static_cast<int32_t>(m.back_rows), m.ws_grouped.p,
+                                           m.ws_grouped_bytes, stream));
+    } else {
+        raise_if(xs_moe_grouped_mlp(&c_local, &w_local, m.rows.p, m.fmt == XS_MOE_BF16 ? nullptr : m.scales.as<float>(), m.offsets_local,
+                                    static_cast<int32_t>(m.capacity), m.y_grouped.as<float>(), m.ws_grouped.p, m.ws_grouped_bytes, stream));
+        raise_if(xs_moe_ep_return(&c_route, R, m.rank, m.y_grouped.as<float>(), m.all_counts, m.offsets_local, m.src_offsets,
+                                  static_cast<int32_t>(m.capacity), t_back, static_cast<int32_t>(m.back_rows), m.wire_bf16 ? 1 : 0,
+                                  m.ws_route.p, stream));
+    }
     raise_if(xs_moe_comm_barrier(m.comm, m.token, stream)); // every expert output for this rank's tokens has landed
     const float *shared_y = nullptr;
     if (m.shape.shared) {
