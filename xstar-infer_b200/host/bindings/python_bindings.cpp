@@ -13,6 +13,7 @@
 #include "ops/moe_ep.h"
 #include "parallel/ep_group.h"
 #include "tensor.h"
+#include "weight_io.h"
 
 namespace py = pybind11;
 
@@ -141,6 +142,7 @@ PYBIND11_MODULE(xstar_cpp, m)
         .value("Float4E2M1x2", DType::Float4E2M1x2)
         .value("UE8M0", DType::UE8M0)
         .value("Int32", DType::Int32)
+        .value("UInt8", DType::UInt8)
         .export_values();
     py::enum_<Device>(m, "Device").value("CPU", Device::CPU).value("CUDA", Device::CUDA).export_values();
 
@@ -199,6 +201,41 @@ PYBIND11_MODULE(xstar_cpp, m)
           py::arg("gate_up_scale") = py::none(), py::arg("down_scale") = py::none(), py::arg("shared_gate_up_weight") = py::none(),
           py::arg("shared_down_weight") = py::none(), py::arg("shared_gate_up_scale") = py::none(),
           py::arg("shared_down_scale") = py::none());
+    // checkpoint IO (same names as the reference's module: MMapFile, parse_safetensors_header, make_weight_view)
+    py::class_<MMapFile>(m, "MMapFile").def(py::init<const std::string &>(), py::arg("path")).def("size", &MMapFile::size);
+    py::class_<TensorMeta>(m, "TensorMeta")
+        .def_readonly("offset", &TensorMeta::offset)
+        .def_readonly("shape", &TensorMeta::shape)
+        .def_readonly("dtype", &TensorMeta::dtype);
+    m.def("parse_safetensors_header", &parse_safetensors_header, py::arg("file"));
+    m.def("make_weight_view", &make_weight_view, py::arg("file"), py::arg("offset"), py::arg("shape"), py::arg("dtype"),
+          py::keep_alive<0, 1>()); // the view borrows the mapping
+    py::class_<MoeLayerWeights>(m, "MoeLayerWeights")
+        .def_readonly("num_experts", &MoeLayerWeights::num_experts)
+        .def_readonly("first_expert", &MoeLayerWeights::first_expert)
+        .def_readonly("expert_count", &MoeLayerWeights::expert_count)
+        .def_readonly("hidden", &MoeLayerWeights::hidden)
+        .def_readonly("intermediate", &MoeLayerWeights::intermediate)
+        .def_property_readonly("router_weight", [](const MoeLayerWeights &w) { return &w.router_weight; }, py::return_value_policy::reference_internal)
+        .def_property_readonly("gate_up_weight", [](const MoeLayerWeights &w) { return &w.gate_up_weight; }, py::return_value_policy::reference_internal)
+        .def_property_readonly("down_weight", [](const MoeLayerWeights &w) { return &w.down_weight; }, py::return_value_policy::reference_internal)
+        .def("optional",
+             [](const MoeLayerWeights &w, const std::string &name) -> const Tensor * {
+                 const std::optional<Tensor> *o = name == "router_bias"             ? &w.router_bias
+                                                  : name == "gate_up_scale"         ? &w.gate_up_scale
+                                                  : name == "down_scale"            ? &w.down_scale
+                                                  : name == "shared_gate_up_weight" ? &w.shared_gate_up_weight
+                                                  : name == "shared_down_weight"    ? &w.shared_down_weight
+                                                  : name == "shared_gate_up_scale"  ? &w.shared_gate_up_scale
+                                                  : name == "shared_down_scale"     ? &w.shared_down_scale
+                                                                                    : nullptr;
+                 if (!o)
+                     throw std::runtime_error("unknown tensor name");
+                 return o->has_value() ? &o->value() : nullptr;
+             },
+             py::arg("name"), py::return_value_policy::reference_internal);
+    m.def("load_moe_layer", &load_moe_layer, py::arg("file"), py::arg("meta"), py::arg("prefix"), py::arg("num_experts"),
+          py::arg("first_expert"), py::arg("expert_count"), py::arg("device") = Device::CPU, py::call_guard<py::gil_scoped_release>());
     m.def("set_device", &cuda_set_device, py::arg("device"));
     m.def("current_device", &cuda_current_device);
     m.def("ep_unique_id", [] {

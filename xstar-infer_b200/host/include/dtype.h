@@ -12,6 +12,7 @@ enum class DType {
     Float4E2M1x2, // two e2m1 codes per byte (low nibble = even index); shapes count BYTES in the last dim
     UE8M0,        // power-of-two scale, biased exponent
     Int32,
+    UInt8, // raw bytes: how a checkpoint file stores packed FP4 codes and e8m0 scales before the loader tags them
 };
 
 inline std::size_t dtype_size(DType d)
@@ -25,6 +26,7 @@ inline std::size_t dtype_size(DType d)
     case DType::Float8E4M3:
     case DType::Float4E2M1x2:
     case DType::UE8M0:
+    case DType::UInt8:
         return 1;
     }
     throw std::runtime_error("unknown DType");
@@ -39,6 +41,7 @@ inline const char *dtype_name(DType d)
     case DType::Float4E2M1x2: return "Float4E2M1x2";
     case DType::UE8M0: return "UE8M0";
     case DType::Int32: return "Int32";
+    case DType::UInt8: return "UInt8";
     }
     return "?";
 }

@@ -14,6 +14,8 @@ class Tensor
 public:
     using Shape = std::vector<std::int64_t>;
 
+    // empty (shape {0}, no bytes): a slot to move a tensor into
+    Tensor();
     // owning, uninitialised
     Tensor(Shape shape, DType dtype, Device device = Device::CPU);
     // borrowing view of memory that outlives this object

@@ -28,6 +28,11 @@ void Tensor::layout()
     }
 }
 
+Tensor::Tensor() : shape_{0}
+{
+    layout();
+}
+
 Tensor::Tensor(Shape shape, DType dtype, Device device) : shape_(std::move(shape)), dtype_(dtype), device_(device), owner_(true)
 {
     layout();
