@@ -406,6 +406,13 @@ int launch_logits_filtered(const XsMoeConfig *c, const void *x, const void *rw, 
     xs::router_wnorm_kernel<<<(E + 7) / 8, 256, 0, st>>>(rwb, E, H, wnorm);
     note_launch();
     dim3 grid((T + xs::kRtTokens - 1) / xs::kRtTokens, (E + xs::kRtMaxN - 1) / xs::kRtMaxN);
+    // few tiles: split the hidden dimension over up to kRtMaxSplits CTAs per tile (partial sums added into zeroed logits)
+    int splits = 1;
+    while (splits < xs::kRtMaxSplits && static_cast<int>(grid.x * grid.y) * splits * 2 <= di.sms && (H / xs::kBlockK) % (splits * 2) == 0)
+        splits *= 2;
+    grid.z = splits;
+    if (splits > 1)
+        XS_CUDA(cudaMemsetAsync(logits, 0, static_cast<size_t>(T) * E * sizeof(float), st));
     xs::router_logits_tc_kernel<<<grid, xs::kRtThreads, smem, st>>>(t_x, t_w, logits, T, H, E, n, status, stages);
     note_launch();
     const int blocks = (T + xs::kRcWarps - 1) / xs::kRcWarps;
@@ -417,9 +424,13 @@ int launch_logits_filtered(const XsMoeConfig *c, const void *x, const void *rw, 
     else
         xs::router_candidates_kernel<32><<<blocks, xs::kRcWarps * 32, 0, st>>>(xb, bias, logits, wnorm, cand, cand_meta, T, H, E, K, coeff);
     note_launch();
-    if (E <= xs::kRxMaxExperts)
-        xs::router_exact_slices_kernel<<<(T + xs::kRxTokens - 1) / xs::kRxTokens, xs::kRxThreads, xs::kRxSmemBytes, st>>>(
-            xb, rwb, logits, cand, cand_meta, T, H, E, counters);
+    if (E <= xs::kRxMaxExperts) {
+        int tpb = xs::kRxTokens; // halve the tokens per block while that still leaves SMs without a block
+        while (tpb > 8 && (T + tpb - 1) / tpb * 2 <= di.sms)
+            tpb /= 2;
+        xs::router_exact_slices_kernel<<<(T + tpb - 1) / tpb, xs::kRxThreads, xs::kRxSmemBytes, st>>>(xb, rwb, logits, cand, cand_meta, T, H, E,
+                                                                                                  counters, tpb);
+    }
     else
         xs::router_exact_rows_kernel<<<T, 32, xs::kReSmemBytes, st>>>(xb, rwb, logits, cand, cand_meta, T, H, E, counters, status);
     note_launch();

@@ -40,7 +40,11 @@ __host__ __device__ constexpr int rt_stage_bytes(int n)
 }
 
 // logits[t, e0 + c] ~= x[t, :] . router_w[e0 + c, :] for one tile of 128 tokens x n experts (n a multiple of 16, <= kRtMaxN).
-// grid = (token tiles, expert tiles).  Rows past T / E are zero-filled by the TMA unit and not stored.
+// grid = (token tiles, expert tiles, k splits).  Rows past T / E are zero-filled by the TMA unit and not stored.  With
+// gridDim.z > 1 every CTA takes 1 / gridDim.z of the hidden dimension and ADDS its partial sums (red.global.add.f32 into
+// logits the launcher zeroed): a small batch has few tiles, and one CTA walking all of H alone takes as long as a whole
+// wave of them.  The order of those additions is not fixed, and need not be: these logits are the approximate ones, and
+// the few extra roundings are inside the error bound (router_delta_coeff).
 __global__ void __launch_bounds__(kRtThreads, 1)
 router_logits_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w, float *__restrict__ logits,
                         int T, int H, int E, int n, int32_t *__restrict__ status, int stages)
@@ -77,7 +81,9 @@ router_logits_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
     const int t0 = blockIdx.x * kRtTokens, e0 = blockIdx.y * kRtMaxN;
-    const int num_kb = H / kBlockK;
+    const int num_kb = H / kBlockK / static_cast<int>(gridDim.z); // the launcher picks a split that divides H / kBlockK
+    const int kb0 = static_cast<int>(blockIdx.z) * num_kb;
+    const bool add = gridDim.z > 1;
 
     if (warp == 0) {
         if (lane == 0) {
@@ -91,8 +97,8 @@ router_logits_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid
                 }
                 uint8_t *st = smem + static_cast<size_t>(stage) * stage_bytes;
                 mbar_arrive_expect_tx(&full[stage], static_cast<uint32_t>(stage_bytes));
-                tma_load_2d(st, &tmap_x, &full[stage], kb * kBlockK, t0, pol);
-                tma_load_2d(st + X_BYTES, &tmap_w, &full[stage], kb * kBlockK, e0, pol);
+                tma_load_2d(st, &tmap_x, &full[stage], (kb0 + kb) * kBlockK, t0, pol);
+                tma_load_2d(st + X_BYTES, &tmap_w, &full[stage], (kb0 + kb) * kBlockK, e0, pol);
             }
             if (!ok) {
                 *abort_flag = 1;
@@ -136,7 +142,12 @@ router_logits_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid
                 tmem_ld_wait_16(v);
                 if (t < T) {
                     float *row = logits + static_cast<size_t>(t) * E + e0 + c0;
-                    if (e0 + c0 + 16 <= E && (E & 3) == 0) {
+                    if (add) {
+#pragma unroll
+                        for (int j = 0; j < 16; j++)
+                            if (e0 + c0 + j < E)
+                                atomicAdd(row + j, __uint_as_float(v[j])); // result unused: compiles to a reduction
+                    } else if (e0 + c0 + 16 <= E && (E & 3) == 0) {
 #pragma unroll
                         for (int j = 0; j < 4; j++)
                             *reinterpret_cast<uint4 *>(row + 4 * j) = make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
@@ -195,11 +206,13 @@ router_wnorm_kernel(const __nv_bfloat16 *__restrict__ rw, int E, int H, float *_
         atomicMax(reinterpret_cast<int *>(out), __float_as_int(sqrtf(s) * 1.001f));
 }
 
-// delta = coeff * ||x|| * max ||w||: (H / 16) * 2^-22 for the tensor core's accumulation plus H * 2^-24 * 1.01 (>= gamma_H
-// for H < 2^17) for the sequential sum's own rounding, times 1.6.
+// delta = coeff * ||x|| * max ||w||: (H / 16) * 2^-22 for the tensor core's accumulation (+ 8 * 2^-22, far more than the
+// up to kRtMaxSplits - 1 extra roundings of a split hidden dimension lose) plus H * 2^-24 * 1.01 (>= gamma_H for H < 2^17)
+// for the sequential sum's own rounding, times 1.6.
+constexpr int kRtMaxSplits = 4;
 __host__ __device__ inline float router_delta_coeff(int H)
 {
-    return 1.6f * (static_cast<float>(H / 16 + 1) * 2.384185791015625e-07f + static_cast<float>(H) * 5.9604644775390625e-08f * 1.01f);
+    return 1.6f * (static_cast<float>(H / 16 + 8) * 2.384185791015625e-07f + static_cast<float>(H) * 5.9604644775390625e-08f * 1.01f);
 }
 
 constexpr int kRcWarps = 4;      // tokens per block of the candidates kernel
@@ -476,15 +489,17 @@ constexpr int kRxSmemBytes = kRxStages * kRxStageBytes + (kRxTokens + 1) * 4 * 2
 __global__ void __launch_bounds__(kRxThreads)
 router_exact_slices_kernel(const __nv_bfloat16 *__restrict__ x, const __nv_bfloat16 *__restrict__ rw, float *__restrict__ logits,
                            const int32_t *__restrict__ cand, const int32_t *__restrict__ cand_meta, int T, int H, int E,
-                           unsigned long long *__restrict__ counters)
+                           unsigned long long *__restrict__ counters, int tokens_per_block)
 {
+    // tokens_per_block <= kRxTokens: smaller batches give each block fewer tokens so that the grid still covers the SMs (a
+    // block's time is set by walking H once, whatever its token count)
     extern __shared__ __align__(16) uint8_t rx_smem[];
     int *s_off = reinterpret_cast<int *>(rx_smem + kRxStages * kRxStageBytes); // [kRxTokens + 1] exclusive prefix of chain counts
     int *s_cnt = s_off + kRxTokens + 1;                                        // [kRxTokens + 1] candidates per token (E = all)
     int *s_bad = s_cnt + kRxTokens + 1;                                        // [kRxTokens] token needs the full recomputation
     const int tid = threadIdx.x;
-    const int t0 = blockIdx.x * kRxTokens;
-    const int nt = T - t0 < kRxTokens ? T - t0 : kRxTokens;
+    const int t0 = blockIdx.x * tokens_per_block;
+    const int nt = T - t0 < tokens_per_block ? T - t0 : tokens_per_block;
     const int slices = H / kRxK;
 
     auto issue = [&](int sl, int st) {
