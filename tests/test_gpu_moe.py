@@ -383,7 +383,7 @@ def test_quantize_rows_mxfp8_bit_exact(oracle):
 
 
 @pytest.mark.parametrize("T,S,E,K,H,I", [(1, 0, 8, 2, 256, 256), (9, 0, 8, 3, 512, 256), (70, 1, 16, 4, 256, 384),
-                                         (200, 1, 8, 2, 384, 256), (333, 0, 4, 2, 256, 128)])
+                                         (200, 1, 8, 2, 384, 256), (333, 0, 4, 2, 256, 128), (5, 0, 8, 2, 384, 128), (40, 1, 8, 2, 640, 256)])
 def test_forward_fp4_ragged_shapes(oracle, T, S, E, K, H, I):
     dims = _dims(T=T, S=S, E=E, K=K, H=H, I=I, fmt="fp4")
     d = synth.make_inputs(dims, seed=T + 2, device="cuda")

@@ -243,20 +243,13 @@ int check_cfg(const XsMoeConfig *c)
 // Rows per token tile.  bf16: 16..128 tokens as the N of a 128-weight-row MMA.  FP8/FP4: up to 64 in that shape (the
 // FP8 epilogue keeps one f32 accumulator per token column in registers); FP8 batches with many tokens per expert use
 // the prefill kernel instead, whose tiles are 128 tokens as the M of an N = 256 MMA (needs hidden % 256 == 0).
-#ifdef XS_FP4_SWAPAB_DECODE
-#define XS_FP4_TOKENS_AS_M 0
-#else
-#define XS_FP4_TOKENS_AS_M 1
-#endif
 int pick_n_tile(long rows, int groups, int fmt, int hidden)
 {
     const long avg = groups > 0 ? (rows + groups - 1) / groups : rows;
-#ifndef XS_FP4_SWAPAB_DECODE
     // FP4: the tokens-as-M kernel at every batch size (an N = 256 block-scaled MMA consumes twice the packed weight bytes of
     // a weights-as-M one); 32-row token boxes while experts see a handful of tokens, 128-row ones beyond
     if (fmt == XS_MOE_FP4_MX32 && hidden % 256 == 0)
         return avg <= 20 ? 32 : 128;
-#endif
     if (avg <= 8)
         return 16;
     if (avg <= 20)
@@ -830,7 +823,7 @@ struct GroupedArgs {
 // does run_grouped take the tokens-as-M FP4 kernels for this problem (the ones whose down epilogue can store to peers)?
 bool grouped_supports_fused_return(int fmt, int H, int I, const GroupedPlan &gp)
 {
-    return fmt == XS_MOE_FP4_MX32 && H % 256 == 0 && I % 128 == 0 && (gp.n_tile == 128 || (gp.n_tile == 32 && XS_FP4_TOKENS_AS_M));
+    return fmt == XS_MOE_FP4_MX32 && H % 256 == 0 && I % 128 == 0 && (gp.n_tile == 128 || gp.n_tile == 32);
 }
 
 int run_grouped(const GroupedArgs &a, cudaStream_t st, cudaEvent_t mid = nullptr)
@@ -901,7 +894,7 @@ int run_grouped(const GroupedArgs &a, cudaStream_t st, cudaEvent_t mid = nullptr
         if (int rc = make_tmap_2d(&t_act, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, act, a.max_rows, I, a.gp.n_tile, xs::kBlockK8))
             return rc;
         uint8_t *act_scale = a.scratch + a.gp.off_act_scale;
-        if (a.gp.n_tile == 128 || (a.gp.n_tile == 32 && H % 256 == 0 && XS_FP4_TOKENS_AS_M)) {
+        if (H % 256 == 0 && (a.gp.n_tile == 128 || a.gp.n_tile == 32)) {
             // tokens as the M of N = 256 block-scaled MMAs (token box of 32 or 128 rows)
             xs::MxScales p1{static_cast<const uint8_t *>(a.gu_scale), reinterpret_cast<const uint8_t *>(a.row_scale), act_scale, a.max_rows};
             if (int rc = launch_prefill_fp4<true>(t_wgu, t_x, offs, tt, p1, 2 * I, static_cast<uint64_t>(groups) * 2 * I, I, H, act, a.status,
