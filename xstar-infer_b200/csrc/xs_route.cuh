@@ -321,12 +321,12 @@ router_logits_mid_kernel(const __nv_bfloat16 *__restrict__ x, const __nv_bfloat1
 // The smallest batches (a few tokens per SM at most): the floor of the router is the chain of H dependent FMAs of one
 // output (about 10 us at H = 4096), so the kernel is built to keep that chain fed and nothing else in its way.  One WARP
 // per block: lane = expert (32 experts per block), TPW tokens per lane (the launcher uses 1: one token per block; more
-// chains per lane measured slower).  Router rows arrive through an 8-stage
+// chains per lane measured slower).  Router rows arrive through a 4-stage
 // cp.async pipeline of 128-wide k chunks and are widened on the fly (one ALU operation per k); the token rows are widened
 // ONCE per chunk by the whole warp into an f32 buffer (so the per-lane cost of a token operand is a broadcast shared
 // read, not a conversion), one chunk ahead of the FMAs that use it.  With a single warp there is no block barrier;
 // __syncwarp orders the hand-overs.  Same contract: every accumulator sees k = 0, 1, 2, ... in order.
-constexpr int kRsK = 128, kRsStages = 8, kRsWStride = kRsK + 8; // bf16 elements; 272-byte rows are conflict-free for 16-byte reads
+constexpr int kRsK = 128, kRsStages = 4, kRsWStride = kRsK + 8; // bf16 elements; 272-byte rows are conflict-free for 16-byte reads
 template <int TPW>
 constexpr int rs_smem_bytes()
 {
