@@ -106,6 +106,18 @@ def test_comm_layer_loads_nccl_by_name():
     assert capi.lib().xs_moe_comm_available() == 0, capi.lib().xs_moe_last_error()
 
 
+def test_fused_return_is_offered_for_fp4_experts_only():
+    """xs_moe_grouped_mlp_return_supported needs no GPU: FP4 experts with hidden % 256 == 0 take the tokens-as-M kernels,
+    whose down epilogue can store into the source ranks; everything else uses the two-step return."""
+    import ctypes as C
+    L = capi.lib()
+    ok = C.c_int32(-1)
+    for fmt, H, want in ((capi.FP4_MX32, 4096, 1), (capi.FP4_MX32, 384, 0), (capi.FP8_BLOCK128, 4096, 0), (capi.BF16, 4096, 0)):
+        cfg = capi.make_config(2048, H, 256, 6, 2048, 0, fmt, capi.FP8_BLOCK128 if fmt == capi.FP4_MX32 else fmt, 32, 32)
+        assert L.xs_moe_grouped_mlp_return_supported(C.byref(cfg), 12288, C.byref(ok)) == 0, L.xs_moe_last_error()
+        assert ok.value == want, (fmt, H)
+
+
 # ---- on GPUs ---------------------------------------------------------------------------------------------------------
 _DT = {"bf16": "BFloat16", "fp8": "Float8E4M3", "fp4": "Float4E2M1x2"}
 
@@ -199,10 +211,12 @@ def test_cpp_ep_two_rank_threads_match_oracle(oracle, fmt, tol):
 
 
 @pytest.mark.gpu
-def test_cpp_ep_flags_a_receive_buffer_that_is_too_small():
+@pytest.mark.parametrize("fmt", ["bf16", "fp4"])
+def test_cpp_ep_flags_a_receive_buffer_that_is_too_small(fmt):
     """capacity_factor far below the rows that arrive: the dispatch kernel skips the rows that do not fit and flags it, the
-    grouped MLP clamps its segments to the capacity, and check() raises on the host -- nothing is written out of bounds."""
-    dims = dict(T=256, H=256, E=8, K=4, I=128, S=0, fmt="bf16", bias=None)
+    grouped MLP clamps its segments to the capacity (FP4: with the return folded into its epilogue), and check() raises on
+    the host -- nothing is written out of bounds."""
+    dims = dict(T=256, H=256, E=8, K=4, I=128, S=0, fmt=fmt, bias=None)
     d, res = _run_world(dims, 1, seed=3, capacity_factor=0.25, steps=1)
     assert res[0][0] == "err" and "out-of-range index" in str(res[0][1]), res[0]
 

@@ -40,6 +40,7 @@ struct EpReturnArgs {
     const int32_t *all_counts = nullptr;
     const int32_t *src_offsets = nullptr;
     int experts = 0, ranks = 1, me = 0, back_capacity = 0;
+    int y_bf16 = 0; // no peers: store the rows to `out` as bf16 instead of f32 (the layer's own combine reads them)
 };
 
 // smallest e8m0 exponent whose power of two is >= v (v > 0, normal)

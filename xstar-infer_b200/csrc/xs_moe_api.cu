@@ -660,7 +660,7 @@ int launch_gemm_fp8(int n_tile, const CUtensorMap &tw, const CUtensorMap &tw2, c
 template <bool GATE_UP>
 int launch_prefill_fp8(const CUtensorMap &tw, const CUtensorMap &tw2, const CUtensorMap &tx, const int32_t *offsets, xs::TileTable tt,
                        xs::Fp8Scales sc, int groups, int w_rows, int n_out, int K, void *out, int32_t *status, int max_work,
-                       cudaStream_t st)
+                       cudaStream_t st, int y_bf16 = 0)
 {
     DeviceInfo di;
     if (int rc = device_info(&di))
@@ -683,7 +683,7 @@ int launch_prefill_fp8(const CUtensorMap &tw, const CUtensorMap &tw2, const CUte
     int grid = di.sms < max_work ? di.sms : max_work;
     if (grid < 1)
         grid = 1;
-    kern<<<grid, xs::kPfThreads, smem, st>>>(tw, tw2, tx, offsets, tt, sc, groups, w_rows, n_out, K, out, status, stages);
+    kern<<<grid, xs::kPfThreads, smem, st>>>(tw, tw2, tx, offsets, tt, sc, groups, w_rows, n_out, K, out, status, stages, y_bf16);
     note_launch();
     XS_CUDA(cudaGetLastError());
     return 0;
@@ -818,7 +818,21 @@ struct GroupedArgs {
     int32_t *status = nullptr;
     bool tiles_ready = false; // the tile table was already built (fused routing kernel)
     xs::EpReturnArgs ret;     // expert-parallel return folded into the down epilogue (kernels that support it)
+    bool y_bf16 = false;      // y receives bf16 rows (only honoured by the tokens-as-M FP8 / FP4 kernels: see grouped_writes_bf16)
 };
+
+// The quantised tokens-as-M kernels can hand their result rows to the layer's combine as bf16 (half the bytes written and
+// read back; the extra rounding is what the expert-parallel wire already applies to these formats).  Which problems they serve:
+bool grouped_writes_bf16(int fmt, int H, const GroupedPlan &gp, int gemm_impl)
+{
+    if (gemm_impl != 0 || H % 256 != 0)
+        return false;
+    if (fmt == XS_MOE_FP8_BLOCK128)
+        return gp.n_tile == 128;
+    if (fmt == XS_MOE_FP4_MX32)
+        return gp.n_tile == 128 || gp.n_tile == 32;
+    return false;
+}
 
 // does run_grouped take the tokens-as-M FP4 kernels for this problem (the ones whose down epilogue can store to peers)?
 bool grouped_supports_fused_return(int fmt, int H, int I, const GroupedPlan &gp)
@@ -903,8 +917,10 @@ int run_grouped(const GroupedArgs &a, cudaStream_t st, cudaEvent_t mid = nullptr
             if (mid)
                 XS_CUDA(cudaEventRecord(mid, st));
             xs::MxScales p2{static_cast<const uint8_t *>(a.dw_scale), act_scale, nullptr, a.max_rows};
+            xs::EpReturnArgs ret = a.ret;
+            ret.y_bf16 = a.y_bf16 ? 1 : 0;
             return launch_prefill_fp4<false>(t_wd, t_act, offs, tt, p2, H, static_cast<uint64_t>(groups) * H, H, I, a.y, a.status,
-                                             a.gp.max_tiles * (H / 256), a.gp.n_tile, st, a.ret);
+                                             a.gp.max_tiles * (H / 256), a.gp.n_tile, st, ret);
         }
         if (a.ret.peer_back)
             return fail(XS_MOE_ERR_UNSUPPORTED, "the fused expert-parallel return needs the tokens-as-M FP4 kernels (hidden % 256 == 0)");
@@ -960,7 +976,7 @@ int run_grouped(const GroupedArgs &a, cudaStream_t st, cudaEvent_t mid = nullptr
             XS_CUDA(cudaEventRecord(mid, st));
         xs::Fp8Scales p2{static_cast<const float *>(a.dw_scale), static_cast<const float *>(a.dw2_scale), act_scale, nullptr, a.max_rows};
         return launch_prefill_fp8<false>(t_wd, t_wd2, t_act, offs, tt, p2, groups, H, H, I, a.y, a.status,
-                                         a.gp.max_tiles * (H / 256), st);
+                                         a.gp.max_tiles * (H / 256), st, a.y_bf16 ? 1 : 0);
     }
     xs::Fp8Scales s1{static_cast<const float *>(a.gu_scale), static_cast<const float *>(a.gu2_scale), a.row_scale, act_scale, a.max_rows};
     if (int rc = launch_gemm_fp8<true>(a.gp.n_tile, t_wgu, t_wgu2, t_x, offs, tt, s1, groups, 2 * I, I, H, act, a.status, work_gu, st))
@@ -1320,8 +1336,32 @@ static int combine_impl(const XsMoeConfig *cfg, const float *y, const int32_t *i
     if (T == 0)
         return 0;
     int gy = (H + 1023) / 1024;
-    xs::combine_kernel<float><<<dim3(T, gy), 128, 0, static_cast<cudaStream_t>(stream)>>>(
+    xs::combine_kernel<float, float><<<dim3(T, gy), 128, 0, static_cast<cudaStream_t>(stream)>>>(
         y, inv, topk_w, shared, static_cast<__nv_bfloat16 *>(out), T, H, K, static_cast<const __nv_bfloat16 *>(residual));
+    note_launch();
+    XS_CUDA(cudaGetLastError());
+    return 0;
+}
+
+// y rows bf16; the always-on expert's rows f32 or bf16
+static int combine_bf16_impl(const XsMoeConfig *cfg, const __nv_bfloat16 *y, const int32_t *inv, const float *topk_w, const void *shared,
+                             bool shared_is_bf16, void *out, const void *residual, void *stream)
+{
+    if (int rc = check_cfg(cfg))
+        return rc;
+    if (!y || !inv || !topk_w || !out)
+        return fail(XS_MOE_ERR_INVALID_ARG, "null tensor pointer");
+    const int T = cfg->num_tokens, H = cfg->hidden, K = cfg->top_k;
+    if (T == 0)
+        return 0;
+    const dim3 grid(T, (H + 1023) / 1024);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    __nv_bfloat16 *o = static_cast<__nv_bfloat16 *>(out);
+    const __nv_bfloat16 *res = static_cast<const __nv_bfloat16 *>(residual);
+    if (shared_is_bf16)
+        xs::combine_kernel<__nv_bfloat16, __nv_bfloat16><<<grid, 128, 0, st>>>(y, inv, topk_w, static_cast<const __nv_bfloat16 *>(shared), o, T, H, K, res);
+    else
+        xs::combine_kernel<__nv_bfloat16, float><<<grid, 128, 0, st>>>(y, inv, topk_w, static_cast<const float *>(shared), o, T, H, K, res);
     note_launch();
     XS_CUDA(cudaGetLastError());
     return 0;
@@ -1361,7 +1401,7 @@ int xs_moe_combine_bf16_rows(const XsMoeConfig *cfg, const void *y_bf16, const i
     if (T == 0)
         return 0;
     int gy = (H + 1023) / 1024;
-    xs::combine_kernel<__nv_bfloat16><<<dim3(T, gy), 128, 0, static_cast<cudaStream_t>(stream)>>>(
+    xs::combine_kernel<__nv_bfloat16, float><<<dim3(T, gy), 128, 0, static_cast<cudaStream_t>(stream)>>>(
         static_cast<const __nv_bfloat16 *>(y_bf16), inv, topk_w, shared, static_cast<__nv_bfloat16 *>(out), T, H, K);
     note_launch();
     XS_CUDA(cudaGetLastError());
@@ -1581,12 +1621,24 @@ static int forward_impl(const XsMoeConfig *cfg, const XsMoeWeights *w, const voi
     a.gp = p.grouped;
     a.status = status;
     a.tiles_ready = tiles_ready;
+    // quantised experts on the tokens-as-M kernels: result rows as bf16 (the routed rows; for FP8 also the always-on expert's,
+    // which ride in the same launches)
+    const bool y_bf16 = grouped_writes_bf16(cfg->routed_format, H, p.grouped, cfg->gemm_impl);
+    a.y_bf16 = y_bf16;
     if (int rc = run_grouped(a, st, ev ? ev[4] : nullptr))
         return rc;
     if (joined)
         XS_CUDA(cudaStreamWaitEvent(st, side.join, 0));
     XS_MARK(5);
-    if (int rc = combine_impl(cfg, y, inv, tw, S ? y + static_cast<size_t>(n_routed) * H : nullptr, out, residual, stream))
+    if (y_bf16) {
+        // FP4: the always-on expert ran in launches of its own and wrote f32 rows at the f32 layout's offset; FP8: its rows are
+        // bf16 rows n_routed.. of the same buffer
+        const __nv_bfloat16 *yb = reinterpret_cast<const __nv_bfloat16 *>(y);
+        const void *sh = !S ? nullptr : (fp4 ? static_cast<const void *>(y + static_cast<size_t>(n_routed) * H)
+                                             : static_cast<const void *>(yb + static_cast<size_t>(n_routed) * H));
+        if (int rc = combine_bf16_impl(cfg, yb, inv, tw, sh, /*shared_is_bf16=*/!fp4, out, residual, stream))
+            return rc;
+    } else if (int rc = combine_impl(cfg, y, inv, tw, S ? y + static_cast<size_t>(n_routed) * H : nullptr, out, residual, stream))
         return rc;
     XS_MARK(6);
     return 0;

@@ -372,10 +372,10 @@ __device__ __forceinline__ void load8(const __nv_bfloat16 *p, float (&v)[8])
 // residual (T, H) bf16 or null: the block's skip connection, added the way the engine's `add` op adds two bf16 tensors
 // (xstar_cpp/src/ops/add.cpp:27-49 in the reference): the layer's result is rounded to bf16 first, then
 // out = bf16(float(residual) + float(result)).
-template <typename YT>
+template <typename YT, typename ST>
 __global__ void __launch_bounds__(128)
 combine_kernel(const YT *__restrict__ y, const int32_t *__restrict__ inv, const float *__restrict__ topk_w,
-               const float *__restrict__ shared, __nv_bfloat16 *__restrict__ out, int T, int H, int K,
+               const ST *__restrict__ shared, __nv_bfloat16 *__restrict__ out, int T, int H, int K,
                const __nv_bfloat16 *__restrict__ residual = nullptr)
 {
     const int t = blockIdx.x;

@@ -98,7 +98,7 @@
             if (lane == 0)
                 mbar_arrive(tmem_empty);
             // (all lanes of an active warp take part in the quad transposes; rows past the segment are not stored)
-            if (active && ret.peer_back == nullptr) {
+            if (active && ret.peer_back == nullptr && !ret.y_bf16) {
                 const int qd = lane & 3;
                 const int rq = q * 32 + (lane & ~3); // first row of the quad within the tile
                 float *ybase = static_cast<float *>(out) + static_cast<size_t>(row0 + rq) * n_out + nt * 256 + 128 * half;
@@ -115,10 +115,12 @@
                             *reinterpret_cast<uint4 *>(ybase + static_cast<size_t>(r) * n_out + i * 16 + qd * 4) = b[r];
                 }
             } else if (active) {
-                // Expert-parallel return: this thread's row is the j-th row source rank s sent for this expert; it goes, as
-                // bf16, to row src_offsets[s][e] + j of that rank's return buffer.
+                // bf16 rows.  Expert-parallel return: this thread's row is the j-th row source rank s sent for this expert; it
+                // goes to row src_offsets[s][e] + j of that rank's return buffer.  Without peers: to its own row of `out`.
                 uint8_t *dst = nullptr;
-                if (valid) {
+                if (valid && ret.peer_back == nullptr) {
+                    dst = static_cast<uint8_t *>(out) + (static_cast<size_t>(row0 + r) * n_out + nt * 256 + 128 * half) * 2; // local bf16 rows
+                } else if (valid) {
                     const int El = ret.experts / ret.ranks;
                     const int eg = ret.me * El + e;
                     int j = row0 + r - offsets[e];

@@ -50,7 +50,7 @@ __global__ void __launch_bounds__(kPfThreads, 1)
 prefill_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_w2,
                         const __grid_constant__ CUtensorMap tmap_x, const int32_t *__restrict__ offsets, TileTable tt, Fp8Scales sc,
                         int groups, int w_rows_per_expert, int n_out, int K, void *__restrict__ out, int32_t *__restrict__ status,
-                        int stages)
+                        int stages, int y_bf16)
 {
     constexpr int X_BYTES = kPfTokens * kBlockK8;
     constexpr int W_HALF = 128 * kBlockK8;

@@ -193,52 +193,51 @@
             // q + 8, q + 12 of each of the quad's four rows, and one store instruction writes 64 contiguous bytes per quad,
             // 8 rows instead of 32.
             const int qd = lane & 3;
+            const int rq = q * 32 + (lane & ~3); // first row of the quad within the tile
+            if (y_bf16) {
+                // the layer's own combine reads these rows: bf16 halves the store and the read (the quantised formats'
+                // tolerance allows the extra rounding, as on the expert-parallel wire).  64 columns = 8 chunks of 8.
+#pragma unroll
+                for (int m = 0; m < 2; m++) {
+                    uint4 b[4];
+#pragma unroll
+                    for (int v = 0; v < 4; v++) {
+                        uint32_t pk[4];
+#pragma unroll
+                        for (int u = 0; u < 4; u++) {
+                            const __nv_bfloat162 h2 = __floats2bfloat162_rn(acc[(4 * m + v) * 8 + 2 * u], acc[(4 * m + v) * 8 + 2 * u + 1]);
+                            pk[u] = *reinterpret_cast<const uint32_t *>(&h2);
+                        }
+                        b[v] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+                    }
+                    quad_transpose_chunks(b, qd); // b[i] = chunk 4 m + qd (8 columns) of row rq + i
+#pragma unroll
+                    for (int i = 0; i < 4; i++)
+                        if (rq + i < nvalid) {
+                            __nv_bfloat16 *dst = static_cast<__nv_bfloat16 *>(out) + static_cast<size_t>(row0 + rq + i) * n_out + nt * 256 + CPT * g;
+                            *reinterpret_cast<uint4 *>(dst + (4 * m + qd) * 8) = b[i];
+                        }
+                }
+            } else {
             float4 ch[16];
 #pragma unroll
             for (int v = 0; v < 16; v++)
                 ch[v] = make_float4(acc[v * 4], acc[v * 4 + 1], acc[v * 4 + 2], acc[v * 4 + 3]);
-            auto shfl4 = [](const float4 &v, int m) {
-                return make_float4(__shfl_xor_sync(0xffffffffu, v.x, m), __shfl_xor_sync(0xffffffffu, v.y, m),
-                                   __shfl_xor_sync(0xffffffffu, v.z, m), __shfl_xor_sync(0xffffffffu, v.w, m));
-            };
 #pragma unroll
             for (int m = 0; m < 4; m++) {
-                float4 *b = ch + 4 * m; // b[j] = chunk 4m + j of my row; transpose b across the quad
-                // round 1: lanes l and l ^ 1 swap the off-diagonal elements of each 2 x 2 block
-                {
-                    const bool odd = qd & 1;
-                    const float4 s0 = shfl4(odd ? b[0] : b[1], 1), s1 = shfl4(odd ? b[2] : b[3], 1);
-                    if (odd) {
-                        b[0] = s0;
-                        b[2] = s1;
-                    } else {
-                        b[1] = s0;
-                        b[3] = s1;
+                uint4 b[4];
+#pragma unroll
+                for (int j = 0; j < 4; j++)
+                    b[j] = make_uint4(__float_as_uint(ch[4 * m + j].x), __float_as_uint(ch[4 * m + j].y), __float_as_uint(ch[4 * m + j].z),
+                                      __float_as_uint(ch[4 * m + j].w));
+                quad_transpose_chunks(b, qd); // b[i] = chunk 4 m + qd of row rq + i
+#pragma unroll
+                for (int i = 0; i < 4; i++)
+                    if (rq + i < nvalid) {
+                        float *dst = static_cast<float *>(out) + static_cast<size_t>(row0 + rq + i) * n_out + nt * 256 + CPT * g;
+                        *reinterpret_cast<uint4 *>(dst + (4 * m + qd) * 4) = b[i];
                     }
-                }
-                // round 2: lanes l and l ^ 2 swap the off-diagonal 2 x 2 blocks
-                {
-                    const bool hi = qd & 2;
-                    const float4 s0 = shfl4(hi ? b[0] : b[2], 2), s1 = shfl4(hi ? b[1] : b[3], 2);
-                    if (hi) {
-                        b[0] = s0;
-                        b[1] = s1;
-                    } else {
-                        b[2] = s0;
-                        b[3] = s1;
-                    }
-                }
-                // now b[i] = chunk 4m + qd of row (lane & ~3) + i of this warp's 32 rows
             }
-            const int rq = q * 32 + (lane & ~3); // first row of the quad within the tile
-#pragma unroll
-            for (int i = 0; i < 4; i++) {
-                if (rq + i < nvalid) {
-                    float *dst = static_cast<float *>(out) + static_cast<size_t>(row0 + rq + i) * n_out + nt * 256 + CPT * g;
-#pragma unroll
-                    for (int m = 0; m < 4; m++)
-                        *reinterpret_cast<float4 *>(dst + (4 * m + qd) * 4) = ch[4 * m + i];
-                }
             }
         }
         w_tail += prof_clock() - t_tail;
