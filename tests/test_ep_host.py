@@ -234,3 +234,80 @@ def test_cpp_ep_rejects_calls_that_do_not_fit_the_context():
         xstar_cpp.EpContext(None, xstar_cpp.ep_unique_id(), 0, 3, 0, 32, 256, 8, 2, 128, xstar_cpp.DType.BFloat16, False)
     out = cpp_to_torch(xstar_cpp.to_cpu(ctx.moe(x, rw, gu, dw, 2)), (32, 256))
     assert torch.isfinite(out.float()).all()
+
+
+# ---- batch composition and rank workers -------------------------------------------------------------------------------
+def test_batch_is_balanced_without_splitting_sequences():
+    rng = np.random.default_rng(5)
+    lens = rng.integers(1, 400, size=37).tolist()
+    cu = np.concatenate([[0], np.cumsum(lens)]).tolist()
+    for ranks in (1, 2, 4, 8):
+        p = xstar_cpp.ep_balance_batch(cu, ranks)
+        assert sorted(s for r in p["sequences_of_rank"] for s in r) == list(range(len(lens)))  # every sequence exactly once
+        for r, seqs in enumerate(p["sequences_of_rank"]):
+            assert seqs == sorted(seqs) and sum(lens[s] for s in seqs) == p["tokens_of_rank"][r]
+            assert all(p["rank_of_sequence"][s] == r for s in seqs)
+        mean = sum(lens) / ranks
+        assert p["max_tokens"] <= mean + max(lens)  # longest-first greedy: within one sequence of the mean
+        assert abs(p["imbalance"] - p["max_tokens"] / mean) < 1e-9
+    # a decode batch (one token per sequence) splits evenly
+    p = xstar_cpp.ep_balance_batch(list(range(0, 129)), 8)
+    assert p["tokens_of_rank"] == [16] * 8 and p["imbalance"] == 1.0
+    # fewer sequences than ranks: some ranks stay empty, nothing is split
+    p = xstar_cpp.ep_balance_batch([0, 5, 9], 4)
+    assert sorted(p["tokens_of_rank"]) == [0, 0, 4, 5]
+    assert xstar_cpp.ep_balance_batch([0], 2)["imbalance"] == 1.0
+
+
+def test_batch_balancer_errors():
+    with pytest.raises(RuntimeError, match="batch does not fit: rank 0 would hold 300 tokens, capacity 256"):
+        xstar_cpp.ep_balance_batch([0, 300, 310], 2, 256)
+    with pytest.raises(RuntimeError, match="bad cu_seqlens"):
+        xstar_cpp.ep_balance_batch([1, 5], 2)
+    with pytest.raises(RuntimeError, match="bad cu_seqlens"):
+        xstar_cpp.ep_balance_batch([0, 5, 3], 2)
+    with pytest.raises(RuntimeError, match="bad rank count"):
+        xstar_cpp.ep_balance_batch([0, 5], 0)
+
+
+def _pool_run(oracle, dims, world, tokens_of_rank, seed):
+    """One worker thread per rank inside the module; the ranks' batches hold different numbers of tokens."""
+    total = sum(tokens_of_rank)
+    d = synth.make_inputs(dict(dims, T=total), seed=seed)
+    El = dims["E"] // world
+    pool = xstar_cpp.EpWorkerPool(world, list(range(world)), max(tokens_of_rank), dims["H"], dims["E"], dims["K"], dims["I"],
+                                  getattr(xstar_cpp.DType, _DT[dims["fmt"]]), bool(dims["S"]))
+    xs, rw, gu, dw, extra = [], [], [], [], {}
+    start = 0
+    for r in range(world):
+        xstar_cpp.set_device(r)
+        T = tokens_of_rank[r]
+        (_, a, b, c), kw = _rank_tensors(d, dict(dims, T=0), r, world)  # weights only; the rank's rows are cut here
+        x = xstar_cpp.to_cuda(_cpp(d["x"][start:start + T].contiguous()))
+        start += T
+        xs.append(x), rw.append(a), gu.append(b), dw.append(c)
+        for k, v in kw.items():
+            extra.setdefault(k, []).append(v)
+    xstar_cpp.set_device(0)
+    outs = pool.run(xs, rw, gu, dw, dims["K"], **extra)
+    got = torch.cat([cpp_to_torch(xstar_cpp.to_cpu(o), (tokens_of_rank[r], dims["H"])) for r, o in enumerate(outs)])
+    ref = _oracle(oracle, dict(dims, T=total), d)
+    return synth.rel_l2(got.float().numpy(), synth.bf16_bits_to_f32(ref["out"]))
+
+
+@pytest.mark.gpu
+def test_worker_pool_single_rank(oracle):
+    dims = dict(T=0, H=512, E=16, K=4, I=256, S=1, fmt="bf16", bias=None)
+    assert _pool_run(oracle, dims, 1, [80], seed=41) <= 2e-3
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("fmt,tol", [("bf16", 2e-3), ("fp4", 1e-2)])
+def test_worker_pool_two_ranks_with_uneven_batches(oracle, fmt, tol):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs on one box")
+    dims = dict(T=0, H=512, E=16, K=4, I=256, S=1, fmt=fmt, bias=None)
+    plan = xstar_cpp.ep_balance_batch([0, 40, 100, 130, 166], 2)  # sequences of 40, 60, 30, 36 tokens
+    assert plan["tokens_of_rank"] == [90, 76]
+    # the layer does not care which tokens sit on which rank: the global batch in rank order must equal the oracle's
+    assert _pool_run(oracle, dims, 2, plan["tokens_of_rank"], seed=42) <= tol

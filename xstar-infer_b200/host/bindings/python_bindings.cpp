@@ -12,6 +12,7 @@
 #include "ops/moe.h"
 #include "ops/moe_ep.h"
 #include "parallel/ep_group.h"
+#include "parallel/ep_scheduler.h"
 #include "tensor.h"
 #include "weight_io.h"
 
@@ -307,6 +308,71 @@ PYBIND11_MODULE(xstar_cpp, m)
             },
             py::arg("x"), py::arg("out"), py::arg("stream"), py::arg("router_weight"), py::arg("gate_up_weight"), py::arg("down_weight"),
             py::arg("top_k"), py::arg("router_bias") = py::none(), py::arg("gate_up_scale") = py::none(), py::arg("down_scale") = py::none(),
+            py::arg("shared_gate_up_weight") = py::none(), py::arg("shared_down_weight") = py::none(),
+            py::arg("shared_gate_up_scale") = py::none(), py::arg("shared_down_scale") = py::none());
+    m.def(
+        "ep_balance_batch",
+        [](const std::vector<std::int64_t> &cu_seqlens, int ranks, std::int64_t max_tokens_per_rank) {
+            const EpBatchPlan p = ep_balance_batch(cu_seqlens, ranks, max_tokens_per_rank);
+            py::dict d;
+            d["sequences_of_rank"] = p.sequences_of_rank;
+            d["tokens_of_rank"] = p.tokens_of_rank;
+            d["rank_of_sequence"] = p.rank_of_sequence;
+            d["max_tokens"] = p.max_tokens();
+            d["imbalance"] = p.imbalance();
+            return d;
+        },
+        py::arg("cu_seqlens"), py::arg("ranks"), py::arg("max_tokens_per_rank") = 0);
+    py::class_<EpWorkerPool>(m, "EpWorkerPool")
+        .def(py::init([](int world, std::vector<int> devices, std::int64_t max_tokens, std::int64_t hidden, std::int64_t experts,
+                         std::int64_t top_k, std::int64_t intermediate, DType expert_dtype, bool shared, double capacity_factor, int timeout_ms) {
+                 EpOptions o;
+                 o.capacity_factor = capacity_factor;
+                 const EpShape s = ep_shape(max_tokens, hidden, experts, top_k, intermediate, expert_dtype, shared);
+                 py::gil_scoped_release nogil;
+                 return std::make_unique<EpWorkerPool>(world, std::move(devices), s, o, std::chrono::milliseconds(timeout_ms));
+             }),
+             py::arg("world"), py::arg("devices"), py::arg("max_tokens"), py::arg("hidden"), py::arg("experts"), py::arg("top_k"),
+             py::arg("intermediate"), py::arg("expert_dtype"), py::arg("shared"), py::arg("capacity_factor") = 0.0, py::arg("timeout_ms") = 30000)
+        .def("world", &EpWorkerPool::world)
+        // per-rank lists: x[r], router_weight[r], gate_up_weight[r], down_weight[r]; the optional lists hold one tensor per rank
+        .def(
+            "run",
+            [](EpWorkerPool &pool, py::list x, py::list router_weight, py::list gate_up_weight, py::list down_weight, std::int64_t top_k,
+               py::object router_bias, py::object gate_up_scale, py::object down_scale, py::object shared_gate_up_weight,
+               py::object shared_down_weight, py::object shared_gate_up_scale, py::object shared_down_scale) {
+                const int R = pool.world();
+                auto at = [&](py::object lst, int r) -> py::object {
+                    if (lst.is_none())
+                        return py::none();
+                    py::list l = lst.cast<py::list>();
+                    if (static_cast<int>(l.size()) != R)
+                        throw std::runtime_error("bad rank count");
+                    return l[r];
+                };
+                std::vector<const Tensor *> xs(R);
+                std::vector<MoEWeights> ws(R);
+                for (int r = 0; r < R; r++) {
+                    xs[r] = &at(x, r).cast<const Tensor &>();
+                    ws[r] = weights_of(at(router_weight, r).cast<const Tensor &>(), at(gate_up_weight, r).cast<const Tensor &>(),
+                                       at(down_weight, r).cast<const Tensor &>(), at(router_bias, r), at(gate_up_scale, r), at(down_scale, r),
+                                       at(shared_gate_up_weight, r), at(shared_down_weight, r), at(shared_gate_up_scale, r),
+                                       at(shared_down_scale, r));
+                }
+                MoEConfig cfg;
+                cfg.top_k = top_k;
+                std::vector<Tensor> out;
+                {
+                    py::gil_scoped_release nogil;
+                    out = pool.run(xs, ws, cfg);
+                }
+                py::list res;
+                for (auto &t : out)
+                    res.append(py::cast(std::move(t)));
+                return res;
+            },
+            py::arg("x"), py::arg("router_weight"), py::arg("gate_up_weight"), py::arg("down_weight"), py::arg("top_k"),
+            py::arg("router_bias") = py::none(), py::arg("gate_up_scale") = py::none(), py::arg("down_scale") = py::none(),
             py::arg("shared_gate_up_weight") = py::none(), py::arg("shared_down_weight") = py::none(),
             py::arg("shared_gate_up_scale") = py::none(), py::arg("shared_down_scale") = py::none());
     m.def("moe_route", &moe_route_py, py::arg("x"), py::arg("router_weight"), py::arg("top_k"), py::arg("router_bias") = py::none());
