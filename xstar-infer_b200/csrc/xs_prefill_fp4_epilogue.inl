@@ -52,7 +52,7 @@
                     for (int h = 0; h < 2; h++)
 #pragma unroll
                         for (int c = 0; c < 16; c++)
-                            a[g][h * 16 + c] = silu_fast(__uint_as_float(pg[g][h][c])) * __uint_as_float(pu[g][h][c]);
+                            a[g][h * 16 + c] = silu_tanh(__uint_as_float(pg[g][h][c])) * __uint_as_float(pu[g][h][c]);
             }
             if (active) {
                 uint8_t *arow = static_cast<uint8_t *>(out) + static_cast<size_t>(row0 + r) * n_out + nt * 128;

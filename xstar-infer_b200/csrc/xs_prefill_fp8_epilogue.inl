@@ -149,7 +149,7 @@
             float m = 0.0f;
 #pragma unroll
             for (int c = 0; c < HALF; c++) {
-                acc[c] = __fdividef(acc[c], 1.0f + __expf(-acc[c])) * acc[HALF + c]; // SiLU with the approximate reciprocal
+                acc[c] = silu_tanh(acc[c]) * acc[HALF + c];
                 m = fmaxf(m, fabsf(acc[c]));
             }
             float *ax = amax_x + (it & 1) * (kPfGroups * 128);
