@@ -355,7 +355,7 @@ int check_workspace(const void *ws, size_t have, size_t need)
 }
 
 // ---- launches --------------------------------------------------------------------------------------------
-constexpr int kRouterSmallTokens = 64;
+constexpr int kRouterSmallTokens = 32;
 
 constexpr size_t kOffWnorm = 192;        // status block: f32 max router-row norm
 constexpr size_t kOffRefineCounters = 200; // status block: two u64 (tokens recomputed in full, exact logits computed)
@@ -446,17 +446,16 @@ int launch_logits(const XsMoeConfig *c, const void *x, const void *rw, float *lo
     }
     const __nv_bfloat16 *xb = static_cast<const __nv_bfloat16 *>(x), *rwb = static_cast<const __nv_bfloat16 *>(rw);
     if (T <= kRouterSmallTokens) {
-        // a few tokens per SM at most: one warp per block, lane = expert, one token per block (measured faster than the
-        // 8 x 32 tile up to 64 tokens, level at 96, slower beyond)
+        // a few tokens per SM at most: a feeder warp and a chain warp per block, lane = expert, one token per block
         static bool configured_rs[64] = {};
         int dev_rs = 0;
         XS_CUDA(cudaGetDevice(&dev_rs));
         if (dev_rs >= 64 || !configured_rs[dev_rs]) {
-            XS_CUDA(cudaFuncSetAttribute(xs::router_logits_small_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, xs::rs_smem_bytes<1>()));
+            XS_CUDA(cudaFuncSetAttribute(xs::router_logits_small_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, xs::rs_smem_bytes()));
             if (dev_rs < 64)
                 configured_rs[dev_rs] = true;
         }
-        xs::router_logits_small_kernel<1><<<dim3((E + 31) / 32, T), 32, xs::rs_smem_bytes<1>(), st>>>(xb, rwb, logits, T, H, E);
+        xs::router_logits_small_kernel<<<dim3((E + 31) / 32, T), xs::kRsThreads, xs::rs_smem_bytes(), st>>>(xb, rwb, logits, T, H, E);
         note_launch();
     } else if (T <= 1024) {
         // decode-sized batch: one output per thread, 8 experts x 32 tokens per block, cp.async pipeline

@@ -124,7 +124,9 @@ router_logits_big_kernel(const __nv_bfloat16 *__restrict__ x, const __nv_bfloat1
 // read (the router row is a warp-wide broadcast, the token rows are padded to stay bank-conflict free).
 // One accumulator per thread, touched once per k in ascending order: the contract's summation order -- which makes the
 // H dependent FMAs the floor of this kernel; the pipeline is eight chunks deep because at decode sizes the kernel is
-// otherwise bound by the latency of fetching its operands.
+// otherwise bound by the latency of fetching its operands.  (A version with feeder warps that widen the operands to f32 once
+// per block, as the small-batch kernel below does, was no faster here: 256 chain threads reading their token's f32 operand
+// are bound by shared-memory wavefronts, 40 per 4 k and SM against the 19 cycles the chains need.)
 constexpr int kRdExperts = 8, kRdTokens = 32, kRdK = 128, kRdStages = 8, kRdThreads = 256;
 constexpr int kRdXStride = kRdK + 8; // bf16 elements; 272-byte rows: 16-byte aligned and conflict-free for 16-byte reads
 constexpr int kRdSmemBytes = kRdStages * (kRdExperts * kRdK + kRdTokens * kRdXStride) * 2;
@@ -319,115 +321,110 @@ router_logits_mid_kernel(const __nv_bfloat16 *__restrict__ x, const __nv_bfloat1
 }
 
 // The smallest batches (a few tokens per SM at most): the floor of the router is the chain of H dependent FMAs of one
-// output (about 10 us at H = 4096), so the kernel is built to keep that chain fed and nothing else in its way.  One WARP
-// per block: lane = expert (32 experts per block), TPW tokens per lane (the launcher uses 1: one token per block; more
-// chains per lane measured slower).  Router rows arrive through a 4-stage
-// cp.async pipeline of 128-wide k chunks and are widened on the fly (one ALU operation per k); the token rows are widened
-// ONCE per chunk by the whole warp into an f32 buffer (so the per-lane cost of a token operand is a broadcast shared
-// read, not a conversion), one chunk ahead of the FMAs that use it.  With a single warp there is no block barrier;
-// __syncwarp orders the hand-overs.  Same contract: every accumulator sees k = 0, 1, 2, ... in order.
+// output (about 10 us at H = 4096), so the kernel is built to keep that chain fed and to put nothing else into the warp that
+// runs it.  A warp issues in program order: every instruction that shares a warp with the chain -- widening bf16 to f32,
+// address arithmetic, the copies' issue -- takes an issue slot the chain's next FMA then waits behind (a single-warp version
+// of this kernel executed 4 instructions per k and spent 3 cycles on each).  So a block is FOUR warps for 32 experts x one
+// token:
+//   warps 1..3, the feeders: each thread issues the cp.async copies of its own 16-byte pieces of the router rows (4 stages
+//     of 128-wide k chunks) and of the token row, and widens exactly those pieces to f32 in shared memory once they have
+//     landed (so a thread only ever waits for its own copies), one chunk ahead of the chain (one feeder warp alone took
+//     longer per chunk than the chain does);
+//   warp 0, the chain: lane = expert; per 4 k one 16-byte read of its own f32 row, one broadcast read of the token's, 4 FMAs.
+// All four meet once per chunk at a named barrier.  Same contract: every accumulator sees k = 0, 1, 2, ... in order.
 constexpr int kRsK = 128, kRsStages = 4, kRsWStride = kRsK + 8; // bf16 elements; 272-byte rows are conflict-free for 16-byte reads
-template <int TPW>
+constexpr int kRsFStride = kRsK + 4;                            // f32 elements; 528-byte rows: conflict-free 16-byte reads per quarter warp
+constexpr int kRsThreads = 128, kRsFeeders = kRsThreads - 32;
 constexpr int rs_smem_bytes()
 {
-    return kRsStages * (32 * kRsWStride + TPW * kRsK) * 2 + 2 * TPW * kRsK * 4;
+    return kRsStages * (32 * kRsWStride + kRsK) * 2 + 2 * (32 * kRsFStride + kRsK) * 4;
 }
-template <int TPW>
-__global__ void __launch_bounds__(32)
+__global__ void __launch_bounds__(kRsThreads)
 router_logits_small_kernel(const __nv_bfloat16 *__restrict__ x, const __nv_bfloat16 *__restrict__ rw, float *__restrict__ logits,
                            int T, int H, int E)
 {
     extern __shared__ __align__(16) uint8_t rs_smem[];
     __nv_bfloat16 (*wsm)[32][kRsWStride] = reinterpret_cast<__nv_bfloat16 (*)[32][kRsWStride]>(rs_smem);
-    __nv_bfloat16 (*xsm)[TPW][kRsK] =
-        reinterpret_cast<__nv_bfloat16 (*)[TPW][kRsK]>(rs_smem + kRsStages * 32 * kRsWStride * 2);
-    float (*xf)[TPW][kRsK] = reinterpret_cast<float (*)[TPW][kRsK]>(rs_smem + kRsStages * (32 * kRsWStride + TPW * kRsK) * 2);
-    const int lane = threadIdx.x;
-    const int e0 = blockIdx.x * 32, t0 = blockIdx.y * TPW;
+    __nv_bfloat16 (*xsm)[kRsK] = reinterpret_cast<__nv_bfloat16 (*)[kRsK]>(rs_smem + kRsStages * 32 * kRsWStride * 2);
+    float *fbase = reinterpret_cast<float *>(rs_smem + kRsStages * (32 * kRsWStride + kRsK) * 2);
+    auto wf = [&](int buf) { return fbase + buf * (32 * kRsFStride + kRsK); };                  // [32][kRsFStride]
+    auto xf = [&](int buf) { return fbase + buf * (32 * kRsFStride + kRsK) + 32 * kRsFStride; }; // [kRsK]
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int e0 = blockIdx.x * 32, t = blockIdx.y;
     const int chunks = H / kRsK;
-
-    auto issue = [&](int ch, int st) {
-        const int k0 = ch * kRsK;
-#pragma unroll
-        for (int i = 0; i < 16; i++) { // 32 router rows x 16 pieces of 8 bf16
-            const int p = lane + 32 * i;
-            const int r = p >> 4, c = (p & 15) * 8;
-            const bool ok = e0 + r < E;
-            cp_async16(&wsm[st][r][c], rw + static_cast<size_t>(ok ? e0 + r : 0) * H + k0 + c, ok);
-        }
-#pragma unroll
-        for (int i = 0; i < (TPW * 16 + 31) / 32; i++) {
-            const int p = lane + 32 * i;
-            if (p < TPW * 16) {
-                const int r = p >> 4, c = (p & 15) * 8;
-                const bool ok = t0 + r < T;
-                cp_async16(&xsm[st][r][c], x + static_cast<size_t>(ok ? t0 + r : 0) * H + k0 + c, ok);
-            }
-        }
-    };
-    auto widen = [&](int st, int buf) { // token rows of one chunk: bf16 -> f32, 4 elements per lane and token
-#pragma unroll
-        for (int j = 0; j < TPW; j++) {
-            const uint2 v = *reinterpret_cast<const uint2 *>(&xsm[st][j][lane * 4]);
-            *reinterpret_cast<float4 *>(&xf[buf][j][lane * 4]) =
-                make_float4(__uint_as_float(v.x << 16), __uint_as_float(v.x & 0xffff0000u), __uint_as_float(v.y << 16),
-                            __uint_as_float(v.y & 0xffff0000u));
-        }
+    auto meet = [] { asm volatile("bar.sync 1, %0;" ::"n"(kRsThreads) : "memory"); };
+    auto widen8 = [](const uint4 &v, float *d) {
+        *reinterpret_cast<float4 *>(d) = make_float4(__uint_as_float(v.x << 16), __uint_as_float(v.x & 0xffff0000u), __uint_as_float(v.y << 16),
+                                                    __uint_as_float(v.y & 0xffff0000u));
+        *reinterpret_cast<float4 *>(d + 4) = make_float4(__uint_as_float(v.z << 16), __uint_as_float(v.z & 0xffff0000u),
+                                                        __uint_as_float(v.w << 16), __uint_as_float(v.w & 0xffff0000u));
     };
 
+    if (warp >= 1) {
+        const int fid = threadIdx.x - 32; // 0 .. kRsFeeders - 1
+        constexpr int kPieces = 32 * (kRsK / 8), kIters = (kPieces + kRsFeeders - 1) / kRsFeeders;
+        auto issue = [&](int ch, int st) {
+            const int k0 = ch * kRsK;
 #pragma unroll
-    for (int s = 0; s < kRsStages - 1; s++) {
-        if (s < chunks)
-            issue(s, s);
-        asm volatile("cp.async.commit_group;" ::: "memory");
-    }
-    asm volatile("cp.async.wait_group %0;" ::"n"(kRsStages - 2) : "memory");
-    __syncwarp();
-    widen(0, 0);
-    float acc[TPW];
+            for (int i = 0; i < kIters; i++) { // 32 router rows x 16 pieces of 8 bf16
+                const int p = fid + kRsFeeders * i;
+                if (p < kPieces) {
+                    const int r = p >> 4, c = (p & 15) * 8;
+                    const bool ok = e0 + r < E;
+                    cp_async16(&wsm[st][r][c], rw + static_cast<size_t>(ok ? e0 + r : 0) * H + k0 + c, ok);
+                }
+            }
+            if (fid < kRsK / 8)
+                cp_async16(&xsm[st][fid * 8], x + static_cast<size_t>(t) * H + k0 + fid * 8, true);
+        };
+        auto widen = [&](int st, int buf) { // this thread's own pieces of the landed chunk: bf16 -> f32
+            float *w = wf(buf);
 #pragma unroll
-    for (int j = 0; j < TPW; j++)
-        acc[j] = 0.0f;
-    for (int ch = 0; ch < chunks; ch++) {
-        asm volatile("cp.async.wait_group %0;" ::"n"(kRsStages - 3) : "memory"); // chunk ch + 1 has landed
-        __syncwarp(); // ... for every lane; every lane has finished chunk ch - 1; xf[ch & 1] is written
-        const int nxt = ch + kRsStages - 1;
-        if (nxt < chunks)
-            issue(nxt, nxt % kRsStages);
-        asm volatile("cp.async.commit_group;" ::: "memory");
-        if (ch + 1 < chunks)
-            widen((ch + 1) % kRsStages, (ch + 1) & 1);
-        const int st = ch % kRsStages, buf = ch & 1;
-        const uint4 *wp = reinterpret_cast<const uint4 *>(&wsm[st][lane][0]);
-#pragma unroll 4
-        for (int i = 0; i < kRsK / 8; i++) {
-            const uint4 w = wp[i];
-            const float w0 = __uint_as_float(w.x << 16), w1 = __uint_as_float(w.x & 0xffff0000u);
-            const float w2 = __uint_as_float(w.y << 16), w3 = __uint_as_float(w.y & 0xffff0000u);
-            const float w4 = __uint_as_float(w.z << 16), w5 = __uint_as_float(w.z & 0xffff0000u);
-            const float w6 = __uint_as_float(w.w << 16), w7 = __uint_as_float(w.w & 0xffff0000u);
+            for (int i = 0; i < kIters; i++) {
+                const int p = fid + kRsFeeders * i;
+                if (p < kPieces) {
+                    const int r = p >> 4, c = (p & 15) * 8;
+                    widen8(*reinterpret_cast<const uint4 *>(&wsm[st][r][c]), w + r * kRsFStride + c);
+                }
+            }
+            if (fid < kRsK / 8)
+                widen8(*reinterpret_cast<const uint4 *>(&xsm[st][fid * 8]), xf(buf) + fid * 8);
+        };
 #pragma unroll
-            for (int j = 0; j < TPW; j++) {
-                const float4 a = *reinterpret_cast<const float4 *>(&xf[buf][j][i * 8]);
-                const float4 b = *reinterpret_cast<const float4 *>(&xf[buf][j][i * 8 + 4]);
-                float c = acc[j];
-                c = __fmaf_rn(a.x, w0, c);
-                c = __fmaf_rn(a.y, w1, c);
-                c = __fmaf_rn(a.z, w2, c);
-                c = __fmaf_rn(a.w, w3, c);
-                c = __fmaf_rn(b.x, w4, c);
-                c = __fmaf_rn(b.y, w5, c);
-                c = __fmaf_rn(b.z, w6, c);
-                c = __fmaf_rn(b.w, w7, c);
-                acc[j] = c;
+        for (int sidx = 0; sidx < kRsStages - 1; sidx++) {
+            if (sidx < chunks)
+                issue(sidx, sidx);
+            asm volatile("cp.async.commit_group;" ::: "memory");
+        }
+        for (int ch = 0; ch < chunks; ch++) {
+            asm volatile("cp.async.wait_group %0;" ::"n"(kRsStages - 2) : "memory"); // this thread's pieces of chunk ch have landed
+            widen(ch % kRsStages, ch & 1);
+            const int nxt = ch + kRsStages - 1; // the pieces just read out are this thread's own: refill them
+            if (nxt < chunks)
+                issue(nxt, nxt % kRsStages);
+            asm volatile("cp.async.commit_group;" ::: "memory");
+            // hand chunk ch over; the chain finished chunk ch - 1 by then, so buffer (ch + 1) & 1 is free for the next chunk
+            meet();
+        }
+    } else {
+        float acc = 0.0f;
+        for (int ch = 0; ch < chunks; ch++) {
+            meet(); // chunk ch is widened
+            const float4 *wp = reinterpret_cast<const float4 *>(wf(ch & 1) + lane * kRsFStride);
+            const float4 *xp = reinterpret_cast<const float4 *>(xf(ch & 1));
+#pragma unroll 8
+            for (int i = 0; i < kRsK / 4; i++) {
+                const float4 w = wp[i], a = xp[i];
+                acc = __fmaf_rn(a.x, w.x, acc);
+                acc = __fmaf_rn(a.y, w.y, acc);
+                acc = __fmaf_rn(a.z, w.z, acc);
+                acc = __fmaf_rn(a.w, w.w, acc);
             }
         }
+        const int e = e0 + lane;
+        if (e < E)
+            logits[static_cast<size_t>(t) * E + e] = acc;
     }
-    const int e = e0 + lane;
-#pragma unroll
-    for (int j = 0; j < TPW; j++)
-        if (e < E && t0 + j < T)
-            logits[static_cast<size_t>(t0 + j) * E + e] = acc[j];
 }
 
 // One warp per token.  Lane l holds experts l, l+32, l+64, ...  (NPL per lane).
