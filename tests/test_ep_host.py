@@ -311,3 +311,13 @@ def test_worker_pool_two_ranks_with_uneven_batches(oracle, fmt, tol):
     assert plan["tokens_of_rank"] == [90, 76]
     # the layer does not care which tokens sit on which rank: the global batch in rank order must equal the oracle's
     assert _pool_run(oracle, dims, 2, plan["tokens_of_rank"], seed=42) <= tol
+
+
+@pytest.mark.gpu
+def test_worker_pool_with_a_rank_that_holds_no_tokens(oracle):
+    """Fewer sequences than ranks: a rank with an empty batch still takes part in every collective of the step."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs on one box")
+    dims = dict(T=0, H=512, E=16, K=4, I=256, S=1, fmt="bf16", bias=None)
+    assert _pool_run(oracle, dims, 2, [0, 50], seed=43) <= 2e-3
+    assert _pool_run(oracle, dims, 2, [33, 0], seed=44) <= 2e-3
