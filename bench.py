@@ -570,7 +570,7 @@ class CppEpStep:
     """One rank's expert-parallel step through the C++ host: torch owns x / out / the weights, xstar_cpp.EpContext owns the
     exchange buffers and drives the stage calls and NCCL.  The unique id travels through torch.distributed once."""
 
-    def __init__(self, dims, rank, local_rank, world, x, weights, shared, bias):
+    def __init__(self, dims, rank, local_rank, world, x, weights, shared, bias, fused_return=True):
         import torch
         import torch.distributed as dist
 
@@ -583,7 +583,8 @@ class CppEpStep:
         box = [xstar_cpp.ep_unique_id() if rank == 0 else None]
         dist.broadcast_object_list(box, src=0)
         dt = {"bf16": xstar_cpp.DType.BFloat16, "fp8": xstar_cpp.DType.Float8E4M3, "fp4": xstar_cpp.DType.Float4E2M1x2}[fmt]
-        self.ctx = xstar_cpp.EpContext(None, box[0], rank, world, local_rank, T, H, E, K, I, dt, bool(S), 0.0)
+        self.ctx = xstar_cpp.EpContext(None, box[0], rank, world, local_rank, T, H, E, K, I, dt, bool(S), 0.0, fused_return)
+        self.fused_return = self.ctx.fused_return()
         self.shape = (T, H)
         self.K = K
         self.keep = (weights, shared, bias)
@@ -673,7 +674,7 @@ def measure_ep(name, dims, args, steps, repeats, rank, local_rank, world, want_e
     cpp = None
     if peer and args.ep_host == "cpp":
         try:
-            cpp = CppEpStep(dims, rank, local_rank, world, x, weights, shared, bias)
+            cpp = CppEpStep(dims, rank, local_rank, world, x, weights, shared, bias, args.ep_fused_return == "on")
         except Exception as e:  # noqa: BLE001 - any failure here means "use the Python host", on every rank
             print(f"rank {rank}: C++ expert-parallel host unavailable ({type(e).__name__}: {e})", file=sys.stderr, flush=True)
         agreed = torch.tensor([1 if cpp is not None else 0], dtype=torch.int32, device="cuda")
@@ -829,6 +830,7 @@ def measure_ep(name, dims, args, steps, repeats, rank, local_rank, world, want_e
                     "parallelism": f"ep{world}: experts sharded, " + ("dispatch/return by peer-memory stores over NVLink, no host synchronisation"
                                                                      if peer else "NCCL all-to-all dispatch/combine"),
                     "cuda_graph": bool(use_graph), "exchange_fallback": fallback,
+                    "return_trip": ("folded into the down GEMM's epilogue" if (cpp is not None and cpp.fused_return) else "separate return kernel"),
                     "host": ("C++ (xstar_cpp.EpContext: NCCL all-gather / all-reduce + peer stores, one process per GPU)" if cpp is not None
                              else "Python composition of the stage calls (torch.distributed for the collectives)"),
                     "l2": "inputs larger than L2: expert weights streamed per step exceed 126 MB"},
@@ -971,6 +973,8 @@ def main():
     ap.add_argument("--ep-host", default="cpp", choices=["cpp", "py"],
                     help="N > 1 with the peer exchange: the step is driven by the C++ host (xstar_cpp.EpContext, default) or by the "
                          "Python composition of the stage calls")
+    ap.add_argument("--ep-fused-return", default="on", choices=["on", "off"],
+                    help="N > 1, C++ host: let the down GEMM's epilogue store result rows into their source ranks where the kernels support it")
     ap.add_argument("--mma-rate", action="store_true", help="print the tensor-pipe and TMEM read-rate probe tables and exit")
     args = ap.parse_args()
     if args.mma_rate:
