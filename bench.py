@@ -472,7 +472,7 @@ def run_ours(args, dims):
         for name in SINGLE_GPU_WORKLOADS:
             wd = dict(synth.CONFIGS[name])
             try:
-                r = measure_single(name, wd, args, args.workload_steps, 3)
+                r = measure_single(name, wd, args, args.workload_steps, 5)
                 r.pop("inputs")
                 torch.cuda.empty_cache()
                 rf = roofline_single(wd, r)
@@ -886,7 +886,7 @@ def run_ours_ep(args, dims):
     extra = []
     if args.workloads == "all" and args.workload != "ep_fp4":
         try:
-            e = measure_ep("ep_fp4", dict(synth.CONFIGS["ep_fp4"]), args, args.workload_steps, 3, rank, local_rank, world)
+            e = measure_ep("ep_fp4", dict(synth.CONFIGS["ep_fp4"]), args, args.workload_steps, 5, rank, local_rank, world)
             if e is not None:
                 extra.append(e)
         except Exception as ex:
