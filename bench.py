@@ -570,7 +570,7 @@ class CppEpStep:
     """One rank's expert-parallel step through the C++ host: torch owns x / out / the weights, xstar_cpp.EpContext owns the
     exchange buffers and drives the stage calls and NCCL.  The unique id travels through torch.distributed once."""
 
-    def __init__(self, dims, rank, local_rank, world, x, weights, shared, bias, fused_return=True):
+    def __init__(self, dims, rank, local_rank, world, x, weights, shared, bias, fused_return=True, signal_barriers=True):
         import torch
         import torch.distributed as dist
 
@@ -583,8 +583,9 @@ class CppEpStep:
         box = [xstar_cpp.ep_unique_id() if rank == 0 else None]
         dist.broadcast_object_list(box, src=0)
         dt = {"bf16": xstar_cpp.DType.BFloat16, "fp8": xstar_cpp.DType.Float8E4M3, "fp4": xstar_cpp.DType.Float4E2M1x2}[fmt]
-        self.ctx = xstar_cpp.EpContext(None, box[0], rank, world, local_rank, T, H, E, K, I, dt, bool(S), 0.0, fused_return)
+        self.ctx = xstar_cpp.EpContext(None, box[0], rank, world, local_rank, T, H, E, K, I, dt, bool(S), 0.0, fused_return, signal_barriers)
         self.fused_return = self.ctx.fused_return()
+        self.signal_barriers = self.ctx.signal_barriers()
         self.shape = (T, H)
         self.K = K
         self.keep = (weights, shared, bias)
@@ -674,7 +675,7 @@ def measure_ep(name, dims, args, steps, repeats, rank, local_rank, world, want_e
     cpp = None
     if peer and args.ep_host == "cpp":
         try:
-            cpp = CppEpStep(dims, rank, local_rank, world, x, weights, shared, bias, args.ep_fused_return == "on")
+            cpp = CppEpStep(dims, rank, local_rank, world, x, weights, shared, bias, args.ep_fused_return == "on", args.ep_signal == "on")
         except Exception as e:  # noqa: BLE001 - any failure here means "use the Python host", on every rank
             print(f"rank {rank}: C++ expert-parallel host unavailable ({type(e).__name__}: {e})", file=sys.stderr, flush=True)
         agreed = torch.tensor([1 if cpp is not None else 0], dtype=torch.int32, device="cuda")
@@ -830,6 +831,8 @@ def measure_ep(name, dims, args, steps, repeats, rank, local_rank, world, want_e
                     "parallelism": f"ep{world}: experts sharded, " + ("dispatch/return by peer-memory stores over NVLink, no host synchronisation"
                                                                      if peer else "NCCL all-to-all dispatch/combine"),
                     "cuda_graph": bool(use_graph), "exchange_fallback": fallback,
+                    "barriers": ("peer-memory flags (xs_moe_ep_signal), counts exchanged by the same kernel" if (cpp is not None and cpp.signal_barriers)
+                                 else "NCCL all-gather + one-element all-reduces"),
                     "return_trip": ("folded into the down GEMM's epilogue" if (cpp is not None and cpp.fused_return) else "separate return kernel"),
                     "host": ("C++ (xstar_cpp.EpContext: NCCL all-gather / all-reduce + peer stores, one process per GPU)" if cpp is not None
                              else "Python composition of the stage calls (torch.distributed for the collectives)"),
@@ -975,6 +978,8 @@ def main():
                          "Python composition of the stage calls")
     ap.add_argument("--ep-fused-return", default="on", choices=["on", "off"],
                     help="N > 1, C++ host: let the down GEMM's epilogue store result rows into their source ranks where the kernels support it")
+    ap.add_argument("--ep-signal", default="on", choices=["on", "off"],
+                    help="N > 1, C++ host: counts exchange and barriers through peer-memory flags instead of NCCL collectives")
     ap.add_argument("--mma-rate", action="store_true", help="print the tensor-pipe and TMEM read-rate probe tables and exit")
     args = ap.parse_args()
     if args.mma_rate:

@@ -257,6 +257,19 @@ int xs_moe_ipc_close(void *ptr_dev);
 int xs_moe_ep_plan(const int32_t *all_counts_dev, int32_t ranks, int32_t num_experts, int32_t rank, int32_t *dest_base_dev,
                    int32_t *offsets_local_dev, int32_t *src_offsets_dev, void *stream);
 
+/* Barrier between the ranks of one box over peer memory, in one warp per GPU: every rank stores its launch epoch into row
+ * `rank` of every peer's flag array (peer_flags_dev: `ranks` pointers to arrays of `ranks` int32, zero at start) and polls its
+ * own array (my_flags_dev) until every rank's entry has reached the epoch; *epoch_dev (int32, zero at start) advances by one
+ * per call, on the device, so the call can be replayed inside a CUDA graph.  Everything the ranks enqueued before the call on
+ * their streams (peer stores among them) is visible to what they enqueue after it.  With counts_dev != NULL the call is also
+ * the layer's all-gather: this rank's `experts` counts are stored into row `rank` of every rank's all_counts first
+ * (peer_all_counts_dev: `ranks` pointers to (ranks, experts) int32).  A replacement for the all-gather and the one-element
+ * all-reduces of include/xs_moe_comm.h at a third of their latency; unlike them it WAITS for the peers inside a kernel, with a
+ * bound (about two seconds), after which the wait-timeout bit is set in the status word of workspace_dev: call it only once
+ * the ranks have agreed on the host that all of them will (EpGroup's check-in), and never for two ranks that share one GPU. */
+int xs_moe_ep_signal(int32_t ranks, int32_t rank, const int32_t *counts_dev, int32_t experts, void *const *peer_all_counts_dev,
+                     void *const *peer_flags_dev, int32_t *my_flags_dev, int32_t *epoch_dev, void *workspace_dev, void *stream);
+
 /* Quantise (per cfg->routed_format: bf16 rows | e4m3 + 1x128 f32 scales | e4m3 + 1x32 e8m0 scales) each local token
  * once and store it for each of its k experts into row dest_base[e] + (inv[t,j] - my_offsets[e]) of the owner's
  * buffers.  peer_rows_dev / peer_scales_dev: device arrays of `ranks` pointers (this rank's own buffer included).

@@ -6,8 +6,9 @@
 //   * rank d keeps the rows it receives GROUPED by local expert, inside an expert ordered by source rank, then by the
 //     source's own row order:   row(d; e, s, j) = offsets_local_d[e mod El] + sum_{s' < s} counts[s'][e] + j
 //   * the result of that row goes back to the source's row  offsets_s[e] + j  (its permuted row index)
-// No kernel here waits for another GPU: completion of the stores is established between kernels by a collective
-// barrier on the stream, so nothing can spin or hang on a peer.
+// The dispatch, return and plan kernels never wait for another GPU: completion of the stores is established between kernels
+// by a barrier on the stream -- a collective of the caller's, or ep_signal_kernel below, the one kernel of this file that
+// does wait for peers, with a bounded wait.
 #pragma once
 #include <cuda_bf16.h>
 #include <cuda_fp8.h>
@@ -58,6 +59,56 @@ ep_plan_kernel(const int32_t *__restrict__ all_counts, int R, int E, int me, int
             run += all_counts[threadIdx.x * E + k];
         }
     }
+}
+
+// Barrier between the ranks of one box over peer memory, optionally carrying every rank's per-expert counts (the layer's
+// all-gather): one warp per GPU.  Each rank keeps a launch counter (`epoch`, in its own memory: it advances by itself, so the
+// kernel can be replayed inside a CUDA graph) and a row of R flags that its peers write.
+//   1. (counts != null) lane-strided copy of my E counts into row `me` of every rank's all_counts (my own included);
+//   2. __threadfence_system: these stores, and all stores of the kernels before this one on the stream (the rows a dispatch
+//      or return kernel put into the peers' buffers), are ordered before
+//   3. flag[me] = epoch, stored into every peer's flag row;
+//   4. lanes 0..R-1 poll my own flag row until flags[r] >= epoch for every r, then fence again: what the peers wrote before
+//      their flag is visible to the kernels that follow on this stream.
+// ">=": a peer that is already one barrier ahead has passed this one.  The wait is bounded (about two seconds of polling with
+// back-off); when it runs out the kernel sets the wait-timeout bit of the status word and returns, and the
+// host raises -- a rank must only call this after the ranks agreed on the host that all of them will (the host check-in).
+// Never run two ranks' signal kernels on ONE GPU (virtual ranks): they would wait for each other across launches.
+__global__ void __launch_bounds__(32)
+ep_signal_kernel(const int32_t *__restrict__ counts, int E, int32_t *const *__restrict__ peer_all_counts, int32_t *const *__restrict__ peer_flags,
+                 volatile int32_t *my_flags, int32_t *epoch_counter, int R, int me, int32_t *status)
+{
+    const int lane = threadIdx.x;
+    int epoch = 0;
+    if (lane == 0) {
+        epoch = *epoch_counter + 1;
+        *epoch_counter = epoch;
+    }
+    epoch = __shfl_sync(0xffffffffu, epoch, 0);
+    if (counts)
+        for (int r = 0; r < R; r++)
+            for (int e = lane; e < E; e += 32)
+                peer_all_counts[r][me * E + e] = counts[e];
+    __threadfence_system();
+    __syncwarp();
+    __threadfence_system(); // cumulative: the other lanes' stores, ordered before the barrier above, come before my flag store
+    if (lane < R)
+        *reinterpret_cast<volatile int32_t *>(peer_flags[lane] + me) = epoch;
+    bool ok = true;
+    if (lane < R) {
+        unsigned spins = 0;
+        while (my_flags[lane] - epoch < 0) { // wrap-safe comparison
+            if (++spins > (1u << 24)) {
+                ok = false;
+                break;
+            }
+            if (spins > 64)
+                __nanosleep(spins > 4096 ? 128 : 32);
+        }
+    }
+    __threadfence_system();
+    if (!ok)
+        atomicOr(status, 1);
 }
 
 // FMT: 0 = bf16 rows, 1 = e4m3 codes + f32 scale per 128, 2 = e4m3 codes + e8m0 scale per 32 (MX-FP8).

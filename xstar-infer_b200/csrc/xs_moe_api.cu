@@ -2039,6 +2039,21 @@ int xs_moe_ep_plan(const int32_t *all_counts, int32_t ranks, int32_t experts, in
     return 0;
 }
 
+int xs_moe_ep_signal(int32_t ranks, int32_t rank, const int32_t *counts, int32_t experts, void *const *peer_all_counts,
+                     void *const *peer_flags, int32_t *my_flags, int32_t *epoch, void *ws, void *stream)
+{
+    if (int rc = check_ep(ranks, rank, experts > 0 ? experts : ranks))
+        return rc;
+    if (!peer_flags || !my_flags || !epoch || !ws || (counts && !peer_all_counts))
+        return fail(XS_MOE_ERR_INVALID_ARG, "null tensor pointer");
+    xs::ep_signal_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(counts, experts, reinterpret_cast<int32_t *const *>(peer_all_counts),
+                                                                          reinterpret_cast<int32_t *const *>(peer_flags), my_flags, epoch, ranks, rank,
+                                                                          static_cast<int32_t *>(ws));
+    note_launch();
+    XS_CUDA(cudaGetLastError());
+    return 0;
+}
+
 int xs_moe_ep_dispatch(const XsMoeConfig *cfg, int32_t ranks, const void *x, const int32_t *ids, const int32_t *inv,
                        const int32_t *my_offsets, const int32_t *dest_base, void *const *peer_rows, void *const *peer_scales,
                        int32_t capacity_rows, void *ws, void *stream)

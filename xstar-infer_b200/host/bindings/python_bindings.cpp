@@ -255,7 +255,7 @@ PYBIND11_MODULE(xstar_cpp, m)
     py::class_<EpContext>(m, "EpContext")
         .def(py::init([](std::shared_ptr<EpGroup> group, py::bytes id, int rank, int world, int device, std::int64_t max_tokens,
                          std::int64_t hidden, std::int64_t experts, std::int64_t top_k, std::int64_t intermediate, DType expert_dtype,
-                         bool shared, double capacity_factor, bool fused_return) {
+                         bool shared, double capacity_factor, bool fused_return, bool signal_barriers) {
                  const std::string raw = id;
                  if (raw.size() != 128)
                      throw std::runtime_error("unique id must be 128 bytes");
@@ -264,15 +264,17 @@ PYBIND11_MODULE(xstar_cpp, m)
                  EpOptions o;
                  o.capacity_factor = capacity_factor;
                  o.fused_return = fused_return;
+                 o.signal_barriers = signal_barriers;
                  const EpShape s = ep_shape(max_tokens, hidden, experts, top_k, intermediate, expert_dtype, shared);
                  py::gil_scoped_release nogil; // collective: the other ranks' threads must be able to run
                  return std::make_unique<EpContext>(std::move(group), u, rank, world, device, s, o);
              }),
              py::arg("group"), py::arg("unique_id"), py::arg("rank"), py::arg("world"), py::arg("device"), py::arg("max_tokens"),
              py::arg("hidden"), py::arg("experts"), py::arg("top_k"), py::arg("intermediate"), py::arg("expert_dtype"), py::arg("shared"),
-             py::arg("capacity_factor") = 0.0, py::arg("fused_return") = true)
+             py::arg("capacity_factor") = 0.0, py::arg("fused_return") = true, py::arg("signal_barriers") = true)
         .def("rank", &EpContext::rank)
         .def("fused_return", &EpContext::fused_return)
+        .def("signal_barriers", &EpContext::signal_barriers)
         .def("world", &EpContext::world)
         .def("capacity_rows", &EpContext::capacity_rows)
         .def("abandon", &EpContext::abandon)

@@ -47,6 +47,11 @@ struct EpOptions {
     // Let the down GEMM's epilogue store the result rows into their source ranks (where the kernels support it: FP4 experts
     // with hidden % 256 == 0) instead of a separate return kernel after the GEMM.  Same bits either way.
     bool fused_return = true;
+    // Exchange the per-expert counts and run the two barriers of a step through peer memory (xs_moe_ep_signal: one warp per
+    // GPU, bounded wait) instead of NCCL's all-gather and one-element all-reduces: a third of the latency at 8 GPUs.  The
+    // host check-in of the EpGroup (or, between processes, the caller's own agreement) must precede every step, since the
+    // kernel waits for its peers.
+    bool signal_barriers = true;
 };
 
 // rows a receive buffer holds for these sizes (the rule of EpOptions::capacity_factor), a multiple of 128
@@ -66,6 +71,7 @@ public:
     int world() const;
     std::int64_t capacity_rows() const;
     bool fused_return() const; // whether steps of this context take the fused return path
+    bool signal_barriers() const; // whether its counts exchange and barriers go through peer memory
 
     // One step, enqueued on `stream` (nullptr = the default stream), no host synchronisation after the check-in with
     // the group: x (T, H) bf16 and out (T, H) bf16 on this rank's device, T <= max_tokens.  `weights` holds the router

@@ -76,12 +76,13 @@ struct DevBuf {
 };
 
 // what a rank tells the others about its three exchange buffers
+constexpr int kPeerBuffers = 5; // rows, scales, return rows, counts matrix, barrier flags
 struct PeerInfo {
     std::int64_t pid;
     std::int32_t device;
     std::int32_t pad;
-    std::uint64_t ptr[3];
-    std::uint8_t ipc[3][XS_MOE_IPC_HANDLE_BYTES];
+    std::uint64_t ptr[kPeerBuffers];
+    std::uint8_t ipc[kPeerBuffers][XS_MOE_IPC_HANDLE_BYTES];
 };
 
 std::uint64_t mix(std::uint64_t h, std::uint64_t v)
@@ -100,6 +101,7 @@ struct EpContext::Impl {
     std::int64_t El = 0, capacity = 0, back_rows = 0;
     bool wire_bf16 = false;
     bool fused_return = false; // the down GEMM's epilogue stores the result rows into their source ranks itself
+    bool signal = false;       // counts exchange and barriers through peer memory instead of NCCL
     void *comm = nullptr;
     void *side = nullptr, *ev_fork = nullptr, *ev_join = nullptr;
     std::uint64_t steps = 0;
@@ -107,7 +109,7 @@ struct EpContext::Impl {
     bool abandoned = false;
 
     // exchange buffers other ranks store into, and every rank's addresses of them as this rank sees them
-    DevBuf rows, scales, back, tables;
+    DevBuf rows, scales, back, tables, counts_all, flags, epoch;
     std::vector<void *> imported;
     // step scratch
     DevBuf ints, ws_route, ws_grouped, y_grouped, sh_codes, sh_scales, sh_y, ws_shared, topk_w;
@@ -202,13 +204,19 @@ EpContext::EpContext(std::shared_ptr<EpGroup> group, const EpUniqueId &id, int r
     m.rows = DevBuf(m.capacity * row_bytes);
     m.scales = DevBuf(m.capacity * scale_bytes);
     m.back = DevBuf(m.back_rows * H * (m.wire_bf16 ? 2 : 4));
-    m.tables = DevBuf(3 * R * sizeof(void *));
+    m.tables = DevBuf(kPeerBuffers * R * sizeof(void *));
+    m.counts_all = DevBuf(R * E * 4);
+    m.flags = DevBuf(R * 4);
+    m.epoch = DevBuf(4);
+    raise_if(xs_moe_memset_async(m.counts_all.p, 0, R * E * 4, nullptr));
+    raise_if(xs_moe_memset_async(m.flags.p, 0, 256, nullptr));
+    raise_if(xs_moe_memset_async(m.epoch.p, 0, 256, nullptr));
     m.topk_w = DevBuf(T * K * 4);
 
     // small int arrays carved from one allocation (each 256-byte aligned)
     auto up = [](std::size_t n) { return (n * 4 + 255) / 256 * 256; };
     const std::size_t n_ids = up(T * K), n_e = up(E), n_e1 = up(E + 1), n_re = up(R * E), n_el1 = up(m.El + 1);
-    m.ints = DevBuf(4 * n_ids + 2 * n_e + n_e1 + 2 * n_re + n_el1 + 3 * 256);
+    m.ints = DevBuf(4 * n_ids + 2 * n_e + n_e1 + n_re + n_el1 + 3 * 256);
     std::uint8_t *b = m.ints.as<std::uint8_t>();
     auto take = [&](std::size_t bytes) {
         std::int32_t *p = reinterpret_cast<std::int32_t *>(b);
@@ -222,7 +230,7 @@ EpContext::EpContext(std::shared_ptr<EpGroup> group, const EpUniqueId &id, int r
     m.counts = take(n_e);
     m.dest_base = take(n_e);
     m.offsets = take(n_e1);
-    m.all_counts = take(n_re);
+    m.all_counts = m.counts_all.as<std::int32_t>(); // an allocation of its own: peers store into it
     m.src_offsets = take(n_re);
     m.offsets_local = take(n_el1);
     m.token = take(256);
@@ -259,8 +267,8 @@ EpContext::EpContext(std::shared_ptr<EpGroup> group, const EpUniqueId &id, int r
     PeerInfo mine{};
     mine.pid = static_cast<std::int64_t>(getpid());
     mine.device = device;
-    void *bufs[3] = {m.rows.p, m.scales.p, m.back.p};
-    for (int i = 0; i < 3; i++) {
+    void *bufs[kPeerBuffers] = {m.rows.p, m.scales.p, m.back.p, m.counts_all.p, m.flags.p};
+    for (int i = 0; i < kPeerBuffers; i++) {
         mine.ptr[i] = reinterpret_cast<std::uint64_t>(bufs[i]);
         raise_if(xs_moe_ipc_export(bufs[i], mine.ipc[i]));
     }
@@ -270,9 +278,15 @@ EpContext::EpContext(std::shared_ptr<EpGroup> group, const EpUniqueId &id, int r
     raise_if(xs_moe_stream_synchronize(nullptr));
     std::vector<PeerInfo> all(R);
     cuda_memcpy_d2h(all.data(), recv.p, sizeof(PeerInfo) * R);
-    std::vector<void *> table(3 * R, nullptr);
+    std::vector<void *> table(kPeerBuffers * R, nullptr);
+    bool distinct_devices = true; // two ranks on one GPU (virtual ranks) must not wait for each other inside kernels
+    for (std::size_t a = 0; a < R; a++)
+        for (std::size_t b2 = a + 1; b2 < R; b2++)
+            if (all[a].pid == all[b2].pid && all[a].device == all[b2].device)
+                distinct_devices = false;
+    m.signal = options.signal_barriers && distinct_devices;
     for (std::size_t r = 0; r < R; r++)
-        for (int i = 0; i < 3; i++) {
+        for (int i = 0; i < kPeerBuffers; i++) {
             if (static_cast<int>(r) == rank) {
                 table[i * R + r] = bufs[i];
             } else if (all[r].pid == mine.pid) {
@@ -312,6 +326,10 @@ std::int64_t EpContext::capacity_rows() const
 bool EpContext::fused_return() const
 {
     return impl_->fused_return;
+}
+bool EpContext::signal_barriers() const
+{
+    return impl_->signal;
 }
 
 void EpContext::abandon() noexcept
@@ -379,11 +397,24 @@ void EpContext::forward_into(const Tensor &x, const MoEWeights &weights, const M
     raise_if(xs_moe_route(&c_route, x.data(), c.w.router_w_dev, c.w.router_bias_dev, nullptr, m.ids, tw, m.ws_route.p, m.ws_route_bytes,
                           stream));
     raise_if(xs_moe_permute(&c_route, m.ids, m.counts, m.offsets, m.perm, m.inv, m.ws_route.p, m.ws_route_bytes, stream));
-    raise_if(xs_moe_comm_all_gather(m.comm, m.counts, m.all_counts, static_cast<std::size_t>(m.shape.experts) * 4, stream));
+    void *const *t_counts = t_rows + 3 * R;
+    void *const *t_flags = t_rows + 4 * R;
+    auto barrier = [&]() {
+        if (m.signal)
+            raise_if(xs_moe_ep_signal(R, m.rank, nullptr, 0, nullptr, t_flags, m.flags.as<std::int32_t>(), m.epoch.as<std::int32_t>(),
+                                      m.ws_route.p, stream));
+        else
+            raise_if(xs_moe_comm_barrier(m.comm, m.token, stream));
+    };
+    if (m.signal) // every rank's counts into every rank's matrix, and a barrier
+        raise_if(xs_moe_ep_signal(R, m.rank, m.counts, c_route.num_experts, t_counts, t_flags, m.flags.as<std::int32_t>(),
+                                  m.epoch.as<std::int32_t>(), m.ws_route.p, stream));
+    else
+        raise_if(xs_moe_comm_all_gather(m.comm, m.counts, m.all_counts, static_cast<std::size_t>(m.shape.experts) * 4, stream));
     raise_if(xs_moe_ep_plan(m.all_counts, R, c_route.num_experts, m.rank, m.dest_base, m.offsets_local, m.src_offsets, stream));
     raise_if(xs_moe_ep_dispatch(&c_route, R, x.data(), m.ids, m.inv, m.offsets, m.dest_base, t_rows, t_scales,
                                 static_cast<int32_t>(m.capacity), m.ws_route.p, stream));
-    raise_if(xs_moe_comm_barrier(m.comm, m.token, stream)); // every rank's rows have landed
+    barrier(); // every rank's rows have landed
     XsMoeWeights w_local = c.w;
     if (m.fused_return) {
         // the down GEMM stores each finished tile's rows into their source ranks: the return trip overlaps the math
@@ -397,7 +428,7 @@ void EpContext::forward_into(const Tensor &x, const MoEWeights &weights, const M
                                   static_cast<int32_t>(m.capacity), t_back, static_cast<int32_t>(m.back_rows), m.wire_bf16 ? 1 : 0,
                                   m.ws_route.p, stream));
     }
-    raise_if(xs_moe_comm_barrier(m.comm, m.token, stream)); // every expert output for this rank's tokens has landed
+    barrier(); // every expert output for this rank's tokens has landed
     const float *shared_y = nullptr;
     if (m.shape.shared) {
         raise_if(xs_moe_stream_wait_event(stream, m.ev_join));

@@ -45,7 +45,7 @@ EXPORTS = [
     "xs_moe_stream_synchronize", "xs_moe_workspace_bytes", "xs_moe_workspace_init", "xs_moe_forward",
     "xs_moe_forward_host", "xs_moe_forward_profile", "xs_moe_block_workspace_bytes", "xs_moe_block_forward", "xs_moe_rmsnorm", "xs_moe_route", "xs_moe_topk", "xs_moe_permute", "xs_moe_permute_noalloc", "xs_moe_grouped_mlp_workspace_bytes",
     "xs_moe_grouped_mlp", "xs_moe_quantize_rows_fp8", "xs_moe_quantize_rows_mxfp8", "xs_moe_gather_rows", "xs_moe_combine", "xs_moe_combine_bf16_rows", "xs_moe_gather_rows_f32_to_bf16", "xs_moe_check_flags", "xs_moe_debug_counters", "xs_moe_probe_mma_rate", "xs_moe_probe_tmem_ld_rate", "xs_moe_probe_handoff", "xs_moe_launch_count", "xs_moe_plan_info",
-    "xs_moe_ipc_export", "xs_moe_ipc_import", "xs_moe_ipc_close", "xs_moe_ep_plan", "xs_moe_ep_dispatch", "xs_moe_ep_return",
+    "xs_moe_ipc_export", "xs_moe_ipc_import", "xs_moe_ipc_close", "xs_moe_ep_plan", "xs_moe_ep_dispatch", "xs_moe_ep_return", "xs_moe_ep_signal",
     "xs_moe_grouped_mlp_return_supported", "xs_moe_grouped_mlp_return",
     "xs_moe_comm_available", "xs_moe_comm_unique_id", "xs_moe_comm_create", "xs_moe_comm_destroy", "xs_moe_comm_abort",
     "xs_moe_comm_async_error", "xs_moe_comm_all_gather", "xs_moe_comm_barrier", "xs_moe_comm_all_to_all_v", "xs_moe_stream_create",
@@ -110,6 +110,7 @@ def lib():
             "xs_moe_permute_noalloc": [cfgp, vp, vp, vp, vp, vp, vp],
             "xs_moe_grouped_mlp_workspace_bytes": [cfgp, i32, C.POINTER(sz)],
             "xs_moe_grouped_mlp": [cfgp, wp, vp, vp, vp, i32, vp, vp, sz, vp],
+            "xs_moe_ep_signal": [i32, i32, vp, i32, vp, vp, vp, vp, vp, vp],
             "xs_moe_grouped_mlp_return_supported": [cfgp, i32, C.POINTER(i32)],
             "xs_moe_grouped_mlp_return": [cfgp, wp, vp, vp, vp, i32, i32, i32, vp, vp, vp, i32, vp, sz, vp],
             "xs_moe_quantize_rows_fp8": [vp, i32, i32, vp, vp, vp],
