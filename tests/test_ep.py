@@ -1,8 +1,10 @@
 """Expert parallelism: the host-side planning on its own, the whole exchange on two CPU ranks (gloo) with a
 stand-in for the device ops, and -- where two GPUs are visible -- the real thing over NCCL."""
+import ctypes as C
 import datetime
 import os
 import sys
+import time
 
 import numpy as np
 import pytest
@@ -15,7 +17,7 @@ for p in (ROOT, os.path.join(ROOT, "xstar-infer_b200"), os.path.join(ROOT, "test
     if p not in sys.path:
         sys.path.insert(0, p)
 
-from xstar_moe import ep, synth  # noqa: E402
+from xstar_moe import capi, ep, synth  # noqa: E402
 
 
 # ---- planning (numpy only) --------------------------------------------------------------------------------------
@@ -447,3 +449,37 @@ def test_ep_peer_exchange_on_gpus_matches_oracle(oracle, tmp_path, fmt, tol):
     got = np.concatenate([np.load(tmp_path / f"out{r}.npy") for r in range(world)])
     rel = synth.rel_l2(synth.bf16_bits_to_f32(got), synth.bf16_bits_to_f32(ref["out"]))
     assert rel <= tol, rel
+
+
+@pytest.mark.gpu
+def test_signal_barrier_passes_alone_and_gives_up_when_a_peer_never_arrives():
+    """xs_moe_ep_signal on one GPU: a one-rank barrier passes at once and carries the counts; with a second rank that never
+    stores its flag the bounded wait runs out (about two seconds), the kernel returns, and the status word reports it."""
+    L = capi.lib()
+    st = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    ws = torch.zeros(4096, dtype=torch.uint8, device="cuda")
+    E = 8
+    counts = torch.arange(1, E + 1, dtype=torch.int32, device="cuda")
+    all_counts = torch.zeros(2 * E, dtype=torch.int32, device="cuda")
+    flags = torch.zeros(2, dtype=torch.int32, device="cuda")
+    epoch = torch.zeros(1, dtype=torch.int32, device="cuda")
+    t_counts = torch.tensor([all_counts.data_ptr()], dtype=torch.int64, device="cuda")
+    t_flags = torch.tensor([flags.data_ptr()], dtype=torch.int64, device="cuda")
+    for step in (1, 2, 3):
+        capi.check(L.xs_moe_ep_signal(1, 0, capi.ptr(counts), E, capi.ptr(t_counts), capi.ptr(t_flags), capi.ptr(flags), capi.ptr(epoch),
+                                      capi.ptr(ws), st))
+        capi.check(L.xs_moe_check_flags(capi.ptr(ws), st))
+        assert int(epoch.item()) == step and int(flags[0].item()) == step
+    assert torch.equal(all_counts[:E], counts)
+    # two ranks, of which only rank 0 ever signals: rank 0's wait for flags[1] runs out
+    flags.zero_()
+    epoch.zero_()
+    t_flags2 = torch.tensor([flags.data_ptr(), flags.data_ptr()], dtype=torch.int64, device="cuda")  # "rank 1"'s row is never read
+    t0 = time.time()
+    capi.check(L.xs_moe_ep_signal(2, 0, None, 0, None, capi.ptr(t_flags2), capi.ptr(flags), capi.ptr(epoch), capi.ptr(ws), st))
+    with pytest.raises(RuntimeError, match="wait timed out"):
+        capi.check(L.xs_moe_check_flags(capi.ptr(ws), st))
+    assert 0.2 < time.time() - t0 < 30.0
+    capi.check(L.xs_moe_check_flags(capi.ptr(ws), st))  # the flag is cleared; the context is still usable
+    x = torch.ones(8, device="cuda")
+    assert float((x * 2).sum().item()) == 16.0
