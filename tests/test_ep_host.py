@@ -321,3 +321,79 @@ def test_worker_pool_with_a_rank_that_holds_no_tokens(oracle):
     dims = dict(T=0, H=512, E=16, K=4, I=256, S=1, fmt="bf16", bias=None)
     assert _pool_run(oracle, dims, 2, [0, 50], seed=43) <= 2e-3
     assert _pool_run(oracle, dims, 2, [33, 0], seed=44) <= 2e-3
+
+
+# ---- the collective layer by itself (include/xs_moe_comm.h) -----------------------------------------------------------
+def _comm_rank(L, uid, rank, world, results):
+    """One rank of the collective layer through ctypes: all-gather, barrier, all-to-all with uneven splits."""
+    import ctypes as C
+    capi.check(L.xs_moe_set_device(rank))
+    comm = C.c_void_p()
+    capi.check(L.xs_moe_comm_create(C.byref(comm), uid, rank, world))
+    stream = C.c_void_p()
+    capi.check(L.xs_moe_stream_create(C.byref(stream)))
+
+    def dev(nbytes):
+        p = C.c_void_p()
+        capi.check(L.xs_moe_device_alloc(C.byref(p), max(nbytes, 256)))
+        return p
+
+    def up(p, a):
+        capi.check(L.xs_moe_memcpy_h2d(p, a.ctypes.data_as(C.c_void_p), a.nbytes))
+
+    def down(p, n, dtype):
+        a = np.empty(n, dtype)
+        capi.check(L.xs_moe_memcpy_d2h(a.ctypes.data_as(C.c_void_p), p, a.nbytes))
+        return a
+
+    # all-gather of 5 int32 per rank
+    mine = np.arange(5, dtype=np.int32) + 100 * rank
+    s, r = dev(20), dev(20 * world)
+    up(s, mine)
+    capi.check(L.xs_moe_comm_all_gather(comm, s, r, 20, stream))
+    tok = dev(4)
+    capi.check(L.xs_moe_memset_async(tok, 0, 4, stream))
+    capi.check(L.xs_moe_comm_barrier(comm, tok, stream))
+    capi.check(L.xs_moe_stream_synchronize(stream))
+    gathered = down(r, 5 * world, np.int32)
+    # all-to-all: rank a sends (a + 1) * (b + 1) bytes of value 16 * a + b to rank b
+    send_n = [(rank + 1) * (b + 1) for b in range(world)]
+    recv_n = [(a + 1) * (rank + 1) for a in range(world)]
+    sbuf = np.concatenate([np.full(send_n[b], 16 * rank + b, np.uint8) for b in range(world)])
+    sp, rp = dev(sbuf.nbytes), dev(sum(recv_n))
+    up(sp, sbuf)
+    sz = C.c_size_t * world
+    soff = np.concatenate([[0], np.cumsum(send_n)[:-1]]).tolist()
+    roff = np.concatenate([[0], np.cumsum(recv_n)[:-1]]).tolist()
+    capi.check(L.xs_moe_comm_all_to_all_v(comm, world, sp, sz(*send_n), sz(*soff), rp, sz(*recv_n), sz(*roff), stream))
+    capi.check(L.xs_moe_stream_synchronize(stream))
+    got = down(rp, sum(recv_n), np.uint8)
+    code = C.c_int32(-1)
+    capi.check(L.xs_moe_comm_async_error(comm, C.byref(code)))
+    results[rank] = (gathered, got, recv_n, code.value)
+    for p in (s, r, tok, sp, rp):
+        capi.check(L.xs_moe_device_free(p))
+    capi.check(L.xs_moe_stream_destroy(stream))
+    capi.check(L.xs_moe_comm_destroy(comm))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("world", [1, 2])
+def test_collective_layer_all_gather_barrier_all_to_all(world):
+    import ctypes as C
+    if torch.cuda.device_count() < world:
+        pytest.skip("needs two GPUs on one box")
+    L = capi.lib()
+    uid = (C.c_uint8 * 128)()
+    capi.check(L.xs_moe_comm_unique_id(uid))
+    results = [None] * world
+    res = _run_threads([(lambda r=r: _comm_rank(L, uid, r, world, results)) for r in range(world)])
+    for k, v in res:
+        assert k == "ok", v
+    for rank in range(world):
+        gathered, got, recv_n, code = results[rank]
+        assert code == 0
+        assert gathered.tolist() == [v + 100 * a for a in range(world) for v in range(5)]
+        want = np.concatenate([np.full(recv_n[a], 16 * a + rank, np.uint8) for a in range(world)])
+        assert np.array_equal(got, want)
+    capi.check(L.xs_moe_set_device(0))
