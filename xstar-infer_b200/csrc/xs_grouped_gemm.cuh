@@ -405,6 +405,7 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
     unsigned long long *prof = reinterpret_cast<unsigned long long *>(status + 16); // role profile, see xs_moe_debug_counters
     const long long t_start = prof_clock();
     long long w0 = 0, w1 = 0;
+    pdl_launch_dependents();
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < stages; s++) {
@@ -430,6 +431,7 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    pdl_wait(); // everything above touches only this CTA's shared memory and TMEM
 
     const int n_f_tiles = n_out / kTileM;
     const int num_tiles = *tt.num_tiles;

@@ -13,6 +13,7 @@
 #include <cstring>
 #include <atomic>
 #include <mutex>
+#include <utility>
 #include <type_traits>
 #include <vector>
 #include <string>
@@ -36,6 +37,33 @@ std::atomic<unsigned long long> g_launches{0};
 inline void note_launch()
 {
     g_launches.fetch_add(1, std::memory_order_relaxed);
+}
+
+// Launch with the programmatic-serialisation attribute (see pdl_wait in xs_ptx.cuh): only for kernels whose every thread
+// calls xs::pdl_wait() before its first access to global memory that other kernels of the stream write or read.
+// XS_MOE_PDL=0 in the environment turns the attribute off (the kernels then start after their predecessor, as usual).
+inline bool pdl_enabled()
+{
+    static const bool on = [] {
+        const char *e = getenv("XS_MOE_PDL");
+        return !(e && e[0] == '0');
+    }();
+    return on;
+}
+template <typename... KArgs, typename... Args>
+cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args &&...args)
+{
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kern, KArgs(std::forward<Args>(args))...);
 }
 
 int fail(int status, const char *fmt, ...)
@@ -455,7 +483,7 @@ int launch_logits(const XsMoeConfig *c, const void *x, const void *rw, float *lo
             if (dev_rs < 64)
                 configured_rs[dev_rs] = true;
         }
-        xs::router_logits_small_kernel<<<dim3((E + 31) / 32, T), xs::kRsThreads, xs::rs_smem_bytes(), st>>>(xb, rwb, logits, T, H, E);
+        XS_CUDA(launch_pdl(xs::router_logits_small_kernel, dim3((E + 31) / 32, T), xs::kRsThreads, xs::rs_smem_bytes(), st, xb, rwb, logits, T, H, E));
         note_launch();
     } else if (T <= 1024) {
         // decode-sized batch: one output per thread, 8 experts x 32 tokens per block, cp.async pipeline
@@ -500,13 +528,13 @@ int launch_topk(const XsMoeConfig *c, const float *logits, const float *bias, in
         return 0;
     const int blocks = (T + 3) / 4;
     if (E <= 32) {
-        xs::topk_kernel<1><<<blocks, 128, 0, st>>>(logits, bias, ids, w, T, E, K);
+        XS_CUDA(launch_pdl(xs::topk_kernel<1>, blocks, 128, 0, st, logits, bias, ids, w, T, E, K));
         note_launch();
     } else if (E <= 256) {
-        xs::topk_kernel<8><<<blocks, 128, 0, st>>>(logits, bias, ids, w, T, E, K);
+        XS_CUDA(launch_pdl(xs::topk_kernel<8>, blocks, 128, 0, st, logits, bias, ids, w, T, E, K));
         note_launch();
     } else {
-        xs::topk_kernel<32><<<blocks, 128, 0, st>>>(logits, bias, ids, w, T, E, K);
+        XS_CUDA(launch_pdl(xs::topk_kernel<32>, blocks, 128, 0, st, logits, bias, ids, w, T, E, K));
         note_launch();
     }
     XS_CUDA(cudaGetLastError());
@@ -556,8 +584,8 @@ int launch_permute_small(const XsMoeConfig *c, const int32_t *ids, int32_t *coun
 {
     const int T = c->num_tokens, E = c->num_experts, K = c->top_k;
     const size_t smem = static_cast<size_t>(E) * xs::kChunkWords * 4 + static_cast<size_t>(E) * 4;
-    xs::permute_small_kernel<<<1, xs::kChunkTokens, smem, st>>>(ids, counts, offsets, perm, inv, T, E, K, extra_rows, gp.n_tile,
-                                                                gp.max_tiles, tb.tile_expert, tb.tile_row0, tb.num_tiles, status);
+    XS_CUDA(launch_pdl(xs::permute_small_kernel, 1, xs::kChunkTokens, smem, st, ids, counts, offsets, perm, inv, T, E, K, extra_rows,
+                       gp.n_tile, gp.max_tiles, tb.tile_expert, tb.tile_row0, tb.num_tiles, status));
     note_launch();
     XS_CUDA(cudaGetLastError());
     return 0;
@@ -637,7 +665,7 @@ int launch_gemm_fp8_t(const CUtensorMap &tw, const CUtensorMap &tw2, const CUten
     int grid = di.sms < max_work ? di.sms : max_work;
     if (grid < 1)
         grid = 1;
-    kern<<<grid, xs::kGemmThreads, smem, st>>>(tw, tw2, tx, offsets, tt, sc, groups, w_rows, n_out, K, out, status, stages);
+    XS_CUDA(launch_pdl(kern, grid, xs::kGemmThreads, smem, st, tw, tw2, tx, offsets, tt, sc, groups, w_rows, n_out, K, out, status, stages));
     note_launch();
     XS_CUDA(cudaGetLastError());
     return 0;
@@ -1335,8 +1363,8 @@ static int combine_impl(const XsMoeConfig *cfg, const float *y, const int32_t *i
     if (T == 0)
         return 0;
     int gy = (H + 1023) / 1024;
-    xs::combine_kernel<float, float><<<dim3(T, gy), 128, 0, static_cast<cudaStream_t>(stream)>>>(
-        y, inv, topk_w, shared, static_cast<__nv_bfloat16 *>(out), T, H, K, static_cast<const __nv_bfloat16 *>(residual));
+    XS_CUDA(launch_pdl(xs::combine_kernel<float, float>, dim3(T, gy), 128, 0, static_cast<cudaStream_t>(stream), y, inv, topk_w, shared,
+                       static_cast<__nv_bfloat16 *>(out), T, H, K, static_cast<const __nv_bfloat16 *>(residual)));
     note_launch();
     XS_CUDA(cudaGetLastError());
     return 0;
@@ -1587,10 +1615,12 @@ static int forward_impl(const XsMoeConfig *cfg, const XsMoeWeights *w, const voi
         if (int rc = launch_quantize_rows_mx(x, inv, K, rows, reinterpret_cast<uint8_t *>(rows_scale), T, H, st))
             return rc;
     } else if (fp8) {
-        xs::scatter_rows_kernel<true><<<T, 256, 0, st>>>(static_cast<const __nv_bfloat16 *>(x), inv, rows, rows_scale, T, H, K, n_routed, S);
+        XS_CUDA(launch_pdl(xs::scatter_rows_kernel<true>, T, 256, 0, st, static_cast<const __nv_bfloat16 *>(x), inv, rows, rows_scale, T, H, K,
+                           n_routed, S));
         note_launch();
     } else {
-        xs::scatter_rows_kernel<false><<<T, 256, 0, st>>>(static_cast<const __nv_bfloat16 *>(x), inv, rows, nullptr, T, H, K, n_routed, S);
+        XS_CUDA(launch_pdl(xs::scatter_rows_kernel<false>, T, 256, 0, st, static_cast<const __nv_bfloat16 *>(x), inv, rows, nullptr, T, H, K,
+                           n_routed, S));
         note_launch();
     }
     XS_CUDA(cudaGetLastError());

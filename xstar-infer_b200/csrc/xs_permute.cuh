@@ -195,6 +195,8 @@ permute_small_kernel(const int32_t *__restrict__ topk_ids, int32_t *__restrict__
     int *s_off = reinterpret_cast<int *>(bits + E * kChunkWords);
     __shared__ int warp_sums[32];
     __shared__ int total;
+    pdl_launch_dependents();
+    pdl_wait();
     build_bits(bits, topk_ids, T, E, K, 0, status);
     // counts and offsets: experts in passes of blockDim.x, carrying the running total
     int carry = 0;
@@ -278,6 +280,8 @@ scatter_rows_kernel(const __nv_bfloat16 *__restrict__ x, const int32_t *__restri
                     float *__restrict__ row_scales, int T, int H, int K, int n_routed, int with_shared)
 {
     const int t = blockIdx.x;
+    pdl_launch_dependents();
+    pdl_wait();
     if (t >= T)
         return;
     __shared__ int dst[33];
@@ -379,6 +383,8 @@ combine_kernel(const YT *__restrict__ y, const int32_t *__restrict__ inv, const 
                const __nv_bfloat16 *__restrict__ residual = nullptr)
 {
     const int t = blockIdx.x;
+    pdl_launch_dependents();
+    pdl_wait();
     if (t >= T)
         return;
     __shared__ int s_row[32];

@@ -146,6 +146,22 @@ __device__ __forceinline__ void reg_alloc()
 }
 
 // ---- TMA ----------------------------------------------------------------------------------------------
+// Programmatic dependent launch.  A kernel launched with the programmatic-serialisation attribute may be scheduled while
+// the kernel before it in the stream is still running: pdl_wait() returns once that kernel has completed and its writes
+// are visible, so everything before it (barrier setup, TMEM allocation, tensor-map prefetch) overlaps the predecessor's
+// tail, and nothing before it may read or write global memory that another kernel of the stream produces or reads.  Every
+// thread of a kernel launched that way calls pdl_wait() on every path, so that "kernel k completed" implies "kernel k - 1
+// completed".  pdl_launch_dependents() lets the next kernel be scheduled as soon as every CTA of this one has called it.
+// Both are no-ops in a kernel launched without the attribute.
+__device__ __forceinline__ void pdl_wait()
+{
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+__device__ __forceinline__ void pdl_launch_dependents()
+{
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
 __device__ __forceinline__ void prefetch_tmap(const CUtensorMap *m)
 {
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(m)) : "memory");

@@ -6,6 +6,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "xs_ptx.cuh"
+
 namespace xs {
 
 // Large batches: (16 * TPT) tokens x 128 experts per block, TPT x 8 outputs per thread (launched with TPT = 4: 64-token
@@ -354,6 +356,8 @@ router_logits_small_kernel(const __nv_bfloat16 *__restrict__ x, const __nv_bfloa
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int e0 = blockIdx.x * 32, t = blockIdx.y;
     const int chunks = H / kRsK;
+    pdl_launch_dependents();
+    pdl_wait();
     auto meet = [] { asm volatile("bar.sync 1, %0;" ::"n"(kRsThreads) : "memory"); };
     auto widen8 = [](const uint4 &v, float *d) {
         *reinterpret_cast<float4 *>(d) = make_float4(__uint_as_float(v.x << 16), __uint_as_float(v.x & 0xffff0000u), __uint_as_float(v.y << 16),
@@ -539,6 +543,8 @@ topk_kernel(const float *__restrict__ logits, const float *__restrict__ bias, in
 {
     const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const int lane = threadIdx.x & 31;
+    pdl_launch_dependents();
+    pdl_wait();
     if (warp >= T)
         return;
     topk_warp<NPL>(logits, bias, topk_ids, topk_w, warp, lane, E, K);
