@@ -115,6 +115,7 @@ grouped_gemm_fp4_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    pdl_wait(); // everything above touches only this CTA's shared memory and TMEM
     const uint32_t sf_base = tmem_base + 2 * ACC_COLS;
 
     const int n_f_tiles = n_out / kTileM;
@@ -395,6 +396,8 @@ quantize_rows_mxfp8_kernel(const __nv_bfloat16 *__restrict__ x, const int32_t *_
                            uint8_t *__restrict__ scale, int rows, int cols)
 {
     const int r = blockIdx.x;
+    pdl_launch_dependents();
+    pdl_wait();
     if (r >= rows)
         return;
     const int groups = cols / 32;

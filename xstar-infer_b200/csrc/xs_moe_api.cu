@@ -496,7 +496,7 @@ int launch_logits(const XsMoeConfig *c, const void *x, const void *rw, float *lo
             if (dev_rd < 64)
                 configured_rd[dev_rd] = true;
         }
-        xs::router_logits_decode_kernel<<<grid, xs::kRdThreads, xs::kRdSmemBytes, st>>>(xb, rwb, logits, T, H, E);
+        XS_CUDA(launch_pdl(xs::router_logits_decode_kernel, grid, xs::kRdThreads, xs::kRdSmemBytes, st, xb, rwb, logits, T, H, E));
         note_launch();
     } else {
         static bool configured[64] = {};
@@ -617,7 +617,7 @@ int launch_gemm_t(const CUtensorMap &tw, const CUtensorMap &tw2, const CUtensorM
     int grid = di.sms < max_work ? di.sms : max_work;
     if (grid < 1)
         grid = 1;
-    kern<<<grid, xs::kGemmThreads, smem, st>>>(tw, tw2, tx, offsets, tt, groups, w_rows, n_out, K, out, status, stages);
+    XS_CUDA(launch_pdl(kern, grid, xs::kGemmThreads, smem, st, tw, tw2, tx, offsets, tt, groups, w_rows, n_out, K, out, status, stages));
     note_launch();
     XS_CUDA(cudaGetLastError());
     return 0;
@@ -710,7 +710,7 @@ int launch_prefill_fp8(const CUtensorMap &tw, const CUtensorMap &tw2, const CUte
     int grid = di.sms < max_work ? di.sms : max_work;
     if (grid < 1)
         grid = 1;
-    kern<<<grid, xs::kPfThreads, smem, st>>>(tw, tw2, tx, offsets, tt, sc, groups, w_rows, n_out, K, out, status, stages, y_bf16);
+    XS_CUDA(launch_pdl(kern, grid, xs::kPfThreads, smem, st, tw, tw2, tx, offsets, tt, sc, groups, w_rows, n_out, K, out, status, stages, y_bf16));
     note_launch();
     XS_CUDA(cudaGetLastError());
     return 0;
@@ -744,7 +744,7 @@ int launch_gemm_fp4_t(const CUtensorMap &tw, const CUtensorMap &tx, const int32_
     int grid = di.sms < max_work ? di.sms : max_work;
     if (grid < 1)
         grid = 1;
-    kern<<<grid, xs::kFp4Threads, smem, st>>>(tw, tx, offsets, tt, sc, w_rows, n_out, K, out, status, stages);
+    XS_CUDA(launch_pdl(kern, grid, xs::kFp4Threads, smem, st, tw, tx, offsets, tt, sc, w_rows, n_out, K, out, status, stages));
     note_launch();
     XS_CUDA(cudaGetLastError());
     return 0;
@@ -802,7 +802,8 @@ int launch_prefill_fp4(const CUtensorMap &tw, const CUtensorMap &tx, const int32
     int grid = di.sms < max_work ? di.sms : max_work;
     if (grid < 1)
         grid = 1;
-    kern<<<grid, xs::kPf4Threads, smem, st>>>(tw, tx, t_ws, t_xs, offsets, tt, sc, w_rows, n_out, K, out, status, stages, tile_rows, sf_tma, ret);
+    XS_CUDA(launch_pdl(kern, grid, xs::kPf4Threads, smem, st, tw, tx, t_ws, t_xs, offsets, tt, sc, w_rows, n_out, K, out, status, stages, tile_rows,
+                       sf_tma, ret));
     note_launch();
     XS_CUDA(cudaGetLastError());
     return 0;
@@ -1024,7 +1025,7 @@ int launch_quantize_rows_mx(const void *x, const int32_t *dst, int nd, uint8_t *
 {
     if (rows == 0)
         return 0;
-    xs::quantize_rows_mxfp8_kernel<<<rows, 256, 0, st>>>(static_cast<const __nv_bfloat16 *>(x), dst, nd, q, scale, rows, cols);
+    XS_CUDA(launch_pdl(xs::quantize_rows_mxfp8_kernel, rows, 256, 0, st, static_cast<const __nv_bfloat16 *>(x), dst, nd, q, scale, rows, cols));
     note_launch();
     XS_CUDA(cudaGetLastError());
     return 0;
@@ -1036,7 +1037,7 @@ int launch_quantize_rows(const void *x, uint8_t *q, float *scale, int rows, int 
         return 0;
     const long warps = static_cast<long>(rows) * (cols / 128);
     const int blocks = static_cast<int>((warps + 7) / 8);
-    xs::quantize_rows_fp8_kernel<<<blocks, 256, 0, st>>>(static_cast<const __nv_bfloat16 *>(x), q, scale, rows, cols);
+    XS_CUDA(launch_pdl(xs::quantize_rows_fp8_kernel, blocks, 256, 0, st, static_cast<const __nv_bfloat16 *>(x), q, scale, rows, cols));
     note_launch();
     XS_CUDA(cudaGetLastError());
     return 0;
@@ -1386,9 +1387,10 @@ static int combine_bf16_impl(const XsMoeConfig *cfg, const __nv_bfloat16 *y, con
     __nv_bfloat16 *o = static_cast<__nv_bfloat16 *>(out);
     const __nv_bfloat16 *res = static_cast<const __nv_bfloat16 *>(residual);
     if (shared_is_bf16)
-        xs::combine_kernel<__nv_bfloat16, __nv_bfloat16><<<grid, 128, 0, st>>>(y, inv, topk_w, static_cast<const __nv_bfloat16 *>(shared), o, T, H, K, res);
+        XS_CUDA(launch_pdl(xs::combine_kernel<__nv_bfloat16, __nv_bfloat16>, grid, 128, 0, st, y, inv, topk_w, static_cast<const __nv_bfloat16 *>(shared), o, T,
+                           H, K, res));
     else
-        xs::combine_kernel<__nv_bfloat16, float><<<grid, 128, 0, st>>>(y, inv, topk_w, static_cast<const float *>(shared), o, T, H, K, res);
+        XS_CUDA(launch_pdl(xs::combine_kernel<__nv_bfloat16, float>, grid, 128, 0, st, y, inv, topk_w, static_cast<const float *>(shared), o, T, H, K, res));
     note_launch();
     XS_CUDA(cudaGetLastError());
     return 0;

@@ -99,6 +99,7 @@ prefill_gemm_fp4_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    pdl_wait(); // everything above touches only this CTA's shared memory and TMEM
     const uint32_t sf_base = tmem_base + kPfCols;
 
     const int n_n_tiles = n_out / N_PER_TILE;

@@ -102,6 +102,7 @@ prefill_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    pdl_wait(); // everything above touches only this CTA's shared memory and TMEM
 
     const int n_n_tiles = n_out / N_PER_TILE;
     const int num_tiles = *tt.num_tiles;

@@ -152,6 +152,8 @@ router_logits_decode_kernel(const __nv_bfloat16 *__restrict__ x, const __nv_bflo
     const int el = tid >> 5, tl = tid & 31;
     const int e0 = blockIdx.x * kRdExperts, t0 = blockIdx.y * kRdTokens;
     const int chunks = H / kRdK;
+    pdl_launch_dependents();
+    pdl_wait();
 
     auto issue = [&](int chunk, int stage) {
         const int k0 = chunk * kRdK;
