@@ -446,9 +446,9 @@ int launch_logits_filtered(const XsMoeConfig *c, const void *x, const void *rw, 
         xs::router_candidates_kernel<32><<<blocks, xs::kRcWarps * 32, 0, st>>>(xb, bias, logits, wnorm, cand, cand_meta, T, H, E, K, coeff);
     note_launch();
     if (E <= xs::kRxMaxExperts) {
-        int tpb = xs::kRxTokens; // halve the tokens per block while that still leaves SMs without a block
-        while (tpb > 8 && (T + tpb - 1) / tpb * 2 <= di.sms)
-            tpb /= 2;
+        // a block's time is set by walking H once and by its chains' shared-memory reads: spread the tokens over the SMs
+        int tpb = ((T + di.sms - 1) / di.sms + 7) / 8 * 8;
+        tpb = tpb < 8 ? 8 : (tpb > xs::kRxTokens ? xs::kRxTokens : tpb);
         xs::router_exact_slices_kernel<<<(T + tpb - 1) / tpb, xs::kRxThreads, xs::kRxSmemBytes, st>>>(xb, rwb, logits, cand, cand_meta, T, H, E,
                                                                                                   counters, tpb);
     }

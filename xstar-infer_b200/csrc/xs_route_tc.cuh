@@ -484,7 +484,7 @@ router_exact_rows_kernel(const __nv_bfloat16 *__restrict__ x, const __nv_bfloat1
 // FMA chains.  Every accumulator still sees k = 0, 1, 2, ... in order.
 constexpr int kRxTokens = 64, kRxThreads = 512, kRxK = 64, kRxStages = 4, kRxStride = kRxK + 8, kRxMaxExperts = 256;
 constexpr int kRxStageBytes = (kRxMaxExperts + kRxTokens) * kRxStride * 2;
-constexpr int kRxSmemBytes = kRxStages * kRxStageBytes + (kRxTokens + 1) * 4 * 2 + kRxTokens * 4;
+constexpr int kRxSmemBytes = kRxStages * kRxStageBytes + (kRxTokens + 1) * 4 * 2 + kRxTokens * 4 + (2 * kRxThreads + 16 * 8 + 24) * 4;
 
 __global__ void __launch_bounds__(kRxThreads)
 router_exact_slices_kernel(const __nv_bfloat16 *__restrict__ x, const __nv_bfloat16 *__restrict__ rw, float *__restrict__ logits,
@@ -497,6 +497,10 @@ router_exact_slices_kernel(const __nv_bfloat16 *__restrict__ x, const __nv_bfloa
     int *s_off = reinterpret_cast<int *>(rx_smem + kRxStages * kRxStageBytes); // [kRxTokens + 1] exclusive prefix of chain counts
     int *s_cnt = s_off + kRxTokens + 1;                                        // [kRxTokens + 1] candidates per token (E = all)
     int *s_bad = s_cnt + kRxTokens + 1;                                        // [kRxTokens] token needs the full recomputation
+    int *s_chain = s_bad + kRxTokens; // [kRxThreads] thread slot -> token << 16 | expert, -1: idle
+    int *s_spill = s_chain + kRxThreads; // [kRxThreads] chains whose bucket was full
+    int *s_wcnt = s_spill + kRxThreads;  // [16 warps][8 buckets] counts, then exclusive prefixes
+    int *s_bcnt = s_wcnt + 16 * 8;       // [8] chains per bucket, [8] prefix of idle slots, [1] spilled chains
     const int tid = threadIdx.x;
     const int t0 = blockIdx.x * tokens_per_block;
     const int nt = T - t0 < tokens_per_block ? T - t0 : tokens_per_block;
@@ -542,7 +546,7 @@ router_exact_slices_kernel(const __nv_bfloat16 *__restrict__ x, const __nv_bfloa
         const int chains = s_off[nt];
         for (int base = 0; base < chains; base += kRxThreads) {
             const int c = base + tid;
-            const bool live = c < chains;
+            bool live = c < chains;
             int tl = 0, e = 0;
             if (live) {
                 int lo = 0, hi = nt; // token with s_off[lo] <= c < s_off[lo + 1]
@@ -556,6 +560,67 @@ router_exact_slices_kernel(const __nv_bfloat16 *__restrict__ x, const __nv_bfloa
                 tl = lo;
                 const int j = c - s_off[tl];
                 e = (s_cnt[tl] == E && (phase == 1 || cand_meta[2 * (t0 + tl)] > 32)) ? j : cand[static_cast<size_t>(t0 + tl) * 32 + j];
+            }
+            if (chains <= kRxThreads) {
+                // One round: re-deal the chains so that the 8 lanes of a quarter warp hold 8 different values of
+                // (expert mod 8).  A 16-byte read of a router row lands in the bank group 4 * expert mod 32, so a quarter
+                // warp of arbitrary experts needs 2 to 3 passes over shared memory per read and one of distinct residues
+                // needs one; the token rows follow (rows 4 * token mod 32; buckets keep token order, so a quarter warp sees
+                // neighbouring tokens).  Stable counting sort by residue: bucket b fills slots b, 8 + b, 16 + b, ...; what
+                // overflows a bucket takes the slots that emptier buckets leave idle.  Which thread runs a chain changes
+                // nothing in its result.
+                const int wid = tid >> 5, ln = tid & 31;
+                if (tid < 16 * 8)
+                    s_wcnt[tid] = 0;
+                if (tid == 0)
+                    s_bcnt[16] = 0;
+                s_chain[tid] = -1;
+                __syncthreads();
+                const int b = live ? (e & 7) : 8;
+                const unsigned peers = __match_any_sync(0xffffffffu, b);
+                const int rank = __popc(peers & ((1u << ln) - 1u));
+                if (live && rank == 0)
+                    s_wcnt[wid * 8 + b] = __popc(peers);
+                __syncthreads();
+                if (tid < 8) {
+                    int run = 0;
+                    for (int w = 0; w < 16; w++) {
+                        const int n = s_wcnt[w * 8 + tid];
+                        s_wcnt[w * 8 + tid] = run;
+                        run += n;
+                    }
+                    s_bcnt[tid] = run;
+                }
+                __syncthreads();
+                const int packed = (tl << 16) | e;
+                if (live) {
+                    const int pos = s_wcnt[wid * 8 + b] + rank;
+                    if (pos < kRxThreads / 8)
+                        s_chain[pos * 8 + b] = packed;
+                    else
+                        s_spill[atomicAdd(&s_bcnt[16], 1)] = packed;
+                }
+                if (tid == 0) {
+                    int run = 0;
+                    for (int i = 0; i < 8; i++) {
+                        s_bcnt[8 + i] = run;
+                        const int used = s_bcnt[i] < kRxThreads / 8 ? s_bcnt[i] : kRxThreads / 8;
+                        run += kRxThreads / 8 - used;
+                    }
+                }
+                __syncthreads();
+                if (tid < s_bcnt[16]) {
+                    int bb = 7;
+                    while (bb > 0 && s_bcnt[8 + bb] > tid)
+                        bb--;
+                    const int used = s_bcnt[bb] < kRxThreads / 8 ? s_bcnt[bb] : kRxThreads / 8;
+                    s_chain[(used + tid - s_bcnt[8 + bb]) * 8 + bb] = s_spill[tid];
+                }
+                __syncthreads();
+                const int mine = s_chain[tid];
+                live = mine >= 0;
+                tl = live ? mine >> 16 : 0;
+                e = live ? mine & 0xffff : 0;
             }
             float acc = 0.0f;
             __syncthreads(); // the stages of the previous round are no longer read
