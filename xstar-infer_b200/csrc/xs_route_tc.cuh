@@ -484,7 +484,7 @@ router_exact_rows_kernel(const __nv_bfloat16 *__restrict__ x, const __nv_bfloat1
 // FMA chains.  Every accumulator still sees k = 0, 1, 2, ... in order.
 constexpr int kRxTokens = 64, kRxThreads = 512, kRxK = 64, kRxStages = 4, kRxStride = kRxK + 8, kRxMaxExperts = 256;
 constexpr int kRxStageBytes = (kRxMaxExperts + kRxTokens) * kRxStride * 2;
-constexpr int kRxSmemBytes = kRxStages * kRxStageBytes + (kRxTokens + 1) * 4 * 2 + kRxTokens * 4 + (2 * kRxThreads + 16 * 8 + 24) * 4;
+constexpr int kRxSmemBytes = kRxStages * kRxStageBytes + (kRxTokens + 1) * 4 * 2 + kRxTokens * 4 + (2 * kRxThreads + 16 * 8 + 24 + 2 * kRxMaxExperts + 4) * 4;
 
 __global__ void __launch_bounds__(kRxThreads)
 router_exact_slices_kernel(const __nv_bfloat16 *__restrict__ x, const __nv_bfloat16 *__restrict__ rw, float *__restrict__ logits,
@@ -501,6 +501,9 @@ router_exact_slices_kernel(const __nv_bfloat16 *__restrict__ x, const __nv_bfloa
     int *s_spill = s_chain + kRxThreads; // [kRxThreads] chains whose bucket was full
     int *s_wcnt = s_spill + kRxThreads;  // [16 warps][8 buckets] counts, then exclusive prefixes
     int *s_bcnt = s_wcnt + 16 * 8;       // [8] chains per bucket, [8] prefix of idle slots, [1] spilled chains
+    int *s_slot = s_bcnt + 24;           // [kRxMaxExperts] expert -> row of the stage that holds its router row, -1: not staged
+    int *s_rows = s_slot + kRxMaxExperts; // [kRxMaxExperts] row of the stage -> expert
+    int *s_nrows = s_rows + kRxMaxExperts; // rows staged per slice
     const int tid = threadIdx.x;
     const int t0 = blockIdx.x * tokens_per_block;
     const int nt = T - t0 < tokens_per_block ? T - t0 : tokens_per_block;
@@ -510,9 +513,10 @@ router_exact_slices_kernel(const __nv_bfloat16 *__restrict__ x, const __nv_bfloa
         const int k0 = sl * kRxK;
         __nv_bfloat16 *wst = reinterpret_cast<__nv_bfloat16 *>(rx_smem + st * kRxStageBytes);
         __nv_bfloat16 *xst = wst + kRxMaxExperts * kRxStride;
-        for (int p = tid; p < E * 8; p += kRxThreads) { // E rows x 8 pieces of 8 bf16
+        const int nrows = *s_nrows;
+        for (int p = tid; p < nrows * 8; p += kRxThreads) { // staged router rows x 8 pieces of 8 bf16
             const int r = p >> 3, c = (p & 7) * 8;
-            cp_async16(wst + r * kRxStride + c, rw + static_cast<size_t>(r) * H + k0 + c, true);
+            cp_async16(wst + r * kRxStride + c, rw + static_cast<size_t>(s_rows[r]) * H + k0 + c, true);
         }
         for (int p = tid; p < nt * 8; p += kRxThreads) {
             const int r = p >> 3, c = (p & 7) * 8;
@@ -561,10 +565,38 @@ router_exact_slices_kernel(const __nv_bfloat16 *__restrict__ x, const __nv_bfloa
                 const int j = c - s_off[tl];
                 e = (s_cnt[tl] == E && (phase == 1 || cand_meta[2 * (t0 + tl)] > 32)) ? j : cand[static_cast<size_t>(t0 + tl) * 32 + j];
             }
+            // Router rows to stage: a block with few chains touches few experts, and what bounds it is what an SM can take in
+            // (about 25 bytes per cycle: 53 us for the whole 2 MB matrix), so one round of chains stages only the rows
+            // its chains read, compacted; more rounds, or a token that needs its whole row, stage every row.
+            if (tid < kRxMaxExperts)
+                s_slot[tid] = -1;
+            __syncthreads();
+            if (chains <= kRxThreads && live)
+                s_slot[e] = 0; // needed (same value from every writer)
+            __syncthreads();
+            if (tid < 32) {
+                int run = 0;
+                for (int i = 0; i < kRxMaxExperts / 32; i++) {
+                    const int ex = i * 32 + tid;
+                    const bool need = ex < E && (chains > kRxThreads || s_slot[ex] == 0);
+                    const unsigned m = __ballot_sync(0xffffffffu, need);
+                    if (need) {
+                        const int sl = run + __popc(m & ((1u << tid) - 1u));
+                        s_slot[ex] = sl;
+                        s_rows[sl] = ex;
+                    }
+                    run += __popc(m);
+                }
+                if (tid == 0)
+                    *s_nrows = run;
+            }
+            __syncthreads();
+            if (live)
+                e |= s_slot[e] << 8; // bits 8..: the row of the stage
             if (chains <= kRxThreads) {
                 // One round: re-deal the chains so that the 8 lanes of a quarter warp hold 8 different values of
-                // (expert mod 8).  A 16-byte read of a router row lands in the bank group 4 * expert mod 32, so a quarter
-                // warp of arbitrary experts needs 2 to 3 passes over shared memory per read and one of distinct residues
+                // (staged row mod 8).  A 16-byte read of a staged router row lands in the bank group 4 * row mod 32, so a quarter
+                // warp of arbitrary rows needs 2 to 3 passes over shared memory per read and one of distinct residues
                 // needs one; the token rows follow (rows 4 * token mod 32; buckets keep token order, so a quarter warp sees
                 // neighbouring tokens).  Stable counting sort by residue: bucket b fills slots b, 8 + b, 16 + b, ...; what
                 // overflows a bucket takes the slots that emptier buckets leave idle.  Which thread runs a chain changes
@@ -576,7 +608,7 @@ router_exact_slices_kernel(const __nv_bfloat16 *__restrict__ x, const __nv_bfloa
                     s_bcnt[16] = 0;
                 s_chain[tid] = -1;
                 __syncthreads();
-                const int b = live ? (e & 7) : 8;
+                const int b = live ? ((e >> 8) & 7) : 8;
                 const unsigned peers = __match_any_sync(0xffffffffu, b);
                 const int rank = __popc(peers & ((1u << ln) - 1u));
                 if (live && rank == 0)
@@ -592,7 +624,7 @@ router_exact_slices_kernel(const __nv_bfloat16 *__restrict__ x, const __nv_bfloa
                     s_bcnt[tid] = run;
                 }
                 __syncthreads();
-                const int packed = (tl << 16) | e;
+                const int packed = (tl << 16) | e; // token, row of the stage, expert
                 if (live) {
                     const int pos = s_wcnt[wid * 8 + b] + rank;
                     if (pos < kRxThreads / 8)
@@ -639,7 +671,7 @@ router_exact_slices_kernel(const __nv_bfloat16 *__restrict__ x, const __nv_bfloa
                 asm volatile("cp.async.commit_group;" ::: "memory");
                 if (live) {
                     const __nv_bfloat16 *wst = reinterpret_cast<const __nv_bfloat16 *>(rx_smem + (sl % kRxStages) * kRxStageBytes);
-                    const uint4 *wp = reinterpret_cast<const uint4 *>(wst + e * kRxStride);
+                    const uint4 *wp = reinterpret_cast<const uint4 *>(wst + (e >> 8) * kRxStride);
                     const uint4 *xp = reinterpret_cast<const uint4 *>(wst + (kRxMaxExperts + tl) * kRxStride);
 #pragma unroll
                     for (int i = 0; i < kRxK / 8; i++) {
@@ -657,7 +689,7 @@ router_exact_slices_kernel(const __nv_bfloat16 *__restrict__ x, const __nv_bfloa
             }
             asm volatile("cp.async.wait_group 0;" ::: "memory");
             if (live) {
-                float *cell = logits + static_cast<size_t>(t0 + tl) * E + e;
+                float *cell = logits + static_cast<size_t>(t0 + tl) * E + (e & 0xff);
                 if (phase == 0 && s_cnt[tl] != E) {
                     const float delta = __int_as_float(cand_meta[2 * (t0 + tl) + 1]);
                     if (!(fabsf(acc - *cell) <= delta)) // the assumed bound does not hold here (or a NaN turned up)
