@@ -613,3 +613,37 @@ def test_block_forward_matches_the_reference_composition(oracle, fmt, T, tol):
     layer = gu.forward(dims, dn)
     fused = oracle.add_bf16(d["x"].cpu().view(torch.uint16).numpy(), layer.cpu().view(torch.uint16).numpy())
     assert np.array_equal(out.cpu().view(torch.uint16).numpy(), fused)
+
+
+# ---- programmatic dependent launch on / off --------------------------------------------------------------------------
+_PDL_CHILD = r"""
+import hashlib, os, sys
+sys.path.insert(0, sys.argv[1]); sys.path.insert(0, sys.argv[2])
+import torch
+from xstar_moe import synth
+import gpu_util as gu
+h = hashlib.sha1()
+for fmt, T in (("bf16", 5), ("fp8", 1), ("fp8", 40), ("fp4", 24)):
+    dims = dict(T=T, H=512, E=16, K=3, I=256, S=1, fmt=fmt, bias=None)
+    d = synth.make_inputs(dims, seed=7, device="cuda")
+    outs = [gu.forward(dims, d) for _ in range(3)]  # back to back: each launch may start under its predecessor's tail
+    assert all(torch.equal(outs[0], o) for o in outs)
+    h.update(outs[0].cpu().view(torch.uint8).numpy().tobytes())
+print("sha", h.hexdigest())
+"""
+
+
+def test_forward_equal_with_and_without_programmatic_dependent_launch():
+    """The layer's kernels are launched as programmatic dependents of one another (each waits before it touches what its
+    predecessor wrote); XS_MOE_PDL=0 launches them the ordinary way.  Same bits either way, for every weight format."""
+    import subprocess
+    import sys
+    here = os.path.dirname(os.path.abspath(__file__))
+    pkg = os.path.join(os.path.dirname(here), "xstar-infer_b200")
+    shas = []
+    for flag in ("1", "0"):
+        env = dict(os.environ, XS_MOE_PDL=flag)
+        r = subprocess.run([sys.executable, "-c", _PDL_CHILD, pkg, here], env=env, capture_output=True, text=True, timeout=600)
+        assert r.returncode == 0, r.stderr[-2000:]
+        shas.append([l for l in r.stdout.splitlines() if l.startswith("sha")][-1])
+    assert shas[0] == shas[1], shas
